@@ -1,0 +1,96 @@
+// Shared helpers of the sm_100a kernels: element access in float32 and bfloat16, reductions,
+// the step's batch description and the paged cache's addressing.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define PTB_API extern "C" __attribute__((visibility("default")))
+
+// dtype codes used by every entry point
+enum { PTB_F32 = 0, PTB_BF16 = 1 };
+
+// error codes returned by entry points (0 = launched)
+enum {
+  PTB_OK = 0,
+  PTB_ERR_DTYPE = 1,      // unknown dtype code
+  PTB_ERR_SIZE = 2,       // a size that the kernel does not take
+  PTB_ERR_LAUNCH = 3,     // the launch itself failed (cudaGetLastError)
+  PTB_ERR_ALIGN = 4,      // a pointer or a row size that is not aligned as the kernel needs
+};
+
+// tokens of a cache page; a sequence holds whole pages
+constexpr int PTB_PAGE = 64;
+
+template <typename T> __device__ __forceinline__ float to_f(T v);
+template <> __device__ __forceinline__ float to_f<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_f(float v);
+template <> __device__ __forceinline__ float from_f<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+// round a float to the nearest bfloat16 value (ties to even), kept as float
+__device__ __forceinline__ float round_bf16(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Sum over a block; every thread gets the result. `scratch` holds at least 32 floats.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();  // scratch may still be read from an earlier call
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  float r = (lane < nwarp) ? scratch[lane] : 0.f;
+  return warp_sum(r);
+}
+__device__ __forceinline__ float block_max(float v, float* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = (blockDim.x + 31) >> 5;
+  v = warp_max(v);
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  float r = (lane < nwarp) ? scratch[lane] : -INFINITY;
+  return warp_max(r);
+}
+
+// The ragged batch of one step, as device arrays of int32 (built on the host).
+//   tok_seq[t], tok_pos[t]   sequence index in the batch and absolute position of token t
+//   seq_start[b]             index of sequence b's first token among the step's tokens
+//   seq_new[b], seq_past[b]  tokens of b in this step, tokens of b already in the cache
+//   pages[b * pages_stride + i]  cache page that holds positions [64 i, 64 i + 63] of sequence b
+struct StepBatch {
+  const int* tok_seq;
+  const int* tok_pos;
+  const int* seq_start;
+  const int* seq_new;
+  const int* seq_past;
+  const int* pages;
+  int pages_stride;
+  int n_tokens;
+  int n_seqs;
+};
+
+// Element offset of (page, kv head, slot in page, 0) in a layer's K or V pool laid out as
+// [pages][kv_heads][PTB_PAGE][head_dim].
+__device__ __forceinline__ size_t kv_offset(int page, int kv_head, int in_page, int kv_heads, int head_dim) {
+  return ((size_t(page) * kv_heads + kv_head) * PTB_PAGE + in_page) * size_t(head_dim);
+}
+
+// ALiBi bias of a key position as the reference forms it: bfloat16(slope) * bfloat16(position),
+// the product rounded to bfloat16. `slope_bf16` is the slope already rounded.
+__device__ __forceinline__ float alibi_bias(float slope_bf16, int key_pos) {
+  return round_bf16(slope_bf16 * round_bf16(float(key_pos)));
+}
+
+inline int launch_status() { return cudaGetLastError() == cudaSuccess ? PTB_OK : PTB_ERR_LAUNCH; }

@@ -1,0 +1,203 @@
+// Row-wise and elementwise kernels: embedding gather, row gather, LayerNorm / RMSNorm with one
+// or two affine outputs, bias + activation, residual sums. All arithmetic is float32; tensors of
+// activations are float32 or bfloat16 (template T); gains, biases are float32 vectors.
+#include "common.cuh"
+
+// blocks of a grid-stride launch: enough to cover `total`, at most 16 per SM of a 148-SM device
+static int grid_for(size_t total, int threads) {
+  const size_t want = (total + threads - 1) / threads;
+  return int(want < size_t(148 * 16) ? want : size_t(148 * 16));
+}
+
+// ------------------------------------------------------------------------------------------------
+// rows of a table: out[t, :] = table[ids[t], :]. An id outside [0, rows) raises bit 0 of *status
+// and reads row 0.
+template <typename T>
+__global__ void gather_rows_kernel(const int* __restrict__ ids, const T* __restrict__ table, T* __restrict__ out,
+                                   int width, int rows, int* status) {
+  const int t = blockIdx.x;
+  int id = ids[t];
+  if (id < 0 || id >= rows) {
+    if (threadIdx.x == 0 && status) atomicOr(status, 1);
+    id = 0;
+  }
+  const T* src = table + size_t(id) * width;
+  T* dst = out + size_t(t) * width;
+  const size_t row_bytes = size_t(width) * sizeof(T);
+  if (row_bytes % 16 == 0 && (reinterpret_cast<uintptr_t>(table) % 16 == 0) && (reinterpret_cast<uintptr_t>(out) % 16 == 0)) {
+    const int4* s4 = reinterpret_cast<const int4*>(src);
+    int4* d4 = reinterpret_cast<int4*>(dst);
+    const int n4 = int(row_bytes / 16);
+    for (int i = threadIdx.x; i < n4; i += blockDim.x) d4[i] = s4[i];
+  } else {
+    for (int i = threadIdx.x; i < width; i += blockDim.x) dst[i] = src[i];
+  }
+}
+
+PTB_API int ptb_gather_rows(int dtype, const int* ids, const void* table, void* out, int n, int width, int rows,
+                            int* status, cudaStream_t stream) {
+  if (n <= 0) return PTB_OK;
+  if (width <= 0 || rows <= 0) return PTB_ERR_SIZE;
+  if (dtype == PTB_F32)
+    gather_rows_kernel<float><<<n, 256, 0, stream>>>(ids, (const float*)table, (float*)out, width, rows, status);
+  else if (dtype == PTB_BF16)
+    gather_rows_kernel<__nv_bfloat16><<<n, 256, 0, stream>>>(ids, (const __nv_bfloat16*)table, (__nv_bfloat16*)out,
+                                                             width, rows, status);
+  else
+    return PTB_ERR_DTYPE;
+  return launch_status();
+}
+
+// ------------------------------------------------------------------------------------------------
+// Normalisation of rows. kind 0: LayerNorm, y = (x - mean) / sqrt(var + eps) * gain + bias with the
+// biased variance; kind 1: RMSNorm, y = x / sqrt(mean(x^2) + eps) * gain (+ bias if given).
+// With gain2 != nullptr a second output with its own gain and bias is written from the same
+// statistics (two norms of one input share the read and the reductions).
+// The row is held in shared memory as float32: 4 * width bytes of dynamic shared memory.
+template <typename T>
+__global__ void norm_kernel(const T* __restrict__ x, const float* __restrict__ gain1, const float* __restrict__ bias1,
+                            T* __restrict__ y1, const float* __restrict__ gain2, const float* __restrict__ bias2,
+                            T* __restrict__ y2, int width, float eps, int kind) {
+  extern __shared__ float row[];
+  __shared__ float scratch[32];
+  const size_t base = size_t(blockIdx.x) * width;
+  float s = 0.f;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+    const float v = to_f(x[base + i]);
+    row[i] = v;
+    s += v;
+  }
+  float mean = 0.f;
+  if (kind == 0) mean = block_sum(s, scratch) / float(width);
+  float q = 0.f;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+    const float c = row[i] - mean;
+    q += c * c;
+  }
+  const float var = block_sum(q, scratch) / float(width);
+  const float rstd = 1.0f / sqrtf(var + eps);
+  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+    const float n = (row[i] - mean) * rstd;
+    float a = n * gain1[i];
+    if (bias1) a += bias1[i];
+    y1[base + i] = from_f<T>(a);
+    if (gain2) {
+      float b = n * gain2[i];
+      if (bias2) b += bias2[i];
+      y2[base + i] = from_f<T>(b);
+    }
+  }
+}
+
+PTB_API int ptb_norm(int dtype, const void* x, const float* gain1, const float* bias1, void* y1, const float* gain2,
+                     const float* bias2, void* y2, int n, int width, float eps, int kind, cudaStream_t stream) {
+  if (n <= 0) return PTB_OK;
+  if (width <= 0 || kind < 0 || kind > 1) return PTB_ERR_SIZE;
+  const size_t smem = size_t(width) * sizeof(float);
+  if (smem > 200 * 1024) return PTB_ERR_SIZE;
+  const int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
+  cudaError_t e = cudaSuccess;
+  if (dtype == PTB_F32) {
+    if (smem > 48 * 1024)
+      e = cudaFuncSetAttribute(norm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+    if (e != cudaSuccess) return PTB_ERR_LAUNCH;
+    norm_kernel<float><<<n, threads, smem, stream>>>((const float*)x, gain1, bias1, (float*)y1, gain2, bias2,
+                                                     (float*)y2, width, eps, kind);
+  } else if (dtype == PTB_BF16) {
+    if (smem > 48 * 1024)
+      e = cudaFuncSetAttribute(norm_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+    if (e != cudaSuccess) return PTB_ERR_LAUNCH;
+    norm_kernel<__nv_bfloat16><<<n, threads, smem, stream>>>((const __nv_bfloat16*)x, gain1, bias1,
+                                                             (__nv_bfloat16*)y1, gain2, bias2, (__nv_bfloat16*)y2,
+                                                             width, eps, kind);
+  } else {
+    return PTB_ERR_DTYPE;
+  }
+  return launch_status();
+}
+
+// ------------------------------------------------------------------------------------------------
+// Activations. 0 none, 1 GELU (erf form), 2 GELU (tanh form), 3 ReLU.
+__device__ __forceinline__ float activate(float v, int act) {
+  switch (act) {
+    case 1: return 0.5f * v * (1.0f + erff(v * 0.70710678118654752440f));
+    case 2: return 0.5f * v * (1.0f + tanhf(0.79788456080286535588f * (v + 0.044715f * v * v * v)));
+    case 3: return fmaxf(v, 0.f);
+    default: return v;
+  }
+}
+
+// y[r, c] = act(y[r, c] + bias[c]) in place (bias may be null).
+template <typename T>
+__global__ void bias_act_kernel(T* __restrict__ y, const float* __restrict__ bias, size_t total, int width, int act) {
+  const size_t stride = size_t(gridDim.x) * blockDim.x;
+  for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+    float v = to_f(y[i]);
+    if (bias) v += bias[i % width];
+    y[i] = from_f<T>(activate(v, act));
+  }
+}
+
+PTB_API int ptb_bias_act(int dtype, void* y, const float* bias, int rows, int width, int act, cudaStream_t stream) {
+  const size_t total = size_t(rows) * width;
+  if (total == 0) return PTB_OK;
+  if (act < 0 || act > 3) return PTB_ERR_SIZE;
+  const int threads = 256;
+  const int blocks = grid_for(total, threads);
+  if (dtype == PTB_F32)
+    bias_act_kernel<float><<<blocks, threads, 0, stream>>>((float*)y, bias, total, width, act);
+  else if (dtype == PTB_BF16)
+    bias_act_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>((__nv_bfloat16*)y, bias, total, width, act);
+  else
+    return PTB_ERR_DTYPE;
+  return launch_status();
+}
+
+// out = x + (a + b), or x + a when b is null: the residual sum, formed in float32 and rounded once.
+template <typename T>
+__global__ void residual_kernel(const T* __restrict__ x, const T* __restrict__ a, const T* __restrict__ b,
+                                T* __restrict__ out, size_t total) {
+  const size_t stride = size_t(gridDim.x) * blockDim.x;
+  for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+    float s = to_f(a[i]);
+    if (b) s += to_f(b[i]);
+    out[i] = from_f<T>(to_f(x[i]) + s);
+  }
+}
+
+PTB_API int ptb_residual(int dtype, const void* x, const void* a, const void* b, void* out, long long total,
+                         cudaStream_t stream) {
+  if (total <= 0) return PTB_OK;
+  const int threads = 256;
+  const int blocks = grid_for(size_t(total), threads);
+  if (dtype == PTB_F32)
+    residual_kernel<float><<<blocks, threads, 0, stream>>>((const float*)x, (const float*)a, (const float*)b,
+                                                           (float*)out, size_t(total));
+  else if (dtype == PTB_BF16)
+    residual_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)a,
+                                                                   (const __nv_bfloat16*)b, (__nv_bfloat16*)out,
+                                                                   size_t(total));
+  else
+    return PTB_ERR_DTYPE;
+  return launch_status();
+}
+
+// float32 copy of rows of any dtype: out[r, :] = float(x[r, :]) (logits of a bfloat16 head)
+template <typename T>
+__global__ void to_float_kernel(const T* __restrict__ x, float* __restrict__ out, size_t total) {
+  const size_t stride = size_t(gridDim.x) * blockDim.x;
+  for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) out[i] = to_f(x[i]);
+}
+
+PTB_API int ptb_to_float(int dtype, const void* x, float* out, long long total, cudaStream_t stream) {
+  if (total <= 0) return PTB_OK;
+  const int threads = 256;
+  const int blocks = grid_for(size_t(total), threads);
+  if (dtype == PTB_F32)
+    to_float_kernel<float><<<blocks, threads, 0, stream>>>((const float*)x, out, size_t(total));
+  else if (dtype == PTB_BF16)
+    to_float_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>((const __nv_bfloat16*)x, out, size_t(total));
+  else
+    return PTB_ERR_DTYPE;
+  return launch_status();
+}

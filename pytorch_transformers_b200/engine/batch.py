@@ -1,0 +1,113 @@
+"""The description of one step: which tokens run, where they sit, where their cache pages are.
+
+A step is a ragged batch: sequence ``b`` brings ``new[b]`` tokens that continue the
+``past[b]`` tokens it already has in the cache. All index arrays are built on the host in one
+int32 buffer and reach the device in one copy; the kernels read them through ``StepBatch``
+(csrc/common.cuh). The reference pads prompts on the left and carries ``attention_mask``,
+``position_ids`` and ``cache_position`` tensors instead
+(src/transformers/generation/utils.py:349-481); here positions are arithmetic on lengths.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from .. import kernels as K
+from ..cache.paged import PAGE, Cache
+
+
+class StepError(ValueError):
+    """A step that cannot be run as asked (bad slot, empty token list, token id out of range...)."""
+
+
+class StepContext:
+    """Everything a part may read about the running step."""
+
+    def __init__(self, cache: Cache, slots: Sequence[int], token_lists: Sequence[Sequence[int]], vocab_size: int,
+                 want: Sequence[Sequence[int]], tile_rows: int):
+        if len(slots) != len(token_lists) or len(slots) != len(want):
+            raise StepError("slots, token lists and wanted positions must have one item per sequence")
+        if len(slots) == 0:
+            raise StepError("a step needs at least one sequence")
+        if len(set(slots)) != len(slots):
+            raise StepError(f"a slot is named twice in one step: {list(slots)}")
+        self.cache = cache
+        self.slots = [int(s) for s in slots]
+        self.n_seqs = len(slots)
+        self.new = [len(t) for t in token_lists]
+        if min(self.new) < 1:
+            raise StepError("every sequence of a step must bring at least one token")
+        self.past = [cache.length(s) for s in self.slots]
+        self.n_tokens = int(sum(self.new))
+        self.is_decode = all(n == 1 for n in self.new)
+        self.max_context = max(p + n for p, n in zip(self.past, self.new))
+
+        tokens = np.fromiter((t for lst in token_lists for t in lst), dtype=np.int64, count=self.n_tokens)
+        if tokens.min() < 0 or tokens.max() >= vocab_size:
+            bad = int(tokens[(tokens < 0) | (tokens >= vocab_size)][0])
+            raise StepError(f"token id {bad} is outside the vocabulary 0..{vocab_size - 1}")
+        seq_start = np.zeros(self.n_seqs + 1, dtype=np.int64)
+        np.cumsum(self.new, out=seq_start[1:])
+        tok_seq = np.repeat(np.arange(self.n_seqs), self.new)
+        tok_pos = np.concatenate([np.arange(p, p + n) for p, n in zip(self.past, self.new)])
+
+        logits_at: List[int] = []
+        for b, w in enumerate(want):
+            for i in w:
+                if not (0 <= int(i) < self.new[b]):
+                    raise StepError(f"wanted position {i} is outside the {self.new[b]} tokens that sequence {b} brings")
+                logits_at.append(int(seq_start[b]) + int(i))
+        self.n_wanted = len(logits_at)
+
+        # tiles of the general attention kernel: (sequence, first row) every `tile_rows` rows
+        tile_seq, tile_q0 = [], []
+        for b, n in enumerate(self.new):
+            for q0 in range(0, n, tile_rows):
+                tile_seq.append(b)
+                tile_q0.append(q0)
+        self.n_tiles = len(tile_seq)
+
+        # page tables, one per storage group, padded to the longest
+        cache.reserve_all(list(zip(self.slots, self.new)))
+        tables = []
+        for gi in range(len(cache.groups)):
+            rows = [cache.pages(s, gi) for s in self.slots]
+            width = max(1, max(len(r) for r in rows))
+            tab = np.full((self.n_seqs, width), -1, dtype=np.int64)
+            for b, r in enumerate(rows):
+                tab[b, :len(r)] = r
+            tables.append(tab)
+
+        parts = {"tokens": tokens, "tok_seq": tok_seq, "tok_pos": tok_pos, "seq_start": seq_start[:-1],
+                 "seq_new": np.asarray(self.new), "seq_past": np.asarray(self.past),
+                 "slots": np.asarray(self.slots), "logits_at": np.asarray(logits_at, dtype=np.int64),
+                 "tile_seq": np.asarray(tile_seq), "tile_q0": np.asarray(tile_q0)}
+        for gi, tab in enumerate(tables):
+            parts[f"pages{gi}"] = tab.reshape(-1)
+        offsets, total = {}, 0
+        for name, arr in parts.items():
+            offsets[name] = (total, arr.size)
+            total += (arr.size + 3) // 4 * 4  # keep every array 16-byte aligned
+        packed = np.zeros(max(total, 4), dtype=np.int32)
+        for name, arr in parts.items():
+            o, n = offsets[name]
+            packed[o:o + n] = arr
+        self.host = {name: packed[o:o + n] for name, (o, n) in offsets.items()}
+        dev = torch.from_numpy(packed).to(cache.device)
+        self.dev: Dict[str, torch.Tensor] = {name: dev[o:o + n] for name, (o, n) in offsets.items()}
+        self._packed_dev = dev
+
+        self.batch_c: List[K.StepBatchC] = []
+        for gi, tab in enumerate(tables):
+            c = K.StepBatchC()
+            c.tok_seq, c.tok_pos = self.dev["tok_seq"].data_ptr(), self.dev["tok_pos"].data_ptr()
+            c.seq_start, c.seq_new = self.dev["seq_start"].data_ptr(), self.dev["seq_new"].data_ptr()
+            c.seq_past, c.pages = self.dev["seq_past"].data_ptr(), self.dev[f"pages{gi}"].data_ptr()
+            c.pages_stride, c.n_tokens, c.n_seqs = tab.shape[1], self.n_tokens, self.n_seqs
+            self.batch_c.append(c)
+
+    def commit(self) -> None:
+        for s, n in zip(self.slots, self.new):
+            self.cache.commit(s, n)

@@ -1,0 +1,161 @@
+"""The model as the engine sees it: parts put together from a ModelSpec, and the step function.
+
+``CausalLM.step`` is the one forward pass of the library: a ragged batch of sequences (whole
+prompts, chunks of prompts or single tokens, in any mix) runs from the cache and returns
+float32 logits at the wanted positions. Generation, trace replay and the benchmark all go
+through it. It stands where ``FalconForCausalLM.forward`` stands in the reference
+(src/transformers/models/falcon/modeling_falcon.py:1185-1254: embedding, blocks, ln_f, lm_head
+on the last ``num_logits_to_keep`` positions), without padding or mask tensors.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional, Sequence, Tuple, Union
+
+import torch
+
+from .. import kernels as K
+from ..cache.paged import Cache
+from ..parts.base import BuildContext, ModelSpec, ParamDecl, Part, make_part
+from ..parts.linear import linear
+from .batch import StepContext, StepError
+
+
+class CausalLM:
+    """A decoder-only language model built from parts."""
+
+    def __init__(self, spec: ModelSpec, config, device="cuda", dtype=torch.bfloat16, kernels=K):
+        if dtype not in (torch.float32, torch.bfloat16):
+            raise ValueError(f"model dtype must be float32 or bfloat16, got {dtype}")
+        self.spec, self.config = spec, config
+        self.device, self.dtype = torch.device(device), dtype
+        self.build = BuildContext(device=self.device, dtype=dtype, kernels=kernels)
+        self.blocks: List[Part] = [make_part(self.build, b) for b in spec.blocks]
+        self.final_norm: Part = make_part(self.build, spec.final_norm)
+        self.schedule = spec.resolved_schedule()
+        for e in self.schedule:
+            if not (0 <= e.block < len(self.blocks)):
+                raise ValueError(f"schedule names block {e.block} but the model has {len(self.blocks)} blocks")
+        writers = {e.cache_entry for e in self.schedule if e.writes_cache}
+        for e in self.schedule:
+            if not e.writes_cache and e.cache_entry not in writers:
+                raise ValueError(f"schedule entry reads cache entry {e.cache_entry}, which no entry writes")
+        self.embedding: Optional[torch.Tensor] = None
+        self.head: Optional[torch.Tensor] = None
+        self.status = None  # device int32 word raised by kernels that clamp a bad index
+
+    # ------------------------------------------------------------------ parameters
+    def param_table(self) -> Dict[str, Tuple[Optional[Part], str, ParamDecl]]:
+        """Checkpoint tensor name -> (owning part, logical name, declaration)."""
+        table: Dict[str, Tuple[Optional[Part], str, ParamDecl]] = {}
+        v, h = self.spec.vocab_size, self.spec.hidden_size
+        table[self.spec.embedding_name] = (None, "embedding", ParamDecl((v, h)))
+        if self.spec.head_name is not None:
+            table[self.spec.head_name] = (None, "head", ParamDecl((v, h)))
+        for top in self.blocks + [self.final_norm]:
+            for part in top.walk():
+                for logical, decl in part.param_decls().items():
+                    try:
+                        name = part.spec.names[logical]
+                    except KeyError:
+                        raise ValueError(f"{part.spec.family} part {part.spec.kind!r} declares parameter "
+                                         f"{logical!r} but its spec gives no checkpoint name for it") from None
+                    if name in table:
+                        raise ValueError(f"checkpoint tensor {name!r} is claimed by two parameters")
+                    table[name] = (part, logical, decl)
+        return table
+
+    def device_dtype(self, decl: ParamDecl) -> torch.dtype:
+        if decl.role == "vector":
+            return torch.float32
+        if decl.role == "int":
+            return torch.int32
+        return self.dtype
+
+    def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
+        """Give every part its device tensors (keys are checkpoint names)."""
+        per_part: Dict[int, Tuple[Part, Dict[str, torch.Tensor]]] = {}
+        for name, (part, logical, decl) in self.param_table().items():
+            t = tensors[name]
+            if part is None:
+                if logical == "embedding":
+                    self.embedding = t
+                else:
+                    self.head = t
+            else:
+                per_part.setdefault(id(part), (part, {}))[1][logical] = t
+        for part, group in per_part.values():
+            part.bind(group)
+        if self.spec.head_name is None:
+            self.head = self.embedding  # one device buffer for the gather and the output product
+        self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+
+    def weight_bytes(self) -> int:
+        seen, total = set(), 0
+        tensors = [self.embedding, self.head]
+        for top in self.blocks + [self.final_norm]:
+            for part in top.walk():
+                tensors += [getattr(part, a) for a in vars(part) if a.startswith("p_")]
+        for t in tensors:
+            if t is not None and t.data_ptr() not in seen:
+                seen.add(t.data_ptr())
+                total += t.numel() * t.element_size()
+        return total
+
+    # ------------------------------------------------------------------ cache
+    def cache_needs(self):
+        needs = []
+        for e in self.schedule:
+            if not e.writes_cache:
+                continue
+            mixer = self.blocks[e.block].children.get("mixer")
+            needs.append((e.cache_entry, mixer.cache_need() if mixer else None,
+                          mixer.state_need() if mixer else None))
+        return needs
+
+    def new_cache(self, max_tokens: int, max_slots: Optional[int] = None) -> Cache:
+        return Cache(self.cache_needs(), max_tokens, self.dtype, self.device, max_slots=max_slots)
+
+    # ------------------------------------------------------------------ the step
+    def step(self, cache: Cache, slots: Sequence[int], token_lists: Sequence[Sequence[int]],
+             want: Union[str, Sequence[Sequence[int]]] = "last") -> torch.Tensor:
+        """Run the given tokens of the given sequences as one batch from the cache.
+
+        ``token_lists[b]`` are the next tokens of the sequence in ``slots[b]`` (its whole prompt,
+        a chunk of it, or one token). ``want[b]`` lists the places among these tokens whose
+        logits are returned ("last": the last token of each; "all": every token; "none").
+        Returns float32 logits [wanted, vocab] in the order of the sequences and of ``want``.
+        The sequences' lengths in the cache advance by the tokens run.
+        """
+        if self.embedding is None:
+            raise RuntimeError("the model has no weights yet (load a checkpoint or initialise at random)")
+        if isinstance(want, str):
+            if want == "last":
+                want = [[len(t) - 1] for t in token_lists]
+            elif want == "all":
+                want = [list(range(len(t))) for t in token_lists]
+            elif want == "none":
+                want = [[] for _ in token_lists]
+            else:
+                raise StepError(f"want must be 'last', 'all', 'none' or lists of positions, got {want!r}")
+        ctx = StepContext(cache, slots, token_lists, self.spec.vocab_size, want, K.generic_tile_rows())
+        logits = self.forward(ctx)
+        ctx.commit()
+        return logits
+
+    def forward(self, ctx: StepContext) -> torch.Tensor:
+        k = self.build.kernels
+        x = k.gather_rows(ctx.dev["tokens"], self.embedding, self.status)
+        for entry in self.schedule:
+            x = self.blocks[entry.block].forward(x, ctx, entry)
+        if ctx.n_wanted == 0:
+            return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=self.device)
+        rows = k.gather_rows(ctx.dev["logits_at"], x, self.status)
+        rows = self.final_norm.forward(rows)
+        return self.logits(rows)
+
+    def logits(self, rows: torch.Tensor) -> torch.Tensor:
+        """float32 logits of normed rows: rows @ head.T (no bias, modeling_falcon.py:1168)."""
+        k = self.build.kernels
+        if self.dtype == torch.float32:
+            return k.linear_f32(rows, self.head)
+        return k.matmul_nt(rows, self.head, out_dtype=torch.float32)

@@ -1,0 +1,209 @@
+"""Python face of the sm_100a kernel library: one function per entry point, torch tensors in.
+
+Every function launches on the current CUDA stream of the tensors' device and raises
+``KernelError`` if the entry point refuses its arguments. Nothing here computes on the host
+and nothing falls back to torch: without a CUDA device, or without the compiled library, the
+calls fail.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from . import native
+
+PAGE = 64  # tokens of a cache page (PTB_PAGE in csrc/common.cuh)
+ACTIVATIONS = {"none": 0, "gelu": 1, "gelu_new": 2, "gelu_pytorch_tanh": 2, "relu": 3}
+NORM_KINDS = {"layernorm": 0, "rmsnorm": 1}
+_ERRORS = {1: "unknown dtype code", 2: "a size that the kernel does not take", 3: "the CUDA launch failed",
+           4: "a pointer or row size is not aligned as the kernel needs"}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+class StepBatchC(ctypes.Structure):
+    """Mirror of ``StepBatch`` in csrc/common.cuh."""
+    _fields_ = [("tok_seq", ctypes.c_void_p), ("tok_pos", ctypes.c_void_p), ("seq_start", ctypes.c_void_p),
+                ("seq_new", ctypes.c_void_p), ("seq_past", ctypes.c_void_p), ("pages", ctypes.c_void_p),
+                ("pages_stride", ctypes.c_int), ("n_tokens", ctypes.c_int), ("n_seqs", ctypes.c_int)]
+
+
+def _dtype_code(t: torch.Tensor) -> int:
+    if t.dtype == torch.float32:
+        return 0
+    if t.dtype == torch.bfloat16:
+        return 1
+    raise KernelError(f"kernels take float32 or bfloat16 tensors, got {t.dtype}")
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return ctypes.c_void_p(0 if t is None else t.data_ptr())
+
+
+def _stream(t: torch.Tensor):
+    return ctypes.c_void_p(torch.cuda.current_stream(t.device).cuda_stream)
+
+
+def _check(code: int, what: str) -> None:
+    if code != 0:
+        raise KernelError(f"{what}: {_ERRORS.get(code, f'error {code}')}")
+
+
+def _need_cuda(*tensors) -> None:
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise KernelError("the kernels run on a CUDA device only; got a tensor on " + str(t.device))
+        if t is not None and not t.is_contiguous():
+            raise KernelError("kernels take contiguous tensors")
+
+
+_configured = False
+
+
+def lib():
+    global _configured
+    L = native.library()
+    if not _configured:
+        for name in ("ptb_gather_rows", "ptb_norm", "ptb_bias_act", "ptb_residual", "ptb_to_float",
+                     "ptb_linear_f32", "ptb_split_rotate_store", "ptb_attention_generic", "ptb_sample",
+                     "ptb_attention_generic_tile_rows"):
+            getattr(L, name).restype = ctypes.c_int
+        _configured = True
+    return L
+
+
+def generic_tile_rows() -> int:
+    return 16  # BQ of csrc/attention_generic.cu (checked against the library in the GPU tests)
+
+
+# ------------------------------------------------------------------------------------------------
+def gather_rows(ids: torch.Tensor, table: torch.Tensor, status: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[t] = table[ids[t]] (int32 ids). An id out of range sets bit 0 of ``status``."""
+    _need_cuda(ids, table)
+    out = torch.empty((ids.numel(), table.shape[1]), dtype=table.dtype, device=table.device)
+    _check(lib().ptb_gather_rows(_dtype_code(table), _ptr(ids), _ptr(table), _ptr(out), ids.numel(),
+                                 table.shape[1], table.shape[0], _ptr(status), _stream(table)), "gather_rows")
+    return out
+
+
+def norm(x: torch.Tensor, gain: torch.Tensor, bias: Optional[torch.Tensor], eps: float, kind: str = "layernorm",
+         gain2: Optional[torch.Tensor] = None, bias2: Optional[torch.Tensor] = None):
+    """LayerNorm / RMSNorm of rows; with ``gain2`` a second output from the same statistics."""
+    _need_cuda(x, gain, bias, gain2, bias2)
+    n, width = x.shape
+    y1 = torch.empty_like(x)
+    y2 = torch.empty_like(x) if gain2 is not None else None
+    _check(lib().ptb_norm(_dtype_code(x), _ptr(x), _ptr(gain), _ptr(bias), _ptr(y1), _ptr(gain2), _ptr(bias2),
+                          _ptr(y2), n, width, ctypes.c_float(eps), NORM_KINDS[kind], _stream(x)), "norm")
+    return y1 if gain2 is None else (y1, y2)
+
+
+def bias_act_(y: torch.Tensor, bias: Optional[torch.Tensor], act: str) -> torch.Tensor:
+    """y = act(y + bias) in place."""
+    _need_cuda(y, bias)
+    _check(lib().ptb_bias_act(_dtype_code(y), _ptr(y), _ptr(bias), y.shape[0], y.shape[1], ACTIVATIONS[act],
+                              _stream(y)), "bias_act")
+    return y
+
+
+def residual(x: torch.Tensor, a: torch.Tensor, b: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """x + (a + b), the sum formed in float32."""
+    _need_cuda(x, a, b)
+    out = torch.empty_like(x)
+    _check(lib().ptb_residual(_dtype_code(x), _ptr(x), _ptr(a), _ptr(b), _ptr(out), ctypes.c_longlong(x.numel()),
+                              _stream(x)), "residual")
+    return out
+
+
+def to_float(x: torch.Tensor) -> torch.Tensor:
+    _need_cuda(x)
+    out = torch.empty(x.shape, dtype=torch.float32, device=x.device)
+    _check(lib().ptb_to_float(_dtype_code(x), _ptr(x), _ptr(out), ctypes.c_longlong(x.numel()), _stream(x)),
+           "to_float")
+    return out
+
+
+def linear_f32(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None, act: str = "none"):
+    """act(x @ w.T + bias) in true float32 on the CUDA cores."""
+    _need_cuda(x, w, bias)
+    if x.dtype != torch.float32 or w.dtype != torch.float32:
+        raise KernelError("linear_f32 takes float32 tensors")
+    m, k = x.shape
+    n = w.shape[0]
+    if w.shape[1] != k:
+        raise KernelError(f"linear_f32: x is [{m}, {k}] but w is {list(w.shape)}")
+    y = torch.empty((m, n), dtype=torch.float32, device=x.device)
+    _check(lib().ptb_linear_f32(_ptr(x), _ptr(w), _ptr(bias), _ptr(y), m, n, k, ACTIVATIONS[act], _stream(x)),
+           "linear_f32")
+    return y
+
+
+def split_rotate_store(fused: torch.Tensor, k_pool: Optional[torch.Tensor], v_pool: Optional[torch.Tensor],
+                       batch: StepBatchC, inv_freq: Optional[torch.Tensor], kv_heads: int, q_per_kv: int,
+                       head_dim: int, write_cache: bool = True) -> torch.Tensor:
+    """Fused projection -> rotated queries [tokens, heads, head_dim]; K (rotated) and V go to the pools."""
+    _need_cuda(fused, k_pool, v_pool, inv_freq)
+    n = fused.shape[0]
+    q = torch.empty((n, kv_heads * q_per_kv, head_dim), dtype=fused.dtype, device=fused.device)
+    if fused.shape[1] != kv_heads * (q_per_kv + 2) * head_dim:
+        raise KernelError(f"fused projection has width {fused.shape[1]}, expected "
+                          f"{kv_heads * (q_per_kv + 2) * head_dim}")
+    pairs = 0 if inv_freq is None else inv_freq.numel()
+    _check(lib().ptb_split_rotate_store(_dtype_code(fused), _ptr(fused), _ptr(q), _ptr(k_pool), _ptr(v_pool),
+                                        ctypes.byref(batch), _ptr(inv_freq), pairs, kv_heads, q_per_kv, head_dim,
+                                        1 if write_cache else 0, _stream(fused)), "split_rotate_store")
+    return q
+
+
+def attention_generic(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, batch: StepBatchC,
+                      tile_seq: torch.Tensor, tile_q0: torch.Tensor, n_tiles: int,
+                      slopes: Optional[torch.Tensor], kv_heads: int, scale: float, window: int = 0) -> torch.Tensor:
+    """Causal attention of the step's tokens over the paged cache; returns [tokens, heads * head_dim]."""
+    _need_cuda(q, k_pool, v_pool, tile_seq, tile_q0, slopes)
+    n, heads, head_dim = q.shape
+    out = torch.empty((n, heads * head_dim), dtype=q.dtype, device=q.device)
+    _check(lib().ptb_attention_generic(_dtype_code(q), _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out),
+                                       ctypes.byref(batch), _ptr(tile_seq), _ptr(tile_q0), n_tiles, _ptr(slopes),
+                                       heads, kv_heads, head_dim, ctypes.c_float(scale), window, _stream(q)),
+           "attention_generic")
+    return out
+
+
+def sample(logits: torch.Tensor, work: torch.Tensor, out: torch.Tensor, *, do_sample: bool, temperature: float = 1.0,
+           top_k: int = 0, top_p: float = 1.0, min_p: float = 0.0, repetition_penalty: float = 1.0,
+           history: Optional[torch.Tensor] = None, history_len: Optional[torch.Tensor] = None,
+           suppress: Optional[torch.Tensor] = None, seed: int = 0, streams: Optional[torch.Tensor] = None,
+           counters: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Select one token per row of float32 logits into ``out`` (int32). ``work`` is scratch of the
+    logits' shape; ``streams`` and ``counters`` (int64 per row) key the uniform draw."""
+    _need_cuda(logits, work, out, history, history_len, suppress, streams, counters)
+    if logits.dtype != torch.float32 or work.dtype != torch.float32 or out.dtype != torch.int32:
+        raise KernelError("sample takes float32 logits and scratch and an int32 output")
+    rows, vocab = logits.shape
+    if work.numel() < logits.numel() or out.numel() < rows:
+        raise KernelError("sample: scratch or output too small")
+    if do_sample and (streams is None or counters is None):
+        raise KernelError("sample: sampling needs the per-row stream and counter tensors")
+    _check(lib().ptb_sample(_ptr(logits), _ptr(work), _ptr(out), rows, vocab, 1 if do_sample else 0,
+                            ctypes.c_float(temperature), int(top_k), ctypes.c_float(top_p), ctypes.c_float(min_p),
+                            ctypes.c_float(repetition_penalty), _ptr(history), _ptr(history_len),
+                            0 if history is None else history.shape[1], _ptr(suppress),
+                            0 if suppress is None else suppress.numel(), ctypes.c_ulonglong(seed & (2 ** 64 - 1)),
+                            _ptr(streams), _ptr(counters), _stream(logits)), "sample")
+    return out
+
+
+def matmul_nt(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """Library matrix product x @ w.T for the bfloat16 path (cuBLAS through torch), where the
+    reference's engine uses the same library. float32 inputs are refused: the float32 path has
+    its own kernel (linear_f32)."""
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        raise KernelError("matmul_nt is the bfloat16 library product; float32 goes through linear_f32")
+    _need_cuda(x, w)
+    if out_dtype is None or out_dtype == torch.bfloat16:
+        return torch.mm(x, w.t())
+    return torch.mm(x, w.t(), out_dtype=out_dtype)

@@ -1,0 +1,65 @@
+"""The attention mixer: fused query/key/value projection, position encoding, attention over
+the paged cache, output projection.
+
+The fused projection's rows are grouped per K/V head as (q_per_kv query heads, K, V). This one
+layout covers the three that the reference's ``_split_heads`` distinguishes
+(src/transformers/models/falcon/modeling_falcon.py:269-298): the new decoder architecture
+(kv_heads groups), multi-query (one group: all queries, K, V) and per-head q,k,v (heads
+groups of one query). Query head h reads K/V head h // q_per_kv. Scores are
+``(q.k + bias) / sqrt(head_dim)`` over the keys at positions <= the query's
+(modeling_falcon.py:388-393, 1139-1144), softmax in float32.
+"""
+from __future__ import annotations
+
+import math
+from typing import Dict, Optional
+
+from .base import BuildContext, CacheNeed, ParamDecl, Part, PartSpec, register_part
+from .linear import linear
+
+
+@register_part("mixer", "attention")
+class Attention(Part):
+    def __init__(self, build: BuildContext, spec: PartSpec, hidden: int, heads: int, kv_heads: int, head_dim: int,
+                 bias: bool = False, window: int = 0, scale: Optional[float] = None):
+        super().__init__(build, spec)
+        if heads % kv_heads:
+            raise ValueError(f"heads ({heads}) must be a multiple of kv_heads ({kv_heads})")
+        self.hidden, self.heads, self.kv_heads, self.head_dim = int(hidden), int(heads), int(kv_heads), int(head_dim)
+        self.q_per_kv = self.heads // self.kv_heads
+        self.has_bias, self.window = bool(bias), int(window)
+        self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(self.head_dim)
+        self.position = self.children.get("position")
+        self.p_qkv_weight = self.p_qkv_bias = self.p_out_weight = self.p_out_bias = None
+
+    def param_decls(self) -> Dict[str, ParamDecl]:
+        fused = (self.heads + 2 * self.kv_heads) * self.head_dim
+        d = {"qkv.weight": ParamDecl((fused, self.hidden)),
+             "out.weight": ParamDecl((self.hidden, self.heads * self.head_dim))}
+        if self.has_bias:
+            d["qkv.bias"] = ParamDecl((fused,), role="vector")
+            d["out.bias"] = ParamDecl((self.hidden,), role="vector")
+        return d
+
+    def cache_need(self):
+        return CacheNeed("window" if self.window > 0 else "full", self.kv_heads, self.head_dim, self.window)
+
+    def state_need(self):
+        return None
+
+    def forward(self, x, ctx, entry):
+        k = self.build.kernels
+        fused = linear(k, x, self.p_qkv_weight, self.p_qkv_bias)
+        k_pool, v_pool, group = ctx.cache.entry_storage(entry.cache_entry)
+        batch = ctx.batch_c[group]
+        rotation = self.position.rotation() if self.position is not None else None
+        slopes = self.position.score_bias() if self.position is not None else None
+        q = k.split_rotate_store(fused, k_pool, v_pool, batch, rotation, self.kv_heads, self.q_per_kv,
+                                 self.head_dim, write_cache=entry.writes_cache)
+        o = self.attend(q, k_pool, v_pool, ctx, batch, slopes)
+        return linear(k, o, self.p_out_weight, self.p_out_bias)
+
+    def attend(self, q, k_pool, v_pool, ctx, batch, slopes):
+        return self.build.kernels.attention_generic(q, k_pool, v_pool, batch, ctx.dev["tile_seq"],
+                                                    ctx.dev["tile_q0"], ctx.n_tiles, slopes, self.kv_heads,
+                                                    self.scale, self.window)

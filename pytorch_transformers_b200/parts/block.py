@@ -1,0 +1,47 @@
+"""Block parts: how norms, mixer and feed-forward are arranged around the residual stream.
+
+``parallel``: mixer and feed-forward both read normed copies of the block input, and the
+output is ``x + (ff + mixer)`` (FalconDecoderLayer with parallel attention,
+src/transformers/models/falcon/modeling_falcon.py:630-634, 652-654, 673-676); with a
+``norm_ff`` child the feed-forward has its own norm of x, else it shares the mixer's.
+``sequential``: ``r = x + mixer(norm(x))``, then ``r + ff(norm_ff(r))`` (:656-659, 676).
+Sums are formed in float32 and rounded once.
+"""
+from __future__ import annotations
+
+from .base import BuildContext, Part, PartSpec, register_part
+
+
+@register_part("block", "parallel")
+class ParallelBlock(Part):
+    def __init__(self, build: BuildContext, spec: PartSpec):
+        super().__init__(build, spec)
+        self.norm_mixer = self.children["norm_mixer"]
+        self.norm_ff = self.children.get("norm_ff")
+        self.mixer = self.children["mixer"]
+        self.feed_forward = self.children["feed_forward"]
+
+    def forward(self, x, ctx, entry):
+        if self.norm_ff is not None:
+            a, m = self.norm_mixer.forward_pair(x, self.norm_ff)
+        else:
+            a = self.norm_mixer.forward(x)
+            m = a
+        mixed = self.mixer.forward(a, ctx, entry)
+        ff = self.feed_forward.forward(m, ctx)
+        return self.build.kernels.residual(x, ff, mixed)
+
+
+@register_part("block", "sequential")
+class SequentialBlock(Part):
+    def __init__(self, build: BuildContext, spec: PartSpec):
+        super().__init__(build, spec)
+        self.norm_mixer = self.children["norm_mixer"]
+        self.norm_ff = self.children["norm_ff"]
+        self.mixer = self.children["mixer"]
+        self.feed_forward = self.children["feed_forward"]
+
+    def forward(self, x, ctx, entry):
+        k = self.build.kernels
+        r = k.residual(x, self.mixer.forward(self.norm_mixer.forward(x), ctx, entry))
+        return k.residual(r, self.feed_forward.forward(self.norm_ff.forward(r), ctx))

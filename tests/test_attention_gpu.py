@@ -1,0 +1,62 @@
+"""The split/rotate/store kernel and attention over the paged cache, alone, against plain attention
+of whole sequences: head sizes in steps of 16 and one that is not, any number of heads and
+groups, prompts, chunks after a past, single tokens, keys far back, page and window edges."""
+import pytest
+import torch
+
+from engine_helpers import attention_case
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def K():
+    from pytorch_transformers_b200 import kernels
+    kernels.lib()
+    assert kernels.lib().ptb_attention_generic_tile_rows() == kernels.generic_tile_rows()
+    return kernels
+
+
+def tol(dtype):
+    return dict(atol=1e-5, rtol=1e-5) if dtype == torch.float32 else dict(atol=2e-2, rtol=2e-2)
+
+
+SHAPES = [  # heads, kv_heads, head_dim
+    (4, 1, 16), (8, 2, 12), (6, 6, 16), (6, 3, 32), (71, 1, 64), (5, 5, 48), (4, 2, 128), (3, 1, 80), (2, 1, 256),
+]
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("heads,kv,d", SHAPES)
+@pytest.mark.parametrize("position", ["rotary", "alibi"])
+def test_prompts_of_unequal_lengths(K, dtype, heads, kv, d, position):
+    out, ref = attention_case(K, dtype, heads, kv, d, pasts=[0, 0, 0, 0], news=[1, 17, 64, 131], position=position)
+    torch.testing.assert_close(out, ref, **tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("heads,kv,d", [(4, 1, 16), (8, 2, 12), (71, 1, 64), (6, 3, 32)])
+@pytest.mark.parametrize("position", ["rotary", "alibi"])
+def test_single_tokens_and_chunks_after_a_past(K, dtype, heads, kv, d, position):
+    # decode at a page's last slot, at a page's first slot, in the middle; a chunk across a page edge
+    out, ref = attention_case(K, dtype, heads, kv, d, pasts=[63, 64, 200, 1, 60], news=[1, 1, 1, 1, 10],
+                              position=position, seed=3)
+    torch.testing.assert_close(out, ref, **tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("key_pos", [0, 63, 64, 300])
+def test_a_far_key_among_hundreds_is_found(K, dtype, key_pos):
+    out, ref = attention_case(K, dtype, 5, 1, 32, pasts=[0, 699], news=[40, 1], position="alibi" if key_pos % 2 else "none",
+                              seed=5, needle=(1, key_pos))
+    torch.testing.assert_close(out, ref, **tol(dtype))
+    # the needle row really is dominated by one key: its output is far from the mean of values
+    assert ref[-1].abs().max() > 0.5
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("window", [1, 5, 64, 65, 100])
+def test_window(K, dtype, window):
+    out, ref = attention_case(K, dtype, 4, 2, 16, pasts=[0, 130, 64], news=[150, 1, 3], position="rotary",
+                              window=window, seed=7)
+    torch.testing.assert_close(out, ref, **tol(dtype))

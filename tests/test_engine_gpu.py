@@ -1,0 +1,188 @@
+"""The engine against the plain implementation, in float32 and in bfloat16: each request alone
+and whole; with the last 32 tokens one by one; in batches of unequal lengths whose shorter
+requests end earlier, one batch after another on a small cache so that slots and pages are used
+again; long decoding; the first tokens of a sequence; greedy generation through the entry point."""
+import numpy as np
+import pytest
+import torch
+
+import plain_falcon as plain
+import tiny_models as tm
+
+pytestmark = pytest.mark.gpu
+
+CASES = {
+    "A": ("A", {}), "B": ("B", {}), "C": ("C", {}), "D": ("D", {}),
+    "A_sequential": ("A", {"parallel_attn": False}),
+    "B_one_norm": ("B", {"num_ln_in_parallel_attn": 1}),
+}
+DTYPES = ["float32", "bfloat16"]
+# float32: rounding of float32 sums against a float64 oracle, logits of magnitude ~1.
+# bfloat16: weights and activations carry 8 bits; the oracle runs in float64 on the same
+# bfloat16-rounded weights, so the difference is the activations' rounding alone.
+TOL = {"float32": dict(atol=1e-5, rtol=1e-4), "bfloat16": dict(atol=2e-2, rtol=3e-2)}
+
+
+class Loaded:
+    def __init__(self, tmp, case, dtype):
+        import pytorch_transformers_b200 as ptb
+        name, overrides = CASES[case]
+        self.name = name
+        self.folder = tm.tiny_folder(str(tmp), name, bf16=(dtype == "bfloat16"), **overrides)
+        self.model = ptb.AutoModelForCausalLM.from_pretrained(self.folder, dtype=dtype)
+        self.cfg, self.w = plain.load_folder(self.folder, torch.float64)
+        self.vocab = self.cfg["vocab_size"]
+
+    def plain_logits(self, ids):
+        return plain.model_logits(ids, self.cfg, self.w)
+
+
+@pytest.fixture(scope="module")
+def loaded(tmp_path_factory):
+    cache = {}
+
+    def get(case, dtype):
+        if (case, dtype) not in cache:
+            cache[(case, dtype)] = Loaded(tmp_path_factory.mktemp(f"{case}_{dtype}"), case, dtype)
+        return cache[(case, dtype)]
+    return get
+
+
+def close(a, b, dtype, what=""):
+    torch.testing.assert_close(a.double().cpu(), b.double().cpu(), msg=lambda m: f"{what}: {m}", **TOL[dtype])
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("case", sorted(CASES))
+def test_each_request_alone_and_whole(loaded, case, dtype):
+    L = loaded(case, dtype)
+    cache = L.model.new_cache(256)
+    for n, ids in zip((1, 5, 70, 129), tm.prompts(L.name, (1, 5, 70, 129), seed=11)):
+        slot = cache.open()
+        logits = L.model.step(cache, [slot], [ids], want="all")
+        assert logits.shape == (n, L.vocab) and logits.dtype == torch.float32
+        close(logits, L.plain_logits(ids), dtype, f"{case} whole prompt of {n}")
+        cache.close(slot)
+        cache.check()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("case", ["A", "B", "C", "D"])
+def test_last_32_tokens_one_by_one(loaded, case, dtype):
+    L = loaded(case, dtype)
+    cache = L.model.new_cache(192)
+    for ids in tm.prompts(L.name, (33, 100, 140), seed=12):
+        ref = L.plain_logits(ids)
+        slot = cache.open()
+        head = len(ids) - 32
+        got = [L.model.step(cache, [slot], [ids[:head]], want="last")]
+        for t in ids[head:]:
+            got.append(L.model.step(cache, [slot], [[t]], want="last"))
+        got = torch.cat(got)
+        close(got, ref[head - 1:], dtype, f"{case} tail of {len(ids)}")
+        cache.close(slot)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("case", ["A", "B", "C", "D"])
+def test_batches_of_unequal_lengths_with_slot_reuse(loaded, case, dtype):
+    L = loaded(case, dtype)
+    # 9 requests, batches of 3, a cache that holds one batch only: pages and slots are reused
+    lengths = [40, 7, 66, 1 + 12, 130, 64 + 3, 23, 65, 90]
+    decode = [5, 3, 12, 12, 2, 9, 1, 20, 6]          # tokens fed one by one after the prompt part
+    reqs = tm.prompts(L.name, lengths, seed=13)
+    refs = [L.plain_logits(ids) for ids in reqs]
+    cache = L.model.new_cache(64 * 6, max_slots=3)
+    for b0 in range(0, 9, 3):
+        idx = list(range(b0, b0 + 3))
+        slots = {i: cache.open() for i in idx}
+        assert sorted(slots.values()) == [0, 1, 2]
+        heads = {i: lengths[i] - decode[i] for i in idx}
+        out = L.model.step(cache, [slots[i] for i in idx], [reqs[i][:heads[i]] for i in idx], want="last")
+        for r, i in enumerate(idx):
+            close(out[r], refs[i][heads[i] - 1], dtype, f"{case} request {i} prompt end")
+        live = list(idx)
+        t = 0
+        while live:
+            done = [i for i in live if t >= decode[i]]
+            for i in done:                              # shorter requests end earlier
+                cache.close(slots[i])
+            live = [i for i in live if i not in done]
+            if not live:
+                break
+            out = L.model.step(cache, [slots[i] for i in live], [[reqs[i][heads[i] + t]] for i in live], want="last")
+            for r, i in enumerate(live):
+                close(out[r], refs[i][heads[i] + t], dtype, f"{case} request {i} decode step {t}")
+            t += 1
+        cache.check()
+        assert cache.live_tokens() == 0 and all(g.pool.in_use == 0 for g in cache.groups)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_padding_free_batch_equals_alone(loaded, dtype):
+    # what else is in the batch changes nothing beyond rounding: in float32 not even that
+    L = loaded("B", dtype)
+    reqs = tm.prompts("B", (3, 50, 77), seed=14)
+    cache = L.model.new_cache(512)
+    alone = []
+    for ids in reqs:
+        s = cache.open()
+        alone.append(L.model.step(cache, [s], [ids], want="all"))
+        cache.close(s)
+    slots = [cache.open() for _ in reqs]
+    together = L.model.step(cache, slots, reqs, want="all")
+    if dtype == "float32":
+        assert torch.equal(together, torch.cat(alone))
+    else:
+        close(together, torch.cat(alone), dtype, "batch vs alone")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("case", ["A", "C"])
+def test_long_decoding_and_first_tokens(loaded, case, dtype):
+    L = loaded(case, dtype)
+    ids = tm.prompts(L.name, (260,), seed=15)[0]
+    ref = L.plain_logits(ids)
+    cache = L.model.new_cache(320)
+    slot = cache.open()
+    got = [L.model.step(cache, [slot], [[t]], want="last") for t in ids]   # from the very first token on
+    got = torch.cat(got)
+    close(got[:4], ref[:4], dtype, f"{case} first tokens")
+    close(got, ref, dtype, f"{case} 260 single-token steps")
+    assert cache.length(slot) == 260
+
+
+@pytest.mark.parametrize("case", ["A", "B", "C", "D"])
+def test_greedy_generation_through_the_entry_point(loaded, case):
+    L = loaded(case, "float32")
+    prompts = tm.prompts(L.name, (5, 11, 17, 2), seed=16)
+    out = L.model.generate(prompts, max_new_tokens=8, do_sample=False, eos_token_id=None, max_batch_size=3)
+    for p, seq in zip(prompts, out):
+        assert seq[:len(p)] == p
+        assert seq[len(p):] == plain.greedy(p, L.cfg, L.w, 8)
+    # the reference's calling form: left-padded ids with an attention mask
+    width = max(len(p) for p in prompts)
+    ids = torch.zeros(len(prompts), width, dtype=torch.long)
+    mask = torch.zeros_like(ids)
+    for i, p in enumerate(prompts):
+        ids[i, width - len(p):] = torch.tensor(p)
+        mask[i, width - len(p):] = 1
+    seqs = L.model.generate(input_ids=ids, attention_mask=mask, max_new_tokens=8, do_sample=False,
+                            eos_token_id=None)
+    assert seqs.shape == (len(prompts), width + 8)
+    for i, p in enumerate(prompts):
+        assert seqs[i, width:].tolist() == out[i][len(p):]
+
+
+def test_stop_tokens_end_a_sequence_early(loaded):
+    L = loaded("B", "float32")
+    prompts = tm.prompts("B", (9, 30, 4), seed=17)
+    free = L.model.generate(prompts, max_new_tokens=10, eos_token_id=None)
+    # make the 3rd new token of request 1 the stop token
+    stop = free[1][len(prompts[1]) + 2]
+    out = L.model.generate(prompts, max_new_tokens=10, eos_token_id=[stop], return_dict_in_generate=True)
+    for i, p in enumerate(prompts):
+        new_free = free[i][len(p):]
+        want = new_free[:new_free.index(stop) + 1] if stop in new_free else new_free
+        assert out.sequences[i][len(p):] == want
+    assert out.finish_reasons[1] == "stop"

@@ -1,0 +1,123 @@
+"""Each kernel alone against a plain float32/float64 torch computation, at sizes other than the
+tiny models': widths and vocabularies that are no power of two, odd head counts, head sizes in
+steps of 16 (and one that is not), long and short rows."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import plain_falcon as plain
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def tol(dtype):
+    return dict(atol=2e-5, rtol=1e-5) if dtype == torch.float32 else dict(atol=2e-2, rtol=2e-2)
+
+
+@pytest.fixture(scope="module")
+def K():
+    from pytorch_transformers_b200 import kernels
+    kernels.lib()
+    return kernels
+
+
+def rnd(*shape, dtype=torch.float32, scale=1.0, seed=0):
+    g = torch.Generator().manual_seed(seed + sum(shape))
+    return (torch.randn(*shape, generator=g) * scale).to(dtype).cuda()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("width", [7, 96, 1000, 4544])
+def test_gather_rows(K, dtype, width):
+    table = rnd(333, width, dtype=dtype)
+    ids = torch.tensor([0, 332, 5, 5, 17], dtype=torch.int32).cuda()
+    status = torch.zeros(1, dtype=torch.int32).cuda()
+    out = K.gather_rows(ids, table, status)
+    assert torch.equal(out, table[ids.long()])
+    assert status.item() == 0
+    bad = torch.tensor([1, 400], dtype=torch.int32).cuda()
+    K.gather_rows(bad, table, status)
+    assert status.item() == 1
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("rows,width,eps", [(1, 64, 1e-5), (5, 96, 1e-6), (3, 4544, 1e-5), (2, 8192, 1e-5),
+                                            (4, 1001, 1e-3), (2, 20000, 1e-5)])
+def test_layernorm_and_pair(K, dtype, rows, width, eps):
+    x = rnd(rows, width, dtype=dtype, scale=3.0) + 0.5
+    g1, b1 = rnd(width, seed=1) + 1, rnd(width, seed=2)
+    g2, b2 = rnd(width, seed=3) + 1, rnd(width, seed=4)
+    ref1 = plain.layer_norm(x.double().cpu(), g1.double().cpu(), b1.double().cpu(), eps)
+    ref2 = plain.layer_norm(x.double().cpu(), g2.double().cpu(), b2.double().cpu(), eps)
+    y = K.norm(x, g1, b1, eps)
+    torch.testing.assert_close(y.double().cpu(), ref1, **tol(dtype))
+    y1, y2 = K.norm(x, g1, b1, eps, gain2=g2, bias2=b2)
+    assert torch.equal(y1, y)
+    torch.testing.assert_close(y2.double().cpu(), ref2, **tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_rmsnorm(K, dtype):
+    x = rnd(6, 200, dtype=dtype, scale=2.0)
+    g = rnd(200, seed=1) + 1
+    xd = x.double().cpu()
+    ref = xd / torch.sqrt((xd ** 2).mean(-1, keepdim=True) + 1e-6) * g.double().cpu()
+    torch.testing.assert_close(K.norm(x, g, None, 1e-6, "rmsnorm").double().cpu(), ref, **tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("act", ["none", "gelu", "gelu_new", "relu"])
+def test_bias_act(K, dtype, act):
+    y = rnd(9, 333, dtype=dtype, scale=2.0)
+    b = rnd(333, seed=5)
+    ref = y.double().cpu() + b.double().cpu()
+    ref = ref if act == "none" else plain.activation(ref, act)
+    out = K.bias_act_(y.clone(), b, act)
+    torch.testing.assert_close(out.double().cpu(), ref, **tol(dtype))
+    out2 = K.bias_act_(y.clone(), None, act)
+    ref2 = y.double().cpu() if act == "none" else plain.activation(y.double().cpu(), act)
+    torch.testing.assert_close(out2.double().cpu(), ref2, **tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_residual(K, dtype):
+    x, a, b = (rnd(11, 97, dtype=dtype, seed=s) for s in (1, 2, 3))
+    ref = x.double() + (a.double() + b.double())
+    torch.testing.assert_close(K.residual(x, a, b).double(), ref, **tol(dtype))
+    torch.testing.assert_close(K.residual(x, a).double(), x.double() + a.double(), **tol(dtype))
+    if dtype == torch.bfloat16:
+        # one rounding of the float32 sum, not a rounding per addition
+        exact = (x.float() + (a.float() + b.float())).bfloat16()
+        assert torch.equal(K.residual(x, a, b), exact)
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 64, 64), (37, 101, 53), (64, 64, 16), (130, 4672 // 8, 71), (5, 1000, 96),
+                                   (2, 65, 4544)])
+@pytest.mark.parametrize("act,bias", [("none", False), ("gelu", True), ("none", True)])
+def test_linear_f32(K, m, n, k, act, bias):
+    x, w = rnd(m, k, seed=1), rnd(n, k, seed=2, scale=0.1)
+    b = rnd(n, seed=3) if bias else None
+    ref = x.double().cpu() @ w.double().cpu().T
+    if bias:
+        ref = ref + b.double().cpu()
+    if act != "none":
+        ref = plain.activation(ref, act)
+    out = K.linear_f32(x, w, b, act)
+    torch.testing.assert_close(out.double().cpu(), ref, atol=1e-5, rtol=1e-5)
+
+
+def test_linear_f32_rows_do_not_depend_on_the_batch(K):
+    x, w = rnd(70, 300, seed=1), rnd(129, 300, seed=2)
+    full = K.linear_f32(x, w)
+    for rows in ([0], [3, 4], list(range(65, 70))):
+        part = K.linear_f32(x[rows].contiguous(), w)
+        assert torch.equal(part, full[rows])
+
+
+def test_to_float(K):
+    x = rnd(3, 1000, dtype=torch.bfloat16)
+    assert torch.equal(K.to_float(x), x.float())
