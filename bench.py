@@ -1,0 +1,359 @@
+"""Benchmark of the headline metric: decoded tokens per second of a Falcon-7B-shaped model in
+bfloat16 with random weights on one B200, batch 8 at context 2,048; plus prefill of 2,048
+tokens, decode at batch 1 and 64, the HBM roofline of the decode step, and the same decode rate
+end to end through ``generate`` (host tokens in and out).
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--impl ours|reference]
+
+One JSON line on stdout. A "step" is one decode step of the whole batch. Timing: CUDA events on
+the launching stream around exactly K steps after W warm-up steps, a synchronize on both sides;
+every step reads all weights (13.8 GB, far beyond the 126 MB L2), so no cache flush is needed
+between steps. SM clocks and throttle reasons are sampled with nvidia-smi during the timed
+region. ``--impl reference`` runs the reference's own FalconForCausalLM.generate from
+baseline/_ref on the same shapes.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+FALCON_7B = dict(vocab_size=65024, hidden_size=4544, num_hidden_layers=32, num_attention_heads=71,
+                 multi_query=True, parallel_attn=True, new_decoder_architecture=False, bias=False, alibi=False,
+                 rope_theta=10000.0, layer_norm_epsilon=1e-5, max_position_embeddings=2048,
+                 tie_word_embeddings=True, activation="gelu")
+CONTEXT = 2048
+PREFILL_TOKENS = 2048
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(path):
+        try:
+            raw = json.load(open(path))
+            return {"hbm_gbs": float(raw["hbm_gbs"]), "bf16_tflops": float(raw["bf16_tflops"]), "source": "measured"}
+        except Exception:
+            pass
+    return dict(FALLBACK_PEAKS, source="fallback")
+
+
+class ClockSampler:
+    """nvidia-smi samples of SM clock and throttle reasons while a region runs."""
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int = 0):
+        self.index, self.samples, self.proc = index, [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                                          "-lms", "100", "-i", str(self.index)], stdout=subprocess.PIPE, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.samples.append([c.strip() for c in line.split(",")])
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            time.sleep(0.15)
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+            self.thread.join(timeout=2)
+
+    def summary(self):
+        mhz, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for s in self.samples:
+            try:
+                mhz.append(int(s[0]))
+                mx.append(int(s[1]))
+            except (ValueError, IndexError):
+                continue
+            for n, v in zip(names, s[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        if not mhz:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        return {"sm_mhz": int(statistics.median(mhz)), "sm_max_mhz": max(mx), "reasons": sorted(reasons)}
+
+
+def falcon_param_count(c, layers):
+    h, nh, f, v = c["hidden_size"], c["num_attention_heads"], 4 * c["hidden_size"], c["vocab_size"]
+    d = h // nh
+    per_layer = (nh + 2) * d * h + h * h + 2 * f * h + 2 * h
+    return layers * per_layer + v * h + 2 * h, per_layer
+
+
+def decode_bytes(c, layers, batch, context):
+    """Bytes a decode step has to read: every weight it uses once (the tied table serves as head)
+    and the cached keys and values of the live requests, in bfloat16."""
+    h, nh = c["hidden_size"], c["num_attention_heads"]
+    d = h // nh
+    params, _ = falcon_param_count(c, layers)
+    kv = batch * context * layers * 2 * d * 2      # one K/V head
+    return 2 * params + kv
+
+
+def prefill_flops(c, layers, tokens):
+    h, nh, f, v = c["hidden_size"], c["num_attention_heads"], 4 * c["hidden_size"], c["vocab_size"]
+    d = h // nh
+    gemm = 2 * tokens * layers * ((nh + 2) * d * h + h * h + 2 * f * h)
+    attn = layers * nh * 2 * 2 * d * tokens * (tokens + 1) / 2      # QK^T and PV over the causal half
+    head = 2 * v * h
+    return gemm + attn + head
+
+
+def run_ours(args):
+    import torch
+
+    import pytorch_transformers_b200 as ptb
+    from pytorch_transformers_b200 import kernels
+    from pytorch_transformers_b200.config.generation import GenerationConfig
+    from pytorch_transformers_b200.sampling import DeviceSelector
+
+    torch.cuda.set_device(0)
+    layers = args.layers or FALCON_7B["num_hidden_layers"]
+    cfg = ptb.FalconConfig.from_dict(dict(FALCON_7B, num_hidden_layers=layers))
+    model = ptb.AutoModelForCausalLM.from_config(cfg, seed=0, dtype="bfloat16", device="cuda:0")
+    pk = peaks()
+    gen = torch.Generator().manual_seed(0)
+
+    def prompts(n, length):
+        return torch.randint(0, cfg.vocab_size, (n, length), generator=gen).tolist()
+
+    def decode_run(batch, steps, warmup, sample_clocks=False):
+        """Prefill `batch` prompts of CONTEXT tokens, then time `steps` decode steps."""
+        total = CONTEXT + steps + warmup + 1
+        cache = model.new_cache(batch * ((total + 63) // 64 * 64))
+        slots = [cache.open() for _ in range(batch)]
+        opts = GenerationConfig(do_sample=False)
+        sel = DeviceSelector(kernels, model.device, cfg.vocab_size, opts, max_rows=batch)
+        ps = prompts(batch, CONTEXT)
+        chunk = max(1, 8192 // CONTEXT)                      # prompts go in a few at a time to bound activations
+        for i in range(0, batch, chunk):
+            logits = model.step(cache, slots[i:i + chunk], ps[i:i + chunk], want="last")
+        toks = sel.select(model.step(cache, slots, [[1]] * batch, want="last"), list(range(batch)), 0)
+
+        def one():
+            nonlocal toks
+            logits = model.step(cache, slots, [[t] for t in toks], want="last")
+            toks = sel.select(logits, list(range(batch)), 0)
+
+        for _ in range(warmup):
+            one()
+        torch.cuda.synchronize()
+        sampler = ClockSampler() if sample_clocks else None
+        l0 = kernels.launches
+        if sampler:
+            sampler.__enter__()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        start.record()
+        for _ in range(steps):
+            one()
+        end.record()
+        torch.cuda.synchronize()
+        if sampler:
+            sampler.__exit__()
+        ms = start.elapsed_time(end) / steps
+        launches = kernels.launches - l0
+        ctx_mid = CONTEXT + 1 + warmup + steps / 2
+        cache.close_all()
+        del cache
+        torch.cuda.empty_cache()
+        return ms, launches, ctx_mid, (sampler.summary() if sampler else None)
+
+    # ---- prefill of 2,048 tokens (one prompt) ----
+    cache = model.new_cache(PREFILL_TOKENS + 64)
+    p = prompts(1, PREFILL_TOKENS)
+    times = []
+    for i in range(2 + 3):
+        s = cache.open()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        model.step(cache, [s], p, want="last")
+        b.record()
+        torch.cuda.synchronize()
+        if i >= 2:
+            times.append(a.elapsed_time(b))
+        cache.close(s)
+    del cache
+    pre_ms = statistics.median(times)
+    pre_flops = prefill_flops(FALCON_7B, layers, PREFILL_TOKENS)
+    prefill = {"value": round(PREFILL_TOKENS / pre_ms * 1e3, 1), "tokens": PREFILL_TOKENS, "ms": round(pre_ms, 3),
+               "frac": round(pre_flops / (pre_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
+
+    # ---- headline: decode at batch 8 ----
+    batch = args.batch
+    ms, launches, ctx_mid, clocks = decode_run(batch, args.steps, args.warmup, sample_clocks=True)
+    value = batch / ms * 1e3
+    need = decode_bytes(FALCON_7B, layers, batch, ctx_mid)
+    achieved = need / (ms * 1e-3) / 1e9
+    roofline = {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                "frac": round(achieved / pk["hbm_gbs"], 4), "peaks": pk["source"]}
+
+    points = {}
+    for b in (1, 64):
+        pms, _, _, _ = decode_run(b, max(8, args.steps // 2), 3)
+        points[f"decode_b{b}"] = round(b / pms * 1e3, 1)
+
+    # ---- end to end through generate(): host token lists in, host token lists out ----
+    n_new = args.steps + args.warmup
+    ps = prompts(batch, CONTEXT)
+    stamps = []
+    model.generate(ps, max_new_tokens=2, eos_token_id=None, max_batch_size=batch)       # sizes the cache, warms up
+    t_prefill_done = [None]
+
+    def on_token(r, tok):
+        if r == batch - 1:
+            stamps.append(time.perf_counter())
+
+    torch.cuda.synchronize()
+    model.generate(ps, max_new_tokens=n_new, eos_token_id=None, max_batch_size=batch, on_token=on_token)
+    torch.cuda.synchronize()
+    t_end = time.perf_counter()
+    # stamps[i] is taken when step i's tokens have reached the host; steps after the warm-up count
+    e2e_s = (stamps[-1] - stamps[args.warmup - 1]) / (len(stamps) - args.warmup)
+    e2e = {"value": round(batch / e2e_s, 1), "unit": "tokens/s",
+           "h2d_bytes_per_step": int(model.last_h2d_bytes),
+           "d2h_bytes_per_step": 4 * batch}
+
+    out = {
+        "metric": "decode tokens/s, Falcon-7B shape, bf16, batch 8, context 2048", "value": round(value, 1),
+        "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms, 4),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "impl": "ours",
+        "config": {"model": "falcon-7b-shape", "layers": layers, "layers_of_config": FALCON_7B["num_hidden_layers"],
+                   "hidden": 4544, "heads": 71, "kv_heads": 1, "head_dim": 64, "ffn": 18176, "vocab": 65024,
+                   "global_batch": batch, "seq_len": CONTEXT, "prompt_tokens": CONTEXT, "weights": "random seed 0",
+                   "tokens": "uniform seed 0", "parallelism": "none", "sampling": "greedy on device",
+                   "l2": "inputs larger than L2 (all weights read per step)", "cache_page": 64},
+        "prefill": prefill, "roofline": roofline, "points": points, "e2e": e2e, "gpu_launches": launches,
+        "clocks": clocks,
+    }
+    print(json.dumps(out), flush=True)
+    return 0
+
+
+def run_reference(args):
+    """The reference's own FalconForCausalLM.generate (bf16, its default attention path, its
+    DynamicCache) from baseline/_ref, same shapes, random weights, same metric."""
+    ref = os.path.join(ROOT, "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref, "transformers")):
+        print(json.dumps({"impl": "reference", "unavailable": "baseline/_ref holds no installed reference"}))
+        return 0
+    try:
+        import importlib.metadata as md
+        os.environ["HF_HUB_OFFLINE"] = "1"
+        os.environ["TRANSFORMERS_OFFLINE"] = "1"
+        sys.path.insert(0, ref)
+        real = md.version
+        # the reference checks two wheels' versions at import; answer with versions in its range
+        md.version = lambda n: {"tokenizers": "0.21.4", "huggingface-hub": "0.30.0"}.get(
+            n.lower().replace("_", "-")) or real(n)
+        import torch
+        from transformers import FalconConfig, FalconForCausalLM
+        torch.cuda.set_device(0)
+        layers = args.layers or FALCON_7B["num_hidden_layers"]
+        cfg = FalconConfig(**dict(FALCON_7B, num_hidden_layers=layers))
+        torch.manual_seed(0)
+        with torch.device("cuda:0"):
+            model = FalconForCausalLM(cfg).to(torch.bfloat16).eval()
+        batch = args.batch
+        ids = torch.randint(0, cfg.vocab_size, (batch, CONTEXT), generator=torch.Generator().manual_seed(0))
+        pinned = ids.pin_memory()
+        stamps = []
+
+        class Stamp:
+            def put(self, value):
+                value.cpu() if hasattr(value, "cpu") else None
+                stamps.append(time.perf_counter())
+
+            def end(self):
+                pass
+
+        def run(n_new, streamer=None):
+            dev = pinned.to("cuda:0", non_blocking=True)
+            return model.generate(dev, attention_mask=torch.ones_like(dev), max_new_tokens=n_new, do_sample=False,
+                                  eos_token_id=None, pad_token_id=0, streamer=streamer)
+
+        # device-timed decode: (prefill + W+K tokens) - (prefill + W tokens), CUDA events
+        def timed(n_new):
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            run(n_new)
+            b.record()
+            torch.cuda.synchronize()
+            return a.elapsed_time(b)
+
+        timed(2)
+        sampler = ClockSampler()
+        with sampler:
+            t_short = timed(args.warmup)
+            t_long = timed(args.warmup + args.steps)
+        ms = (t_long - t_short) / args.steps
+        # end to end: wall clock between tokens reaching the host, warm-up steps dropped
+        # (generate() batch > 1 cannot stream through TextStreamer; a plain streamer object serves)
+        stamps.clear()
+        try:
+            run(args.warmup + args.steps, streamer=Stamp())
+            per = (stamps[-1] - stamps[args.warmup]) / (len(stamps) - 1 - args.warmup)
+            e2e = {"value": round(batch / per, 1), "unit": "tokens/s", "h2d_bytes_per_step": 0,
+                   "d2h_bytes_per_step": 8 * batch}
+        except Exception as e:  # noqa: BLE001
+            e2e = {"value": None, "unit": "tokens/s", "error": str(e)[:200]}
+        out = {"metric": "decode tokens/s, Falcon-7B shape, bf16, batch 8, context 2048", "impl": "reference",
+               "value": round(batch / ms * 1e3, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
+               "warmup": args.warmup, "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak",
+               "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+               "config": {"model": "falcon-7b-shape", "layers": layers,
+                          "layers_of_config": FALCON_7B["num_hidden_layers"], "global_batch": batch,
+                          "seq_len": CONTEXT, "attention": "sdpa (reference default)", "cache": "DynamicCache",
+                          "timing": "generate(W+K) minus generate(W), CUDA events"},
+               "e2e": e2e, "gpu_launches": 0, "clocks": sampler.summary()}
+        print(json.dumps(out), flush=True)
+    except Exception as e:  # noqa: BLE001
+        print(json.dumps({"impl": "reference", "unavailable": f"{type(e).__name__}: {str(e)[:300]}"}))
+    return 0
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration's (0: all)")
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    args = ap.parse_args()
+    if args.gpus != 1:
+        print(f"bench.py measures one GPU: this library is a single-GPU engine, --gpus {args.gpus} is not run")
+        return 2
+    args.warmup = max(3, args.warmup)
+    if args.impl == "reference":
+        return run_reference(args)
+    return run_ours(args)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -18,6 +18,37 @@ from .. import kernels as K
 from ..cache.paged import PAGE, Cache
 
 
+class PinnedRing:
+    """A few page-locked host buffers used in turn for the step's index arrays, so that the copy
+    to the device is asynchronous and no buffer is rewritten before its copy has run."""
+
+    def __init__(self, depth: int = 4):
+        self.depth = depth
+        self.buffers = [None] * depth
+        self.events = [None] * depth
+        self.next = 0
+
+    def stage(self, packed: np.ndarray, device: torch.device) -> torch.Tensor:
+        if device.type != "cuda":
+            return torch.from_numpy(packed).to(device)
+        i = self.next
+        self.next = (i + 1) % self.depth
+        buf = self.buffers[i]
+        if buf is None or buf.numel() < packed.size:
+            buf = torch.empty(max(4096, 2 * packed.size), dtype=torch.int32, pin_memory=True)
+            self.buffers[i] = buf
+            self.events[i] = torch.cuda.Event()
+        else:
+            self.events[i].synchronize()
+        buf[:packed.size].numpy()[:] = packed
+        dev = buf[:packed.size].to(device, non_blocking=True)
+        self.events[i].record(torch.cuda.current_stream(device))
+        return dev
+
+
+_RING = PinnedRing()
+
+
 class StepError(ValueError):
     """A step that cannot be run as asked (bad slot, empty token list, token id out of range...)."""
 
@@ -95,7 +126,8 @@ class StepContext:
             o, n = offsets[name]
             packed[o:o + n] = arr
         self.host = {name: packed[o:o + n] for name, (o, n) in offsets.items()}
-        dev = torch.from_numpy(packed).to(cache.device)
+        dev = _RING.stage(packed, cache.device)
+        self.h2d_bytes = packed.nbytes
         self.dev: Dict[str, torch.Tensor] = {name: dev[o:o + n] for name, (o, n) in offsets.items()}
         self._packed_dev = dev
 

@@ -138,6 +138,7 @@ class CausalLM:
             else:
                 raise StepError(f"want must be 'last', 'all', 'none' or lists of positions, got {want!r}")
         ctx = StepContext(cache, slots, token_lists, self.spec.vocab_size, want, K.generic_tile_rows())
+        self.last_h2d_bytes = ctx.h2d_bytes     # index arrays copied to the device for this step
         logits = self.forward(ctx)
         ctx.commit()
         return logits

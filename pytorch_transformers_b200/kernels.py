@@ -48,7 +48,12 @@ def _stream(t: torch.Tensor):
     return ctypes.c_void_p(torch.cuda.current_stream(t.device).cuda_stream)
 
 
+launches = 0  # entry points called so far (every one launches one kernel of this library)
+
+
 def _check(code: int, what: str) -> None:
+    global launches
+    launches += 1
     if code != 0:
         raise KernelError(f"{what}: {_ERRORS.get(code, f'error {code}')}")
 

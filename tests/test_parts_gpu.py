@@ -1,0 +1,260 @@
+"""Each part alone against the plain functions, and the generality of the assembly: a toy
+architecture, defined here, with a mixer that keeps per-sequence state of its own, a block that
+runs twice, and a layer that reads another layer's keys and values, registered, built and
+stepped without touching the framework's files."""
+import dataclasses
+import math
+from typing import ClassVar
+
+import pytest
+import torch
+
+import plain_falcon as plain
+import tiny_models as tm
+
+pytestmark = pytest.mark.gpu
+
+
+def build_ctx(dtype=torch.float32):
+    from pytorch_transformers_b200 import kernels
+    from pytorch_transformers_b200.parts import BuildContext
+    return BuildContext(torch.device("cuda"), dtype, kernels)
+
+
+def rnd(*shape, seed=0, scale=1.0):
+    return (torch.randn(*shape, generator=torch.Generator().manual_seed(seed)) * scale)
+
+
+# ------------------------------------------------------------------------------ parts alone
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_norm_part(dtype):
+    from pytorch_transformers_b200.parts import PartSpec, make_part
+    part = make_part(build_ctx(dtype), PartSpec("norm", "layernorm", {"size": 100, "eps": 1e-4}))
+    assert set(part.param_decls()) == {"weight", "bias"} and part.param_decls()["weight"].role == "vector"
+    g, b, x = rnd(100, seed=1) + 1, rnd(100, seed=2), rnd(7, 100, seed=3).to(dtype)
+    part.bind({"weight": g.cuda(), "bias": b.cuda()})
+    ref = plain.layer_norm(x.double(), g.double(), b.double(), 1e-4)
+    tol = dict(atol=1e-5, rtol=1e-5) if dtype == torch.float32 else dict(atol=2e-2, rtol=2e-2)
+    torch.testing.assert_close(part.forward(x.cuda()).double().cpu(), ref, **tol)
+
+
+def test_position_parts():
+    from pytorch_transformers_b200.parts import PartSpec, make_part
+    rot = make_part(build_ctx(), PartSpec("position", "rotary", {"head_dim": 32, "theta": 500042.0, "factor": 2.0}))
+    c = {"hidden_size": 64, "num_attention_heads": 2, "rope_theta": 500042.0,
+         "rope_scaling": {"rope_type": "linear", "factor": 2.0}}
+    assert torch.equal(rot.rotation().cpu(), plain.rope_inv_freq(c)) and rot.score_bias() is None
+    for heads in (4, 6, 8, 71):
+        ali = make_part(build_ctx(), PartSpec("position", "alibi", {"heads": heads}))
+        assert torch.equal(ali.score_bias().cpu(), plain.alibi_slopes(heads).bfloat16().float())
+        assert ali.rotation() is None
+    with pytest.raises(ValueError):
+        make_part(build_ctx(), PartSpec("position", "rotary", {"head_dim": 32, "theta": 1e4, "rotary_dim": 34}))
+    with pytest.raises(ValueError, match="no position part of kind 'learned'"):
+        make_part(build_ctx(), PartSpec("position", "learned", {}))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("act,bias", [("gelu", True), ("gelu_new", False), ("relu", True)])
+def test_feed_forward_part(dtype, act, bias):
+    from pytorch_transformers_b200.parts import PartSpec, make_part
+    part = make_part(build_ctx(dtype), PartSpec("feed_forward", "dense",
+                                                {"hidden": 72, "inner": 200, "activation": act, "bias": bias}))
+    w = {"up.weight": rnd(200, 72, seed=1, scale=0.1), "down.weight": rnd(72, 200, seed=2, scale=0.1)}
+    if bias:
+        w.update({"up.bias": rnd(200, seed=3, scale=0.1), "down.bias": rnd(72, seed=4, scale=0.1)})
+    assert set(part.param_decls()) == set(w)
+    dev = {k: v.to(dtype if k.endswith("weight") else torch.float32).cuda() for k, v in w.items()}
+    part.bind(dev)
+    x = rnd(9, 72, seed=5).to(dtype)
+    wd = {k: (v.to(dtype) if k.endswith("weight") else v).double() for k, v in w.items()}
+    u = plain.activation(plain.linear(x.double(), wd["up.weight"], wd.get("up.bias")), act)
+    ref = plain.linear(u, wd["down.weight"], wd.get("down.bias"))
+    tol = dict(atol=1e-5, rtol=1e-5) if dtype == torch.float32 else dict(atol=2e-2, rtol=2e-2)
+    torch.testing.assert_close(part.forward(x.cuda(), None).double().cpu(), ref, **tol)
+
+
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
+def test_mixer_and_block_alone(name, tmp_path):
+    """One block of each tiny model, fed a random hidden state, against plain.decoder_layer."""
+    import pytorch_transformers_b200 as ptb
+    from pytorch_transformers_b200.engine.batch import StepContext
+    from pytorch_transformers_b200.parts import ScheduleEntry
+    folder = tm.tiny_folder(str(tmp_path), name)
+    model = ptb.AutoModelForCausalLM.from_pretrained(folder, dtype="float32")
+    cfg, w = plain.load_folder(folder, torch.float64)
+    c = plain.resolve(cfg)
+    lens = [19, 70]
+    x = [rnd(n, c["hidden_size"], seed=n) for n in lens]
+    cache = model.new_cache(256)
+    slots = [cache.open() for _ in lens]
+    ctx = StepContext(cache, slots, [[0] * n for n in lens], c["vocab_size"], [[] for _ in lens], 16)
+    layer = 1
+    entry = ScheduleEntry(block=layer, cache_entry=layer)
+    block = model.blocks[layer]
+    xin = torch.cat(x).cuda()
+    got = block.forward(xin, ctx, entry).double().cpu()
+    ref = torch.cat([plain.decoder_layer(t.double(), w, layer, c) for t in x])
+    torch.testing.assert_close(got, ref, atol=1e-5, rtol=1e-5)
+    # the mixer alone, on the block's normed input
+    p = f"transformer.h.{layer}."
+    norm_name = "ln_attn" if c["new_decoder_architecture"] and c["num_ln_in_parallel_attn"] == 2 else "input_layernorm"
+    a = [plain.layer_norm(t.double(), w[p + norm_name + ".weight"], w[p + norm_name + ".bias"],
+                          c["layer_norm_epsilon"]) for t in x]
+    got_attn = block.mixer.forward(torch.cat(a).float().cuda(), ctx, entry).double().cpu()
+    ref_attn = torch.cat([plain.self_attention(t, w, p + "self_attention.", c) for t in a])
+    torch.testing.assert_close(got_attn, ref_attn, atol=1e-5, rtol=1e-5)
+
+
+# ------------------------------------------------------------------------------ a toy architecture
+def _register_toy():
+    import pytorch_transformers_b200 as ptb
+    from pytorch_transformers_b200.config.base import ModelConfig
+    from pytorch_transformers_b200.parts import (ModelSpec, ParamDecl, Part, PartSpec, ScheduleEntry, StateNeed,
+                                                 register_part)
+
+    @register_part("mixer", "toy_running_mean")
+    class RunningMean(Part):
+        """y_t = W mean(x_0 .. x_t): per-sequence state = (sum of inputs, count). Torch ops: a toy."""
+
+        def __init__(self, build, spec, hidden):
+            super().__init__(build, spec)
+            self.hidden = hidden
+            self.p_w_weight = None
+
+        def param_decls(self):
+            return {"w.weight": ParamDecl((self.hidden, self.hidden))}
+
+        def cache_need(self):
+            return None
+
+        def state_need(self):
+            return StateNeed(self.hidden + 1)
+
+        def forward(self, x, ctx, entry):
+            state = ctx.cache.entry_state(entry.cache_entry)
+            out = torch.empty_like(x)
+            start = 0
+            for slot, n in zip(ctx.slots, ctx.new):
+                st = state[slot]
+                sums = st[:-1][None, :] + torch.cumsum(x[start:start + n].float(), 0)
+                counts = st[-1] + torch.arange(1, n + 1, device=x.device, dtype=torch.float32)
+                out[start:start + n] = ((sums / counts[:, None]) @ self.p_w_weight.float().T).to(x.dtype)
+                st[:-1] = sums[-1]
+                st[-1] = counts[-1]
+                start += n
+            return out
+
+    @dataclasses.dataclass
+    class ToyConfig(ModelConfig):
+        model_type: ClassVar[str] = "toy_mix"
+        vocab_size: int = 50
+        hidden_size: int = 32
+        heads: int = 4
+        kv_heads: int = 2
+
+    def block(cfg, i, mixer):
+        p = f"blocks.{i}."
+        norm = PartSpec("norm", "rmsnorm", {"size": cfg.hidden_size, "eps": 1e-5}, names={"weight": p + "norm.weight"})
+        ff = PartSpec("feed_forward", "dense", {"hidden": cfg.hidden_size, "inner": 48, "activation": "relu"},
+                      names={"up.weight": p + "ff.up.weight", "down.weight": p + "ff.down.weight"})
+        return PartSpec("block", "parallel", children={"norm_mixer": norm, "mixer": mixer, "feed_forward": ff})
+
+    def spec(cfg):
+        d = cfg.hidden_size // cfg.heads
+
+        def attn(i):
+            return PartSpec("mixer", "attention", {"hidden": cfg.hidden_size, "heads": cfg.heads,
+                                                   "kv_heads": cfg.kv_heads, "head_dim": d},
+                            children={"position": PartSpec("position", "rotary", {"head_dim": d, "theta": 100.0})},
+                            names={"qkv.weight": f"blocks.{i}.attn.qkv.weight", "out.weight": f"blocks.{i}.attn.out.weight"})
+
+        blocks = [block(cfg, 0, attn(0)),
+                  block(cfg, 1, PartSpec("mixer", "toy_running_mean", {"hidden": cfg.hidden_size},
+                                         names={"w.weight": "blocks.1.mix.w.weight"})),
+                  block(cfg, 2, attn(2))]
+        # block 0 runs twice (two cache entries); block 2 reads block 0's first cache entry
+        schedule = [ScheduleEntry(0, 0), ScheduleEntry(1, 1), ScheduleEntry(0, 2), ScheduleEntry(2, 0, writes_cache=False)]
+        return ModelSpec(cfg.vocab_size, cfg.hidden_size, "embed.weight", blocks,
+                         PartSpec("norm", "rmsnorm", {"size": cfg.hidden_size, "eps": 1e-5},
+                                  names={"weight": "final_norm.weight"}), None, schedule)
+
+    ptb.register_architecture("toy_mix", ("ToyMixForCausalLM",), ToyConfig, spec)
+    return ToyConfig
+
+
+def test_toy_architecture_with_a_stateful_mixer_repeated_block_and_shared_cache(tmp_path):
+    import pytorch_transformers_b200 as ptb
+    ToyConfig = _register_toy()
+    cfg = ToyConfig()
+    folder = ptb.write_random_model(cfg, seed=3, folder=str(tmp_path / "toy"), dtype=torch.float32)
+    assert ptb.AutoConfig.from_pretrained(folder) == cfg
+    model = ptb.AutoModelForCausalLM.from_pretrained(folder, dtype="float32")
+    cache = model.new_cache(512)
+    assert len(cache.groups) == 1 and cache.groups[0].entries == [0, 2]      # entries 0 and 2 hold K/V
+    assert cache.state_width == cfg.hidden_size + 1 and cache.entry_state(1) is not None
+    g = torch.Generator().manual_seed(0)
+    reqs = [torch.randint(0, 50, (n,), generator=g).tolist() for n in (70, 9, 33)]
+    whole = []
+    for ids in reqs:
+        s = cache.open()
+        whole.append(model.step(cache, [s], [ids], want="all"))
+        cache.close(s)
+    # token by token, batched with unequal lengths, on reused slots (state must have been zeroed)
+    slots = [cache.open() for _ in reqs]
+    heads = [5, 2, 33 - 8]
+    out = model.step(cache, slots, [r[:h] for r, h in zip(reqs, heads)], want="last")
+    live = list(range(3))
+    t = 0
+    while live:
+        for i in live:
+            row = live.index(i)
+            torch.testing.assert_close(out[row], whole[i][heads[i] + t - 1], atol=2e-5, rtol=1e-4)
+        live = [i for i in live if heads[i] + t < len(reqs[i])]
+        if not live:
+            break
+        out = model.step(cache, [slots[i] for i in live], [[reqs[i][heads[i] + t]] for i in live], want="last")
+        t += 1
+    # and against a plain computation of the same toy model
+    _, w = plain.load_folder(folder, torch.float64)
+    ref = toy_plain(reqs[0], w, cfg)
+    torch.testing.assert_close(whole[0].double().cpu(), ref, atol=2e-5, rtol=1e-4)
+    # generation works on it as on any model
+    gen = model.generate([reqs[1]], max_new_tokens=4, eos_token_id=None)
+    assert len(gen[0]) == len(reqs[1]) + 4
+
+
+def toy_plain(ids, w, cfg):
+    d = cfg.hidden_size // cfg.heads
+    c = {"num_attention_heads": cfg.heads, "hidden_size": cfg.hidden_size, "new_decoder_architecture": True,
+         "num_kv_heads": cfg.kv_heads, "rope_theta": 100.0, "rope_scaling": None}
+
+    def rms(x, g):
+        return x / torch.sqrt((x ** 2).mean(-1, keepdim=True) + 1e-5) * g
+
+    def ff(x, i):
+        return torch.relu(x @ w[f"blocks.{i}.ff.up.weight"].T) @ w[f"blocks.{i}.ff.down.weight"].T
+
+    def attn(a, i, kv=None):
+        q, k, v = plain.split_heads(a @ w[f"blocks.{i}.attn.qkv.weight"].T, c)
+        pos = torch.arange(a.shape[0])
+        inv = plain.rope_inv_freq(c)
+        q, k = plain.rotary(q, pos, inv), plain.rotary(k, pos, inv)
+        if kv is not None:
+            k, v = kv
+        return plain.attention_core(q, k, v, c) @ w[f"blocks.{i}.attn.out.weight"].T, (k, v)
+
+    x = w["embed.weight"][torch.tensor(ids)]
+    a = rms(x, w["blocks.0.norm.weight"])
+    y, kv0 = attn(a, 0)
+    x = x + (ff(a, 0) + y)
+    a = rms(x, w["blocks.1.norm.weight"])
+    mean = torch.cumsum(a, 0) / torch.arange(1, len(ids) + 1, dtype=a.dtype)[:, None]
+    x = x + (ff(a, 1) + mean @ w["blocks.1.mix.w.weight"].T)
+    a = rms(x, w["blocks.0.norm.weight"])
+    y, _ = attn(a, 0)
+    x = x + (ff(a, 0) + y)
+    a = rms(x, w["blocks.2.norm.weight"])
+    y, _ = attn(a, 2, kv=kv0)
+    x = x + (ff(a, 2) + y)
+    return rms(x, w["final_norm.weight"]) @ w["embed.weight"].T
