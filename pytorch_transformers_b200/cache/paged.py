@@ -15,8 +15,8 @@ count rounded up to a whole page of 64; every group gets ``max_tokens / 64`` pag
 
 Sequences. ``open()`` gives a slot, ``reserve(slot, n)`` gets the pages for ``n`` more tokens
 (or raises CacheFull before anything is launched), ``commit(slot, n)`` advances the length
-after the step, ``close(slot)`` gives pages and slot back. Storage is never cleared: lengths
-and page lists gate every read. The state area is zeroed for a slot when it is opened.
+after the step, ``close(slot)`` gives pages and slot back. Storage is zeroed when it is
+allocated and never again: lengths and page lists gate every read. The state area is zeroed for a slot when it is opened.
 """
 from __future__ import annotations
 
@@ -41,8 +41,9 @@ class StorageGroup:
         self.index_of = {e: i for i, e in enumerate(self.entries)}
         self.pool = IdPool(num_pages, "cache page")
         shape = (len(self.entries), num_pages, need.kv_heads, PAGE, need.head_dim)
-        self.k = torch.empty(shape, dtype=dtype, device=device)
-        self.v = torch.empty(shape, dtype=dtype, device=device)
+        # zeroed once: kernels multiply masked positions of a page by zero, which must not meet a NaN
+        self.k = torch.zeros(shape, dtype=dtype, device=device)
+        self.v = torch.zeros(shape, dtype=dtype, device=device)
 
     def bytes(self) -> int:
         return 2 * self.k.numel() * self.k.element_size()

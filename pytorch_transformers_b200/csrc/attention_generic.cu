@@ -206,10 +206,12 @@ int launch_attention(const void* q, const void* k_pool, const void* v_pool, void
                      const int* tile_seq, const int* tile_q0, int n_tiles, const float* slopes, int heads,
                      int kv_heads, int head_dim, float scale, int window, cudaStream_t stream) {
   const size_t smem = sizeof(float) * (size_t(BQ) * head_dim + size_t(PTB_PAGE) * (head_dim + 1) + BQ * PTB_PAGE);
-  if (smem > 48 * 1024) {
+  static size_t configured = 48 * 1024;  // per element type: raised when a larger head size first comes
+  if (smem > configured) {
     if (cudaFuncSetAttribute(attention_generic_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) !=
         cudaSuccess)
       return PTB_ERR_LAUNCH;
+    configured = smem;
   }
   dim3 grid(n_tiles, heads);
   attention_generic_kernel<T><<<grid, THREADS, smem, stream>>>((const T*)q, (const T*)k_pool, (const T*)v_pool,

@@ -97,15 +97,20 @@ PTB_API int ptb_norm(int dtype, const void* x, const float* gain1, const float* 
   if (smem > 200 * 1024) return PTB_ERR_SIZE;
   const int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
   cudaError_t e = cudaSuccess;
+  static size_t configured_f32 = 48 * 1024, configured_bf16 = 48 * 1024;
   if (dtype == PTB_F32) {
-    if (smem > 48 * 1024)
+    if (smem > configured_f32) {
       e = cudaFuncSetAttribute(norm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+      configured_f32 = smem;
+    }
     if (e != cudaSuccess) return PTB_ERR_LAUNCH;
     norm_kernel<float><<<n, threads, smem, stream>>>((const float*)x, gain1, bias1, (float*)y1, gain2, bias2,
                                                      (float*)y2, width, eps, kind);
   } else if (dtype == PTB_BF16) {
-    if (smem > 48 * 1024)
+    if (smem > configured_bf16) {
       e = cudaFuncSetAttribute(norm_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+      configured_bf16 = smem;
+    }
     if (e != cudaSuccess) return PTB_ERR_LAUNCH;
     norm_kernel<__nv_bfloat16><<<n, threads, smem, stream>>>((const __nv_bfloat16*)x, gain1, bias1,
                                                              (__nv_bfloat16*)y1, gain2, bias2, (__nv_bfloat16*)y2,

@@ -2,14 +2,19 @@
 
 A step is a ragged batch: sequence ``b`` brings ``new[b]`` tokens that continue the
 ``past[b]`` tokens it already has in the cache. All index arrays are built on the host in one
-int32 buffer and reach the device in one copy; the kernels read them through ``StepBatch``
-(csrc/common.cuh). The reference pads prompts on the left and carries ``attention_mask``,
-``position_ids`` and ``cache_position`` tensors instead
+int32 buffer and reach the device in one copy from page-locked memory; the kernels read them
+through ``StepBatch`` (csrc/common.cuh). The reference pads prompts on the left and carries
+``attention_mask``, ``position_ids`` and ``cache_position`` tensors instead
 (src/transformers/generation/utils.py:349-481); here positions are arithmetic on lengths.
+
+The layout of the buffer depends only on the counts (tokens, sequences, wanted rows, tiles,
+width of the page tables). A step of single tokens whose counts equal an earlier one's can
+therefore reuse that step's device buffer: that is what lets a decode step be replayed as a
+CUDA graph (``static`` below).
 """
 from __future__ import annotations
 
-from typing import Dict, List, Optional, Sequence
+from typing import Dict, List, Optional, Sequence, Tuple
 
 import numpy as np
 import torch
@@ -28,9 +33,13 @@ class PinnedRing:
         self.events = [None] * depth
         self.next = 0
 
-    def stage(self, packed: np.ndarray, device: torch.device) -> torch.Tensor:
+    def stage(self, packed: np.ndarray, device: torch.device, into: Optional[torch.Tensor] = None) -> torch.Tensor:
         if device.type != "cuda":
-            return torch.from_numpy(packed).to(device)
+            t = torch.from_numpy(packed).to(device)
+            if into is not None:
+                into.copy_(t)
+                return into
+            return t
         i = self.next
         self.next = (i + 1) % self.depth
         buf = self.buffers[i]
@@ -41,7 +50,11 @@ class PinnedRing:
         else:
             self.events[i].synchronize()
         buf[:packed.size].numpy()[:] = packed
-        dev = buf[:packed.size].to(device, non_blocking=True)
+        if into is not None:
+            into.copy_(buf[:packed.size], non_blocking=True)
+            dev = into
+        else:
+            dev = buf[:packed.size].to(device, non_blocking=True)
         self.events[i].record(torch.cuda.current_stream(device))
         return dev
 
@@ -54,10 +67,15 @@ class StepError(ValueError):
 
 
 class StepContext:
-    """Everything a part may read about the running step."""
+    """Everything a part may read about the running step.
+
+    ``slots``, ``new``, ``past``: per sequence, on the host. ``dev[name]``: int32 device arrays
+    (tokens, tok_seq, tok_pos, seq_start, seq_new, seq_past, slots, logits_at, the tile lists and
+    one page table per storage group). ``batch_c[group]``: the StepBatch struct for the kernels.
+    """
 
     def __init__(self, cache: Cache, slots: Sequence[int], token_lists: Sequence[Sequence[int]], vocab_size: int,
-                 want: Sequence[Sequence[int]], tile_rows: int):
+                 want: Sequence[Sequence[int]], tile_rows: int, page_bucket: int = 0, defer: bool = False):
         if len(slots) != len(token_lists) or len(slots) != len(want):
             raise StepError("slots, token lists and wanted positions must have one item per sequence")
         if len(slots) == 0:
@@ -93,28 +111,36 @@ class StepContext:
         self.n_wanted = len(logits_at)
 
         # tiles of the general attention kernel: (sequence, first row) every `tile_rows` rows
-        tile_seq, tile_q0 = [], []
-        for b, n in enumerate(self.new):
-            for q0 in range(0, n, tile_rows):
-                tile_seq.append(b)
-                tile_q0.append(q0)
+        tile_seq, tile_q0 = self._tiles(tile_rows)
         self.n_tiles = len(tile_seq)
+        # tiles of the tensor-core attention kernel: one token per tile when every sequence brings
+        # a single token (all heads of a K/V group share the tile), else 16, 64 or 128 tokens
+        longest = max(self.new)
+        self.mma_tokens = 1 if longest == 1 else (16 if longest <= 16 else (64 if longest <= 64 else 128))
+        mtile_seq, mtile_q0 = self._tiles(self.mma_tokens)
+        self.n_mma_tiles = len(mtile_seq)
 
-        # page tables, one per storage group, padded to the longest
+        # page tables, one per storage group, padded to the longest (or to a whole bucket)
         cache.reserve_all(list(zip(self.slots, self.new)))
         tables = []
         for gi in range(len(cache.groups)):
             rows = [cache.pages(s, gi) for s in self.slots]
             width = max(1, max(len(r) for r in rows))
+            if page_bucket:
+                width = (width + page_bucket - 1) // page_bucket * page_bucket
             tab = np.full((self.n_seqs, width), -1, dtype=np.int64)
             for b, r in enumerate(rows):
                 tab[b, :len(r)] = r
             tables.append(tab)
+        self.table_widths: Tuple[int, ...] = tuple(t.shape[1] for t in tables)
+        # pages that a sequence of this step may span: sizes the division of keys among blocks
+        self.pages_hint = max(self.table_widths) if (page_bucket and tables) else (self.max_context + PAGE - 1) // PAGE
 
         parts = {"tokens": tokens, "tok_seq": tok_seq, "tok_pos": tok_pos, "seq_start": seq_start[:-1],
                  "seq_new": np.asarray(self.new), "seq_past": np.asarray(self.past),
                  "slots": np.asarray(self.slots), "logits_at": np.asarray(logits_at, dtype=np.int64),
-                 "tile_seq": np.asarray(tile_seq), "tile_q0": np.asarray(tile_q0)}
+                 "tile_seq": np.asarray(tile_seq), "tile_q0": np.asarray(tile_q0),
+                 "mtile_seq": np.asarray(mtile_seq), "mtile_q0": np.asarray(mtile_q0)}
         for gi, tab in enumerate(tables):
             parts[f"pages{gi}"] = tab.reshape(-1)
         offsets, total = {}, 0
@@ -126,12 +152,26 @@ class StepContext:
             o, n = offsets[name]
             packed[o:o + n] = arr
         self.host = {name: packed[o:o + n] for name, (o, n) in offsets.items()}
-        dev = _RING.stage(packed, cache.device)
+        self.layout_key = (self.n_tokens, self.n_seqs, self.n_wanted, self.n_tiles, self.n_mma_tiles,
+                           self.mma_tokens, self.table_widths)
         self.h2d_bytes = packed.nbytes
-        self.dev: Dict[str, torch.Tensor] = {name: dev[o:o + n] for name, (o, n) in offsets.items()}
-        self._packed_dev = dev
-
+        self.packed_size = packed.size
+        self._packed, self._offsets, self._tables = packed, offsets, tables
+        self.dev: Dict[str, torch.Tensor] = {}
         self.batch_c: List[K.StepBatchC] = []
+        if not defer:
+            self.bind()
+
+    def bind(self, static: Optional[torch.Tensor] = None) -> None:
+        """Copy the index arrays to the device: into a new buffer, or into ``static`` (a buffer of
+        exactly this layout's size that a captured graph reads)."""
+        packed, offsets, tables = self._packed, self._offsets, self._tables
+        if static is not None and static.numel() != packed.size:
+            raise StepError("the static step buffer does not fit this step's layout")
+        dev = _RING.stage(packed, self.cache.device, into=static)
+        self.dev = {name: dev[o:o + n] for name, (o, n) in offsets.items()}
+        self.packed_dev = dev
+        self.batch_c = []
         for gi, tab in enumerate(tables):
             c = K.StepBatchC()
             c.tok_seq, c.tok_pos = self.dev["tok_seq"].data_ptr(), self.dev["tok_pos"].data_ptr()
@@ -139,6 +179,14 @@ class StepContext:
             c.seq_past, c.pages = self.dev["seq_past"].data_ptr(), self.dev[f"pages{gi}"].data_ptr()
             c.pages_stride, c.n_tokens, c.n_seqs = tab.shape[1], self.n_tokens, self.n_seqs
             self.batch_c.append(c)
+
+    def _tiles(self, rows: int):
+        seqs, firsts = [], []
+        for b, n in enumerate(self.new):
+            for q0 in range(0, n, rows):
+                seqs.append(b)
+                firsts.append(q0)
+        return seqs, firsts
 
     def commit(self) -> None:
         for s, n in zip(self.slots, self.new):

@@ -42,6 +42,9 @@ class CausalLM:
         self.embedding: Optional[torch.Tensor] = None
         self.head: Optional[torch.Tensor] = None
         self.status = None  # device int32 word raised by kernels that clamp a bad index
+        # replay steps of single tokens as CUDA graphs, if every part allows it
+        self.use_graphs = all(p.graph_safe for top in self.blocks + [self.final_norm] for p in top.walk())
+        self.last_h2d_bytes = 0
 
     # ------------------------------------------------------------------ parameters
     def param_table(self) -> Dict[str, Tuple[Optional[Part], str, ParamDecl]]:
@@ -137,11 +140,55 @@ class CausalLM:
                 want = [[] for _ in token_lists]
             else:
                 raise StepError(f"want must be 'last', 'all', 'none' or lists of positions, got {want!r}")
+        single = all(len(t) == 1 for t in token_lists) and all(list(w) == [0] for w in want)
+        if single and self.use_graphs and self.device.type == "cuda":
+            return self._step_graph(cache, slots, token_lists, want)
         ctx = StepContext(cache, slots, token_lists, self.spec.vocab_size, want, K.generic_tile_rows())
         self.last_h2d_bytes = ctx.h2d_bytes     # index arrays copied to the device for this step
         logits = self.forward(ctx)
         ctx.commit()
         return logits
+
+    # A step of single tokens launches the same kernels with the same shapes as the one before it
+    # when the batch size and the (bucketed) width of the page tables are unchanged: only the index
+    # arrays differ. Such steps are captured once as a CUDA graph and replayed, which removes the
+    # per-kernel launch cost of a few hundred launches per step. The graph reads its index arrays
+    # from a buffer of its own that every replay refills.
+    GRAPH_PAGE_BUCKET = 16
+    MAX_GRAPHS = 16
+
+    def _step_graph(self, cache: Cache, slots, token_lists, want) -> torch.Tensor:
+        ctx = StepContext(cache, slots, token_lists, self.spec.vocab_size, want, K.generic_tile_rows(),
+                          page_bucket=self.GRAPH_PAGE_BUCKET, defer=True)
+        # graphs live on the cache they were captured for (they hold pointers into its storage)
+        graphs = cache.__dict__.setdefault("_step_graphs", {})
+        key = (id(self), ctx.layout_key)
+        entry = graphs.get(key)
+        if entry is None:
+            static = torch.empty(ctx.packed_size, dtype=torch.int32, device=self.device)
+            ctx.bind(static)
+            # one plain run on a side stream first: lazy initialisations must not be captured
+            side = torch.cuda.Stream(device=self.device)
+            side.wait_stream(torch.cuda.current_stream(self.device))
+            with torch.cuda.stream(side):
+                self.forward(ctx)
+            torch.cuda.current_stream(self.device).wait_stream(side)
+            graph = torch.cuda.CUDAGraph()
+            before = K.launches
+            with torch.cuda.graph(graph):
+                out = self.forward(ctx)
+            # kernels of this library that one replay launches (for the launch count of benchmarks)
+            entry = {"static": static, "graph": graph, "out": out, "launches": K.launches - before}
+            while len(graphs) >= self.MAX_GRAPHS:
+                graphs.pop(next(iter(graphs)))
+            graphs[key] = entry
+        else:
+            ctx.bind(entry["static"])
+        self.last_h2d_bytes = ctx.h2d_bytes
+        entry["graph"].replay()
+        K.launches += entry["launches"]
+        ctx.commit()
+        return entry["out"].clone()   # the graph's own output buffer is rewritten by the next replay
 
     def forward(self, ctx: StepContext) -> torch.Tensor:
         k = self.build.kernels

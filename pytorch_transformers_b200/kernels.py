@@ -75,7 +75,7 @@ def lib():
     if not _configured:
         for name in ("ptb_gather_rows", "ptb_norm", "ptb_bias_act", "ptb_residual", "ptb_to_float",
                      "ptb_linear_f32", "ptb_split_rotate_store", "ptb_attention_generic", "ptb_sample",
-                     "ptb_attention_generic_tile_rows"):
+                     "ptb_attention_generic_tile_rows", "ptb_attention_mma", "ptb_attention_mma_supports"):
             getattr(L, name).restype = ctypes.c_int
         _configured = True
     return L
@@ -176,6 +176,46 @@ def attention_generic(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tenso
                                        heads, kv_heads, head_dim, ctypes.c_float(scale), window, _stream(q)),
            "attention_generic")
     return out
+
+
+def attention_mma_supports(head_dim: int) -> bool:
+    return bool(lib().ptb_attention_mma_supports(int(head_dim)))
+
+
+def attention_mma(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, batch: StepBatchC,
+                  tile_seq: torch.Tensor, tile_q0: torch.Tensor, n_tiles: int, slopes: Optional[torch.Tensor],
+                  kv_heads: int, scale: float, window: int, tokens_per_tile: int, heads_per_tile: int, warps: int,
+                  n_splits: int, scratch: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Tensor-core attention over the paged cache (bfloat16). A tile holds ``tokens_per_tile`` tokens
+    x ``heads_per_tile`` heads of one K/V group in ``warps`` x 16 rows; with ``n_splits`` > 1 the key
+    pages are divided among blocks and joined by a second kernel (``scratch``: float32 workspace)."""
+    _need_cuda(q, k_pool, v_pool, tile_seq, tile_q0, slopes, scratch)
+    if q.dtype != torch.bfloat16:
+        raise KernelError("attention_mma takes bfloat16 tensors")
+    n, heads, head_dim = q.shape
+    out = torch.empty((n, heads * head_dim), dtype=q.dtype, device=q.device)
+    if n_splits > 1:
+        need = attention_mma_scratch_floats(n_tiles, heads, kv_heads, heads_per_tile, n_splits, warps, head_dim)
+        if scratch is None:
+            scratch = torch.empty(need, dtype=torch.float32, device=q.device)
+        elif scratch.numel() < need or scratch.dtype != torch.float32:
+            raise KernelError(f"attention_mma: scratch of {need} float32 values needed")
+    _check(lib().ptb_attention_mma(_ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _ptr(scratch),
+                                   ctypes.byref(batch), _ptr(tile_seq), _ptr(tile_q0), n_tiles, _ptr(slopes),
+                                   heads, kv_heads, head_dim, heads_per_tile, tokens_per_tile, n_splits, warps,
+                                   ctypes.c_float(scale), window, _stream(q)), "attention_mma")
+    if n_splits > 1:
+        global launches
+        launches += 1   # the kernel that joins the splits
+    return out
+
+
+def attention_mma_scratch_floats(n_tiles: int, heads: int, kv_heads: int, heads_per_tile: int, n_splits: int,
+                                 warps: int, head_dim: int) -> int:
+    if n_splits <= 1:
+        return 0
+    chunks = (heads // kv_heads + heads_per_tile - 1) // heads_per_tile
+    return n_tiles * kv_heads * chunks * n_splits * warps * 16 * (head_dim + 2)
 
 
 def sample(logits: torch.Tensor, work: torch.Tensor, out: torch.Tensor, *, do_sample: bool, temperature: float = 1.0,

@@ -20,6 +20,7 @@ from .linear import linear
 
 @register_part("mixer", "attention")
 class Attention(Part):
+    graph_safe = True
     def __init__(self, build: BuildContext, spec: PartSpec, hidden: int, heads: int, kv_heads: int, head_dim: int,
                  bias: bool = False, window: int = 0, scale: Optional[float] = None):
         super().__init__(build, spec)
@@ -31,6 +32,8 @@ class Attention(Part):
         self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(self.head_dim)
         self.position = self.children.get("position")
         self.p_qkv_weight = self.p_qkv_bias = self.p_out_weight = self.p_out_bias = None
+        import torch
+        self._bf16 = torch.bfloat16
 
     def param_decls(self) -> Dict[str, ParamDecl]:
         fused = (self.heads + 2 * self.kv_heads) * self.head_dim
@@ -60,6 +63,32 @@ class Attention(Part):
         return linear(k, o, self.p_out_weight, self.p_out_bias)
 
     def attend(self, q, k_pool, v_pool, ctx, batch, slopes):
-        return self.build.kernels.attention_generic(q, k_pool, v_pool, batch, ctx.dev["tile_seq"],
-                                                    ctx.dev["tile_q0"], ctx.n_tiles, slopes, self.kv_heads,
-                                                    self.scale, self.window)
+        k = self.build.kernels
+        if q.dtype == self._bf16 and k.attention_mma_supports(self.head_dim):
+            return self._attend_mma(q, k_pool, v_pool, ctx, batch, slopes)
+        return k.attention_generic(q, k_pool, v_pool, batch, ctx.dev["tile_seq"], ctx.dev["tile_q0"], ctx.n_tiles,
+                                   slopes, self.kv_heads, self.scale, self.window)
+
+    def _attend_mma(self, q, k_pool, v_pool, ctx, batch, slopes):
+        """Tile shape of the tensor-core kernel for this step. Single tokens: all heads of a K/V
+        group in one tile, and the key pages divided among enough blocks to fill the device.
+        Prompts: 128 rows of (tokens x heads of a group)."""
+        k = self.build.kernels
+        tokens = ctx.mma_tokens
+        if tokens == 1:
+            hpk = min(self.q_per_kv, 128)
+            warps = (hpk + 15) // 16
+        else:
+            warps = 8
+            hpk = max(1, min(self.q_per_kv, 128 // tokens))
+        chunks = (self.q_per_kv + hpk - 1) // hpk
+        splits = 1
+        if tokens == 1:
+            blocks = ctx.n_mma_tiles * self.kv_heads * chunks
+            pages = ctx.pages_hint
+            if self.window > 0:
+                pages = min(pages, self.window // k.PAGE + 2)
+            # enough blocks for ~2 per SM, at least 2 pages per block
+            splits = max(1, min((2 * 148 + blocks - 1) // blocks, pages // 2, 64))
+        return k.attention_mma(q, k_pool, v_pool, batch, ctx.dev["mtile_seq"], ctx.dev["mtile_q0"], ctx.n_mma_tiles,
+                               slopes, self.kv_heads, self.scale, self.window, tokens, hpk, warps, splits)

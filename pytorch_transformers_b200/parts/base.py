@@ -135,7 +135,13 @@ class BuildContext:
 
 class Part:
     """Base of every part. Subclasses set ``family`` through registration and implement
-    ``param_decls`` and their family's methods."""
+    ``param_decls`` and their family's methods.
+
+    ``graph_safe``: the part's forward only launches work whose shapes and addresses depend on the
+    step's counts, and reads everything else (slots, positions, pages) from the step's device
+    arrays. Only then may a step be captured once and replayed as a CUDA graph; a part that loops
+    over the step's host lists leaves it False and the model steps without graphs."""
+    graph_safe = False
 
     def __init__(self, build: BuildContext, spec: PartSpec):
         self.build = build

@@ -14,6 +14,7 @@ from .base import BuildContext, Part, PartSpec, register_part
 
 @register_part("block", "parallel")
 class ParallelBlock(Part):
+    graph_safe = True
     def __init__(self, build: BuildContext, spec: PartSpec):
         super().__init__(build, spec)
         self.norm_mixer = self.children["norm_mixer"]
@@ -34,6 +35,7 @@ class ParallelBlock(Part):
 
 @register_part("block", "sequential")
 class SequentialBlock(Part):
+    graph_safe = True
     def __init__(self, build: BuildContext, spec: PartSpec):
         super().__init__(build, spec)
         self.norm_mixer = self.children["norm_mixer"]

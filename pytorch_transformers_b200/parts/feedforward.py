@@ -11,6 +11,7 @@ from .linear import linear
 
 @register_part("feed_forward", "dense")
 class DenseFeedForward(Part):
+    graph_safe = True
     def __init__(self, build: BuildContext, spec: PartSpec, hidden: int, inner: int, activation: str = "gelu",
                  bias: bool = False):
         super().__init__(build, spec)

@@ -13,6 +13,7 @@ from .base import BuildContext, ParamDecl, Part, PartSpec, register_part
 @register_part("norm", "layernorm")
 class LayerNorm(Part):
     kind = "layernorm"
+    graph_safe = True
 
     def __init__(self, build: BuildContext, spec: PartSpec, size: int, eps: float, bias: bool = True):
         super().__init__(build, spec)

@@ -19,6 +19,7 @@ from .base import BuildContext, Part, PartSpec, register_part
 
 @register_part("position", "none")
 class NoPosition(Part):
+    graph_safe = True
     def __init__(self, build: BuildContext, spec: PartSpec):
         super().__init__(build, spec)
 

@@ -7,7 +7,7 @@ import plain_falcon as plain
 
 
 def attention_case(K, dtype, heads, kv_heads, d, pasts, news, position="rotary", window=0, theta=10000.0,
-                   seed=0, needle=None):
+                   seed=0, needle=None, mma=None):
     """Run the split/rotate/store kernel and an attention function over random projections in two
     steps (first `pasts[b]` tokens, then `news[b]`) and return (engine output of the second step,
     plain output for the same rows) as float64 CPU tensors.
@@ -56,8 +56,16 @@ def attention_case(K, dtype, heads, kv_heads, d, pasts, news, position="rotary",
         ctx = StepContext(cache, [s for s, _ in live], toks, 1, [[] for _ in live], K.generic_tile_rows())
         x = torch.cat([fused[i][r[0]:r[1]] for i, (_, r) in zip(idx, live)]).to(dtype).cuda().contiguous()
         q = K.split_rotate_store(x, k_pool, v_pool, ctx.batch_c[gi], inv_freq, kv_heads, qpk, d)
-        out = K.attention_generic(q, k_pool, v_pool, ctx.batch_c[gi], ctx.dev["tile_seq"], ctx.dev["tile_q0"],
-                                  ctx.n_tiles, slopes, kv_heads, scale, window)
+        if mma is None:
+            out = K.attention_generic(q, k_pool, v_pool, ctx.batch_c[gi], ctx.dev["tile_seq"], ctx.dev["tile_q0"],
+                                      ctx.n_tiles, slopes, kv_heads, scale, window)
+        else:
+            # mma = (heads per tile or None for "all that fit", splits)
+            tokens = ctx.mma_tokens
+            hpk = mma[0] or (min(qpk, 128) if tokens == 1 else max(1, min(qpk, 128 // tokens)))
+            warps = (hpk * tokens + 15) // 16
+            out = K.attention_mma(q, k_pool, v_pool, ctx.batch_c[gi], ctx.dev["mtile_seq"], ctx.dev["mtile_q0"],
+                                  ctx.n_mma_tiles, slopes, kv_heads, scale, window, tokens, hpk, warps, mma[1])
         ctx.commit()
         return out, idx
 

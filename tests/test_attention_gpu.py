@@ -60,3 +60,56 @@ def test_window(K, dtype, window):
     out, ref = attention_case(K, dtype, 4, 2, 16, pasts=[0, 130, 64], news=[150, 1, 3], position="rotary",
                               window=window, seed=7)
     torch.testing.assert_close(out, ref, **tol(dtype))
+
+
+# ------------------------------------------------------------------------------ tensor-core kernel
+MMA_SHAPES = [(71, 1, 64), (4, 1, 64), (8, 2, 64), (32, 8, 128), (128, 8, 64), (6, 6, 64), (5, 1, 128), (3, 3, 128)]
+BF = torch.bfloat16
+
+
+@pytest.mark.parametrize("heads,kv,d", MMA_SHAPES)
+@pytest.mark.parametrize("position", ["rotary", "alibi"])
+@pytest.mark.parametrize("splits", [1, 3])
+def test_mma_single_tokens(K, heads, kv, d, position, splits):
+    out, ref = attention_case(K, BF, heads, kv, d, pasts=[63, 64, 200, 1, 700, 127], news=[1] * 6,
+                              position=position, seed=3, mma=(None, splits))
+    torch.testing.assert_close(out, ref, **tol(BF))
+
+
+@pytest.mark.parametrize("heads,kv,d", MMA_SHAPES)
+@pytest.mark.parametrize("news", [[1, 17, 64, 131], [5, 16, 9], [40, 64, 1], [300]])
+def test_mma_prompts(K, heads, kv, d, news):
+    out, ref = attention_case(K, BF, heads, kv, d, pasts=[0] * len(news), news=news, position="rotary", seed=4,
+                              mma=(None, 1))
+    torch.testing.assert_close(out, ref, **tol(BF))
+
+
+@pytest.mark.parametrize("news,pasts", [([10, 3], [60, 130]), ([70, 2], [1, 64]), ([129], [200])])
+@pytest.mark.parametrize("hpk", [1, None])
+def test_mma_chunks_after_a_past(K, news, pasts, hpk):
+    out, ref = attention_case(K, BF, 8, 2, 64, pasts=pasts, news=news, position="alibi", seed=6, mma=(hpk, 1))
+    torch.testing.assert_close(out, ref, **tol(BF))
+
+
+@pytest.mark.parametrize("key_pos", [0, 63, 64, 300, 698])
+def test_mma_far_key(K, key_pos):
+    out, ref = attention_case(K, BF, 71, 1, 64, pasts=[0, 699], news=[1, 1], position="none", seed=5,
+                              needle=(1, key_pos), mma=(None, 4))
+    torch.testing.assert_close(out, ref, **tol(BF))
+
+
+@pytest.mark.parametrize("window", [1, 5, 64, 65, 100])
+@pytest.mark.parametrize("news,pasts,splits", [([150, 1, 3], [0, 130, 64], 1), ([1, 1, 1], [300, 5, 64], 2)])
+def test_mma_window(K, window, news, pasts, splits):
+    out, ref = attention_case(K, BF, 4, 2, 64, pasts=pasts, news=news, position="rotary", window=window, seed=7,
+                              mma=(None, splits))
+    torch.testing.assert_close(out, ref, **tol(BF))
+
+
+def test_mma_refuses_what_it_does_not_take(K):
+    from pytorch_transformers_b200.kernels import KernelError
+    assert not K.attention_mma_supports(48) and K.attention_mma_supports(64) and K.attention_mma_supports(128)
+    with pytest.raises(KernelError):
+        attention_case(K, BF, 4, 1, 48, pasts=[0], news=[5], mma=(None, 1))
+    with pytest.raises(KernelError):
+        attention_case(K, torch.float32, 4, 1, 64, pasts=[0], news=[5], mma=(None, 1))

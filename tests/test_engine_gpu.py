@@ -12,7 +12,7 @@ import tiny_models as tm
 pytestmark = pytest.mark.gpu
 
 CASES = {
-    "A": ("A", {}), "B": ("B", {}), "C": ("C", {}), "D": ("D", {}),
+    "A": ("A", {}), "B": ("B", {}), "C": ("C", {}), "D": ("D", {}), "E": ("E", {}), "F": ("F", {}),
     "A_sequential": ("A", {"parallel_attn": False}),
     "B_one_norm": ("B", {"num_ln_in_parallel_attn": 1}),
 }
@@ -67,7 +67,7 @@ def test_each_request_alone_and_whole(loaded, case, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("case", ["A", "B", "C", "D"])
+@pytest.mark.parametrize("case", ["A", "B", "C", "D", "E", "F"])
 def test_last_32_tokens_one_by_one(loaded, case, dtype):
     L = loaded(case, dtype)
     cache = L.model.new_cache(192)
@@ -84,7 +84,7 @@ def test_last_32_tokens_one_by_one(loaded, case, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("case", ["A", "B", "C", "D"])
+@pytest.mark.parametrize("case", ["A", "B", "C", "D", "E", "F"])
 def test_batches_of_unequal_lengths_with_slot_reuse(loaded, case, dtype):
     L = loaded(case, dtype)
     # 9 requests, batches of 3, a cache that holds one batch only: pages and slots are reused
@@ -138,7 +138,7 @@ def test_padding_free_batch_equals_alone(loaded, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("case", ["A", "C"])
+@pytest.mark.parametrize("case", ["A", "C", "E"])
 def test_long_decoding_and_first_tokens(loaded, case, dtype):
     L = loaded(case, dtype)
     ids = tm.prompts(L.name, (260,), seed=15)[0]
@@ -186,3 +186,44 @@ def test_stop_tokens_end_a_sequence_early(loaded):
         want = new_free[:new_free.index(stop) + 1] if stop in new_free else new_free
         assert out.sequences[i][len(p):] == want
     assert out.finish_reasons[1] == "stop"
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("case", ["E", "F"])
+def test_decoding_across_a_bucket_of_pages_and_with_a_shrinking_batch(loaded, case, dtype):
+    """Steps of single tokens are replayed as CUDA graphs keyed on the batch size and the width of
+    the page tables (a multiple of 16 pages): decode from below 1024 tokens to above it, with
+    three sequences of which two end early, and compare every step with the whole sequences."""
+    L = loaded(case, dtype)
+    assert L.model.use_graphs
+    lengths = [1000, 1019, 40]
+    decode = [40, 12, 30]
+    reqs = tm.prompts(L.name, [n + d for n, d in zip(lengths, decode)], seed=18)
+    refs = [L.plain_logits(ids) for ids in reqs]
+    cache = L.model.new_cache(64 * 40)
+    slots = [cache.open() for _ in reqs]
+    out = L.model.step(cache, slots, [r[:n] for r, n in zip(reqs, lengths)], want="last")
+    live = [0, 1, 2]
+    for t in range(max(decode)):
+        for row, i in enumerate(live):
+            close(out[row], refs[i][lengths[i] + t - 1], dtype, f"{case} request {i} step {t}")
+        live = [i for i in live if t < decode[i]]
+        if not live:
+            break
+        out = L.model.step(cache, [slots[i] for i in live], [[reqs[i][lengths[i] + t]] for i in live], want="last")
+    graphs = cache.__dict__.get("_step_graphs", {})
+    assert len(graphs) >= 3          # batch sizes 3, 2, 1 and the wider page table
+    # the same steps without graphs give the same numbers
+    L.model.use_graphs = False
+    try:
+        cache2 = L.model.new_cache(64 * 20)
+        s = cache2.open()
+        L.model.step(cache2, [s], [reqs[2][:lengths[2]]], want="none")
+        plain_step = L.model.step(cache2, [s], [[reqs[2][lengths[2]]]], want="last")
+    finally:
+        L.model.use_graphs = True
+    cache3 = L.model.new_cache(64 * 20)
+    s = cache3.open()
+    L.model.step(cache3, [s], [reqs[2][:lengths[2]]], want="none")
+    graph_step = L.model.step(cache3, [s], [[reqs[2][lengths[2]]]], want="last")
+    assert torch.equal(plain_step, graph_step)

@@ -44,8 +44,20 @@ TINY = {
               rope_scaling={"rope_type": "linear", "factor": 2.0}, layer_norm_epsilon=1e-5,
               max_position_embeddings=512, tie_word_embeddings=True, activation="gelu_new",
               bos_token_id=11, eos_token_id=11),
+    # 7B-style with the 7B's head size (64) and an odd head count: the tensor-core attention path
+    "E": dict(vocab_size=400, hidden_size=192, num_hidden_layers=2, num_attention_heads=3,
+              multi_query=True, parallel_attn=True, new_decoder_architecture=False, bias=False,
+              alibi=False, rope_theta=10000.0, layer_norm_epsilon=1e-5, max_position_embeddings=2048,
+              ffn_hidden_size=304, tie_word_embeddings=True, activation="gelu",
+              bos_token_id=1, eos_token_id=2),
+    # 40B-style with head size 128, grouped K/V and ALiBi on the tensor-core path
+    "F": dict(vocab_size=500, hidden_size=512, num_hidden_layers=2, num_attention_heads=4,
+              num_kv_heads=2, new_decoder_architecture=True, num_ln_in_parallel_attn=2,
+              ffn_hidden_size=384, alibi=True, bias=True, layer_norm_epsilon=1e-5,
+              max_position_embeddings=2048, tie_word_embeddings=False, activation="gelu",
+              bos_token_id=0, eos_token_id=7),
 }
-SEEDS = {"A": 0, "B": 1, "C": 2, "D": 3}
+SEEDS = {"A": 0, "B": 1, "C": 2, "D": 3, "E": 4, "F": 5}
 
 
 def config_dict(name: str, **overrides) -> dict:
