@@ -181,6 +181,15 @@ def run_ours(args):
         torch.cuda.empty_cache()
         return ms, launches, ctx_mid, (sampler.summary() if sampler else None)
 
+    if args.no_graphs:
+        model.use_graphs = False
+    if args.only == "decode":
+        ms, launches, ctx_mid, _ = decode_run(args.batch, args.steps, args.warmup)
+        print(json.dumps({"only": "decode", "batch": args.batch, "layers": layers, "ms_per_step": round(ms, 4),
+                          "launches_per_step": launches / args.steps,
+                          "GBps": round(decode_bytes(FALCON_7B, layers, args.batch, ctx_mid) / ms / 1e6, 1)}))
+        return 0
+
     # ---- prefill of 2,048 tokens (one prompt) ----
     cache = model.new_cache(PREFILL_TOKENS + 64)
     p = prompts(1, PREFILL_TOKENS)
@@ -198,6 +207,10 @@ def run_ours(args):
         cache.close(s)
     del cache
     pre_ms = statistics.median(times)
+    if args.only == "prefill":
+        print(json.dumps({"only": "prefill", "layers": layers, "ms": round(pre_ms, 3),
+                          "TFLOPs": round(prefill_flops(FALCON_7B, layers, PREFILL_TOKENS) / pre_ms / 1e9, 1)}))
+        return 0
     pre_flops = prefill_flops(FALCON_7B, layers, PREFILL_TOKENS)
     prefill = {"value": round(PREFILL_TOKENS / pre_ms * 1e3, 1), "tokens": PREFILL_TOKENS, "ms": round(pre_ms, 3),
                "frac": round(pre_flops / (pre_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
@@ -345,6 +358,9 @@ def main():
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration's (0: all)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--only", default="", choices=["", "decode", "prefill"],
+                    help="run one section only and print its numbers (for profilers)")
+    ap.add_argument("--no-graphs", action="store_true", help="launch every kernel of a decode step itself")
     args = ap.parse_args()
     if args.gpus != 1:
         print(f"bench.py measures one GPU: this library is a single-GPU engine, --gpus {args.gpus} is not run")

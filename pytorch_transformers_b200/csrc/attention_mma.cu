@@ -281,38 +281,49 @@ attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
   }
 }
 
-// Joins the partial results of the splits: one block per (tile, group chunk); thread per (row, dim).
+// Joins the partial results of the splits: one warp per row of a tile, a lane per group of D / 32
+// dims; blockIdx.z walks the tile's rows four at a time. Every read of a split's row is one
+// coalesced line.
 template <int D>
-__global__ void attention_mma_reduce_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                            __nv_bfloat16* __restrict__ out, StepBatch sb,
-                                            const int* __restrict__ tile_seq, const int* __restrict__ tile_q0,
-                                            MmaParams p, int rows_total) {
+__global__ void __launch_bounds__(128)
+attention_mma_reduce_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                            __nv_bfloat16* __restrict__ out, StepBatch sb, const int* __restrict__ tile_seq,
+                            const int* __restrict__ tile_q0, MmaParams p, int rows_total) {
+  constexpr int PER = D / 32;  // dims per lane
   const int tile = blockIdx.x;
+  const int lane = threadIdx.x & 31;
+  const int r = blockIdx.z * 4 + (threadIdx.x >> 5);
+  if (r >= rows_total) return;
   const int qpk = p.heads / p.kv_heads;
   const int chunks = (qpk + p.hpk - 1) / p.hpk;
   const int g = blockIdx.y / chunks, h0 = (blockIdx.y % chunks) * p.hpk;
   const int seq = tile_seq[tile], q0 = tile_q0[tile];
-  const int tok_valid = min(p.tokens_per_tile, sb.seq_new[seq] - q0);
-  const int head_valid = min(p.hpk, qpk - h0);
-  const int start = sb.seq_start[seq];
+  const int tok = r / p.hpk, hh = r % p.hpk;
+  if (tok >= min(p.tokens_per_tile, sb.seq_new[seq] - q0) || hh >= min(p.hpk, qpk - h0)) return;
   const size_t slot0 = (size_t(tile) * gridDim.y + blockIdx.y) * p.n_splits;
-  for (int idx = threadIdx.x; idx < rows_total * D; idx += blockDim.x) {
-    const int r = idx / D, d = idx % D;
-    const int tok = r / p.hpk, hh = r % p.hpk;
-    if (tok >= tok_valid || hh >= head_valid) continue;
-    float m = -INFINITY;
-    for (int s = 0; s < p.n_splits; ++s) m = fmaxf(m, part_ml[((slot0 + s) * rows_total + r) * 2]);
-    float l = 0.f, acc = 0.f;
+  // lanes read the splits' (max, sum) pairs in parallel, 32 splits at a time
+  float m = -INFINITY;
+  for (int s = lane; s < p.n_splits; s += 32) m = fmaxf(m, part_ml[((slot0 + s) * rows_total + r) * 2]);
+  m = warp_max(m);
+  float acc[PER];
+#pragma unroll
+  for (int e = 0; e < PER; ++e) acc[e] = 0.f;
+  float l = 0.f;
+  if (m != -INFINITY) {
     for (int s = 0; s < p.n_splits; ++s) {
-      const float ms = part_ml[((slot0 + s) * rows_total + r) * 2];
-      if (ms == -INFINITY) continue;
-      const float w = exp2f(ms - m);
-      l += part_ml[((slot0 + s) * rows_total + r) * 2 + 1] * w;
-      acc += part_o[((slot0 + s) * rows_total + r) * D + d] * w;
+      const float2 ml = *reinterpret_cast<const float2*>(part_ml + ((slot0 + s) * rows_total + r) * 2);
+      if (ml.x == -INFINITY) continue;
+      const float w = exp2f(ml.x - m);
+      l += ml.y * w;
+      const float* po = part_o + ((slot0 + s) * rows_total + r) * D + lane * PER;
+#pragma unroll
+      for (int e = 0; e < PER; ++e) acc[e] += po[e] * w;
     }
-    out[(size_t(start + q0 + tok) * p.heads + (g * qpk + h0 + hh)) * D + d] =
-        __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
   }
+  const float inv = l > 0.f ? 1.f / l : 0.f;
+  __nv_bfloat16* dst = out + (size_t(sb.seq_start[seq] + q0 + tok) * p.heads + (g * qpk + h0 + hh)) * D + lane * PER;
+#pragma unroll
+  for (int e = 0; e < PER; ++e) dst[e] = __float2bfloat16_rn(acc[e] * inv);
 }
 
 template <int D>
@@ -336,8 +347,8 @@ int launch_mma(const void* q, const void* k_pool, const void* v_pool, void* out,
       partial ? part_o : nullptr, partial ? part_ml : nullptr, sb, tile_seq, tile_q0, slopes, p);
   if (cudaGetLastError() != cudaSuccess) return PTB_ERR_LAUNCH;
   if (partial) {
-    dim3 rgrid(n_tiles, p.kv_heads * chunks);
-    attention_mma_reduce_kernel<D><<<rgrid, 256, 0, stream>>>(part_o, part_ml, (__nv_bfloat16*)out, sb, tile_seq,
+    dim3 rgrid(n_tiles, p.kv_heads * chunks, (warps * 16 + 3) / 4);
+    attention_mma_reduce_kernel<D><<<rgrid, 128, 0, stream>>>(part_o, part_ml, (__nv_bfloat16*)out, sb, tile_seq,
                                                              tile_q0, p, warps * 16);
   }
   return launch_status();

@@ -206,4 +206,6 @@ class CausalLM:
         k = self.build.kernels
         if self.dtype == torch.float32:
             return k.linear_f32(rows, self.head)
+        if k.skinny_linear_takes(rows.shape[0], rows.shape[1]):
+            return k.skinny_linear(rows, self.head, out_dtype=torch.float32)
         return k.matmul_nt(rows, self.head, out_dtype=torch.float32)

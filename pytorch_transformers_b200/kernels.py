@@ -75,7 +75,8 @@ def lib():
     if not _configured:
         for name in ("ptb_gather_rows", "ptb_norm", "ptb_bias_act", "ptb_residual", "ptb_to_float",
                      "ptb_linear_f32", "ptb_split_rotate_store", "ptb_attention_generic", "ptb_sample",
-                     "ptb_attention_generic_tile_rows", "ptb_attention_mma", "ptb_attention_mma_supports"):
+                     "ptb_attention_generic_tile_rows", "ptb_attention_mma", "ptb_attention_mma_supports",
+                     "ptb_skinny_linear", "ptb_skinny_linear_max_rows", "ptb_skinny_linear_k_multiple"):
             getattr(L, name).restype = ctypes.c_int
         _configured = True
     return L
@@ -240,6 +241,32 @@ def sample(logits: torch.Tensor, work: torch.Tensor, out: torch.Tensor, *, do_sa
                             0 if suppress is None else suppress.numel(), ctypes.c_ulonglong(seed & (2 ** 64 - 1)),
                             _ptr(streams), _ptr(counters), _stream(logits)), "sample")
     return out
+
+
+SKINNY_MAX_ROWS = 32   # ptb_skinny_linear_max_rows()
+SKINNY_K_MULTIPLE = 32  # ptb_skinny_linear_k_multiple()
+
+
+def skinny_linear_takes(rows: int, k: int) -> bool:
+    return 0 < rows <= SKINNY_MAX_ROWS and k % SKINNY_K_MULTIPLE == 0
+
+
+def skinny_linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None, act: str = "none",
+                  add: Optional[torch.Tensor] = None, out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+    """act(x @ w.T + bias) + add for up to 32 rows of bfloat16 x: one pass over w at memory speed,
+    float32 accumulation and epilogue; the result is bfloat16 or float32."""
+    _need_cuda(x, w, bias, add)
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or (add is not None and add.dtype != torch.bfloat16):
+        raise KernelError("skinny_linear takes bfloat16 x, w and add")
+    m, k = x.shape
+    n = w.shape[0]
+    if w.shape[1] != k or (add is not None and tuple(add.shape) != (m, n)):
+        raise KernelError(f"skinny_linear: shapes x {list(x.shape)}, w {list(w.shape)} do not fit")
+    y = torch.empty((m, n), dtype=out_dtype, device=x.device)
+    ybf, yf = (y, None) if out_dtype == torch.bfloat16 else (None, y)
+    _check(lib().ptb_skinny_linear(_ptr(x), _ptr(w), _ptr(bias), _ptr(add), _ptr(ybf), _ptr(yf), m, n, k,
+                                   ACTIVATIONS[act], _stream(x)), "skinny_linear")
+    return y
 
 
 def matmul_nt(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:

@@ -50,7 +50,11 @@ class Attention(Part):
     def state_need(self):
         return None
 
-    def forward(self, x, ctx, entry):
+    fuses_add = True
+
+    def forward(self, x, ctx, entry, add=None):
+        """Attention of ``x`` (already normed); ``add`` [tokens, hidden] is summed into the result in
+        the output projection's float32 epilogue."""
         k = self.build.kernels
         fused = linear(k, x, self.p_qkv_weight, self.p_qkv_bias)
         k_pool, v_pool, group = ctx.cache.entry_storage(entry.cache_entry)
@@ -60,7 +64,7 @@ class Attention(Part):
         q = k.split_rotate_store(fused, k_pool, v_pool, batch, rotation, self.kv_heads, self.q_per_kv,
                                  self.head_dim, write_cache=entry.writes_cache)
         o = self.attend(q, k_pool, v_pool, ctx, batch, slopes)
-        return linear(k, o, self.p_out_weight, self.p_out_bias)
+        return linear(k, o, self.p_out_weight, self.p_out_bias, add=add)
 
     def attend(self, q, k_pool, v_pool, ctx, batch, slopes):
         k = self.build.kernels

@@ -28,7 +28,9 @@ class DenseFeedForward(Part):
             d["down.bias"] = ParamDecl((self.hidden,), role="vector")
         return d
 
-    def forward(self, x, ctx):
+    fuses_add = True
+
+    def forward(self, x, ctx, add=None):
         k = self.build.kernels
         u = linear(k, x, self.p_up_weight, self.p_up_bias, self.activation)
-        return linear(k, u, self.p_down_weight, self.p_down_bias)
+        return linear(k, u, self.p_down_weight, self.p_down_bias, add=add)

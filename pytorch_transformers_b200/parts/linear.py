@@ -1,10 +1,12 @@
-"""The linear layer that mixers and feed-forwards share: y = act(x @ W.T + b).
+"""The linear layer that mixers and feed-forwards share: y = act(x @ W.T + b) [+ add].
 
 float32 models run the library's own true-float32 kernel (CUDA-core FMAs, bias and activation
-in its epilogue). bfloat16 models use the library matrix product that the reference's engine
-uses too (cuBLAS; ``FalconLinear``, src/transformers/models/falcon/modeling_falcon.py:67-72,
-multiplies and then adds the bias as a separate step) followed by one hand-written kernel for
-bias and activation, computed in float32.
+in its epilogue). bfloat16 models with a few rows (decode steps) run the hand-written
+weight-streaming kernel, which also takes the bias, the activation and a tensor to add (a
+residual) in its float32 epilogue. bfloat16 models with many rows (prompts) use the library
+matrix product that the reference's engine uses too (cuBLAS; ``FalconLinear``,
+src/transformers/models/falcon/modeling_falcon.py:67-72, multiplies and then adds the bias as a
+separate step), followed by hand-written kernels for bias, activation and sum, in float32.
 """
 from __future__ import annotations
 
@@ -14,10 +16,14 @@ import torch
 
 
 def linear(kernels, x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None,
-           act: str = "none") -> torch.Tensor:
+           act: str = "none", add: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """act(x @ weight.T + bias) + add, in the model dtype; ``add`` has the result's shape."""
     if weight.dtype == torch.float32:
-        return kernels.linear_f32(x, weight, bias, act)
+        y = kernels.linear_f32(x, weight, bias, act)
+        return y if add is None else kernels.residual(add, y)
+    if kernels.skinny_linear_takes(x.shape[0], x.shape[1]):
+        return kernels.skinny_linear(x, weight, bias, act, add)
     y = kernels.matmul_nt(x, weight)
     if bias is not None or act != "none":
         kernels.bias_act_(y, bias, act)
-    return y
+    return y if add is None else kernels.residual(add, y)
