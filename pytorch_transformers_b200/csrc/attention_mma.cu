@@ -400,3 +400,74 @@ PTB_API int ptb_attention_mma(const void* q, const void* k_pool, const void* v_p
       return PTB_ERR_SIZE;
   }
 }
+
+// ------------------------------------------------------------------------------------------------
+// The variant that allocates nothing (declared and explained in no_alloc.h).
+#include "no_alloc.h"
+
+#include <mutex>
+
+namespace {
+
+// Workspace for the partial results, part of the library image on every device that loads it.
+// In host code this name is only a handle for cudaGetSymbolAddress, never a device pointer.
+static __device__ __align__(256) float g_fixed_scratch[PTB_FIXED_SCRATCH_FLOATS];
+
+constexpr int kMaxDevices = 64;
+float* g_fixed_scratch_addr[kMaxDevices] = {};
+std::mutex g_fixed_scratch_mutex;
+
+// Device address of the workspace on the current device; looked up once per device.
+int fixed_scratch_address(float** out) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return PTB_ERR_FIXED_SCRATCH_SETUP;
+  std::lock_guard<std::mutex> lock(g_fixed_scratch_mutex);
+  if (g_fixed_scratch_addr[dev] == nullptr) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_fixed_scratch) != cudaSuccess || p == nullptr) {
+      (void)cudaGetLastError();  // leave no sticky error behind for the caller's next call
+      return PTB_ERR_FIXED_SCRATCH_SETUP;
+    }
+    g_fixed_scratch_addr[dev] = static_cast<float*>(p);
+  }
+  *out = g_fixed_scratch_addr[dev];
+  return PTB_OK;
+}
+
+}  // namespace
+
+PTB_API long long ptb_attention_mma_fixed_scratch_capacity(void) { return PTB_FIXED_SCRATCH_FLOATS; }
+
+PTB_API const char* ptb_attention_mma_fixed_scratch_strerror(int code) {
+  switch (code) {
+    case PTB_OK: return "launched";
+    case PTB_ERR_SIZE: return "a size that the kernel does not take";
+    case PTB_ERR_LAUNCH: return "the CUDA launch failed";
+    case PTB_ERR_FIXED_SCRATCH_TOO_SMALL:
+      return "the partial results of this call need more than the built-in workspace of 4194304 float32 values "
+             "(16 MiB): use fewer splits or tiles, or call ptb_attention_mma with a workspace of your own";
+    case PTB_ERR_FIXED_SCRATCH_SETUP:
+      return "the built-in workspace's device address could not be looked up on the current device";
+    default: return "unknown error code";
+  }
+}
+
+PTB_API int ptb_attention_mma_fixed_scratch(const void* q, const void* k_pool, const void* v_pool, void* out,
+                                            const StepBatch* sb, const int* tile_seq, const int* tile_q0,
+                                            int n_tiles, const float* alibi_slopes, int heads, int kv_heads,
+                                            int head_dim, int hpk, int tokens_per_tile, int n_splits, int warps,
+                                            float scale, int window, cudaStream_t stream) {
+  if (n_tiles <= 0) return PTB_OK;
+  if (heads <= 0 || kv_heads <= 0 || heads % kv_heads != 0 || hpk < 1 || warps < 1 || n_splits < 1)
+    return PTB_ERR_SIZE;
+  const long long need =
+      ptb_attention_mma_scratch_floats(n_tiles, heads, kv_heads, hpk, n_splits, warps, head_dim);
+  if (need > (long long)PTB_FIXED_SCRATCH_FLOATS) return PTB_ERR_FIXED_SCRATCH_TOO_SMALL;
+  float* scratch = nullptr;
+  if (need > 0) {
+    const int rc = fixed_scratch_address(&scratch);
+    if (rc != PTB_OK) return rc;
+  }
+  return ptb_attention_mma(q, k_pool, v_pool, out, scratch, sb, tile_seq, tile_q0, n_tiles, alibi_slopes, heads,
+                           kv_heads, head_dim, hpk, tokens_per_tile, n_splits, warps, scale, window, stream);
+}
