@@ -1,0 +1,376 @@
+// Attention of a decode step in one kernel: for every sequence that brings a single token, take the
+// token's row of the fused projection, rotate its queries and its key, put key and value into the
+// paged cache, attend over the cache with all query heads of a K/V group in one tile, divide the key
+// pages among blocks, and let the last block that finishes join the partial results.
+//
+// It does what split_rotate_store + attention_mma + attention_mma_reduce do for such steps, in one
+// launch instead of three: the chain of small kernels between the two projections of a decode layer
+// is what keeps a weight-bound step from the memory roofline.
+//
+//   grid = (sequences, K/V heads x head chunks, splits); block = 16 rows per warp, rows = heads.
+//   Key pages are copied with cp.async into a three-stage ring of swizzled tiles.
+//   The new token's key and value are written to the cache by one block per (sequence, K/V head)
+//   and patched into the shared tile by every block that covers the token's page, so no block reads
+//   a cache row that another block may still be writing.
+//   Joining: the blocks that share a (sequence, head chunk) form one thread-block cluster
+//   (cluster size = number of splits: 1, 2, 4 or 8). Each block leaves (max, sum, unnormalised
+//   output) of its rows in its own shared memory; after a cluster barrier every block joins a
+//   share of the rows, reading the other blocks' shared memory directly (distributed shared
+//   memory), and writes them out. No workspace in global memory, no atomics, no second launch.
+#include <cooperative_groups.h>
+
+#include "mma_common.cuh"
+
+namespace cg = cooperative_groups;
+
+namespace {
+
+constexpr int STAGES = 3;
+
+struct DecodeParams {
+  int heads, kv_heads, hpk, n_splits, rot_pairs, write_cache, window;
+  float scale;
+};
+
+template <int D>
+__global__ void __launch_bounds__(256)
+attention_decode_kernel(const __nv_bfloat16* __restrict__ fused, __nv_bfloat16* __restrict__ k_pool,
+                        __nv_bfloat16* __restrict__ v_pool, __nv_bfloat16* __restrict__ out, StepBatch sb, const float* __restrict__ rope_cos, const float* __restrict__ rope_sin,
+                        const float* __restrict__ alibi_slopes, DecodeParams p) {
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  constexpr int TILE_BYTES = KEYS * D * 2;
+  const uint32_t smem_base = smem_u32(smem_raw);  // stage s: K at s * 2 * TILE_BYTES, V right after
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nthreads = blockDim.x;
+  const int rows_total = 16 * (nthreads >> 5);
+  const int g4 = lane >> 2, t4 = lane & 3;
+
+  const int seq = blockIdx.x;
+  const int qpk = p.heads / p.kv_heads;
+  const int chunks = (qpk + p.hpk - 1) / p.hpk;
+  const int g = blockIdx.y / chunks;
+  const int chunk = blockIdx.y % chunks;
+  const int h0 = chunk * p.hpk;
+  const int split = blockIdx.z;
+  const int pos = sb.seq_past[seq];            // position of the new token
+  const int tok = sb.seq_start[seq];           // its row in the step
+  const int head_valid = min(p.hpk, qpk - h0);
+  const int fused_width = p.kv_heads * (qpk + 2) * D;
+  const __nv_bfloat16* frow = fused + size_t(tok) * fused_width + size_t(g) * (qpk + 2) * D;
+  const float* rc = rope_cos ? rope_cos + size_t(tok) * p.rot_pairs : nullptr;
+  const float* rs = rope_sin ? rope_sin + size_t(tok) * p.rot_pairs : nullptr;
+  const int P = rc ? p.rot_pairs : 0;          // pairs (e, e + P) are rotated for e < P
+
+  // rotated value of element e of a fused row (query head or key)
+  auto rotated = [&](const __nv_bfloat16* row, int e) -> float {
+    const float v = __bfloat162float(row[e]);
+    if (e < P) {
+      float a, b;
+      rotate_pair(v, __bfloat162float(row[e + P]), rc[e], rs[e], a, b);
+      return a;
+    }
+    if (e < 2 * P) {
+      float a, b;
+      rotate_pair(__bfloat162float(row[e - P]), v, rc[e - P], rs[e - P], a, b);
+      return b;
+    }
+    return v;
+  };
+
+  bool row_ok[2];
+  int row_head[2];
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    row_head[i] = warp * 16 + g4 + 8 * i;
+    row_ok[i] = row_head[i] < head_valid;
+  }
+  float slope[2] = {0.f, 0.f};
+  if (alibi_slopes) {
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+      if (row_ok[i]) slope[i] = alibi_slopes[g * qpk + h0 + row_head[i]];
+  }
+  // Q fragments: rotated, rounded to bfloat16 as the stored queries of the three-kernel path are
+  uint32_t qa[D / 16][4];
+#pragma unroll
+  for (int kk = 0; kk < D / 16; ++kk) {
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      uint32_t lo = 0u, hi = 0u;
+      if (row_ok[i]) {
+        const __nv_bfloat16* qr = frow + size_t(h0 + row_head[i]) * D;
+        const int e = kk * 16 + t4 * 2;
+        lo = pack_bf16(rotated(qr, e), rotated(qr, e + 1));
+        hi = pack_bf16(rotated(qr, e + 8), rotated(qr, e + 9));
+      }
+      qa[kk][i] = lo;
+      qa[kk][2 + i] = hi;
+    }
+  }
+
+  // pages of this block
+  int kb_first = 0;
+  if (p.window > 0) kb_first = max(0, pos - p.window + 1) / KEYS;
+  const int kb_last = pos / KEYS;               // page that holds the new token
+  const int n_pages = kb_last + 1 - kb_first;
+  const int per_split = (n_pages + p.n_splits - 1) / p.n_splits;
+  const int kb_begin = kb_first + split * per_split;
+  const int kb_end = min(kb_last + 1, kb_begin + per_split);
+  const int* pages = sb.pages + size_t(seq) * sb.pages_stride;
+  const int n_mine = max(0, kb_end - kb_begin);
+
+  // the new token's key and value go to the cache once per (sequence, K/V head)
+  const __nv_bfloat16* krow = frow + size_t(qpk) * D;
+  const __nv_bfloat16* vrow = krow + D;
+  const bool covers_new = n_mine > 0 && kb_end == kb_last + 1;
+  if (p.write_cache && chunk == 0 && covers_new) {
+    const size_t off = kv_offset(pages[kb_last], g, pos % KEYS, p.kv_heads, D);
+    for (int e = tid; e < D; e += nthreads) {
+      k_pool[off + e] = __float2bfloat16_rn(rotated(krow, e));
+      v_pool[off + e] = vrow[e];
+    }
+  }
+
+  float o[D / 8][4];
+#pragma unroll
+  for (int j = 0; j < D / 8; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+  const float sl2 = p.scale * 1.4426950408889634f;
+
+  auto issue = [&](int i) {  // copy page kb_begin + i into stage i % STAGES (or nothing), one group
+    if (i < n_mine) {
+      const int page = pages[kb_begin + i];
+      const uint32_t dst = smem_base + (i % STAGES) * 2 * TILE_BYTES;
+      load_page<D>(dst, k_pool + kv_offset(page, g, 0, p.kv_heads, D), tid, nthreads);
+      load_page<D>(dst + TILE_BYTES, v_pool + kv_offset(page, g, 0, p.kv_heads, D), tid, nthreads);
+    }
+    cp_async_commit();
+  };
+  for (int i = 0; i < STAGES - 1; ++i) issue(i);
+  for (int i = 0; i < n_mine; ++i) {
+    const int kb = kb_begin + i;
+    issue(i + STAGES - 1);
+    cp_async_wait<STAGES - 1>();
+    __syncthreads();
+    const uint32_t ks = smem_base + (i % STAGES) * 2 * TILE_BYTES, vs = ks + TILE_BYTES;
+    if (kb == kb_last) {
+      // the new token's row, from registers of this block rather than from the cache
+      unsigned char* kt = smem_raw + (i % STAGES) * 2 * TILE_BYTES;
+      const int r = pos % KEYS;
+      for (int e = tid; e < D; e += nthreads) {
+        const uint32_t o2 = swz<D>(r, e >> 3) + (e & 7) * 2;
+        *reinterpret_cast<__nv_bfloat16*>(kt + o2) = __float2bfloat16_rn(rotated(krow, e));
+        *reinterpret_cast<__nv_bfloat16*>(kt + TILE_BYTES + o2) = vrow[e];
+      }
+      __syncthreads();
+    }
+    float s[KEYS / 8][4];
+#pragma unroll
+    for (int j = 0; j < KEYS / 8; ++j) {
+      s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+#pragma unroll
+      for (int kk = 0; kk < D / 16; kk += 2) {
+        uint32_t b0, b1, b2, b3;
+        ldmatrix_x4(b0, b1, b2, b3, ks + swz<D>(j * 8 + (lane & 7), 2 * kk + (lane >> 3)));
+        mma_bf16(s[j], qa[kk], b0, b1);
+        mma_bf16(s[j], qa[kk + 1], b2, b3);
+      }
+    }
+    float m_blk[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int j = 0; j < KEYS / 8; ++j) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int i2 = e >> 1;
+        const int key_pos = kb * KEYS + j * 8 + t4 * 2 + (e & 1);
+        bool visible = row_ok[i2] && key_pos <= pos;
+        if (p.window > 0) visible = visible && key_pos > pos - p.window;
+        float v = s[j][e];
+        if (alibi_slopes) v += alibi_bias(slope[i2], key_pos);
+        v = visible ? v * sl2 : -INFINITY;
+        s[j][e] = v;
+        m_blk[i2] = fmaxf(m_blk[i2], v);
+      }
+    }
+    float corr[2];
+#pragma unroll
+    for (int i2 = 0; i2 < 2; ++i2) {
+      m_blk[i2] = fmaxf(m_blk[i2], __shfl_xor_sync(0xffffffffu, m_blk[i2], 1));
+      m_blk[i2] = fmaxf(m_blk[i2], __shfl_xor_sync(0xffffffffu, m_blk[i2], 2));
+      const float m_new = fmaxf(m_run[i2], m_blk[i2]);
+      corr[i2] = (m_run[i2] == -INFINITY) ? 0.f : exp2f(m_run[i2] - m_new);
+      m_run[i2] = m_new;
+    }
+    uint32_t pa[KEYS / 16][4];
+    float l_blk[2] = {0.f, 0.f};
+#pragma unroll
+    for (int j = 0; j < KEYS / 8; ++j) {
+      float pv[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int i2 = e >> 1;
+        pv[e] = (s[j][e] == -INFINITY) ? 0.f : exp2f(s[j][e] - m_run[i2]);
+        l_blk[i2] += pv[e];
+      }
+      pa[j >> 1][(j & 1) * 2 + 0] = pack_bf16(pv[0], pv[1]);
+      pa[j >> 1][(j & 1) * 2 + 1] = pack_bf16(pv[2], pv[3]);
+    }
+#pragma unroll
+    for (int i2 = 0; i2 < 2; ++i2) l_run[i2] = l_run[i2] * corr[i2] + l_blk[i2];
+#pragma unroll
+    for (int j = 0; j < D / 8; ++j) {
+      o[j][0] *= corr[0]; o[j][1] *= corr[0];
+      o[j][2] *= corr[1]; o[j][3] *= corr[1];
+    }
+#pragma unroll
+    for (int kk = 0; kk < KEYS / 16; ++kk) {
+#pragma unroll
+      for (int j = 0; j < D / 8; j += 2) {
+        uint32_t b0, b1, b2, b3;
+        const int m = lane >> 3;
+        ldmatrix_x4_trans(b0, b1, b2, b3, vs + swz<D>(kk * 16 + (m & 1) * 8 + (lane & 7), j + (m >> 1)));
+        mma_bf16(o[j], pa[kk], b0, b1);
+        mma_bf16(o[j + 1], pa[kk], b2, b3);
+      }
+    }
+    __syncthreads();
+  }
+  cp_async_wait<0>();
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 1);
+    l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 2);
+  }
+
+  __nv_bfloat16* out_tok = out + (size_t(tok) * p.heads + g * qpk + h0) * D;
+  if (p.n_splits == 1) {
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      if (!row_ok[i]) continue;
+      const float inv = l_run[i] > 0.f ? 1.f / l_run[i] : 0.f;
+      __nv_bfloat16* dst = out_tok + size_t(row_head[i]) * D + t4 * 2;
+#pragma unroll
+      for (int j = 0; j < D / 8; ++j)
+        *reinterpret_cast<uint32_t*>(dst + j * 8) = pack_bf16(o[j][2 * i] * inv, o[j][2 * i + 1] * inv);
+    }
+    return;
+  }
+  // partial results of this block, in its own shared memory (the page ring is no longer needed):
+  // po [rows_total][D] float32, then pml [rows_total][2]
+  float* po = reinterpret_cast<float*>(smem_raw);
+  float* pml = po + rows_total * D;
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int r = row_head[i];
+#pragma unroll
+    for (int j = 0; j < D / 8; ++j)
+      *reinterpret_cast<float2*>(po + size_t(r) * D + j * 8 + t4 * 2) = make_float2(o[j][2 * i], o[j][2 * i + 1]);
+    if (t4 == 0) {
+      pml[r * 2 + 0] = m_run[i];
+      pml[r * 2 + 1] = l_run[i];
+    }
+  }
+  cg::cluster_group cluster = cg::this_cluster();
+  cluster.sync();  // every block of the cluster has written its partial results
+  const int n_splits = p.n_splits;
+  // rows r with r % n_splits == split are joined by this block: thread -> (row, 4 dims)
+  constexpr int VEC = 4;
+  const int per_row = D / VEC;
+  const int my_rows = (head_valid - split + n_splits - 1) / n_splits;  // rows split, split + n, ...
+  for (int idx = tid; idx < my_rows * per_row; idx += nthreads) {
+    const int r = split + (idx / per_row) * n_splits;
+    const int d0 = (idx % per_row) * VEC;
+    float m = -INFINITY;
+    for (int s = 0; s < n_splits; ++s) {
+      const float* rml = cluster.map_shared_rank(pml, s);
+      m = fmaxf(m, rml[r * 2]);
+    }
+    float acc[VEC] = {0.f, 0.f, 0.f, 0.f};
+    float l = 0.f;
+    for (int s = 0; s < n_splits; ++s) {
+      const float* rml = cluster.map_shared_rank(pml, s);
+      const float* rpo = cluster.map_shared_rank(po, s);
+      const float ms = rml[r * 2];
+      const float w = (ms == -INFINITY) ? 0.f : exp2f(ms - m);
+      l += rml[r * 2 + 1] * w;
+      const float4 v = *reinterpret_cast<const float4*>(rpo + size_t(r) * D + d0);
+      acc[0] += v.x * w; acc[1] += v.y * w; acc[2] += v.z * w; acc[3] += v.w * w;
+    }
+    const float inv = l > 0.f ? 1.f / l : 0.f;
+    __nv_bfloat16* dst = out_tok + size_t(r) * D + d0;
+    *reinterpret_cast<uint2*>(dst) = make_uint2(pack_bf16(acc[0] * inv, acc[1] * inv), pack_bf16(acc[2] * inv, acc[3] * inv));
+  }
+  cluster.sync();  // no block leaves while another still reads its shared memory
+}
+
+template <int D>
+int launch_decode(const void* fused, void* k_pool, void* v_pool, void* out, const StepBatch& sb,
+                  const float* rope_cos, const float* rope_sin, const float* slopes, const DecodeParams& p,
+                  int warps, cudaStream_t stream) {
+  const int qpk = p.heads / p.kv_heads;
+  const int chunks = (qpk + p.hpk - 1) / p.hpk;
+  size_t smem = size_t(STAGES) * 2 * KEYS * D * 2;
+  const size_t join = size_t(warps) * 16 * (D + 2) * sizeof(float);  // partial results reuse the ring
+  if (join > smem) smem = join;
+  static size_t configured = 0;
+  if (smem > configured) {
+    if (cudaFuncSetAttribute(attention_decode_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) !=
+        cudaSuccess)
+      return PTB_ERR_LAUNCH;
+    configured = smem;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(sb.n_seqs, p.kv_heads * chunks, p.n_splits);
+  cfg.blockDim = dim3(warps * 32);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 1;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = p.n_splits;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  if (cudaLaunchKernelEx(&cfg, attention_decode_kernel<D>, (const __nv_bfloat16*)fused, (__nv_bfloat16*)k_pool,
+                         (__nv_bfloat16*)v_pool, (__nv_bfloat16*)out, sb, rope_cos, rope_sin, slopes,
+                         p) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return PTB_ERR_LAUNCH;
+  }
+  return launch_status();
+}
+
+}  // namespace
+
+// Splits that a launch may use: the blocks of a split set form one cluster.
+PTB_API int ptb_attention_decode_max_splits() { return 8; }
+
+// Every sequence of the step brings exactly one token. fused [n_seqs, kv_heads * (q_per_kv + 2) *
+// head_dim] bfloat16; out [n_seqs, heads * head_dim]. n_splits is 1, 2, 4 or 8. rope_cos/sin:
+// [n_seqs, rot_pairs] float32 tables for the step's tokens, or null for no rotation.
+PTB_API int ptb_attention_decode(const void* fused, void* k_pool, void* v_pool, void* out, const StepBatch* sb,
+                                 const float* rope_cos, const float* rope_sin, int rot_pairs,
+                                 const float* alibi_slopes, int heads, int kv_heads, int head_dim, int hpk,
+                                 int n_splits, int warps, float scale, int window, int write_cache,
+                                 cudaStream_t stream) {
+  if (sb->n_seqs <= 0) return PTB_OK;
+  if (sb->n_tokens != sb->n_seqs) return PTB_ERR_SIZE;
+  if (heads <= 0 || kv_heads <= 0 || heads % kv_heads != 0 || warps < 1 || warps > 8 || hpk < 1 ||
+      hpk > warps * 16 || rot_pairs < 0 || 2 * rot_pairs > head_dim)
+    return PTB_ERR_SIZE;
+  if (n_splits != 1 && n_splits != 2 && n_splits != 4 && n_splits != 8) return PTB_ERR_SIZE;
+  if ((rope_cos == nullptr) != (rope_sin == nullptr)) return PTB_ERR_SIZE;
+  const int qpk = heads / kv_heads;
+  const int chunks = (qpk + hpk - 1) / hpk;
+  if (kv_heads * chunks > 65535) return PTB_ERR_SIZE;
+  DecodeParams p;
+  p.heads = heads; p.kv_heads = kv_heads; p.hpk = hpk; p.n_splits = n_splits; p.rot_pairs = rot_pairs;
+  p.write_cache = write_cache; p.window = window; p.scale = scale;
+  switch (head_dim) {
+    case 64:
+      return launch_decode<64>(fused, k_pool, v_pool, out, *sb, rope_cos, rope_sin, alibi_slopes, p, warps, stream);
+    case 128:
+      return launch_decode<128>(fused, k_pool, v_pool, out, *sb, rope_cos, rope_sin, alibi_slopes, p, warps, stream);
+    default:
+      return PTB_ERR_SIZE;
+  }
+}

@@ -21,11 +21,13 @@ constexpr int DPT = MAX_D / 8;
 // (q_per_kv query heads, K, V), to: q_out [n_tokens, heads, head_dim] (query head = group *
 // q_per_kv + index in group) and the K and V pools of one layer. With inv_freq != nullptr the
 // first 2 * rot_pairs dims of every query and key head are rotated: pairs (i, i + rot_pairs),
-// angle = position * inv_freq[i] in float32, x' = x cos - y sin, y' = y cos + x sin.
-// One block per token.
+// angle = position * inv_freq[i] in float32, x' = x cos - y sin, y' = y cos + x sin. With a table
+// (rope_cos, rope_sin: [n_tokens, rot_pairs], made by rope_table_kernel from the same product) the
+// cosines and sines are read instead of computed. One block per token.
 template <typename T>
 __global__ void split_rotate_store_kernel(const T* __restrict__ fused, T* __restrict__ q_out, T* __restrict__ k_pool,
                                           T* __restrict__ v_pool, StepBatch sb, const float* __restrict__ inv_freq,
+                                          const float* __restrict__ rope_cos, const float* __restrict__ rope_sin,
                                           int rot_pairs, int kv_heads, int q_per_kv, int head_dim, int write_cache) {
   const int t = blockIdx.x;
   const int pos = sb.tok_pos[t];
@@ -54,15 +56,21 @@ __global__ void split_rotate_store_kernel(const T* __restrict__ fused, T* __rest
       T* pool = (r == q_per_kv) ? k_pool : v_pool;
       dst = pool + kv_offset(page, g, in_page, kv_heads, head_dim);
     }
-    const bool rotated_row = (r <= q_per_kv) && inv_freq != nullptr;  // queries and K, not V
+    const bool rotated_row = (r <= q_per_kv) && (inv_freq != nullptr || rope_cos != nullptr);  // queries and K, not V
     if (e < rot_pairs) {
       const float a = to_f(src[e]);
       const float b = to_f(src[e + rot_pairs]);
       if (rotated_row) {
-        float s, c;
-        sincosf(float(pos) * inv_freq[e], &s, &c);
-        dst[e] = from_f<T>(a * c - b * s);
-        dst[e + rot_pairs] = from_f<T>(b * c + a * s);
+        float s, c, ra, rb;
+        if (rope_cos) {
+          c = rope_cos[size_t(t) * rot_pairs + e];
+          s = rope_sin[size_t(t) * rot_pairs + e];
+        } else {
+          sincosf(float(pos) * inv_freq[e], &s, &c);
+        }
+        rotate_pair(a, b, c, s, ra, rb);
+        dst[e] = from_f<T>(ra);
+        dst[e + rot_pairs] = from_f<T>(rb);
       } else {
         dst[e] = src[e];
         dst[e + rot_pairs] = src[e + rot_pairs];
@@ -222,22 +230,43 @@ int launch_attention(const void* q, const void* k_pool, const void* v_pool, void
 
 }  // namespace
 
+// cos and sin of position * inv_freq[i] for every token of the step: [n_tokens, pairs] each, float32.
+__global__ void rope_table_kernel(const int* __restrict__ tok_pos, const float* __restrict__ inv_freq,
+                                  float* __restrict__ cos_out, float* __restrict__ sin_out, int n_tokens, int pairs) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n_tokens * pairs) return;
+  float s, c;
+  sincosf(float(tok_pos[i / pairs]) * inv_freq[i % pairs], &s, &c);
+  cos_out[i] = c;
+  sin_out[i] = s;
+}
+
+PTB_API int ptb_rope_table(const int* tok_pos, const float* inv_freq, float* cos_out, float* sin_out, int n_tokens,
+                           int pairs, cudaStream_t stream) {
+  if (n_tokens <= 0 || pairs <= 0) return PTB_OK;
+  const int total = n_tokens * pairs;
+  rope_table_kernel<<<(total + 255) / 256, 256, 0, stream>>>(tok_pos, inv_freq, cos_out, sin_out, n_tokens, pairs);
+  return launch_status();
+}
+
 PTB_API int ptb_split_rotate_store(int dtype, const void* fused, void* q_out, void* k_pool, void* v_pool,
-                                   const StepBatch* sb, const float* inv_freq, int rot_pairs, int kv_heads,
-                                   int q_per_kv, int head_dim, int write_cache, cudaStream_t stream) {
+                                   const StepBatch* sb, const float* inv_freq, const float* rope_cos,
+                                   const float* rope_sin, int rot_pairs, int kv_heads, int q_per_kv, int head_dim,
+                                   int write_cache, cudaStream_t stream) {
   if (sb->n_tokens <= 0) return PTB_OK;
   if (kv_heads <= 0 || q_per_kv <= 0 || head_dim <= 0 || rot_pairs < 0 || 2 * rot_pairs > head_dim)
     return PTB_ERR_SIZE;
-  if (inv_freq == nullptr) rot_pairs = 0;
+  if (inv_freq == nullptr && rope_cos == nullptr) rot_pairs = 0;
+  if ((rope_cos == nullptr) != (rope_sin == nullptr)) return PTB_ERR_SIZE;
   const int threads = 256;
   if (dtype == PTB_F32)
     split_rotate_store_kernel<float><<<sb->n_tokens, threads, 0, stream>>>(
-        (const float*)fused, (float*)q_out, (float*)k_pool, (float*)v_pool, *sb, inv_freq, rot_pairs, kv_heads,
-        q_per_kv, head_dim, write_cache);
+        (const float*)fused, (float*)q_out, (float*)k_pool, (float*)v_pool, *sb, inv_freq, rope_cos, rope_sin,
+        rot_pairs, kv_heads, q_per_kv, head_dim, write_cache);
   else if (dtype == PTB_BF16)
     split_rotate_store_kernel<__nv_bfloat16><<<sb->n_tokens, threads, 0, stream>>>(
         (const __nv_bfloat16*)fused, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, *sb,
-        inv_freq, rot_pairs, kv_heads, q_per_kv, head_dim, write_cache);
+        inv_freq, rope_cos, rope_sin, rot_pairs, kv_heads, q_per_kv, head_dim, write_cache);
   else
     return PTB_ERR_DTYPE;
   return launch_status();

@@ -93,4 +93,11 @@ __device__ __forceinline__ float alibi_bias(float slope_bf16, int key_pos) {
   return round_bf16(slope_bf16 * round_bf16(float(key_pos)));
 }
 
+// Rotation of one pair (a, b) by an angle given as (cos, sin): every kernel that rotates uses this
+// one form, so that a key written by one kernel equals the key another would have written.
+__device__ __forceinline__ void rotate_pair(float a, float b, float c, float s, float& out_a, float& out_b) {
+  out_a = __fsub_rn(__fmul_rn(a, c), __fmul_rn(b, s));
+  out_b = __fadd_rn(__fmul_rn(b, c), __fmul_rn(a, s));
+}
+
 inline int launch_status() { return cudaGetLastError() == cudaSuccess ? PTB_OK : PTB_ERR_LAUNCH; }

@@ -53,9 +53,13 @@ PTB_API int ptb_gather_rows(int dtype, const int* ids, const void* table, void* 
 // biased variance; kind 1: RMSNorm, y = x / sqrt(mean(x^2) + eps) * gain (+ bias if given).
 // With gain2 != nullptr a second output with its own gain and bias is written from the same
 // statistics (two norms of one input share the read and the reductions).
+// With addend != nullptr the input is the sum x + addend (formed in float32, rounded once to T);
+// the rounded sum is written to sum_out and is what gets normalised: two branches of a residual
+// stream are joined and normed in one pass.
 // The row is held in shared memory as float32: 4 * width bytes of dynamic shared memory.
 template <typename T>
-__global__ void norm_kernel(const T* __restrict__ x, const float* __restrict__ gain1, const float* __restrict__ bias1,
+__global__ void norm_kernel(const T* __restrict__ x, const T* __restrict__ addend, T* __restrict__ sum_out,
+                            const float* __restrict__ gain1, const float* __restrict__ bias1,
                             T* __restrict__ y1, const float* __restrict__ gain2, const float* __restrict__ bias2,
                             T* __restrict__ y2, int width, float eps, int kind) {
   extern __shared__ float row[];
@@ -63,7 +67,12 @@ __global__ void norm_kernel(const T* __restrict__ x, const float* __restrict__ g
   const size_t base = size_t(blockIdx.x) * width;
   float s = 0.f;
   for (int i = threadIdx.x; i < width; i += blockDim.x) {
-    const float v = to_f(x[base + i]);
+    float v = to_f(x[base + i]);
+    if (addend) {
+      const T r = from_f<T>(v + to_f(addend[base + i]));
+      sum_out[base + i] = r;
+      v = to_f(r);
+    }
     row[i] = v;
     s += v;
   }
@@ -89,10 +98,12 @@ __global__ void norm_kernel(const T* __restrict__ x, const float* __restrict__ g
   }
 }
 
-PTB_API int ptb_norm(int dtype, const void* x, const float* gain1, const float* bias1, void* y1, const float* gain2,
-                     const float* bias2, void* y2, int n, int width, float eps, int kind, cudaStream_t stream) {
+PTB_API int ptb_norm(int dtype, const void* x, const void* addend, void* sum_out, const float* gain1,
+                     const float* bias1, void* y1, const float* gain2, const float* bias2, void* y2, int n, int width,
+                     float eps, int kind, cudaStream_t stream) {
   if (n <= 0) return PTB_OK;
   if (width <= 0 || kind < 0 || kind > 1) return PTB_ERR_SIZE;
+  if ((addend == nullptr) != (sum_out == nullptr)) return PTB_ERR_SIZE;
   const size_t smem = size_t(width) * sizeof(float);
   if (smem > 200 * 1024) return PTB_ERR_SIZE;
   const int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
@@ -104,17 +115,17 @@ PTB_API int ptb_norm(int dtype, const void* x, const float* gain1, const float* 
       configured_f32 = smem;
     }
     if (e != cudaSuccess) return PTB_ERR_LAUNCH;
-    norm_kernel<float><<<n, threads, smem, stream>>>((const float*)x, gain1, bias1, (float*)y1, gain2, bias2,
-                                                     (float*)y2, width, eps, kind);
+    norm_kernel<float><<<n, threads, smem, stream>>>((const float*)x, (const float*)addend, (float*)sum_out, gain1,
+                                                     bias1, (float*)y1, gain2, bias2, (float*)y2, width, eps, kind);
   } else if (dtype == PTB_BF16) {
     if (smem > configured_bf16) {
       e = cudaFuncSetAttribute(norm_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
       configured_bf16 = smem;
     }
     if (e != cudaSuccess) return PTB_ERR_LAUNCH;
-    norm_kernel<__nv_bfloat16><<<n, threads, smem, stream>>>((const __nv_bfloat16*)x, gain1, bias1,
-                                                             (__nv_bfloat16*)y1, gain2, bias2, (__nv_bfloat16*)y2,
-                                                             width, eps, kind);
+    norm_kernel<__nv_bfloat16><<<n, threads, smem, stream>>>(
+        (const __nv_bfloat16*)x, (const __nv_bfloat16*)addend, (__nv_bfloat16*)sum_out, gain1, bias1,
+        (__nv_bfloat16*)y1, gain2, bias2, (__nv_bfloat16*)y2, width, eps, kind);
   } else {
     return PTB_ERR_DTYPE;
   }

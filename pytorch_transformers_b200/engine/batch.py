@@ -83,6 +83,9 @@ class StepContext:
         if len(set(slots)) != len(slots):
             raise StepError(f"a slot is named twice in one step: {list(slots)}")
         self.cache = cache
+        self.side_stream = None     # set by the engine for steps of a few tokens (see parts/block.py)
+        self._rope: dict = {}
+        self.keep_alive: list = []  # tensors that must outlive the step's last kernel on another stream
         self.slots = [int(s) for s in slots]
         self.n_seqs = len(slots)
         self.new = [len(t) for t in token_lists]
@@ -179,6 +182,24 @@ class StepContext:
             c.seq_past, c.pages = self.dev["seq_past"].data_ptr(), self.dev[f"pages{gi}"].data_ptr()
             c.pages_stride, c.n_tokens, c.n_seqs = tab.shape[1], self.n_tokens, self.n_seqs
             self.batch_c.append(c)
+
+    def begin_forward(self) -> None:
+        """Forget what an earlier forward pass over this step computed (a step that is captured as a
+        graph runs once plainly and once under capture: the capture must contain every kernel)."""
+        self._rope = {}
+        self.keep_alive = []
+
+    def rope(self, position_part):
+        """(cos, sin) tables of this step's tokens for a rotary position part, computed once per step
+        and part on first use (the reference computes them once per forward pass too,
+        src/transformers/models/falcon/modeling_falcon.py:946); None for parts that do not rotate."""
+        inv_freq = position_part.rotation() if position_part is not None else None
+        if inv_freq is None:
+            return None
+        key = id(position_part)
+        if key not in self._rope:
+            self._rope[key] = K.rope_table(self.dev["tok_pos"], inv_freq)
+        return self._rope[key]
 
     def _tiles(self, rows: int):
         seqs, firsts = [], []

@@ -15,7 +15,7 @@ import torch
 
 from .. import kernels as K
 from ..cache.paged import Cache
-from ..parts.base import BuildContext, ModelSpec, ParamDecl, Part, make_part
+from ..parts.base import BuildContext, ModelSpec, ParamDecl, Part, make_part, resolve
 from ..parts.linear import linear
 from .batch import StepContext, StepError
 
@@ -45,6 +45,7 @@ class CausalLM:
         # replay steps of single tokens as CUDA graphs, if every part allows it
         self.use_graphs = all(p.graph_safe for top in self.blocks + [self.final_norm] for p in top.walk())
         self.last_h2d_bytes = 0
+        self._side_stream = None
 
     # ------------------------------------------------------------------ parameters
     def param_table(self) -> Dict[str, Tuple[Optional[Part], str, ParamDecl]]:
@@ -190,11 +191,19 @@ class CausalLM:
         ctx.commit()
         return entry["out"].clone()   # the graph's own output buffer is rewritten by the next replay
 
+    TWO_STREAM_MAX_TOKENS = 32
+
     def forward(self, ctx: StepContext) -> torch.Tensor:
         k = self.build.kernels
+        ctx.begin_forward()
+        if self.device.type == "cuda" and ctx.n_tokens <= self.TWO_STREAM_MAX_TOKENS and self.dtype == torch.bfloat16:
+            if self._side_stream is None:
+                self._side_stream = torch.cuda.Stream(device=self.device)
+            ctx.side_stream = self._side_stream
         x = k.gather_rows(ctx.dev["tokens"], self.embedding, self.status)
         for entry in self.schedule:
-            x = self.blocks[entry.block].forward(x, ctx, entry)
+            x = self.blocks[entry.block].forward(x, ctx, entry)   # a tensor, or a DeferredSum of two branches
+        x = resolve(k, x)
         if ctx.n_wanted == 0:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=self.device)
         rows = k.gather_rows(ctx.dev["logits_at"], x, self.status)

@@ -76,7 +76,8 @@ def lib():
         for name in ("ptb_gather_rows", "ptb_norm", "ptb_bias_act", "ptb_residual", "ptb_to_float",
                      "ptb_linear_f32", "ptb_split_rotate_store", "ptb_attention_generic", "ptb_sample",
                      "ptb_attention_generic_tile_rows", "ptb_attention_mma", "ptb_attention_mma_supports",
-                     "ptb_skinny_linear", "ptb_skinny_linear_max_rows", "ptb_skinny_linear_k_multiple"):
+                     "ptb_skinny_linear", "ptb_skinny_linear_max_rows", "ptb_skinny_linear_k_multiple",
+                     "ptb_rope_table", "ptb_attention_decode"):
             getattr(L, name).restype = ctypes.c_int
         _configured = True
     return L
@@ -97,15 +98,23 @@ def gather_rows(ids: torch.Tensor, table: torch.Tensor, status: Optional[torch.T
 
 
 def norm(x: torch.Tensor, gain: torch.Tensor, bias: Optional[torch.Tensor], eps: float, kind: str = "layernorm",
-         gain2: Optional[torch.Tensor] = None, bias2: Optional[torch.Tensor] = None):
-    """LayerNorm / RMSNorm of rows; with ``gain2`` a second output from the same statistics."""
-    _need_cuda(x, gain, bias, gain2, bias2)
+         gain2: Optional[torch.Tensor] = None, bias2: Optional[torch.Tensor] = None,
+         addend: Optional[torch.Tensor] = None):
+    """LayerNorm / RMSNorm of rows; with ``gain2`` a second output from the same statistics. With
+    ``addend`` the rows normalised are ``x + addend`` (one rounding), and that sum is returned first:
+    ``(sum, y)`` or ``(sum, y, y2)``."""
+    _need_cuda(x, gain, bias, gain2, bias2, addend)
     n, width = x.shape
     y1 = torch.empty_like(x)
     y2 = torch.empty_like(x) if gain2 is not None else None
-    _check(lib().ptb_norm(_dtype_code(x), _ptr(x), _ptr(gain), _ptr(bias), _ptr(y1), _ptr(gain2), _ptr(bias2),
-                          _ptr(y2), n, width, ctypes.c_float(eps), NORM_KINDS[kind], _stream(x)), "norm")
-    return y1 if gain2 is None else (y1, y2)
+    total = torch.empty_like(x) if addend is not None else None
+    _check(lib().ptb_norm(_dtype_code(x), _ptr(x), _ptr(addend), _ptr(total), _ptr(gain), _ptr(bias), _ptr(y1),
+                          _ptr(gain2), _ptr(bias2), _ptr(y2), n, width, ctypes.c_float(eps), NORM_KINDS[kind],
+                          _stream(x)), "norm")
+    outs = (y1,) if gain2 is None else (y1, y2)
+    if addend is not None:
+        return (total,) + outs
+    return outs[0] if len(outs) == 1 else outs
 
 
 def bias_act_(y: torch.Tensor, bias: Optional[torch.Tensor], act: str) -> torch.Tensor:
@@ -148,10 +157,22 @@ def linear_f32(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = 
     return y
 
 
+def rope_table(tok_pos: torch.Tensor, inv_freq: torch.Tensor):
+    """(cos, sin) of position * inv_freq for every token of a step: float32 [tokens, pairs] each."""
+    _need_cuda(tok_pos, inv_freq)
+    n, pairs = tok_pos.numel(), inv_freq.numel()
+    table = torch.empty((2, n, pairs), dtype=torch.float32, device=inv_freq.device)
+    _check(lib().ptb_rope_table(_ptr(tok_pos), _ptr(inv_freq), _ptr(table[0]), _ptr(table[1]), n, pairs,
+                                _stream(inv_freq)), "rope_table")
+    return table[0], table[1]
+
+
 def split_rotate_store(fused: torch.Tensor, k_pool: Optional[torch.Tensor], v_pool: Optional[torch.Tensor],
                        batch: StepBatchC, inv_freq: Optional[torch.Tensor], kv_heads: int, q_per_kv: int,
-                       head_dim: int, write_cache: bool = True) -> torch.Tensor:
-    """Fused projection -> rotated queries [tokens, heads, head_dim]; K (rotated) and V go to the pools."""
+                       head_dim: int, write_cache: bool = True, rope=None) -> torch.Tensor:
+    """Fused projection -> rotated queries [tokens, heads, head_dim]; K (rotated) and V go to the pools.
+    The rotation comes from ``inv_freq`` (angles computed in the kernel) or from ``rope`` = (cos, sin)
+    tables of ``rope_table`` for this step's tokens."""
     _need_cuda(fused, k_pool, v_pool, inv_freq)
     n = fused.shape[0]
     q = torch.empty((n, kv_heads * q_per_kv, head_dim), dtype=fused.dtype, device=fused.device)
@@ -159,9 +180,15 @@ def split_rotate_store(fused: torch.Tensor, k_pool: Optional[torch.Tensor], v_po
         raise KernelError(f"fused projection has width {fused.shape[1]}, expected "
                           f"{kv_heads * (q_per_kv + 2) * head_dim}")
     pairs = 0 if inv_freq is None else inv_freq.numel()
+    cos = sin = None
+    if rope is not None:
+        cos, sin = rope
+        pairs = cos.shape[1]
+        inv_freq = None
     _check(lib().ptb_split_rotate_store(_dtype_code(fused), _ptr(fused), _ptr(q), _ptr(k_pool), _ptr(v_pool),
-                                        ctypes.byref(batch), _ptr(inv_freq), pairs, kv_heads, q_per_kv, head_dim,
-                                        1 if write_cache else 0, _stream(fused)), "split_rotate_store")
+                                        ctypes.byref(batch), _ptr(inv_freq), _ptr(cos), _ptr(sin), pairs, kv_heads,
+                                        q_per_kv, head_dim, 1 if write_cache else 0, _stream(fused)),
+           "split_rotate_store")
     return q
 
 
@@ -176,6 +203,34 @@ def attention_generic(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tenso
                                        ctypes.byref(batch), _ptr(tile_seq), _ptr(tile_q0), n_tiles, _ptr(slopes),
                                        heads, kv_heads, head_dim, ctypes.c_float(scale), window, _stream(q)),
            "attention_generic")
+    return out
+
+
+DECODE_SPLITS = (1, 2, 4, 8)   # ptb_attention_decode: the blocks of a split set form one cluster
+
+
+def attention_decode(fused: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, batch: StepBatchC, rope,
+                     slopes: Optional[torch.Tensor], kv_heads: int, q_per_kv: int, head_dim: int, scale: float,
+                     window: int, heads_per_tile: int, warps: int, n_splits: int, write_cache: bool = True):
+    """One kernel for the attention of a step of single tokens: rotate q and k of each new token, put
+    k and v into the cache, attend over the cache (all heads of a K/V group in one tile, key pages
+    divided among ``n_splits`` blocks of one cluster, joined through distributed shared memory).
+    Returns [tokens, heads * head_dim]."""
+    _need_cuda(fused, k_pool, v_pool, slopes)
+    if fused.dtype != torch.bfloat16:
+        raise KernelError("attention_decode takes bfloat16 tensors")
+    n = fused.shape[0]
+    heads = kv_heads * q_per_kv
+    if fused.shape[1] != kv_heads * (q_per_kv + 2) * head_dim:
+        raise KernelError(f"fused projection has width {fused.shape[1]}, expected "
+                          f"{kv_heads * (q_per_kv + 2) * head_dim}")
+    out = torch.empty((n, heads * head_dim), dtype=fused.dtype, device=fused.device)
+    cos, sin = rope if rope is not None else (None, None)
+    pairs = 0 if cos is None else cos.shape[1]
+    _check(lib().ptb_attention_decode(_ptr(fused), _ptr(k_pool), _ptr(v_pool), _ptr(out), ctypes.byref(batch),
+                                      _ptr(cos), _ptr(sin), pairs, _ptr(slopes), heads, kv_heads, head_dim,
+                                      heads_per_tile, n_splits, warps, ctypes.c_float(scale), window,
+                                      1 if write_cache else 0, _stream(fused)), "attention_decode")
     return out
 
 

@@ -59,12 +59,32 @@ class Attention(Part):
         fused = linear(k, x, self.p_qkv_weight, self.p_qkv_bias)
         k_pool, v_pool, group = ctx.cache.entry_storage(entry.cache_entry)
         batch = ctx.batch_c[group]
-        rotation = self.position.rotation() if self.position is not None else None
+        rope = ctx.rope(self.position)
         slopes = self.position.score_bias() if self.position is not None else None
-        q = k.split_rotate_store(fused, k_pool, v_pool, batch, rotation, self.kv_heads, self.q_per_kv,
-                                 self.head_dim, write_cache=entry.writes_cache)
-        o = self.attend(q, k_pool, v_pool, ctx, batch, slopes)
+        if ctx.mma_tokens == 1 and fused.dtype == self._bf16 and k.attention_mma_supports(self.head_dim):
+            # a step of single tokens: rotation, cache write, attention and the join in one kernel
+            hpk = min(self.q_per_kv, 128)
+            warps = (hpk + 15) // 16
+            want = self._decode_splits(ctx, hpk)
+            splits = max(s for s in k.DECODE_SPLITS if s <= want)
+            o = k.attention_decode(fused, k_pool, v_pool, batch, rope, slopes, self.kv_heads, self.q_per_kv,
+                                   self.head_dim, self.scale, self.window, hpk, warps, splits,
+                                   write_cache=entry.writes_cache)
+        else:
+            q = k.split_rotate_store(fused, k_pool, v_pool, batch, None, self.kv_heads, self.q_per_kv,
+                                     self.head_dim, write_cache=entry.writes_cache, rope=rope)
+            o = self.attend(q, k_pool, v_pool, ctx, batch, slopes)
         return linear(k, o, self.p_out_weight, self.p_out_bias, add=add)
+
+    def _decode_splits(self, ctx, hpk):
+        """Blocks per (sequence, head chunk) for steps of single tokens: enough to put about two
+        blocks on every SM, each with at least two pages of keys."""
+        chunks = (self.q_per_kv + hpk - 1) // hpk
+        blocks = ctx.n_seqs * self.kv_heads * chunks
+        pages = ctx.pages_hint
+        if self.window > 0:
+            pages = min(pages, self.window // self.build.kernels.PAGE + 2)
+        return max(1, min((2 * 148 + blocks - 1) // blocks, pages // 2, 64))
 
     def attend(self, q, k_pool, v_pool, ctx, batch, slopes):
         k = self.build.kernels
@@ -86,13 +106,6 @@ class Attention(Part):
             warps = 8
             hpk = max(1, min(self.q_per_kv, 128 // tokens))
         chunks = (self.q_per_kv + hpk - 1) // hpk
-        splits = 1
-        if tokens == 1:
-            blocks = ctx.n_mma_tiles * self.kv_heads * chunks
-            pages = ctx.pages_hint
-            if self.window > 0:
-                pages = min(pages, self.window // k.PAGE + 2)
-            # enough blocks for ~2 per SM, at least 2 pages per block
-            splits = max(1, min((2 * 148 + blocks - 1) // blocks, pages // 2, 64))
+        splits = self._decode_splits(ctx, hpk) if tokens == 1 else 1
         return k.attention_mma(q, k_pool, v_pool, batch, ctx.dev["mtile_seq"], ctx.dev["mtile_q0"], ctx.n_mma_tiles,
                                slopes, self.kv_heads, self.scale, self.window, tokens, hpk, warps, splits)

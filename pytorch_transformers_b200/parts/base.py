@@ -126,6 +126,30 @@ class StateNeed:
 
 
 @dataclasses.dataclass
+class DeferredSum:
+    """A residual stream whose last addition has not been done yet: the value is ``base + pending``.
+    A block may hand this to the next block instead of a tensor when ``pending`` is still being
+    computed on ``stream``; whoever needs the value waits for that stream and adds (the next
+    block's norm does both in its own kernel). ``resolve`` gives the plain tensor."""
+    base: Any
+    pending: Any
+    stream: Any = None
+
+    def join(self, device) -> None:
+        if self.stream is not None:
+            torch.cuda.current_stream(device).wait_stream(self.stream)
+            self.stream = None
+
+
+def resolve(kernels, x):
+    """The tensor that ``x`` stands for (``x`` itself, or the sum of a DeferredSum)."""
+    if isinstance(x, DeferredSum):
+        x.join(x.base.device)
+        return kernels.residual(x.base, x.pending)
+    return x
+
+
+@dataclasses.dataclass
 class BuildContext:
     """What parts need at construction: device, model dtype, and the kernel wrappers."""
     device: torch.device

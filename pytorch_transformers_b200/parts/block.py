@@ -10,7 +10,7 @@ Sums are formed in float32 and rounded once.
 """
 from __future__ import annotations
 
-from .base import BuildContext, Part, PartSpec, register_part
+from .base import BuildContext, DeferredSum, Part, PartSpec, register_part, resolve
 
 
 def _plus(kernels, part, base, *args):
@@ -33,14 +33,45 @@ class ParallelBlock(Part):
         self.feed_forward = self.children["feed_forward"]
 
     def forward(self, x, ctx, entry):
-        if self.norm_ff is not None:
-            a, m = self.norm_mixer.forward_pair(x, self.norm_ff)
-        else:
-            a = self.norm_mixer.forward(x)
-            m = a
         k = self.build.kernels
+        side = getattr(ctx, "side_stream", None)
+        two_streams = (side is not None and getattr(self.mixer, "fuses_add", False)
+                       and getattr(self.feed_forward, "fuses_add", False) and hasattr(self.norm_mixer, "forward_sum"))
+        if isinstance(x, DeferredSum) and two_streams:
+            # join the previous block's two branches and norm the sum in one kernel
+            x.join(x.base.device)
+            outs = self.norm_mixer.forward_sum(x.base, x.pending, self.norm_ff)
+            ctx.keep_alive.append((x.base, x.pending))
+            x, a = outs[0], outs[1]
+            m = outs[2] if self.norm_ff is not None else a
+        else:
+            x = resolve(k, x)
+            if self.norm_ff is not None:
+                a, m = self.norm_mixer.forward_pair(x, self.norm_ff)
+            else:
+                a = self.norm_mixer.forward(x)
+                m = a
+        if two_streams:
+            return self._forward_two_streams(x, a, m, ctx, entry, side)
         mixed = _plus(k, self.mixer, x, a, ctx, entry)           # x + mixer
         return _plus(k, self.feed_forward, mixed, m, ctx)        # (x + mixer) + feed-forward
+
+    def _forward_two_streams(self, x, a, m, ctx, entry, side):
+        """Steps of a few tokens are bound by the read of the weights, and the mixer's chain of small
+        kernels (projection, cache write, attention) leaves the memory system idle. Mixer and
+        feed-forward are independent, so the mixer runs on a second stream while the feed-forward
+        streams its weights on the first; the feed-forward takes ``x`` into its last epilogue and
+        the mixer's result stays pending: the block returns ``DeferredSum(x + ff, mixer)``, which
+        the next block's norm (or the model's end) joins. In a captured graph these are two
+        parallel branches per block. Tensors that cross streams stay referenced until the step ends."""
+        import torch
+        main = torch.cuda.current_stream(x.device)
+        side.wait_stream(main)
+        with torch.cuda.stream(side):
+            mixed = self.mixer.forward(a, ctx, entry)
+        t = self.feed_forward.forward(m, ctx, add=x)
+        ctx.keep_alive.append((a, m, x, mixed, t))
+        return DeferredSum(t, mixed, side)
 
 
 @register_part("block", "sequential")
@@ -56,5 +87,6 @@ class SequentialBlock(Part):
 
     def forward(self, x, ctx, entry):
         k = self.build.kernels
+        x = resolve(k, x)
         r = _plus(k, self.mixer, x, self.norm_mixer.forward(x), ctx, entry)
         return _plus(k, self.feed_forward, r, self.norm_ff.forward(r), ctx)

@@ -33,4 +33,6 @@ class DenseFeedForward(Part):
     def forward(self, x, ctx, add=None):
         k = self.build.kernels
         u = linear(k, x, self.p_up_weight, self.p_up_bias, self.activation)
+        if callable(add):
+            add = add()   # resolved as late as possible: the caller may still be producing it on another stream
         return linear(k, u, self.p_down_weight, self.p_down_bias, add=add)

@@ -30,6 +30,17 @@ class LayerNorm(Part):
     def forward(self, x):
         return self.build.kernels.norm(x, self.p_weight, self.p_bias, self.eps, self.kind)
 
+    def forward_sum(self, x, addend, other: "LayerNorm" = None):
+        """Norm of ``x + addend``: returns (the sum, its norm[, ``other``'s norm of it]) from one kernel."""
+        k = self.build.kernels
+        if other is not None and (other.kind != self.kind or other.eps != self.eps or other.size != self.size):
+            total, y = k.norm(x, self.p_weight, self.p_bias, self.eps, self.kind, addend=addend)
+            return total, y, other.forward(total)
+        if other is not None:
+            return k.norm(x, self.p_weight, self.p_bias, self.eps, self.kind, gain2=other.p_weight,
+                          bias2=other.p_bias, addend=addend)
+        return k.norm(x, self.p_weight, self.p_bias, self.eps, self.kind, addend=addend)
+
     def forward_pair(self, x, other: "LayerNorm"):
         """Two norms of the same input with the same statistics: one read, two outputs."""
         if other.kind != self.kind or other.eps != self.eps or other.size != self.size:

@@ -7,7 +7,7 @@ import plain_falcon as plain
 
 
 def attention_case(K, dtype, heads, kv_heads, d, pasts, news, position="rotary", window=0, theta=10000.0,
-                   seed=0, needle=None, mma=None):
+                   seed=0, needle=None, mma=None, fused_decode=None):
     """Run the split/rotate/store kernel and an attention function over random projections in two
     steps (first `pasts[b]` tokens, then `news[b]`) and return (engine output of the second step,
     plain output for the same rows) as float64 CPU tensors.
@@ -55,6 +55,14 @@ def attention_case(K, dtype, heads, kv_heads, d, pasts, news, position="rotary",
         toks = [[0] * (r[1] - r[0]) for _, r in live]
         ctx = StepContext(cache, [s for s, _ in live], toks, 1, [[] for _ in live], K.generic_tile_rows())
         x = torch.cat([fused[i][r[0]:r[1]] for i, (_, r) in zip(idx, live)]).to(dtype).cuda().contiguous()
+        if fused_decode is not None and ctx.mma_tokens == 1:
+            # fused_decode = (heads per tile or None, splits): the one-kernel decode path
+            rope = K.rope_table(ctx.dev["tok_pos"], inv_freq) if inv_freq is not None else None
+            hpk = fused_decode[0] or min(qpk, 128)
+            out = K.attention_decode(x, k_pool, v_pool, ctx.batch_c[gi], rope, slopes, kv_heads, qpk, d, scale,
+                                     window, hpk, (hpk + 15) // 16, fused_decode[1])
+            ctx.commit()
+            return out, idx
         q = K.split_rotate_store(x, k_pool, v_pool, ctx.batch_c[gi], inv_freq, kv_heads, qpk, d)
         if mma is None:
             out = K.attention_generic(q, k_pool, v_pool, ctx.batch_c[gi], ctx.dev["tile_seq"], ctx.dev["tile_q0"],

@@ -113,3 +113,45 @@ def test_mma_refuses_what_it_does_not_take(K):
         attention_case(K, BF, 4, 1, 48, pasts=[0], news=[5], mma=(None, 1))
     with pytest.raises(KernelError):
         attention_case(K, torch.float32, 4, 1, 64, pasts=[0], news=[5], mma=(None, 1))
+
+
+# ------------------------------------------------------------------------------ one-kernel decode
+@pytest.mark.parametrize("heads,kv,d", MMA_SHAPES)
+@pytest.mark.parametrize("position", ["rotary", "alibi"])
+@pytest.mark.parametrize("splits", [1, 2, 4, 8])
+def test_fused_decode(K, heads, kv, d, position, splits):
+    # new tokens at a page's last slot, its first slot, in the middle, as the second token, far out
+    out, ref = attention_case(K, BF, heads, kv, d, pasts=[63, 64, 200, 1, 700, 127], news=[1] * 6,
+                              position=position, seed=3, fused_decode=(None, splits))
+    torch.testing.assert_close(out, ref, **tol(BF))
+
+
+@pytest.mark.parametrize("hpk", [16, 32, None])
+def test_fused_decode_head_chunks_and_repeated_launches(K, hpk):
+    # 71 heads in chunks of 16 or 32: several blocks share a K/V head; launched twice so that the
+    # tickets of the first launch must have been put back
+    for seed in (1, 2):
+        out, ref = attention_case(K, BF, 71, 1, 64, pasts=[300, 65, 5], news=[1, 1, 1], position="rotary", seed=seed,
+                                  fused_decode=(hpk, 4))
+        torch.testing.assert_close(out, ref, **tol(BF))
+
+
+@pytest.mark.parametrize("key_pos", [0, 64, 698, 699])
+def test_fused_decode_far_key_and_own_key(K, key_pos):
+    out, ref = attention_case(K, BF, 71, 1, 64, pasts=[0 + 5, 699], news=[1, 1], position="none", seed=5,
+                              needle=(1, key_pos), fused_decode=(None, 4))
+    torch.testing.assert_close(out, ref, **tol(BF))
+
+
+@pytest.mark.parametrize("window", [1, 5, 64, 65, 100])
+def test_fused_decode_window(K, window):
+    out, ref = attention_case(K, BF, 4, 2, 64, pasts=[300, 5, 64], news=[1, 1, 1], position="rotary", window=window,
+                              seed=7, fused_decode=(None, 2))
+    torch.testing.assert_close(out, ref, **tol(BF))
+
+
+def test_rope_table_equals_in_kernel_angles(K):
+    from engine_helpers import attention_case as case
+    for dtype in (torch.float32, BF):
+        a, ref = case(K, dtype, 4, 2, 64, pasts=[0, 3], news=[70, 9], position="rotary", seed=9)
+        torch.testing.assert_close(a, ref, **tol(dtype))
