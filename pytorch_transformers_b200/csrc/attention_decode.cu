@@ -197,7 +197,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ fused, __nv_bfloat16* 
       m_blk[i2] = fmaxf(m_blk[i2], __shfl_xor_sync(0xffffffffu, m_blk[i2], 1));
       m_blk[i2] = fmaxf(m_blk[i2], __shfl_xor_sync(0xffffffffu, m_blk[i2], 2));
       const float m_new = fmaxf(m_run[i2], m_blk[i2]);
-      corr[i2] = (m_run[i2] == -INFINITY) ? 0.f : exp2f(m_run[i2] - m_new);
+      corr[i2] = (m_run[i2] == -INFINITY) ? 0.f : fast_exp2(m_run[i2] - m_new);
       m_run[i2] = m_new;
     }
     uint32_t pa[KEYS / 16][4];
@@ -208,7 +208,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ fused, __nv_bfloat16* 
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const int i2 = e >> 1;
-        pv[e] = (s[j][e] == -INFINITY) ? 0.f : exp2f(s[j][e] - m_run[i2]);
+        pv[e] = (s[j][e] == -INFINITY) ? 0.f : fast_exp2(s[j][e] - m_run[i2]);
         l_blk[i2] += pv[e];
       }
       pa[j >> 1][(j & 1) * 2 + 0] = pack_bf16(pv[0], pv[1]);

@@ -62,6 +62,9 @@ attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
     for (int i = 0; i < 2; ++i)
       if (row_ok[i]) slope[i] = alibi_slopes[g * qpk + h0 + row_head[i]];
   }
+  // block-uniform facts about the tile's rows (every row of the tile, not only this thread's)
+  const bool all_rows_ok = tok_valid * p.hpk >= rows_total && head_valid == p.hpk;
+  const int min_row_pos = past + q0;
 
   // Q fragments straight from global memory: a[kk][0..3] for k-step kk (16 dims)
   uint32_t qa[D / 16][4];
@@ -138,19 +141,35 @@ attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
       }
       // mask, bias, scale; block maximum per row
       float m_blk[2] = {-INFINITY, -INFINITY};
+      // a page whose last key every row of the tile sees (and no window, no bias, no invalid row)
+      // needs no per-element test: that is all pages of a long prompt but the diagonal ones
+      const bool plain_page = all_rows_ok && p.window <= 0 && alibi_slopes == nullptr &&
+                              (kb * KEYS + KEYS - 1) <= min_row_pos;
+      if (plain_page) {
 #pragma unroll
-      for (int j = 0; j < KEYS / 8; ++j) {
+        for (int j = 0; j < KEYS / 8; ++j) {
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int i = e >> 1;
-          const int key_pos = kb * KEYS + j * 8 + t4 * 2 + (e & 1);
-          bool visible = key_pos <= row_pos[i];
-          if (p.window > 0) visible = visible && key_pos > row_pos[i] - p.window;
-          float v = s[j][e];
-          if (alibi_slopes) v += alibi_bias(slope[i], key_pos);
-          v = visible ? v * sl2 : -INFINITY;
-          s[j][e] = v;
-          m_blk[i] = fmaxf(m_blk[i], v);
+          for (int e = 0; e < 4; ++e) {
+            const float v = s[j][e] * sl2;
+            s[j][e] = v;
+            m_blk[e >> 1] = fmaxf(m_blk[e >> 1], v);
+          }
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < KEYS / 8; ++j) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int i = e >> 1;
+            const int key_pos = kb * KEYS + j * 8 + t4 * 2 + (e & 1);
+            bool visible = key_pos <= row_pos[i];
+            if (p.window > 0) visible = visible && key_pos > row_pos[i] - p.window;
+            float v = s[j][e];
+            if (alibi_slopes) v += alibi_bias(slope[i], key_pos);
+            v = visible ? v * sl2 : -INFINITY;
+            s[j][e] = v;
+            m_blk[i] = fmaxf(m_blk[i], v);
+          }
         }
       }
       float corr[2];
@@ -159,7 +178,7 @@ attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
         m_blk[i] = fmaxf(m_blk[i], __shfl_xor_sync(0xffffffffu, m_blk[i], 1));
         m_blk[i] = fmaxf(m_blk[i], __shfl_xor_sync(0xffffffffu, m_blk[i], 2));
         const float m_new = fmaxf(m_run[i], m_blk[i]);
-        corr[i] = (m_run[i] == -INFINITY) ? 0.f : exp2f(m_run[i] - m_new);
+        corr[i] = (m_run[i] == -INFINITY) ? 0.f : fast_exp2(m_run[i] - m_new);
         m_run[i] = m_new;
       }
       // P = exp2(S - m), row sums, and P as A fragments for the second product
@@ -171,7 +190,7 @@ attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           const int i = e >> 1;
-          pv[e] = (s[j][e] == -INFINITY) ? 0.f : exp2f(s[j][e] - m_run[i]);
+          pv[e] = (s[j][e] == -INFINITY) ? 0.f : fast_exp2(s[j][e] - m_run[i]);
           l_blk[i] += pv[e];
         }
         pa[j >> 1][(j & 1) * 2 + 0] = pack_bf16(pv[0], pv[1]);

@@ -34,6 +34,14 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
+// 2^x by the hardware's approximation unit (relative error about 2^-22, far below bfloat16's): used
+// for softmax weights that are rounded to bfloat16 before they meet the tensor cores.
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+  return y;
+}
+
 // byte offset of 16-byte chunk `c` of row `row` in a [KEYS][D] bfloat16 tile with the XOR swizzle
 template <int D> __device__ __forceinline__ uint32_t swz(int row, int c) {
   return uint32_t(row * (D * 2) + ((c ^ (row & 7)) << 4));
