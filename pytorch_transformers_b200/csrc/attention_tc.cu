@@ -1,0 +1,344 @@
+// Prompt attention on the fifth-generation tensor cores (tcgen05) with the accumulators in tensor
+// memory, for head size 64, bfloat16, causal, over the paged cache.
+//
+// One block = 128 consecutive new tokens of one sequence x one query head; 128 threads, thread t owns
+// query row t (tensor-memory lane t). Keys are walked one cache page (64 keys) at a time:
+//
+//   S = Q K^T      tcgen05.mma  M=128 N=64 K=64   A = Q  (shared, K-major, 128-byte swizzle)
+//                                                 B = K page (shared, K-major, 128-byte swizzle)
+//                                                 D = S in tensor memory, columns [0, 64)
+//   softmax        each thread reads its row of S with tcgen05.ld, masks, keeps the running maximum and
+//                  sum in float32, rescales its row of O in tensor memory when the maximum moved, and
+//                  writes P = exp2(S - max) as bfloat16 into shared memory (K-major, swizzled)
+//   O += P V       tcgen05.mma  M=128 N=64 K=64   A = P, B = V page (shared, MN-major: head dims are
+//                                                 contiguous), D = O in tensor memory, columns [64, 128)
+//
+// The page tiles [64 keys][64 dims] bfloat16 are copied with cp.async into a three-stage ring, each
+// 16-byte chunk XOR-swizzled by its row, which is exactly the canonical 128-byte-swizzle layout that
+// the matrix descriptors name (K-major for Q, K and P; MN-major for V). Completion of the matrix
+// instructions is signalled through tcgen05.commit on mbarriers. Every wait on a barrier is bounded:
+// if it runs out, a flag in global memory is raised and the block carries on to its end (tensor memory
+// is freed on every path), so a fault in the pipeline shows as an error, never as a hang.
+//
+// Two blocks fit on an SM (80 KB of shared memory and 128 columns of tensor memory each): while one
+// block's threads do softmax, the other's matrix instructions run.
+#include "mma_common.cuh"
+
+namespace {
+
+constexpr int TQ = 128;          // query rows per block
+constexpr int D = 64;            // head size
+constexpr int STAGES_TC = 3;
+constexpr int TILE_Q_BYTES = TQ * D * 2;       // 16 KB
+constexpr int TILE_KV_BYTES = KEYS * D * 2;    // 8 KB
+constexpr int TILE_P_BYTES = TQ * KEYS * 2;    // 16 KB
+constexpr uint32_t WAIT_LIMIT = 1u << 20;
+
+// ---- shared-memory matrix descriptor (sm_100): start address, leading and stride byte offsets in
+// 16-byte units, version 1, layout type 2 = 128-byte swizzle
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  return uint64_t((addr & 0x3FFFFu) >> 4) | (uint64_t(lbo_bytes >> 4) << 16) | (uint64_t(sbo_bytes >> 4) << 32) |
+         (1ull << 46) | (2ull << 61);
+}
+// ---- instruction descriptor for kind::f16: D float32, A and B bfloat16, N / 8 at bit 17, M / 16 at bit 24
+__host__ __device__ constexpr uint32_t idesc_bf16(int m, int n, bool b_mn_major) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | (b_mn_major ? (1u << 16) : 0u) | (uint32_t(n >> 3) << 17) |
+         (uint32_t(m >> 4) << 24);
+}
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}\n"
+      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
+// bounded wait: false (and the error flag raised) if the barrier did not complete in time
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* error_flag, int code) {
+  for (uint32_t i = 0; i < WAIT_LIMIT; ++i)
+    if (mbar_try_wait(bar, parity)) return true;
+  atomicExch(error_flag, code);
+  return false;
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void proxy_fence_async() { asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); }
+
+__device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                       uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}\n"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar) : "memory");
+}
+// 32 consecutive columns of this thread's lane
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
+  uint32_t r[32];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&v)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};\n"
+      ::"r"(taddr), "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])),
+        "r"(__float_as_uint(v[3])), "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])),
+        "r"(__float_as_uint(v[6])), "r"(__float_as_uint(v[7])), "r"(__float_as_uint(v[8])),
+        "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])), "r"(__float_as_uint(v[11])),
+        "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])),
+        "r"(__float_as_uint(v[15])), "r"(__float_as_uint(v[16])), "r"(__float_as_uint(v[17])),
+        "r"(__float_as_uint(v[18])), "r"(__float_as_uint(v[19])), "r"(__float_as_uint(v[20])),
+        "r"(__float_as_uint(v[21])), "r"(__float_as_uint(v[22])), "r"(__float_as_uint(v[23])),
+        "r"(__float_as_uint(v[24])), "r"(__float_as_uint(v[25])), "r"(__float_as_uint(v[26])),
+        "r"(__float_as_uint(v[27])), "r"(__float_as_uint(v[28])), "r"(__float_as_uint(v[29])),
+        "r"(__float_as_uint(v[30])), "r"(__float_as_uint(v[31]))
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory"); }
+
+struct TcParams {
+  int heads, kv_heads;
+  float scale;
+};
+
+__global__ void __launch_bounds__(TQ)
+attention_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_pool,
+                    const __nv_bfloat16* __restrict__ v_pool, __nv_bfloat16* __restrict__ out, StepBatch sb,
+                    const int* __restrict__ tile_seq, const int* __restrict__ tile_q0, TcParams p,
+                    int* __restrict__ error_flag) {
+  extern __shared__ unsigned char smem_dyn[];
+  // 1024-byte alignment: the swizzle pattern is a function of address bits 4..9
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
+  unsigned char* q_tile = smem;                                       // 16 KB
+  unsigned char* k_ring = q_tile + TILE_Q_BYTES;                      // 3 x 8 KB
+  unsigned char* v_ring = k_ring + STAGES_TC * TILE_KV_BYTES;         // 3 x 8 KB
+  unsigned char* p_tile = v_ring + STAGES_TC * TILE_KV_BYTES;         // 16 KB
+  uint64_t* bars = reinterpret_cast<uint64_t*>(p_tile + TILE_P_BYTES);  // [0] S done, [1] O done
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2);
+
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const int tile = blockIdx.x, h = blockIdx.y;
+  const int qpk = p.heads / p.kv_heads;
+  const int g = h / qpk;
+  const int seq = tile_seq[tile], q0 = tile_q0[tile];
+  const int n_new = sb.seq_new[seq], past = sb.seq_past[seq], start = sb.seq_start[seq];
+  const int tok_valid = min(TQ, n_new - q0);
+  const bool row_ok = tid < tok_valid;
+  const int row_pos = row_ok ? past + q0 + tid : -1;
+  const int last_pos = past + q0 + tok_valid - 1;
+  const int n_blocks = last_pos / KEYS + 1;
+  const int* pages = sb.pages + size_t(seq) * sb.pages_stride;
+
+  const uint32_t bar_s = smem_u32(&bars[0]), bar_o = smem_u32(&bars[1]);
+  if (tid == 0) {
+    mbar_init(bar_s, 1);
+    mbar_init(bar_o, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  }
+  if (warp == 0) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(tmem_slot)), "r"(128));
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::);
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t lane_addr = tmem_base + (uint32_t(warp * 32) << 16);  // this warp's 32 lanes
+  const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + 64;
+
+  // Q tile: rows of the tile, zero beyond the valid tokens
+  {
+    const uint32_t qs = smem_u32(q_tile);
+    for (int i = tid; i < TQ * (D / 8); i += TQ) {
+      const int row = i / (D / 8), c = i % (D / 8);
+      if (row < tok_valid)
+        cp_async16(qs + swz<D>(row, c), q + (size_t(start + q0 + row) * p.heads + h) * D + c * 8);
+      else
+        *reinterpret_cast<uint4*>(q_tile + swz<D>(row, c)) = make_uint4(0, 0, 0, 0);
+    }
+  }
+  auto load_block = [&](int b) {  // page b of the sequence into stage b % 3; one commit group, maybe empty
+    if (b < n_blocks) {
+      const int page = pages[b];
+      const int st = b % STAGES_TC;
+      load_page<D>(smem_u32(k_ring + st * TILE_KV_BYTES), k_pool + kv_offset(page, g, 0, p.kv_heads, D), tid, TQ);
+      load_page<D>(smem_u32(v_ring + st * TILE_KV_BYTES), v_pool + kv_offset(page, g, 0, p.kv_heads, D), tid, TQ);
+    }
+    cp_async_commit();
+  };
+  load_block(0);  // group 0 also holds the Q tile
+  load_block(1);
+
+  constexpr uint32_t IDESC_S = idesc_bf16(TQ, KEYS, false);
+  constexpr uint32_t IDESC_PV = idesc_bf16(TQ, D, true);
+  const uint64_t desc_q = smem_desc(smem_u32(q_tile), 16, 1024);
+  const uint64_t desc_p = smem_desc(smem_u32(p_tile), 16, 1024);
+
+  float m_run = -INFINITY, l_run = 0.f;
+  const float sl2 = p.scale * 1.4426950408889634f;
+  bool alive = true;  // false after a wait ran out: keep going without waiting, results are void
+
+  for (int i = 0; i < n_blocks; ++i) {
+    const int st = i % STAGES_TC;
+    // (A) page i has landed; make the copies visible to the tensor cores' reads
+    cp_async_wait<1>();
+    proxy_fence_async();
+    __syncthreads();
+    // (B) S = Q K^T
+    if (tid == 0) {
+      tc_fence_after();
+      const uint64_t desc_k = smem_desc(smem_u32(k_ring + st * TILE_KV_BYTES), 16, 1024);
+#pragma unroll
+      for (int kk = 0; kk < D / 16; ++kk)  // 16 dims = 32 bytes = 2 descriptor units along a swizzled row
+        tc_mma(tmem_s, desc_q + 2 * kk, desc_k + 2 * kk, IDESC_S, kk > 0 ? 1u : 0u);
+      tc_commit(bar_s);
+    }
+    // (C) wait for S
+    if (alive) alive = mbar_wait(bar_s, i & 1, error_flag, 1);
+    tc_fence_after();
+    // (D) this thread's row of S: scale, mask, maximum
+    float s[KEYS];
+    {
+      float part[32];
+      tmem_ld32(lane_addr + 0, part);
+#pragma unroll
+      for (int j = 0; j < 32; ++j) s[j] = part[j];
+      tmem_ld32(lane_addr + 32, part);
+#pragma unroll
+      for (int j = 0; j < 32; ++j) s[32 + j] = part[j];
+    }
+    const int visible = row_pos - i * KEYS;  // keys j <= visible are seen by this row
+    float m_blk = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < KEYS; ++j) {
+      const float v = (j <= visible) ? s[j] * sl2 : -INFINITY;
+      s[j] = v;
+      m_blk = fmaxf(m_blk, v);
+    }
+    const float m_new = fmaxf(m_run, m_blk);
+    const float corr = (m_run == -INFINITY) ? 0.f : fast_exp2(m_run - m_new);
+    const bool moved = (m_new != m_run) && (m_run != -INFINITY);
+    m_run = m_new;
+    // (E) the previous O += P V is complete: its page stage and the P tile are free, O may be touched
+    if (i > 0) {
+      if (alive) alive = mbar_wait(bar_o, (i - 1) & 1, error_flag, 2);
+      tc_fence_after();
+    }
+    load_block(i + 2);
+    // (F) rescale this row of O if any row of the warp moved its maximum
+    if (i > 0 && __any_sync(0xffffffffu, moved)) {
+      float o[32];
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        tmem_ld32(lane_addr + 64 + half * 32, o);
+#pragma unroll
+        for (int j = 0; j < 32; ++j) o[j] *= corr;
+        tmem_st32(lane_addr + 64 + half * 32, o);
+      }
+      tmem_st_wait();
+    }
+    l_run *= corr;
+    // (G) P = exp2(S - max) as bfloat16 into the swizzled P tile, row tid
+    float l_blk = 0.f;
+#pragma unroll
+    for (int c = 0; c < KEYS / 8; ++c) {
+      uint32_t w[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float a = (s[c * 8 + 2 * e] == -INFINITY) ? 0.f : fast_exp2(s[c * 8 + 2 * e] - m_run);
+        const float b = (s[c * 8 + 2 * e + 1] == -INFINITY) ? 0.f : fast_exp2(s[c * 8 + 2 * e + 1] - m_run);
+        l_blk += a + b;
+        w[e] = pack_bf16(a, b);
+      }
+      *reinterpret_cast<uint4*>(p_tile + swz<KEYS>(tid, c)) = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+    l_run += l_blk;
+    proxy_fence_async();
+    tc_fence_before();
+    __syncthreads();
+    // (H) O += P V
+    if (tid == 0) {
+      tc_fence_after();
+      const uint64_t desc_v = smem_desc(smem_u32(v_ring + st * TILE_KV_BYTES), 16, 1024);
+#pragma unroll
+      for (int kk = 0; kk < KEYS / 16; ++kk)  // 16 keys: 32 bytes along P's rows, 2048 bytes down V's rows
+        tc_mma(tmem_o, desc_p + 2 * kk, desc_v + 128 * kk, IDESC_PV, (i > 0 || kk > 0) ? 1u : 0u);
+      tc_commit(bar_o);
+    }
+  }
+  cp_async_wait<0>();
+  if (alive) alive = mbar_wait(bar_o, (n_blocks - 1) & 1, error_flag, 3);
+  tc_fence_after();
+  {
+    const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+    __nv_bfloat16* dst = out + (size_t(start + q0 + tid) * p.heads + h) * D;
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      float o[32];
+      tmem_ld32(lane_addr + 64 + half * 32, o);
+      if (row_ok) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint32_t w[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) w[e] = pack_bf16(o[c * 8 + 2 * e] * inv, o[c * 8 + 2 * e + 1] * inv);
+          *reinterpret_cast<uint4*>(dst + half * 32 + c * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0)
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(128));
+}
+
+}  // namespace
+
+PTB_API int ptb_attention_tc_supports(int head_dim) { return head_dim == D ? 1 : 0; }
+PTB_API int ptb_attention_tc_tile_tokens() { return TQ; }
+
+// Causal attention of prompt tiles of 128 tokens (tile_seq / tile_q0 as for the other attention
+// kernels, 128 tokens per tile), bfloat16, head size 64, no bias, no window. `error_flag` is a device
+// int that stays 0 unless a bounded wait inside the kernel ran out.
+PTB_API int ptb_attention_tc(const void* q, const void* k_pool, const void* v_pool, void* out, const StepBatch* sb,
+                             const int* tile_seq, const int* tile_q0, int n_tiles, int heads, int kv_heads,
+                             int head_dim, float scale, int* error_flag, cudaStream_t stream) {
+  if (n_tiles <= 0) return PTB_OK;
+  if (head_dim != D || heads <= 0 || kv_heads <= 0 || heads % kv_heads != 0 || heads > 65535 || error_flag == nullptr)
+    return PTB_ERR_SIZE;
+  const size_t smem = 1024 + TILE_Q_BYTES + 2 * STAGES_TC * TILE_KV_BYTES + TILE_P_BYTES + 64;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(attention_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess)
+      return PTB_ERR_LAUNCH;
+    configured = true;
+  }
+  TcParams p;
+  p.heads = heads; p.kv_heads = kv_heads; p.scale = scale;
+  dim3 grid(n_tiles, heads);
+  attention_tc_kernel<<<grid, TQ, smem, stream>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool,
+                                                  (const __nv_bfloat16*)v_pool, (__nv_bfloat16*)out, *sb, tile_seq,
+                                                  tile_q0, p, error_flag);
+  return launch_status();
+}

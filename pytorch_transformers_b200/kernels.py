@@ -77,7 +77,8 @@ def lib():
                      "ptb_linear_f32", "ptb_split_rotate_store", "ptb_attention_generic", "ptb_sample",
                      "ptb_attention_generic_tile_rows", "ptb_attention_mma", "ptb_attention_mma_supports",
                      "ptb_skinny_linear", "ptb_skinny_linear_max_rows", "ptb_skinny_linear_k_multiple",
-                     "ptb_rope_table", "ptb_attention_decode"):
+                     "ptb_rope_table", "ptb_attention_decode", "ptb_attention_tc", "ptb_attention_tc_supports",
+                     "ptb_attention_tc_tile_tokens"):
             getattr(L, name).restype = ctypes.c_int
         _configured = True
     return L
@@ -231,6 +232,48 @@ def attention_decode(fused: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Te
                                       _ptr(cos), _ptr(sin), pairs, _ptr(slopes), heads, kv_heads, head_dim,
                                       heads_per_tile, n_splits, warps, ctypes.c_float(scale), window,
                                       1 if write_cache else 0, _stream(fused)), "attention_decode")
+    return out
+
+
+_error_flags = {}
+TC_TILE_TOKENS = 128  # ptb_attention_tc_tile_tokens()
+
+
+def error_flag(device) -> torch.Tensor:
+    """Device int32 word that kernels with bounded waits raise when a wait runs out."""
+    device = torch.device(device)
+    if device not in _error_flags:
+        _error_flags[device] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _error_flags[device]
+
+
+def check_device_errors(device) -> None:
+    """Raise if a kernel has reported that one of its bounded waits ran out (synchronises)."""
+    device = torch.device(device)
+    flag = _error_flags.get(device)
+    if flag is not None:
+        code = int(flag.item())
+        if code != 0:
+            flag.zero_()
+            raise KernelError(f"a kernel gave up waiting inside its pipeline (code {code}): its results are void")
+
+
+def attention_tc_supports(head_dim: int) -> bool:
+    return bool(lib().ptb_attention_tc_supports(int(head_dim)))
+
+
+def attention_tc(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, batch: StepBatchC,
+                 tile_seq: torch.Tensor, tile_q0: torch.Tensor, n_tiles: int, kv_heads: int, scale: float):
+    """Causal prompt attention on tcgen05 tensor cores with accumulators in tensor memory: bfloat16,
+    head size 64, tiles of 128 tokens, no bias, no window. Returns [tokens, heads * head_dim]."""
+    _need_cuda(q, k_pool, v_pool, tile_seq, tile_q0)
+    if q.dtype != torch.bfloat16:
+        raise KernelError("attention_tc takes bfloat16 tensors")
+    n, heads, head_dim = q.shape
+    out = torch.empty((n, heads * head_dim), dtype=q.dtype, device=q.device)
+    _check(lib().ptb_attention_tc(_ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), ctypes.byref(batch), _ptr(tile_seq),
+                                  _ptr(tile_q0), n_tiles, heads, kv_heads, head_dim, ctypes.c_float(scale),
+                                  _ptr(error_flag(q.device)), _stream(q)), "attention_tc")
     return out
 
 

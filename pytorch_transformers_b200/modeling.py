@@ -167,6 +167,7 @@ class PreTrainedCausalLM(CausalLM):
         results = run_generation(_CacheStepper(self, cache), selector, expanded, opts, budget, max_batch,
                                  on_token=_on_token if on_token is not None else None,
                                  keep_logits=opts.output_logits)
+        self.build.kernels.check_device_errors(self.device)
         if streamer is not None:
             # the reference pushes the prompt and then every step's tokens (streamers.py:27-233);
             # with unequal lengths per request we hand over each finished request once

@@ -7,7 +7,7 @@ import plain_falcon as plain
 
 
 def attention_case(K, dtype, heads, kv_heads, d, pasts, news, position="rotary", window=0, theta=10000.0,
-                   seed=0, needle=None, mma=None, fused_decode=None):
+                   seed=0, needle=None, mma=None, fused_decode=None, tc=False):
     """Run the split/rotate/store kernel and an attention function over random projections in two
     steps (first `pasts[b]` tokens, then `news[b]`) and return (engine output of the second step,
     plain output for the same rows) as float64 CPU tensors.
@@ -64,7 +64,12 @@ def attention_case(K, dtype, heads, kv_heads, d, pasts, news, position="rotary",
             ctx.commit()
             return out, idx
         q = K.split_rotate_store(x, k_pool, v_pool, ctx.batch_c[gi], inv_freq, kv_heads, qpk, d)
-        if mma is None:
+        if tc:
+            assert ctx.mma_tokens == K.TC_TILE_TOKENS
+            out = K.attention_tc(q, k_pool, v_pool, ctx.batch_c[gi], ctx.dev["mtile_seq"], ctx.dev["mtile_q0"],
+                                 ctx.n_mma_tiles, kv_heads, scale)
+            K.check_device_errors("cuda")
+        elif mma is None:
             out = K.attention_generic(q, k_pool, v_pool, ctx.batch_c[gi], ctx.dev["tile_seq"], ctx.dev["tile_q0"],
                                       ctx.n_tiles, slopes, kv_heads, scale, window)
         else:
