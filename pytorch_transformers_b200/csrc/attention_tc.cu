@@ -6,21 +6,22 @@
 //
 //   S = Q K^T      tcgen05.mma  M=128 N=64 K=64   A = Q  (shared, K-major, 128-byte swizzle)
 //                                                 B = K page (shared, K-major, 128-byte swizzle)
-//                                                 D = S in tensor memory, columns [0, 64)
+//                                                 D = S in tensor memory, two buffers of 64 columns: the
+//                                                 product for the next page runs under this page's softmax
 //   softmax        each thread reads its row of S with tcgen05.ld, masks, keeps the running maximum and
 //                  sum in float32, rescales its row of O in tensor memory when the maximum moved, and
 //                  writes P = exp2(S - max) as bfloat16 into shared memory (K-major, swizzled)
 //   O += P V       tcgen05.mma  M=128 N=64 K=64   A = P, B = V page (shared, MN-major: head dims are
-//                                                 contiguous), D = O in tensor memory, columns [64, 128)
+//                                                 contiguous), D = O in tensor memory, columns [128, 192)
 //
-// The page tiles [64 keys][64 dims] bfloat16 are copied with cp.async into a three-stage ring, each
+// The page tiles [64 keys][64 dims] bfloat16 are copied with cp.async into a four-stage ring, each
 // 16-byte chunk XOR-swizzled by its row, which is exactly the canonical 128-byte-swizzle layout that
 // the matrix descriptors name (K-major for Q, K and P; MN-major for V). Completion of the matrix
 // instructions is signalled through tcgen05.commit on mbarriers. Every wait on a barrier is bounded:
 // if it runs out, a flag in global memory is raised and the block carries on to its end (tensor memory
 // is freed on every path), so a fault in the pipeline shows as an error, never as a hang.
 //
-// Two blocks fit on an SM (80 KB of shared memory and 128 columns of tensor memory each): while one
+// Two blocks fit on an SM (97 KB of shared memory and 256 columns of tensor memory each): while one
 // block's threads do softmax, the other's matrix instructions run.
 #include "mma_common.cuh"
 
@@ -28,7 +29,7 @@ namespace {
 
 constexpr int TQ = 128;          // query rows per block
 constexpr int D = 64;            // head size
-constexpr int STAGES_TC = 3;
+constexpr int STAGES_TC = 4;
 constexpr int TILE_Q_BYTES = TQ * D * 2;       // 16 KB
 constexpr int TILE_KV_BYTES = KEYS * D * 2;    // 8 KB
 constexpr int TILE_P_BYTES = TQ * KEYS * 2;    // 16 KB
@@ -133,8 +134,8 @@ attention_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
   unsigned char* k_ring = q_tile + TILE_Q_BYTES;                      // 3 x 8 KB
   unsigned char* v_ring = k_ring + STAGES_TC * TILE_KV_BYTES;         // 3 x 8 KB
   unsigned char* p_tile = v_ring + STAGES_TC * TILE_KV_BYTES;         // 16 KB
-  uint64_t* bars = reinterpret_cast<uint64_t*>(p_tile + TILE_P_BYTES);  // [0] S done, [1] O done
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(p_tile + TILE_P_BYTES);  // [0], [1] S buffers done, [2] O done
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3);
 
   const int tid = threadIdx.x, warp = tid >> 5;
   const int tile = blockIdx.x, h = blockIdx.y;
@@ -149,14 +150,15 @@ attention_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
   const int n_blocks = last_pos / KEYS + 1;
   const int* pages = sb.pages + size_t(seq) * sb.pages_stride;
 
-  const uint32_t bar_s = smem_u32(&bars[0]), bar_o = smem_u32(&bars[1]);
+  const uint32_t bar_s = smem_u32(&bars[0]), bar_o = smem_u32(&bars[2]);
   if (tid == 0) {
     mbar_init(bar_s, 1);
+    mbar_init(bar_s + 8, 1);
     mbar_init(bar_o, 1);
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
   if (warp == 0) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(tmem_slot)), "r"(128));
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(tmem_slot)), "r"(256));
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::);
   }
   tc_fence_before();
@@ -164,7 +166,7 @@ attention_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t lane_addr = tmem_base + (uint32_t(warp * 32) << 16);  // this warp's 32 lanes
-  const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + 64;
+  const uint32_t tmem_o = tmem_base + 128;   // S buffers at columns [0, 64) and [64, 128), O at [128, 192)
 
   // Q tile: rows of the tile, zero beyond the valid tokens
   {
@@ -177,7 +179,7 @@ attention_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
         *reinterpret_cast<uint4*>(q_tile + swz<D>(row, c)) = make_uint4(0, 0, 0, 0);
     }
   }
-  auto load_block = [&](int b) {  // page b of the sequence into stage b % 3; one commit group, maybe empty
+  auto load_block = [&](int b) {  // page b of the sequence into stage b % STAGES_TC; one commit group, maybe empty
     if (b < n_blocks) {
       const int page = pages[b];
       const int st = b % STAGES_TC;
@@ -188,98 +190,118 @@ attention_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
   };
   load_block(0);  // group 0 also holds the Q tile
   load_block(1);
+  load_block(2);
 
   constexpr uint32_t IDESC_S = idesc_bf16(TQ, KEYS, false);
   constexpr uint32_t IDESC_PV = idesc_bf16(TQ, D, true);
   const uint64_t desc_q = smem_desc(smem_u32(q_tile), 16, 1024);
   const uint64_t desc_p = smem_desc(smem_u32(p_tile), 16, 1024);
+  auto issue_s = [&](int b) {  // S_b = Q K_b^T into S buffer b & 1 (thread 0 only)
+    const uint64_t desc_k = smem_desc(smem_u32(k_ring + (b % STAGES_TC) * TILE_KV_BYTES), 16, 1024);
+#pragma unroll
+    for (int kk = 0; kk < D / 16; ++kk)  // 16 dims = 32 bytes = 2 descriptor units along a swizzled row
+      tc_mma(tmem_base + (b & 1) * 64, desc_q + 2 * kk, desc_k + 2 * kk, IDESC_S, kk > 0 ? 1u : 0u);
+    tc_commit(bar_s + (b & 1) * 8);
+  };
 
-  float m_run = -INFINITY, l_run = 0.f;
+  float m_run = -INFINITY, l_run = 0.f;   // running maximum of the raw scores, running sum
   const float sl2 = p.scale * 1.4426950408889634f;
   bool alive = true;  // false after a wait ran out: keep going without waiting, results are void
 
-  for (int i = 0; i < n_blocks; ++i) {
-    const int st = i % STAGES_TC;
-    // (A) page i has landed; make the copies visible to the tensor cores' reads
-    cp_async_wait<1>();
-    proxy_fence_async();
-    __syncthreads();
-    // (B) S = Q K^T
-    if (tid == 0) {
-      tc_fence_after();
-      const uint64_t desc_k = smem_desc(smem_u32(k_ring + st * TILE_KV_BYTES), 16, 1024);
-#pragma unroll
-      for (int kk = 0; kk < D / 16; ++kk)  // 16 dims = 32 bytes = 2 descriptor units along a swizzled row
-        tc_mma(tmem_s, desc_q + 2 * kk, desc_k + 2 * kk, IDESC_S, kk > 0 ? 1u : 0u);
-      tc_commit(bar_s);
-    }
-    // (C) wait for S
-    if (alive) alive = mbar_wait(bar_s, i & 1, error_flag, 1);
+  // page 0 has landed: first S
+  cp_async_wait<2>();
+  proxy_fence_async();
+  tc_fence_before();
+  __syncthreads();
+  if (tid == 0) {
     tc_fence_after();
-    // (D) this thread's row of S: scale, mask, maximum
+    issue_s(0);
+  }
+
+  for (int i = 0; i < n_blocks; ++i) {
+    // (1) this thread's row of S_i
+    if (alive) alive = mbar_wait(bar_s + (i & 1) * 8, (i >> 1) & 1, error_flag, 1);
+    tc_fence_after();
     float s[KEYS];
     {
       float part[32];
-      tmem_ld32(lane_addr + 0, part);
+      tmem_ld32(lane_addr + (i & 1) * 64 + 0, part);
 #pragma unroll
       for (int j = 0; j < 32; ++j) s[j] = part[j];
-      tmem_ld32(lane_addr + 32, part);
+      tmem_ld32(lane_addr + (i & 1) * 64 + 32, part);
 #pragma unroll
       for (int j = 0; j < 32; ++j) s[32 + j] = part[j];
     }
-    const int visible = row_pos - i * KEYS;  // keys j <= visible are seen by this row
-    float m_blk = -INFINITY;
-#pragma unroll
-    for (int j = 0; j < KEYS; ++j) {
-      const float v = (j <= visible) ? s[j] * sl2 : -INFINITY;
-      s[j] = v;
-      m_blk = fmaxf(m_blk, v);
+    // (2) page i + 1 has landed: start S_{i+1} into the other S buffer; it runs under this softmax
+    cp_async_wait<1>();
+    proxy_fence_async();
+    tc_fence_before();
+    __syncthreads();
+    if (tid == 0 && i + 1 < n_blocks) {
+      tc_fence_after();
+      issue_s(i + 1);
     }
+    // (3) maximum of the visible scores; only pages that reach past some row's position need the test
+    // four independent chains keep the maximum (and below, the sum) from being one long dependency
+    float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+    if (i * KEYS + KEYS - 1 > past + q0 || !row_ok) {   // first part is uniform over the block
+      const int visible = row_pos - i * KEYS;           // keys j <= visible are seen by this row
+#pragma unroll
+      for (int j = 0; j < KEYS; ++j) {
+        s[j] = (j <= visible) ? s[j] : -INFINITY;
+        mx[j & 3] = fmaxf(mx[j & 3], s[j]);
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < KEYS; ++j) mx[j & 3] = fmaxf(mx[j & 3], s[j]);
+    }
+    const float m_blk = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
     const float m_new = fmaxf(m_run, m_blk);
-    const float corr = (m_run == -INFINITY) ? 0.f : fast_exp2(m_run - m_new);
+    const float corr = (m_run == -INFINITY) ? 0.f : fast_exp2((m_run - m_new) * sl2);
     const bool moved = (m_new != m_run) && (m_run != -INFINITY);
     m_run = m_new;
-    // (E) the previous O += P V is complete: its page stage and the P tile are free, O may be touched
+    const float m_off = (m_run == -INFINITY) ? 0.f : m_run * sl2;   // exp2(s * sl2 - m_off); exp2(-inf) = 0
+    // (4) the previous O += P V is complete: its page stage and the P tile are free, O may be touched
     if (i > 0) {
       if (alive) alive = mbar_wait(bar_o, (i - 1) & 1, error_flag, 2);
       tc_fence_after();
     }
-    load_block(i + 2);
-    // (F) rescale this row of O if any row of the warp moved its maximum
+    load_block(i + 3);
+    // (5) rescale this row of O if any row of the warp moved its maximum
     if (i > 0 && __any_sync(0xffffffffu, moved)) {
       float o[32];
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
-        tmem_ld32(lane_addr + 64 + half * 32, o);
+        tmem_ld32(lane_addr + 128 + half * 32, o);
 #pragma unroll
         for (int j = 0; j < 32; ++j) o[j] *= corr;
-        tmem_st32(lane_addr + 64 + half * 32, o);
+        tmem_st32(lane_addr + 128 + half * 32, o);
       }
       tmem_st_wait();
     }
     l_run *= corr;
-    // (G) P = exp2(S - max) as bfloat16 into the swizzled P tile, row tid
-    float l_blk = 0.f;
+    // (6) P = exp2(S - max) as bfloat16 into the swizzled P tile, row tid
+    float ls[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
     for (int c = 0; c < KEYS / 8; ++c) {
       uint32_t w[4];
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
-        const float a = (s[c * 8 + 2 * e] == -INFINITY) ? 0.f : fast_exp2(s[c * 8 + 2 * e] - m_run);
-        const float b = (s[c * 8 + 2 * e + 1] == -INFINITY) ? 0.f : fast_exp2(s[c * 8 + 2 * e + 1] - m_run);
-        l_blk += a + b;
+        const float a = fast_exp2(fmaf(s[c * 8 + 2 * e], sl2, -m_off));
+        const float b = fast_exp2(fmaf(s[c * 8 + 2 * e + 1], sl2, -m_off));
+        ls[e] += a + b;
         w[e] = pack_bf16(a, b);
       }
       *reinterpret_cast<uint4*>(p_tile + swz<KEYS>(tid, c)) = make_uint4(w[0], w[1], w[2], w[3]);
     }
-    l_run += l_blk;
+    l_run += (ls[0] + ls[1]) + (ls[2] + ls[3]);
     proxy_fence_async();
     tc_fence_before();
     __syncthreads();
-    // (H) O += P V
+    // (7) O += P V
     if (tid == 0) {
       tc_fence_after();
-      const uint64_t desc_v = smem_desc(smem_u32(v_ring + st * TILE_KV_BYTES), 16, 1024);
+      const uint64_t desc_v = smem_desc(smem_u32(v_ring + (i % STAGES_TC) * TILE_KV_BYTES), 16, 1024);
 #pragma unroll
       for (int kk = 0; kk < KEYS / 16; ++kk)  // 16 keys: 32 bytes along P's rows, 2048 bytes down V's rows
         tc_mma(tmem_o, desc_p + 2 * kk, desc_v + 128 * kk, IDESC_PV, (i > 0 || kk > 0) ? 1u : 0u);
@@ -295,7 +317,7 @@ attention_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
 #pragma unroll
     for (int half = 0; half < 2; ++half) {
       float o[32];
-      tmem_ld32(lane_addr + 64 + half * 32, o);
+      tmem_ld32(lane_addr + 128 + half * 32, o);
       if (row_ok) {
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
@@ -310,7 +332,7 @@ attention_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
   tc_fence_before();
   __syncthreads();
   if (warp == 0)
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(128));
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(256));
 }
 
 }  // namespace
