@@ -40,6 +40,46 @@ __global__ void split_rotate_store_kernel(const T* __restrict__ fused, T* __rest
   const int heads = kv_heads * q_per_kv;
   // work items: (group g, row r in group, pair or plain element)
   const int rot_dims = 2 * rot_pairs;
+  // bfloat16 with head sizes and rotation widths in multiples of 8 and a table of cosines: 16-byte words
+  if (sizeof(T) == 2 && head_dim % 8 == 0 && rot_pairs % 8 == 0 && (rot_pairs == 0 || rope_cos != nullptr) &&
+      aligned16(fused) && aligned16(q_out) && (!write_cache || (aligned16(k_pool) && aligned16(v_pool)))) {
+    const int chunks = head_dim / 8, rot_chunks = rot_pairs / 8;
+    const int total_v = kv_heads * rows * chunks;
+    for (int w = threadIdx.x; w < total_v; w += blockDim.x) {
+      const int c = w % chunks;
+      const int gr = w / chunks;
+      const int r = gr % rows, g = gr / rows;
+      const T* src = src_tok + size_t(g * rows + r) * head_dim;
+      T* dst;
+      if (r < q_per_kv) {
+        dst = q_out + (size_t(t) * heads + (g * q_per_kv + r)) * head_dim;
+      } else {
+        if (!write_cache) continue;
+        dst = ((r == q_per_kv) ? k_pool : v_pool) + kv_offset(page, g, in_page, kv_heads, head_dim);
+      }
+      const bool rotated_row = (r <= q_per_kv) && rot_chunks > 0;
+      if (rotated_row && c < rot_chunks) {
+        float a[8], b[8], cs[8], sn[8];
+        unpack_bf16x8(*reinterpret_cast<const uint4*>(src + c * 8), a);
+        unpack_bf16x8(*reinterpret_cast<const uint4*>(src + rot_pairs + c * 8), b);
+        const float4* cp = reinterpret_cast<const float4*>(rope_cos + size_t(t) * rot_pairs + c * 8);
+        const float4* sp = reinterpret_cast<const float4*>(rope_sin + size_t(t) * rot_pairs + c * 8);
+        *reinterpret_cast<float4*>(cs) = cp[0];
+        *reinterpret_cast<float4*>(cs + 4) = cp[1];
+        *reinterpret_cast<float4*>(sn) = sp[0];
+        *reinterpret_cast<float4*>(sn + 4) = sp[1];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) rotate_pair(a[e], b[e], cs[e], sn[e], a[e], b[e]);
+        *reinterpret_cast<uint4*>(dst + c * 8) = pack_bf16x8(a);
+        *reinterpret_cast<uint4*>(dst + rot_pairs + c * 8) = pack_bf16x8(b);
+      } else if (rotated_row && c < 2 * rot_chunks) {
+        // the upper half of a rotated pair: written by the thread that holds the lower half
+      } else {
+        *reinterpret_cast<uint4*>(dst + c * 8) = *reinterpret_cast<const uint4*>(src + c * 8);
+      }
+    }
+    return;
+  }
   const int per_row = rot_pairs + (head_dim - rot_dims);  // rotated pairs, then untouched dims
   const int total = kv_heads * rows * per_row;
   for (int w = threadIdx.x; w < total; w += blockDim.x) {

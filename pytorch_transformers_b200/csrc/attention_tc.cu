@@ -1,8 +1,8 @@
 // Prompt attention on the fifth-generation tensor cores (tcgen05) with the accumulators in tensor
 // memory, for head size 64, bfloat16, causal, over the paged cache.
 //
-// One block = 128 consecutive new tokens of one sequence x one query head; 128 threads, thread t owns
-// query row t (tensor-memory lane t). Keys are walked one cache page (64 keys) at a time:
+// One block = 128 consecutive new tokens of one sequence x one query head; 256 threads: threads t and
+// t + 128 share query row t (tensor-memory lane t), each taking 32 of a page's 64 columns. Keys are walked one cache page (64 keys) at a time:
 //
 //   S = Q K^T      tcgen05.mma  M=128 N=64 K=64   A = Q  (shared, K-major, 128-byte swizzle)
 //                                                 B = K page (shared, K-major, 128-byte swizzle)
@@ -122,7 +122,7 @@ struct TcParams {
   float scale;
 };
 
-__global__ void __launch_bounds__(TQ)
+__global__ void __launch_bounds__(2 * TQ)
 attention_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_pool,
                     const __nv_bfloat16* __restrict__ v_pool, __nv_bfloat16* __restrict__ out, StepBatch sb,
                     const int* __restrict__ tile_seq, const int* __restrict__ tile_q0, TcParams p,
@@ -136,16 +136,20 @@ attention_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
   unsigned char* p_tile = v_ring + STAGES_TC * TILE_KV_BYTES;         // 16 KB
   uint64_t* bars = reinterpret_cast<uint64_t*>(p_tile + TILE_P_BYTES);  // [0], [1] S buffers done, [2] O done
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3);
+  float* pmax = reinterpret_cast<float*>(bars + 4);   // [2 buffers][2 halves][TQ]: partial row maxima
 
   const int tid = threadIdx.x, warp = tid >> 5;
+  const int row = tid & (TQ - 1);        // query row of this thread (= its tensor-memory lane)
+  const int half = tid >> 7;             // which 32 of the 64 columns of a page this thread handles
+  constexpr int NT = 2 * TQ;             // threads of the block
   const int tile = blockIdx.x, h = blockIdx.y;
   const int qpk = p.heads / p.kv_heads;
   const int g = h / qpk;
   const int seq = tile_seq[tile], q0 = tile_q0[tile];
   const int n_new = sb.seq_new[seq], past = sb.seq_past[seq], start = sb.seq_start[seq];
   const int tok_valid = min(TQ, n_new - q0);
-  const bool row_ok = tid < tok_valid;
-  const int row_pos = row_ok ? past + q0 + tid : -1;
+  const bool row_ok = row < tok_valid;
+  const int row_pos = row_ok ? past + q0 + row : -1;
   const int last_pos = past + q0 + tok_valid - 1;
   const int n_blocks = last_pos / KEYS + 1;
   const int* pages = sb.pages + size_t(seq) * sb.pages_stride;
@@ -165,26 +169,26 @@ attention_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t lane_addr = tmem_base + (uint32_t(warp * 32) << 16);  // this warp's 32 lanes
+  const uint32_t lane_addr = tmem_base + (uint32_t((warp & 3) * 32) << 16) + half * 32;  // lanes of this warp, its columns
   const uint32_t tmem_o = tmem_base + 128;   // S buffers at columns [0, 64) and [64, 128), O at [128, 192)
 
   // Q tile: rows of the tile, zero beyond the valid tokens
   {
     const uint32_t qs = smem_u32(q_tile);
-    for (int i = tid; i < TQ * (D / 8); i += TQ) {
-      const int row = i / (D / 8), c = i % (D / 8);
-      if (row < tok_valid)
-        cp_async16(qs + swz<D>(row, c), q + (size_t(start + q0 + row) * p.heads + h) * D + c * 8);
+    for (int i = tid; i < TQ * (D / 8); i += NT) {
+      const int r = i / (D / 8), c = i % (D / 8);
+      if (r < tok_valid)
+        cp_async16(qs + swz<D>(r, c), q + (size_t(start + q0 + r) * p.heads + h) * D + c * 8);
       else
-        *reinterpret_cast<uint4*>(q_tile + swz<D>(row, c)) = make_uint4(0, 0, 0, 0);
+        *reinterpret_cast<uint4*>(q_tile + swz<D>(r, c)) = make_uint4(0, 0, 0, 0);
     }
   }
   auto load_block = [&](int b) {  // page b of the sequence into stage b % STAGES_TC; one commit group, maybe empty
     if (b < n_blocks) {
       const int page = pages[b];
       const int st = b % STAGES_TC;
-      load_page<D>(smem_u32(k_ring + st * TILE_KV_BYTES), k_pool + kv_offset(page, g, 0, p.kv_heads, D), tid, TQ);
-      load_page<D>(smem_u32(v_ring + st * TILE_KV_BYTES), v_pool + kv_offset(page, g, 0, p.kv_heads, D), tid, TQ);
+      load_page<D>(smem_u32(k_ring + st * TILE_KV_BYTES), k_pool + kv_offset(page, g, 0, p.kv_heads, D), tid, NT);
+      load_page<D>(smem_u32(v_ring + st * TILE_KV_BYTES), v_pool + kv_offset(page, g, 0, p.kv_heads, D), tid, NT);
     }
     cp_async_commit();
   };
@@ -219,19 +223,27 @@ attention_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
   }
 
   for (int i = 0; i < n_blocks; ++i) {
-    // (1) this thread's row of S_i
+    // (1) this thread's 32 columns of its row of S_i
     if (alive) alive = mbar_wait(bar_s + (i & 1) * 8, (i >> 1) & 1, error_flag, 1);
     tc_fence_after();
-    float s[KEYS];
-    {
-      float part[32];
-      tmem_ld32(lane_addr + (i & 1) * 64 + 0, part);
+    float s[32];
+    tmem_ld32(lane_addr + (i & 1) * 64, s);
+    // partial maximum of the visible scores; only pages that reach past some row's position need the test
+    float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+    if (i * KEYS + KEYS - 1 > past + q0 || !row_ok) {   // first part is uniform over the block
+      const int visible = row_pos - i * KEYS - half * 32;   // columns j <= visible are seen by this row
 #pragma unroll
-      for (int j = 0; j < 32; ++j) s[j] = part[j];
-      tmem_ld32(lane_addr + (i & 1) * 64 + 32, part);
+      for (int j = 0; j < 32; ++j) {
+        s[j] = (j <= visible) ? s[j] : -INFINITY;
+        mx[j & 3] = fmaxf(mx[j & 3], s[j]);
+      }
+    } else {
 #pragma unroll
-      for (int j = 0; j < 32; ++j) s[32 + j] = part[j];
+      for (int j = 0; j < 32; ++j) mx[j & 3] = fmaxf(mx[j & 3], s[j]);
     }
+    const float m_half = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+    float* pm = pmax + (i & 1) * 2 * TQ;
+    pm[half * TQ + row] = m_half;
     // (2) page i + 1 has landed: start S_{i+1} into the other S buffer; it runs under this softmax
     cp_async_wait<1>();
     proxy_fence_async();
@@ -241,21 +253,8 @@ attention_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
       tc_fence_after();
       issue_s(i + 1);
     }
-    // (3) maximum of the visible scores; only pages that reach past some row's position need the test
-    // four independent chains keep the maximum (and below, the sum) from being one long dependency
-    float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-    if (i * KEYS + KEYS - 1 > past + q0 || !row_ok) {   // first part is uniform over the block
-      const int visible = row_pos - i * KEYS;           // keys j <= visible are seen by this row
-#pragma unroll
-      for (int j = 0; j < KEYS; ++j) {
-        s[j] = (j <= visible) ? s[j] : -INFINITY;
-        mx[j & 3] = fmaxf(mx[j & 3], s[j]);
-      }
-    } else {
-#pragma unroll
-      for (int j = 0; j < KEYS; ++j) mx[j & 3] = fmaxf(mx[j & 3], s[j]);
-    }
-    const float m_blk = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+    // (3) the row's maximum from both halves
+    const float m_blk = fmaxf(m_half, pm[(half ^ 1) * TQ + row]);
     const float m_new = fmaxf(m_run, m_blk);
     const float corr = (m_run == -INFINITY) ? 0.f : fast_exp2((m_run - m_new) * sl2);
     const bool moved = (m_new != m_run) && (m_run != -INFINITY);
@@ -267,23 +266,20 @@ attention_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
       tc_fence_after();
     }
     load_block(i + 3);
-    // (5) rescale this row of O if any row of the warp moved its maximum
+    // (5) rescale this thread's 32 columns of its row of O if any row of the warp moved its maximum
     if (i > 0 && __any_sync(0xffffffffu, moved)) {
       float o[32];
+      tmem_ld32(lane_addr + 128, o);
 #pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        tmem_ld32(lane_addr + 128 + half * 32, o);
-#pragma unroll
-        for (int j = 0; j < 32; ++j) o[j] *= corr;
-        tmem_st32(lane_addr + 128 + half * 32, o);
-      }
+      for (int j = 0; j < 32; ++j) o[j] *= corr;
+      tmem_st32(lane_addr + 128, o);
       tmem_st_wait();
     }
     l_run *= corr;
-    // (6) P = exp2(S - max) as bfloat16 into the swizzled P tile, row tid
+    // (6) P = exp2(S - max) as bfloat16 into the swizzled P tile: row, chunks 4 half .. 4 half + 3
     float ls[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-    for (int c = 0; c < KEYS / 8; ++c) {
+    for (int c = 0; c < 4; ++c) {
       uint32_t w[4];
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
@@ -292,9 +288,9 @@ attention_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
         ls[e] += a + b;
         w[e] = pack_bf16(a, b);
       }
-      *reinterpret_cast<uint4*>(p_tile + swz<KEYS>(tid, c)) = make_uint4(w[0], w[1], w[2], w[3]);
+      *reinterpret_cast<uint4*>(p_tile + swz<KEYS>(row, half * 4 + c)) = make_uint4(w[0], w[1], w[2], w[3]);
     }
-    l_run += (ls[0] + ls[1]) + (ls[2] + ls[3]);
+    l_run += (ls[0] + ls[1]) + (ls[2] + ls[3]);   // this thread's half of the row sum
     proxy_fence_async();
     tc_fence_before();
     __syncthreads();
@@ -309,23 +305,24 @@ attention_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
     }
   }
   cp_async_wait<0>();
+  // the two halves of every row sum meet
+  pmax[half * TQ + row] = l_run;
+  __syncthreads();
+  const float l_row = l_run + pmax[(half ^ 1) * TQ + row];
   if (alive) alive = mbar_wait(bar_o, (n_blocks - 1) & 1, error_flag, 3);
   tc_fence_after();
   {
-    const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-    __nv_bfloat16* dst = out + (size_t(start + q0 + tid) * p.heads + h) * D;
+    const float inv = l_row > 0.f ? 1.f / l_row : 0.f;
+    __nv_bfloat16* dst = out + (size_t(start + q0 + row) * p.heads + h) * D + half * 32;
+    float o[32];
+    tmem_ld32(lane_addr + 128, o);
+    if (row_ok) {
 #pragma unroll
-    for (int half = 0; half < 2; ++half) {
-      float o[32];
-      tmem_ld32(lane_addr + 128 + half * 32, o);
-      if (row_ok) {
+      for (int c = 0; c < 4; ++c) {
+        uint32_t w[4];
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          uint32_t w[4];
-#pragma unroll
-          for (int e = 0; e < 4; ++e) w[e] = pack_bf16(o[c * 8 + 2 * e] * inv, o[c * 8 + 2 * e + 1] * inv);
-          *reinterpret_cast<uint4*>(dst + half * 32 + c * 8) = make_uint4(w[0], w[1], w[2], w[3]);
-        }
+        for (int e = 0; e < 4; ++e) w[e] = pack_bf16(o[c * 8 + 2 * e] * inv, o[c * 8 + 2 * e + 1] * inv);
+        *reinterpret_cast<uint4*>(dst + c * 8) = make_uint4(w[0], w[1], w[2], w[3]);
       }
     }
   }
@@ -349,7 +346,7 @@ PTB_API int ptb_attention_tc(const void* q, const void* k_pool, const void* v_po
   if (n_tiles <= 0) return PTB_OK;
   if (head_dim != D || heads <= 0 || kv_heads <= 0 || heads % kv_heads != 0 || heads > 65535 || error_flag == nullptr)
     return PTB_ERR_SIZE;
-  const size_t smem = 1024 + TILE_Q_BYTES + 2 * STAGES_TC * TILE_KV_BYTES + TILE_P_BYTES + 64;
+  const size_t smem = 1024 + TILE_Q_BYTES + 2 * STAGES_TC * TILE_KV_BYTES + TILE_P_BYTES + 64 + 4 * TQ * sizeof(float);
   static bool configured = false;
   if (!configured) {
     if (cudaFuncSetAttribute(attention_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess)
@@ -359,7 +356,7 @@ PTB_API int ptb_attention_tc(const void* q, const void* k_pool, const void* v_po
   TcParams p;
   p.heads = heads; p.kv_heads = kv_heads; p.scale = scale;
   dim3 grid(n_tiles, heads);
-  attention_tc_kernel<<<grid, TQ, smem, stream>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool,
+  attention_tc_kernel<<<grid, 2 * TQ, smem, stream>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool,
                                                   (const __nv_bfloat16*)v_pool, (__nv_bfloat16*)out, *sb, tile_seq,
                                                   tile_q0, p, error_flag);
   return launch_status();

@@ -66,15 +66,42 @@ __global__ void norm_kernel(const T* __restrict__ x, const T* __restrict__ adden
   __shared__ float scratch[32];
   const size_t base = size_t(blockIdx.x) * width;
   float s = 0.f;
-  for (int i = threadIdx.x; i < width; i += blockDim.x) {
-    float v = to_f(x[base + i]);
-    if (addend) {
-      const T r = from_f<T>(v + to_f(addend[base + i]));
-      sum_out[base + i] = r;
-      v = to_f(r);
+  // bfloat16 rows whose width is a multiple of 8 move in 16-byte words (row starts are then aligned)
+  const bool vec = sizeof(T) == 2 && width % 8 == 0 && aligned16(x) && aligned16(y1) &&
+                   (!addend || (aligned16(addend) && aligned16(sum_out))) && (!gain2 || aligned16(y2));
+  if (vec) {
+    const uint4* xv = reinterpret_cast<const uint4*>(x + base);
+    const uint4* av = addend ? reinterpret_cast<const uint4*>(addend + base) : nullptr;
+    uint4* sv = addend ? reinterpret_cast<uint4*>(sum_out + base) : nullptr;
+    for (int i = threadIdx.x; i < width / 8; i += blockDim.x) {
+      float f[8];
+      unpack_bf16x8(xv[i], f);
+      if (av) {
+        float g[8];
+        unpack_bf16x8(av[i], g);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) f[e] += g[e];
+        const uint4 r = pack_bf16x8(f);
+        sv[i] = r;
+        unpack_bf16x8(r, f);
+      }
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        row[i * 8 + e] = f[e];
+        s += f[e];
+      }
     }
-    row[i] = v;
-    s += v;
+  } else {
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+      float v = to_f(x[base + i]);
+      if (addend) {
+        const T r = from_f<T>(v + to_f(addend[base + i]));
+        sum_out[base + i] = r;
+        v = to_f(r);
+      }
+      row[i] = v;
+      s += v;
+    }
   }
   float mean = 0.f;
   if (kind == 0) mean = block_sum(s, scratch) / float(width);
@@ -85,6 +112,29 @@ __global__ void norm_kernel(const T* __restrict__ x, const T* __restrict__ adden
   }
   const float var = block_sum(q, scratch) / float(width);
   const float rstd = 1.0f / sqrtf(var + eps);
+  if (vec) {
+    uint4* o1 = reinterpret_cast<uint4*>(y1 + base);
+    uint4* o2 = gain2 ? reinterpret_cast<uint4*>(y2 + base) : nullptr;
+    for (int i = threadIdx.x; i < width / 8; i += blockDim.x) {
+      float n[8], a[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        n[e] = (row[i * 8 + e] - mean) * rstd;
+        a[e] = n[e] * gain1[i * 8 + e];
+        if (bias1) a[e] += bias1[i * 8 + e];
+      }
+      o1[i] = pack_bf16x8(a);
+      if (o2) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          a[e] = n[e] * gain2[i * 8 + e];
+          if (bias2) a[e] += bias2[i * 8 + e];
+        }
+        o2[i] = pack_bf16x8(a);
+      }
+    }
+    return;
+  }
   for (int i = threadIdx.x; i < width; i += blockDim.x) {
     const float n = (row[i] - mean) * rstd;
     float a = n * gain1[i];
@@ -154,10 +204,48 @@ __global__ void bias_act_kernel(T* __restrict__ y, const float* __restrict__ bia
   }
 }
 
+// GELU (erf form) for values that are rounded to bfloat16 afterwards: erf by the rational
+// approximation 7.1.26 of Abramowitz and Stegun (absolute error below 1.5e-7, three orders of
+// magnitude under bfloat16's resolution), one reciprocal and one exp2 instead of erff's long
+// polynomial. The float32 kernels keep erff.
+__device__ __forceinline__ float gelu_erf_for_bf16(float v) {
+  const float z = fabsf(v) * 0.70710678118654752440f;
+  const float t = __frcp_rn(fmaf(0.3275911f, z, 1.0f));
+  float poly = fmaf(1.061405429f, t, -1.453152027f);
+  poly = fmaf(poly, t, 1.421413741f);
+  poly = fmaf(poly, t, -0.284496736f);
+  poly = fmaf(poly, t, 0.254829592f);
+  float e;
+  asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(e) : "f"(-z * z * 1.4426950408889634f));
+  const float erf_abs = fmaf(-poly * t, e, 1.0f);
+  return 0.5f * v * (1.0f + copysignf(erf_abs, v));
+}
+
+// the same, eight bfloat16 values per thread and step (width a multiple of 8, 16-byte aligned rows)
+__global__ void bias_act_bf16x8_kernel(uint4* __restrict__ y, const float* __restrict__ bias, size_t total8, int width,
+                                       int act) {
+  const size_t stride = size_t(gridDim.x) * blockDim.x;
+  for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total8; i += stride) {
+    float f[8];
+    unpack_bf16x8(y[i], f);
+    const int col = int((i * 8) % width);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const float v = bias ? f[e] + bias[col + e] : f[e];
+      f[e] = (act == 1) ? gelu_erf_for_bf16(v) : activate(v, act);
+    }
+    y[i] = pack_bf16x8(f);
+  }
+}
+
 PTB_API int ptb_bias_act(int dtype, void* y, const float* bias, int rows, int width, int act, cudaStream_t stream) {
   const size_t total = size_t(rows) * width;
   if (total == 0) return PTB_OK;
   if (act < 0 || act > 3) return PTB_ERR_SIZE;
+  if (dtype == PTB_BF16 && width % 8 == 0 && aligned16(y)) {
+    bias_act_bf16x8_kernel<<<grid_for(total / 8, 256), 256, 0, stream>>>((uint4*)y, bias, total / 8, width, act);
+    return launch_status();
+  }
   const int threads = 256;
   const int blocks = grid_for(total, threads);
   if (dtype == PTB_F32)
@@ -181,9 +269,32 @@ __global__ void residual_kernel(const T* __restrict__ x, const T* __restrict__ a
   }
 }
 
+__global__ void residual_bf16x8_kernel(const uint4* __restrict__ x, const uint4* __restrict__ a,
+                                       const uint4* __restrict__ b, uint4* __restrict__ out, size_t total8) {
+  const size_t stride = size_t(gridDim.x) * blockDim.x;
+  for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total8; i += stride) {
+    float fx[8], fa[8], fb[8];
+    unpack_bf16x8(x[i], fx);
+    unpack_bf16x8(a[i], fa);
+    if (b) {
+      unpack_bf16x8(b[i], fb);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) fa[e] += fb[e];
+    }
+#pragma unroll
+    for (int e = 0; e < 8; ++e) fx[e] += fa[e];
+    out[i] = pack_bf16x8(fx);
+  }
+}
+
 PTB_API int ptb_residual(int dtype, const void* x, const void* a, const void* b, void* out, long long total,
                          cudaStream_t stream) {
   if (total <= 0) return PTB_OK;
+  if (dtype == PTB_BF16 && total % 8 == 0 && aligned16(x) && aligned16(a) && aligned16(b) && aligned16(out)) {
+    residual_bf16x8_kernel<<<grid_for(size_t(total) / 8, 256), 256, 0, stream>>>(
+        (const uint4*)x, (const uint4*)a, (const uint4*)b, (uint4*)out, size_t(total) / 8);
+    return launch_status();
+  }
   const int threads = 256;
   const int blocks = grid_for(size_t(total), threads);
   if (dtype == PTB_F32)
