@@ -77,7 +77,7 @@ def lib():
                      "ptb_linear_f32", "ptb_split_rotate_store", "ptb_attention_generic", "ptb_sample",
                      "ptb_attention_generic_tile_rows", "ptb_attention_mma", "ptb_attention_mma_supports",
                      "ptb_skinny_linear", "ptb_skinny_linear_max_rows", "ptb_skinny_linear_k_multiple",
-                     "ptb_rope_table", "ptb_attention_decode", "ptb_attention_tc", "ptb_attention_tc_supports",
+                     "ptb_rope_table", "ptb_attention_decode", "ptb_stream_linear", "ptb_stream_linear_max_rows", "ptb_attention_tc", "ptb_attention_tc_supports",
                      "ptb_attention_tc_tile_tokens"):
             getattr(L, name).restype = ctypes.c_int
         _configured = True
@@ -364,6 +364,36 @@ def skinny_linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor]
     ybf, yf = (y, None) if out_dtype == torch.bfloat16 else (None, y)
     _check(lib().ptb_skinny_linear(_ptr(x), _ptr(w), _ptr(bias), _ptr(add), _ptr(ybf), _ptr(yf), m, n, k,
                                    ACTIVATIONS[act], _stream(x)), "skinny_linear")
+    return y
+
+
+STREAM_MAX_ROWS = 16  # ptb_stream_linear_max_rows()
+_sm_count = {}
+
+
+def stream_linear_takes(rows: int, k: int) -> bool:
+    return 0 < rows <= STREAM_MAX_ROWS and k % 32 == 0
+
+
+def stream_linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None, act: str = "none",
+                  add: Optional[torch.Tensor] = None, out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+    """act(x @ w.T + bias) + add for up to 16 rows of bfloat16 x; the weights go through a ring of
+    shared-memory stages filled by bulk asynchronous copies. Result bfloat16 or float32."""
+    _need_cuda(x, w, bias, add)
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or (add is not None and add.dtype != torch.bfloat16):
+        raise KernelError("stream_linear takes bfloat16 x, w and add")
+    m, k = x.shape
+    n = w.shape[0]
+    if w.shape[1] != k or (add is not None and tuple(add.shape) != (m, n)):
+        raise KernelError(f"stream_linear: shapes x {list(x.shape)}, w {list(w.shape)} do not fit")
+    dev = x.device
+    if dev not in _sm_count:
+        _sm_count[dev] = torch.cuda.get_device_properties(dev).multi_processor_count
+    y = torch.empty((m, n), dtype=out_dtype, device=dev)
+    ybf, yf = (y, None) if out_dtype == torch.bfloat16 else (None, y)
+    _check(lib().ptb_stream_linear(_ptr(x), _ptr(w), _ptr(bias), _ptr(add), _ptr(ybf), _ptr(yf), m, n, k,
+                                   ACTIVATIONS[act], _sm_count[dev], _ptr(error_flag(dev)), _stream(x)),
+           "stream_linear")
     return y
 
 

@@ -160,3 +160,38 @@ def test_skinny_linear_refuses_what_it_does_not_take(K):
         K.skinny_linear(rnd(4, 48, dtype=torch.bfloat16), rnd(16, 48, dtype=torch.bfloat16))
     with pytest.raises(KernelError):
         K.skinny_linear(rnd(4, 64), rnd(16, 64))
+
+
+@pytest.mark.parametrize("m", [1, 5, 8, 9, 16])
+@pytest.mark.parametrize("n,k", [(100, 64), (4672, 4544), (71, 96), (18176 // 2, 4544), (33, 18176 // 4)])
+@pytest.mark.parametrize("act,bias,add,f32", [("none", False, False, False), ("gelu", True, False, False),
+                                               ("none", True, True, False), ("relu", False, True, True)])
+def test_stream_linear(K, m, n, k, act, bias, add, f32):
+    bf = torch.bfloat16
+    x, w = rnd(m, k, dtype=bf, seed=1), rnd(n, k, dtype=bf, seed=2, scale=0.05)
+    b = rnd(n, seed=3) if bias else None
+    a = rnd(m, n, dtype=bf, seed=4) if add else None
+    assert K.stream_linear_takes(m, k)
+    ref = x.double().cpu() @ w.double().cpu().T
+    if bias:
+        ref = ref + b.double().cpu()
+    if act != "none":
+        ref = plain.activation(ref, act)
+    if add:
+        ref = ref + a.double().cpu()
+    out = K.stream_linear(x, w, b, act, a, out_dtype=torch.float32 if f32 else bf)
+    K.check_device_errors("cuda")
+    if f32:
+        torch.testing.assert_close(out.double().cpu(), ref, atol=1e-3, rtol=1e-4)
+    else:
+        torch.testing.assert_close(out.double().cpu(), ref, **tol(bf))
+
+
+def test_stream_linear_refuses_what_it_does_not_take(K):
+    from pytorch_transformers_b200.kernels import KernelError
+    assert K.lib().ptb_stream_linear_max_rows() == K.STREAM_MAX_ROWS
+    assert not K.stream_linear_takes(17, 64) and not K.stream_linear_takes(4, 48)
+    with pytest.raises(KernelError):
+        K.stream_linear(rnd(17, 64, dtype=torch.bfloat16), rnd(16, 64, dtype=torch.bfloat16))
+    with pytest.raises(KernelError):
+        K.stream_linear(rnd(4, 48, dtype=torch.bfloat16), rnd(16, 48, dtype=torch.bfloat16))
