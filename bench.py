@@ -30,6 +30,16 @@ FALCON_7B = dict(vocab_size=65024, hidden_size=4544, num_hidden_layers=32, num_a
                  multi_query=True, parallel_attn=True, new_decoder_architecture=False, bias=False, alibi=False,
                  rope_theta=10000.0, layer_norm_epsilon=1e-5, max_position_embeddings=2048,
                  tie_word_embeddings=True, activation="gelu")
+# the other two shapes that the reference's Falcon family has (for `--only decode --shape ...`)
+FALCON_11B = dict(vocab_size=65024, hidden_size=4096, num_hidden_layers=60, num_attention_heads=32, num_kv_heads=8,
+                  new_decoder_architecture=True, num_ln_in_parallel_attn=1, ffn_hidden_size=16384,
+                  rope_theta=500042.0, bias=False, alibi=False, layer_norm_epsilon=1e-5,
+                  max_position_embeddings=8192, tie_word_embeddings=True, activation="gelu")
+FALCON_40B = dict(vocab_size=65024, hidden_size=8192, num_hidden_layers=60, num_attention_heads=128, num_kv_heads=8,
+                  new_decoder_architecture=True, ffn_hidden_size=32768, rope_theta=10000.0, bias=False, alibi=False,
+                  layer_norm_epsilon=1e-5, max_position_embeddings=2048, tie_word_embeddings=False,
+                  activation="gelu")
+SHAPES = {"7b": FALCON_7B, "11b": FALCON_11B, "40b": FALCON_40B}
 CONTEXT = 2048
 PREFILL_TOKENS = 2048
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
@@ -130,8 +140,9 @@ def run_ours(args):
     from pytorch_transformers_b200.sampling import DeviceSelector
 
     torch.cuda.set_device(0)
-    layers = args.layers or FALCON_7B["num_hidden_layers"]
-    cfg = ptb.FalconConfig.from_dict(dict(FALCON_7B, num_hidden_layers=layers))
+    shape = SHAPES[args.shape]
+    layers = args.layers or shape["num_hidden_layers"]
+    cfg = ptb.FalconConfig.from_dict(dict(shape, num_hidden_layers=layers))
     model = ptb.AutoModelForCausalLM.from_config(cfg, seed=0, dtype="bfloat16", device="cuda:0")
     pk = peaks()
     gen = torch.Generator().manual_seed(0)
@@ -185,9 +196,12 @@ def run_ours(args):
         model.use_graphs = False
     if args.only == "decode":
         ms, launches, ctx_mid, _ = decode_run(args.batch, args.steps, args.warmup)
-        print(json.dumps({"only": "decode", "batch": args.batch, "layers": layers, "ms_per_step": round(ms, 4),
-                          "launches_per_step": launches / args.steps,
-                          "GBps": round(decode_bytes(FALCON_7B, layers, args.batch, ctx_mid) / ms / 1e6, 1)}))
+        kv_bytes = args.batch * ctx_mid * layers * 2 * cfg.kv_heads_eff * cfg.head_dim * 2
+        print(json.dumps({"only": "decode", "shape": args.shape, "batch": args.batch, "layers": layers,
+                          "ms_per_step": round(ms, 4), "launches_per_step": launches / args.steps,
+                          "GBps": round((model.weight_bytes() - (0 if cfg.tie_word_embeddings else
+                                                                cfg.vocab_size * cfg.hidden_size * 2) + kv_bytes)
+                                        / ms / 1e6, 1)}))
         return 0
 
     # ---- prefill of 2,048 tokens (one prompt) ----
@@ -360,12 +374,16 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--only", default="", choices=["", "decode", "prefill"],
                     help="run one section only and print its numbers (for profilers)")
+    ap.add_argument("--shape", default="7b", choices=sorted(SHAPES), help="model shape for --only decode")
     ap.add_argument("--no-graphs", action="store_true", help="launch every kernel of a decode step itself")
     args = ap.parse_args()
     if args.gpus != 1:
         print(f"bench.py measures one GPU: this library is a single-GPU engine, --gpus {args.gpus} is not run")
         return 2
     args.warmup = max(3, args.warmup)
+    if args.shape != "7b" and args.only != "decode":
+        print("--shape other than 7b goes with --only decode (the headline is measured on the 7B shape)")
+        return 2
     if args.impl == "reference":
         return run_reference(args)
     return run_ours(args)

@@ -1,7 +1,8 @@
 // True float32 linear layer on the CUDA cores: y[m, n] = act(sum_k x[m, k] * w[n, k] + bias[n]).
 // No tensor cores and no reduced-precision mode: every product and sum is an IEEE float32 FMA.
-// Each output element is accumulated by one thread over k = 0 .. K-1 in ascending order, so a
-// row's result does not depend on how many other rows are in the launch or on the tiling.
+// Each output element is accumulated by one thread over k in ascending order (16 products at a
+// time, then into the total), so a row's result does not depend on how many other rows are in the
+// launch or on the tiling, and the rounding error stays small for K in the tens of thousands.
 #include "common.cuh"
 
 namespace {
@@ -44,6 +45,13 @@ __global__ void __launch_bounds__(256) linear_f32_kernel(const float* __restrict
       ws[lk + q][lrow] = (gn < N && k < K) ? w[size_t(gn) * K + k] : 0.f;
     }
     __syncthreads();
+    // two levels of summation: the 16 products of this step are summed on their own and then added
+    // to the total, so the rounding error grows with K / 16 + 16 instead of with K
+    float part[TM][TN];
+#pragma unroll
+    for (int i = 0; i < TM; ++i)
+#pragma unroll
+      for (int j = 0; j < TN; ++j) part[i][j] = 0.f;
 #pragma unroll
     for (int k = 0; k < BK; ++k) {
       float a[TM], b[TN];
@@ -54,8 +62,12 @@ __global__ void __launch_bounds__(256) linear_f32_kernel(const float* __restrict
 #pragma unroll
       for (int i = 0; i < TM; ++i)
 #pragma unroll
-        for (int j = 0; j < TN; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+        for (int j = 0; j < TN; ++j) part[i][j] = fmaf(a[i], b[j], part[i][j]);
     }
+#pragma unroll
+    for (int i = 0; i < TM; ++i)
+#pragma unroll
+      for (int j = 0; j < TN; ++j) acc[i][j] += part[i][j];
     __syncthreads();
   }
 #pragma unroll

@@ -191,7 +191,7 @@ class CausalLM:
         ctx.commit()
         return entry["out"].clone()   # the graph's own output buffer is rewritten by the next replay
 
-    TWO_STREAM_MAX_TOKENS = 32
+    TWO_STREAM_MAX_TOKENS = 16
 
     def forward(self, ctx: StepContext) -> torch.Tensor:
         k = self.build.kernels
@@ -215,6 +215,6 @@ class CausalLM:
         k = self.build.kernels
         if self.dtype == torch.float32:
             return k.linear_f32(rows, self.head)
-        if k.skinny_linear_takes(rows.shape[0], rows.shape[1]):
+        if k.skinny_linear_preferred(rows.shape[0], rows.shape[1]):
             return k.skinny_linear(rows, self.head, out_dtype=torch.float32)
         return k.matmul_nt(rows, self.head, out_dtype=torch.float32)

@@ -345,8 +345,15 @@ SKINNY_MAX_ROWS = 32   # ptb_skinny_linear_max_rows()
 SKINNY_K_MULTIPLE = 32  # ptb_skinny_linear_k_multiple()
 
 
+SKINNY_BEST_ROWS = 16   # beyond this the library product is faster (measured on B200)
+
+
 def skinny_linear_takes(rows: int, k: int) -> bool:
     return 0 < rows <= SKINNY_MAX_ROWS and k % SKINNY_K_MULTIPLE == 0
+
+
+def skinny_linear_preferred(rows: int, k: int) -> bool:
+    return 0 < rows <= SKINNY_BEST_ROWS and k % SKINNY_K_MULTIPLE == 0
 
 
 def skinny_linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None, act: str = "none",

@@ -78,7 +78,8 @@ class Attention(Part):
 
     def _decode_splits(self, ctx, hpk):
         """Blocks per (sequence, head chunk) for steps of single tokens: enough to put about two
-        blocks on every SM, each with at least two pages of keys."""
+        blocks on every SM, each with at least two pages of keys (measured: more, smaller blocks
+        are slower at batch 64, clusters of 8 are harder to place than clusters of 4)."""
         chunks = (self.q_per_kv + hpk - 1) // hpk
         blocks = ctx.n_seqs * self.kv_heads * chunks
         pages = ctx.pages_hint

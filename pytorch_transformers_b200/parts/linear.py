@@ -32,7 +32,7 @@ def linear(kernels, x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.
             and kernels.stream_linear_takes(rows, k)):
         # wide outputs: the TMA ring keeps more bytes in flight than register loads can
         return kernels.stream_linear(x, weight, bias, act, add)
-    if kernels.skinny_linear_takes(rows, k):
+    if kernels.skinny_linear_preferred(rows, k):
         return kernels.skinny_linear(x, weight, bias, act, add)
     y = kernels.matmul_nt(x, weight)
     if bias is not None or act != "none":

@@ -227,3 +227,33 @@ def test_decoding_across_a_bucket_of_pages_and_with_a_shrinking_batch(loaded, ca
     L.model.step(cache3, [s], [reqs[2][:lengths[2]]], want="none")
     graph_step = L.model.step(cache3, [s], [[reqs[2][lengths[2]]]], want="last")
     assert torch.equal(plain_step, graph_step)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_falcon_7b_widths_two_layers(tmp_path, dtype):
+    """The real widths of Falcon-7B (hidden 4544 = 71 heads of 64, one K/V head, fused projection
+    of 4672 rows, feed-forward 18176) in a two-layer model with a small vocabulary: prompts in one
+    step, then tokens one by one, against the plain implementation."""
+    import pytorch_transformers_b200 as ptb
+    cfg = tm.config_dict("A", hidden_size=4544, num_attention_heads=71, ffn_hidden_size=18176, vocab_size=1000,
+                         max_position_embeddings=2048)
+    rng = np.random.Generator(np.random.PCG64(77))
+    weights = {}
+    for name, shape in tm.tensor_shapes(cfg).items():
+        w = rng.standard_normal(shape, dtype=np.float32) * np.float32(0.02)
+        weights[name] = w + np.float32(1.0) if (name.endswith(".weight") and len(shape) == 1) else w
+    folder = tm.write_model_folder(str(tmp_path / "wide"), cfg, weights, bf16=(dtype == "bfloat16"))
+    model = ptb.AutoModelForCausalLM.from_pretrained(folder, dtype=dtype)
+    raw, w = plain.load_folder(folder, torch.float64)
+    g = np.random.Generator(np.random.PCG64(5))
+    reqs = [g.integers(0, 1000, size=n).tolist() for n in (150, 9)]
+    refs = [plain.model_logits(ids, raw, w) for ids in reqs]
+    cache = model.new_cache(512)
+    slots = [cache.open() for _ in reqs]
+    heads = [140, 3]
+    out = model.step(cache, slots, [r[:h] for r, h in zip(reqs, heads)], want="last")
+    for t in range(6):
+        for row, i in enumerate(range(2)):
+            close(out[row], refs[i][heads[i] + t - 1], dtype, f"7B widths request {i} step {t}")
+        out = model.step(cache, slots, [[reqs[i][heads[i] + t]] for i in range(2)], want="last")
+    model.build.kernels.check_device_errors("cuda")
