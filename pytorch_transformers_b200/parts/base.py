@@ -17,7 +17,8 @@ engine.batch.StepContext of the running step; ``x`` is [tokens, hidden] in the m
                      ``state_need() -> StateNeed | None``. ``entry`` is the ScheduleEntry being
                      run: it names the cache entry to read and whether to write it.
 * ``feed_forward``:  ``forward(x, ctx) -> y``.
-* ``block``:         ``forward(x, ctx, entry) -> x'`` from its child parts.
+* ``block``:         ``forward(x, ctx, entry) -> x'`` from its child parts; ``x`` and ``x'`` may be a
+                     ``DeferredSum`` (two terms whose sum the next norm forms); ``resolve`` gives the tensor.
 
 Every part declares its parameters in ``param_decls()`` (logical name -> ParamDecl) and
 receives them in ``bind(tensors)``.

@@ -37,8 +37,9 @@ class ParallelBlock(Part):
         side = getattr(ctx, "side_stream", None)
         two_streams = (side is not None and getattr(self.mixer, "fuses_add", False)
                        and getattr(self.feed_forward, "fuses_add", False) and hasattr(self.norm_mixer, "forward_sum"))
-        if isinstance(x, DeferredSum) and two_streams:
-            # join the previous block's two branches and norm the sum in one kernel
+        can_join = hasattr(self.norm_mixer, "forward_sum")
+        if isinstance(x, DeferredSum) and can_join:
+            # join the previous block's two terms and norm the sum in one kernel
             x.join(x.base.device)
             outs = self.norm_mixer.forward_sum(x.base, x.pending, self.norm_ff)
             ctx.keep_alive.append((x.base, x.pending))
@@ -54,7 +55,9 @@ class ParallelBlock(Part):
         if two_streams:
             return self._forward_two_streams(x, a, m, ctx, entry, side)
         mixed = _plus(k, self.mixer, x, a, ctx, entry)           # x + mixer
-        return _plus(k, self.feed_forward, mixed, m, ctx)        # (x + mixer) + feed-forward
+        # (x + mixer) + feed-forward: the last sum is left to whoever needs the value (the next
+        # block's norm adds and norms in one kernel; the model's end adds)
+        return DeferredSum(mixed, self.feed_forward.forward(m, ctx))
 
     def _forward_two_streams(self, x, a, m, ctx, entry, side):
         """Steps of a few tokens are bound by the read of the weights, and the mixer's chain of small
