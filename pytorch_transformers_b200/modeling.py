@@ -57,10 +57,13 @@ class GenerateOutput:
 
 
 class _CacheStepper:
-    """The generation loop's view of a model and a cache."""
+    """The generation loop's view of a model and a cache. Prompts that together exceed
+    ``max_step_tokens`` are fed in several steps (whole prompts grouped, a longer prompt cut into
+    chunks) so that a step's activations stay bounded; the logits of each prompt's last token come
+    back in the order asked for, as from one step."""
 
-    def __init__(self, model: CausalLM, cache: Cache):
-        self.model, self.cache = model, cache
+    def __init__(self, model: CausalLM, cache: Cache, max_step_tokens: int = 16384):
+        self.model, self.cache, self.max_step_tokens = model, cache, max(1, int(max_step_tokens))
 
     def open(self) -> int:
         return self.cache.open()
@@ -69,7 +72,38 @@ class _CacheStepper:
         self.cache.close(slot)
 
     def step(self, slots, token_lists):
-        return self.model.step(self.cache, slots, token_lists, want="last")
+        total = sum(len(t) for t in token_lists)
+        if total <= self.max_step_tokens:
+            return self.model.step(self.cache, slots, token_lists, want="last")
+        rows = [None] * len(slots)
+        group_slots, group_tokens, group_rows, used = [], [], [], 0
+
+        def flush():
+            nonlocal group_slots, group_tokens, group_rows, used
+            if group_slots:
+                out = self.model.step(self.cache, group_slots, group_tokens, want="last")
+                for r, i in enumerate(group_rows):
+                    if i is not None:
+                        rows[i] = out[r]
+            group_slots, group_tokens, group_rows, used = [], [], [], 0
+
+        for i, (slot, toks) in enumerate(zip(slots, token_lists)):
+            pos = 0
+            while pos < len(toks):
+                room = self.max_step_tokens - used
+                if room == 0:
+                    flush()
+                    room = self.max_step_tokens
+                piece = toks[pos:pos + room]
+                pos += len(piece)
+                group_slots.append(slot)
+                group_tokens.append(piece)
+                group_rows.append(i if pos == len(toks) else None)   # only a prompt's end gives its logits
+                used += len(piece)
+                if pos < len(toks):
+                    flush()   # the same slot cannot appear twice in one step
+        flush()
+        return torch.stack(rows)
 
 
 class PreTrainedCausalLM(CausalLM):
@@ -111,7 +145,7 @@ class PreTrainedCausalLM(CausalLM):
 
     @torch.no_grad()
     def generate(self, inputs=None, generation_config: Optional[GenerationConfig] = None, *, input_ids=None,
-                 attention_mask=None, streamer=None, max_batch_size: int = 64,
+                 attention_mask=None, streamer=None, max_batch_size: int = 64, max_step_tokens: int = 16384,
                  on_token: Optional[Callable[[int, int], None]] = None, **kwargs):
         if inputs is None:
             inputs = input_ids
@@ -164,7 +198,7 @@ class PreTrainedCausalLM(CausalLM):
             if on_token is not None:
                 on_token(r, tok)
 
-        results = run_generation(_CacheStepper(self, cache), selector, expanded, opts, budget, max_batch,
+        results = run_generation(_CacheStepper(self, cache, max_step_tokens), selector, expanded, opts, budget, max_batch,
                                  on_token=_on_token if on_token is not None else None,
                                  keep_logits=opts.output_logits)
         self.build.kernels.check_device_errors(self.device)

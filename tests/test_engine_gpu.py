@@ -257,3 +257,17 @@ def test_falcon_7b_widths_two_layers(tmp_path, dtype):
             close(out[row], refs[i][heads[i] + t - 1], dtype, f"7B widths request {i} step {t}")
         out = model.step(cache, slots, [[reqs[i][heads[i] + t]] for i in range(2)], want="last")
     model.build.kernels.check_device_errors("cuda")
+
+
+@pytest.mark.parametrize("case", ["B", "E"])
+def test_long_prompt_batches_are_fed_in_several_steps(loaded, case):
+    L = loaded(case, "float32")
+    prompts = tm.prompts(L.name, (70, 3, 41, 150, 9), seed=19)
+    whole = L.model.generate(prompts, max_new_tokens=5, eos_token_id=None, return_dict_in_generate=True,
+                             output_logits=True)
+    for limit in (64, 100, 7):
+        cut = L.model.generate(prompts, max_new_tokens=5, eos_token_id=None, max_step_tokens=limit,
+                               return_dict_in_generate=True, output_logits=True)
+        assert cut.sequences == whole.sequences
+        for a, b in zip(cut.logits, whole.logits):
+            torch.testing.assert_close(a, b, atol=1e-5, rtol=1e-4)
