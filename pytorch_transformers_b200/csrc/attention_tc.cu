@@ -1,8 +1,10 @@
 // Prompt attention on the fifth-generation tensor cores (tcgen05) with the accumulators in tensor
 // memory, for head size 64, bfloat16, causal, over the paged cache.
 //
-// One block = 128 consecutive new tokens of one sequence x one query head; 256 threads: threads t and
-// t + 128 share query row t (tensor-memory lane t), each taking 32 of a page's 64 columns. Keys are walked one cache page (64 keys) at a time:
+// One block = 128 consecutive new tokens of one sequence x one query head. 256 softmax threads: threads t
+// and t + 128 share query row t (tensor-memory lane t), each taking 32 of a page's 64 columns; they also
+// copy the pages. One more warp's first lane issues every matrix instruction. The roles meet only at
+// mbarriers (page landed, S written, P written, O updated): there is no block-wide barrier in the loop. Keys are walked one cache page (64 keys) at a time:
 //
 //   S = Q K^T      tcgen05.mma  M=128 N=64 K=64   A = Q  (shared, K-major, 128-byte swizzle)
 //                                                 B = K page (shared, K-major, 128-byte swizzle)
@@ -122,7 +124,16 @@ struct TcParams {
   float scale;
 };
 
-__global__ void __launch_bounds__(2 * TQ)
+constexpr int SOFTMAX_THREADS = 2 * TQ;             // two threads per query row
+constexpr int BLOCK_THREADS = SOFTMAX_THREADS + 32;  // and one warp whose first lane issues the matrix instructions
+
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
+}
+// barrier among the 64 threads of two warps (ids 1..4 are used)
+__device__ __forceinline__ void pair_sync(int id) { asm volatile("bar.sync %0, 64;\n" ::"r"(id) : "memory"); }
+
+__global__ void __launch_bounds__(BLOCK_THREADS)
 attention_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_pool,
                     const __nv_bfloat16* __restrict__ v_pool, __nv_bfloat16* __restrict__ out, StepBatch sb,
                     const int* __restrict__ tile_seq, const int* __restrict__ tile_q0, TcParams p,
@@ -131,17 +142,18 @@ attention_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
   // 1024-byte alignment: the swizzle pattern is a function of address bits 4..9
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
   unsigned char* q_tile = smem;                                       // 16 KB
-  unsigned char* k_ring = q_tile + TILE_Q_BYTES;                      // 3 x 8 KB
-  unsigned char* v_ring = k_ring + STAGES_TC * TILE_KV_BYTES;         // 3 x 8 KB
+  unsigned char* k_ring = q_tile + TILE_Q_BYTES;                      // STAGES_TC x 8 KB
+  unsigned char* v_ring = k_ring + STAGES_TC * TILE_KV_BYTES;         // STAGES_TC x 8 KB
   unsigned char* p_tile = v_ring + STAGES_TC * TILE_KV_BYTES;         // 16 KB
-  uint64_t* bars = reinterpret_cast<uint64_t*>(p_tile + TILE_P_BYTES);  // [0], [1] S buffers done, [2] O done
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3);
-  float* pmax = reinterpret_cast<float*>(bars + 4);   // [2 buffers][2 halves][TQ]: partial row maxima
+  // barriers: [0], [1] S buffer written; [2] O updated; [3] P written; [4 ..] page landed, per stage
+  uint64_t* bars = reinterpret_cast<uint64_t*>(p_tile + TILE_P_BYTES);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 4 + STAGES_TC);
+  float* pmax = reinterpret_cast<float*>(tmem_slot + 2);   // [2 buffers][2 halves][TQ]: partial row maxima
 
-  const int tid = threadIdx.x, warp = tid >> 5;
-  const int row = tid & (TQ - 1);        // query row of this thread (= its tensor-memory lane)
-  const int half = tid >> 7;             // which 32 of the 64 columns of a page this thread handles
-  constexpr int NT = 2 * TQ;             // threads of the block
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const bool mma_warp = warp == SOFTMAX_THREADS / 32;
+  const int row = tid & (TQ - 1);        // query row of a softmax thread (= its tensor-memory lane)
+  const int half = (tid >> 7) & 1;       // which 32 of the 64 columns of a page it handles
   const int tile = blockIdx.x, h = blockIdx.y;
   const int qpk = p.heads / p.kv_heads;
   const int g = h / qpk;
@@ -154,164 +166,174 @@ attention_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
   const int n_blocks = last_pos / KEYS + 1;
   const int* pages = sb.pages + size_t(seq) * sb.pages_stride;
 
-  const uint32_t bar_s = smem_u32(&bars[0]), bar_o = smem_u32(&bars[2]);
+  const uint32_t bar_s = smem_u32(&bars[0]), bar_o = smem_u32(&bars[2]), bar_p = smem_u32(&bars[3]);
+  const uint32_t bar_k = smem_u32(&bars[4]);
   if (tid == 0) {
     mbar_init(bar_s, 1);
     mbar_init(bar_s + 8, 1);
     mbar_init(bar_o, 1);
+    mbar_init(bar_p, SOFTMAX_THREADS);
+    for (int s = 0; s < STAGES_TC; ++s) mbar_init(bar_k + 8 * s, SOFTMAX_THREADS);
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
   if (warp == 0) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(tmem_slot)), "r"(256));
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::);
   }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem_base = *tmem_slot;
-  const uint32_t lane_addr = tmem_base + (uint32_t((warp & 3) * 32) << 16) + half * 32;  // lanes of this warp, its columns
-  const uint32_t tmem_o = tmem_base + 128;   // S buffers at columns [0, 64) and [64, 128), O at [128, 192)
-
-  // Q tile: rows of the tile, zero beyond the valid tokens
-  {
+  auto load_block = [&](int b) {  // softmax threads: page b into stage b % STAGES_TC; one commit group, maybe empty
+    if (b < n_blocks) {
+      const int page = pages[b];
+      const int st = b % STAGES_TC;
+      load_page<D>(smem_u32(k_ring + st * TILE_KV_BYTES), k_pool + kv_offset(page, g, 0, p.kv_heads, D), tid,
+                   SOFTMAX_THREADS);
+      load_page<D>(smem_u32(v_ring + st * TILE_KV_BYTES), v_pool + kv_offset(page, g, 0, p.kv_heads, D), tid,
+                   SOFTMAX_THREADS);
+    }
+    cp_async_commit();
+  };
+  if (!mma_warp) {
+    // Q tile: rows of the tile, zero beyond the valid tokens; then the first three pages
     const uint32_t qs = smem_u32(q_tile);
-    for (int i = tid; i < TQ * (D / 8); i += NT) {
+    for (int i = tid; i < TQ * (D / 8); i += SOFTMAX_THREADS) {
       const int r = i / (D / 8), c = i % (D / 8);
       if (r < tok_valid)
         cp_async16(qs + swz<D>(r, c), q + (size_t(start + q0 + r) * p.heads + h) * D + c * 8);
       else
         *reinterpret_cast<uint4*>(q_tile + swz<D>(r, c)) = make_uint4(0, 0, 0, 0);
     }
+    load_block(0);  // group 0 also holds the Q tile
+    load_block(1);
+    load_block(2);
+    cp_async_wait<2>();   // Q and page 0 have landed (for this thread's copies)
+    proxy_fence_async();
   }
-  auto load_block = [&](int b) {  // page b of the sequence into stage b % STAGES_TC; one commit group, maybe empty
-    if (b < n_blocks) {
-      const int page = pages[b];
-      const int st = b % STAGES_TC;
-      load_page<D>(smem_u32(k_ring + st * TILE_KV_BYTES), k_pool + kv_offset(page, g, 0, p.kv_heads, D), tid, NT);
-      load_page<D>(smem_u32(v_ring + st * TILE_KV_BYTES), v_pool + kv_offset(page, g, 0, p.kv_heads, D), tid, NT);
-    }
-    cp_async_commit();
-  };
-  load_block(0);  // group 0 also holds the Q tile
-  load_block(1);
-  load_block(2);
-
-  constexpr uint32_t IDESC_S = idesc_bf16(TQ, KEYS, false);
-  constexpr uint32_t IDESC_PV = idesc_bf16(TQ, D, true);
-  const uint64_t desc_q = smem_desc(smem_u32(q_tile), 16, 1024);
-  const uint64_t desc_p = smem_desc(smem_u32(p_tile), 16, 1024);
-  auto issue_s = [&](int b) {  // S_b = Q K_b^T into S buffer b & 1 (thread 0 only)
-    const uint64_t desc_k = smem_desc(smem_u32(k_ring + (b % STAGES_TC) * TILE_KV_BYTES), 16, 1024);
-#pragma unroll
-    for (int kk = 0; kk < D / 16; ++kk)  // 16 dims = 32 bytes = 2 descriptor units along a swizzled row
-      tc_mma(tmem_base + (b & 1) * 64, desc_q + 2 * kk, desc_k + 2 * kk, IDESC_S, kk > 0 ? 1u : 0u);
-    tc_commit(bar_s + (b & 1) * 8);
-  };
-
-  float m_run = -INFINITY, l_run = 0.f;   // running maximum of the raw scores, running sum
-  const float sl2 = p.scale * 1.4426950408889634f;
+  tc_fence_before();
+  __syncthreads();        // barriers, tensor memory, Q and page 0 are ready for everyone
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_o = tmem_base + 128;   // S buffers at columns [0, 64) and [64, 128), O at [128, 192)
   bool alive = true;  // false after a wait ran out: keep going without waiting, results are void
 
-  // page 0 has landed: first S
-  cp_async_wait<2>();
-  proxy_fence_async();
-  tc_fence_before();
-  __syncthreads();
-  if (tid == 0) {
-    tc_fence_after();
-    issue_s(0);
-  }
-
-  for (int i = 0; i < n_blocks; ++i) {
-    // (1) this thread's 32 columns of its row of S_i
-    if (alive) alive = mbar_wait(bar_s + (i & 1) * 8, (i >> 1) & 1, error_flag, 1);
-    tc_fence_after();
-    float s[32];
-    tmem_ld32(lane_addr + (i & 1) * 64, s);
-    // partial maximum of the visible scores; only pages that reach past some row's position need the test
-    float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-    if (i * KEYS + KEYS - 1 > past + q0 || !row_ok) {   // first part is uniform over the block
-      const int visible = row_pos - i * KEYS - half * 32;   // columns j <= visible are seen by this row
+  if (mma_warp) {
+    // ------------------------------------------------------------ the thread that issues matrix instructions
+    if (lane == 0) {
+      constexpr uint32_t IDESC_S = idesc_bf16(TQ, KEYS, false);
+      constexpr uint32_t IDESC_PV = idesc_bf16(TQ, D, true);
+      const uint64_t desc_q = smem_desc(smem_u32(q_tile), 16, 1024);
+      const uint64_t desc_p = smem_desc(smem_u32(p_tile), 16, 1024);
+      auto issue_s = [&](int b) {  // S_b = Q K_b^T into S buffer b & 1
+        const uint64_t desc_k = smem_desc(smem_u32(k_ring + (b % STAGES_TC) * TILE_KV_BYTES), 16, 1024);
 #pragma unroll
-      for (int j = 0; j < 32; ++j) {
-        s[j] = (j <= visible) ? s[j] : -INFINITY;
-        mx[j & 3] = fmaxf(mx[j & 3], s[j]);
+        for (int kk = 0; kk < D / 16; ++kk)  // 16 dims = 32 bytes = 2 descriptor units along a swizzled row
+          tc_mma(tmem_base + (b & 1) * 64, desc_q + 2 * kk, desc_k + 2 * kk, IDESC_S, kk > 0 ? 1u : 0u);
+        tc_commit(bar_s + (b & 1) * 8);
+      };
+      issue_s(0);   // page 0 was waited for before the block-wide barrier above
+      for (int i = 0; i < n_blocks && alive; ++i) {
+        if (i + 1 < n_blocks) {
+          // page i + 1 landed (all softmax threads said so); S_{i+1} runs under the softmax of page i.
+          // Its S buffer held S_{i-1}, which every thread had read before it reported P_{i-1}.
+          alive = mbar_wait(bar_k + 8 * ((i + 1) % STAGES_TC), ((i + 1) / STAGES_TC) & 1, error_flag, 4);
+          proxy_fence_async();
+          tc_fence_after();
+          issue_s(i + 1);
+        }
+        // P_i is written and O is rescaled: O += P_i V_i
+        if (alive) alive = mbar_wait(bar_p, i & 1, error_flag, 5);
+        proxy_fence_async();
+        tc_fence_after();
+        const uint64_t desc_v = smem_desc(smem_u32(v_ring + (i % STAGES_TC) * TILE_KV_BYTES), 16, 1024);
+#pragma unroll
+        for (int kk = 0; kk < KEYS / 16; ++kk)  // 16 keys: 32 bytes along P's rows, 2048 bytes down V's rows
+          tc_mma(tmem_o, desc_p + 2 * kk, desc_v + 128 * kk, IDESC_PV, (i > 0 || kk > 0) ? 1u : 0u);
+        tc_commit(bar_o);
       }
-    } else {
-#pragma unroll
-      for (int j = 0; j < 32; ++j) mx[j & 3] = fmaxf(mx[j & 3], s[j]);
     }
-    const float m_half = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
-    float* pm = pmax + (i & 1) * 2 * TQ;
-    pm[half * TQ + row] = m_half;
-    // (2) page i + 1 has landed: start S_{i+1} into the other S buffer; it runs under this softmax
-    cp_async_wait<1>();
-    proxy_fence_async();
-    tc_fence_before();
-    __syncthreads();
-    if (tid == 0 && i + 1 < n_blocks) {
+  } else {
+    // ------------------------------------------------------------ softmax threads
+    const uint32_t lane_addr = tmem_base + (uint32_t((warp & 3) * 32) << 16) + half * 32;  // this warp's lanes, its columns
+    const int pair_id = 1 + (warp & 3);
+    float m_run = -INFINITY, l_run = 0.f;   // running maximum of the raw scores, this thread's half of the sum
+    const float sl2 = p.scale * 1.4426950408889634f;
+    // page 0's arrival (the copies were waited for above)
+    mbar_arrive(bar_k);
+    for (int i = 0; i < n_blocks; ++i) {
+      // (1) this thread's 32 columns of its row of S_i
+      if (alive) alive = mbar_wait(bar_s + (i & 1) * 8, (i >> 1) & 1, error_flag, 1);
       tc_fence_after();
-      issue_s(i + 1);
-    }
-    // (3) the row's maximum from both halves
-    const float m_blk = fmaxf(m_half, pm[(half ^ 1) * TQ + row]);
-    const float m_new = fmaxf(m_run, m_blk);
-    const float corr = (m_run == -INFINITY) ? 0.f : fast_exp2((m_run - m_new) * sl2);
-    const bool moved = (m_new != m_run) && (m_run != -INFINITY);
-    m_run = m_new;
-    const float m_off = (m_run == -INFINITY) ? 0.f : m_run * sl2;   // exp2(s * sl2 - m_off); exp2(-inf) = 0
-    // (4) the previous O += P V is complete: its page stage and the P tile are free, O may be touched
-    if (i > 0) {
-      if (alive) alive = mbar_wait(bar_o, (i - 1) & 1, error_flag, 2);
-      tc_fence_after();
-    }
-    load_block(i + 3);
-    // (5) rescale this thread's 32 columns of its row of O if any row of the warp moved its maximum
-    if (i > 0 && __any_sync(0xffffffffu, moved)) {
-      float o[32];
-      tmem_ld32(lane_addr + 128, o);
-#pragma unroll
-      for (int j = 0; j < 32; ++j) o[j] *= corr;
-      tmem_st32(lane_addr + 128, o);
-      tmem_st_wait();
-    }
-    l_run *= corr;
-    // (6) P = exp2(S - max) as bfloat16 into the swizzled P tile: row, chunks 4 half .. 4 half + 3
-    float ls[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-    for (int c = 0; c < 4; ++c) {
-      uint32_t w[4];
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const float a = fast_exp2(fmaf(s[c * 8 + 2 * e], sl2, -m_off));
-        const float b = fast_exp2(fmaf(s[c * 8 + 2 * e + 1], sl2, -m_off));
-        ls[e] += a + b;
-        w[e] = pack_bf16(a, b);
+      float s[32];
+      tmem_ld32(lane_addr + (i & 1) * 64, s);
+      // (2) page i + 1: this thread's copies have landed; tell the issuing thread
+      if (i + 1 < n_blocks) {
+        cp_async_wait<1>();
+        proxy_fence_async();
+        mbar_arrive(bar_k + 8 * ((i + 1) % STAGES_TC));
       }
-      *reinterpret_cast<uint4*>(p_tile + swz<KEYS>(row, half * 4 + c)) = make_uint4(w[0], w[1], w[2], w[3]);
-    }
-    l_run += (ls[0] + ls[1]) + (ls[2] + ls[3]);   // this thread's half of the row sum
-    proxy_fence_async();
-    tc_fence_before();
-    __syncthreads();
-    // (7) O += P V
-    if (tid == 0) {
-      tc_fence_after();
-      const uint64_t desc_v = smem_desc(smem_u32(v_ring + (i % STAGES_TC) * TILE_KV_BYTES), 16, 1024);
+      // (3) maximum of the visible scores; only pages that reach past some row's position need the test
+      float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+      if (i * KEYS + KEYS - 1 > past + q0 || !row_ok) {   // first part is uniform over the block
+        const int visible = row_pos - i * KEYS - half * 32;   // columns j <= visible are seen by this row
 #pragma unroll
-      for (int kk = 0; kk < KEYS / 16; ++kk)  // 16 keys: 32 bytes along P's rows, 2048 bytes down V's rows
-        tc_mma(tmem_o, desc_p + 2 * kk, desc_v + 128 * kk, IDESC_PV, (i > 0 || kk > 0) ? 1u : 0u);
-      tc_commit(bar_o);
+        for (int j = 0; j < 32; ++j) {
+          s[j] = (j <= visible) ? s[j] : -INFINITY;
+          mx[j & 3] = fmaxf(mx[j & 3], s[j]);
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) mx[j & 3] = fmaxf(mx[j & 3], s[j]);
+      }
+      const float m_half = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+      float* pm = pmax + (i & 1) * 2 * TQ;
+      pm[half * TQ + row] = m_half;
+      pair_sync(pair_id);   // the two warps that share these 32 rows
+      const float m_blk = fmaxf(m_half, pm[(half ^ 1) * TQ + row]);
+      const float m_new = fmaxf(m_run, m_blk);
+      const float corr = (m_run == -INFINITY) ? 0.f : fast_exp2((m_run - m_new) * sl2);
+      const bool moved = (m_new != m_run) && (m_run != -INFINITY);
+      m_run = m_new;
+      const float m_off = (m_run == -INFINITY) ? 0.f : m_run * sl2;   // exp2(s * sl2 - m_off); exp2(-inf) = 0
+      // (4) the previous O += P V is complete: its page stage and the P tile are free, O may be touched
+      if (i > 0) {
+        if (alive) alive = mbar_wait(bar_o, (i - 1) & 1, error_flag, 2);
+        tc_fence_after();
+      }
+      load_block(i + 3);
+      // (5) rescale this thread's 32 columns of its row of O if any row of the warp moved its maximum
+      if (i > 0 && __any_sync(0xffffffffu, moved)) {
+        float o[32];
+        tmem_ld32(lane_addr + 128, o);
+#pragma unroll
+        for (int j = 0; j < 32; ++j) o[j] *= corr;
+        tmem_st32(lane_addr + 128, o);
+        tmem_st_wait();
+      }
+      l_run *= corr;
+      // (6) P = exp2(S - max) as bfloat16 into the swizzled P tile: row, chunks 4 half .. 4 half + 3
+      float ls[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t w[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float a = fast_exp2(fmaf(s[c * 8 + 2 * e], sl2, -m_off));
+          const float b = fast_exp2(fmaf(s[c * 8 + 2 * e + 1], sl2, -m_off));
+          ls[e] += a + b;
+          w[e] = pack_bf16(a, b);
+        }
+        *reinterpret_cast<uint4*>(p_tile + swz<KEYS>(row, half * 4 + c)) = make_uint4(w[0], w[1], w[2], w[3]);
+      }
+      l_run += (ls[0] + ls[1]) + (ls[2] + ls[3]);   // this thread's half of the row sum
+      proxy_fence_async();
+      tc_fence_before();
+      mbar_arrive(bar_p);   // (7) the issuing thread starts O += P V when all 256 have arrived
     }
-  }
-  cp_async_wait<0>();
-  // the two halves of every row sum meet
-  pmax[half * TQ + row] = l_run;
-  __syncthreads();
-  const float l_row = l_run + pmax[(half ^ 1) * TQ + row];
-  if (alive) alive = mbar_wait(bar_o, (n_blocks - 1) & 1, error_flag, 3);
-  tc_fence_after();
-  {
+    cp_async_wait<0>();
+    // the two halves of every row sum meet
+    pmax[half * TQ + row] = l_run;
+    pair_sync(pair_id);
+    const float l_row = l_run + pmax[(half ^ 1) * TQ + row];
+    if (alive) alive = mbar_wait(bar_o, (n_blocks - 1) & 1, error_flag, 3);
+    tc_fence_after();
     const float inv = l_row > 0.f ? 1.f / l_row : 0.f;
     __nv_bfloat16* dst = out + (size_t(start + q0 + row) * p.heads + h) * D + half * 32;
     float o[32];
@@ -346,7 +368,7 @@ PTB_API int ptb_attention_tc(const void* q, const void* k_pool, const void* v_po
   if (n_tiles <= 0) return PTB_OK;
   if (head_dim != D || heads <= 0 || kv_heads <= 0 || heads % kv_heads != 0 || heads > 65535 || error_flag == nullptr)
     return PTB_ERR_SIZE;
-  const size_t smem = 1024 + TILE_Q_BYTES + 2 * STAGES_TC * TILE_KV_BYTES + TILE_P_BYTES + 64 + 4 * TQ * sizeof(float);
+  const size_t smem = 1024 + TILE_Q_BYTES + 2 * STAGES_TC * TILE_KV_BYTES + TILE_P_BYTES + 128 + 4 * TQ * sizeof(float);
   static bool configured = false;
   if (!configured) {
     if (cudaFuncSetAttribute(attention_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess)
@@ -356,7 +378,7 @@ PTB_API int ptb_attention_tc(const void* q, const void* k_pool, const void* v_po
   TcParams p;
   p.heads = heads; p.kv_heads = kv_heads; p.scale = scale;
   dim3 grid(n_tiles, heads);
-  attention_tc_kernel<<<grid, 2 * TQ, smem, stream>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool,
+  attention_tc_kernel<<<grid, BLOCK_THREADS, smem, stream>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool,
                                                   (const __nv_bfloat16*)v_pool, (__nv_bfloat16*)out, *sb, tile_seq,
                                                   tile_q0, p, error_flag);
   return launch_status();

@@ -71,10 +71,16 @@ sample_kernel(const float* __restrict__ logits, float* __restrict__ work, int* _
   __shared__ int s_pick;
   const int row = blockIdx.x, tid = threadIdx.x, V = p.vocab;
   const float* lg = logits + size_t(row) * V;
-  float* w = work + size_t(row) * V;
+  float* w = work + size_t(row) * V;   // scratch copy of the row that the processors may change
 
-  for (int i = tid; i < V; i += ST) w[i] = lg[i];
-  __syncthreads();
+  const bool untouched = !p.do_sample && !(p.repetition_penalty != 1.0f && history) && p.n_suppress <= 0;
+  if (untouched) {
+    // plain greedy: nothing changes a logit, so the maximum is taken from the logits themselves
+    w = const_cast<float*>(lg);
+  } else {
+    for (int i = tid; i < V; i += ST) w[i] = lg[i];
+    __syncthreads();
+  }
   if (p.repetition_penalty != 1.0f && history) {
     const int* hist = history + size_t(row) * p.history_stride;
     const int n = history_len[row];
