@@ -113,13 +113,14 @@ class PreTrainedCausalLM(CausalLM):
 
     # ------------------------------------------------------------------ construction
     @classmethod
-    def from_pretrained(cls, folder: str, dtype=None, device="cuda", torch_dtype=None) -> "PreTrainedCausalLM":
+    def from_pretrained(cls, folder: str, dtype=None, device="cuda", torch_dtype=None,
+                        strict: bool = True) -> "PreTrainedCausalLM":
         raw = read_raw_config(folder)
         arch = lookup(raw)
         config = arch.config_cls.from_dict(raw)
         model = cls(arch.spec_builder(config), config, device=device,
                     dtype=resolve_dtype(dtype if dtype is not None else torch_dtype, config))
-        load_weights(model, folder, arch.name_rules)
+        load_weights(model, folder, arch.name_rules, strict=strict)
         model.generation_config = GenerationConfig.from_pretrained(folder, config)
         return model
 
@@ -233,8 +234,10 @@ class AutoModelForCausalLM:
     """``AutoModelForCausalLM.from_pretrained(folder)``: the model class is chosen by config.json."""
 
     @staticmethod
-    def from_pretrained(folder: str, dtype=None, device="cuda", torch_dtype=None) -> PreTrainedCausalLM:
-        return PreTrainedCausalLM.from_pretrained(folder, dtype=dtype, device=device, torch_dtype=torch_dtype)
+    def from_pretrained(folder: str, dtype=None, device="cuda", torch_dtype=None,
+                        strict: bool = True) -> PreTrainedCausalLM:
+        return PreTrainedCausalLM.from_pretrained(folder, dtype=dtype, device=device, torch_dtype=torch_dtype,
+                                                  strict=strict)
 
     @staticmethod
     def from_config(config: ModelConfig, seed: int = 0, dtype=None, device="cuda") -> PreTrainedCausalLM:
@@ -245,8 +248,8 @@ class FalconForCausalLM(PreTrainedCausalLM):
     """Falcon by name. The class adds nothing: the architecture lives in models/falcon.py as data."""
 
     @classmethod
-    def from_pretrained(cls, folder: str, dtype=None, device="cuda", torch_dtype=None):
+    def from_pretrained(cls, folder: str, dtype=None, device="cuda", torch_dtype=None, strict: bool = True):
         raw = read_raw_config(folder)
         if lookup(raw).model_type != "falcon":
             raise ValueError(f"{folder!r} holds a {raw.get('model_type')!r} model, not a Falcon")
-        return super().from_pretrained(folder, dtype=dtype, device=device, torch_dtype=torch_dtype)
+        return super().from_pretrained(folder, dtype=dtype, device=device, torch_dtype=torch_dtype, strict=strict)

@@ -18,6 +18,9 @@ from .base import BuildContext, CacheNeed, ParamDecl, Part, PartSpec, register_p
 from .linear import linear
 
 
+MAX_HEAD_DIM = 256   # csrc/attention_generic.cu keeps a row's accumulators in registers up to this size
+
+
 @register_part("mixer", "attention")
 class Attention(Part):
     graph_safe = True
@@ -26,6 +29,8 @@ class Attention(Part):
         super().__init__(build, spec)
         if heads % kv_heads:
             raise ValueError(f"heads ({heads}) must be a multiple of kv_heads ({kv_heads})")
+        if not (0 < head_dim <= MAX_HEAD_DIM):
+            raise ValueError(f"the attention kernels take head sizes from 1 to {MAX_HEAD_DIM}, got {head_dim}")
         self.hidden, self.heads, self.kv_heads, self.head_dim = int(hidden), int(heads), int(kv_heads), int(head_dim)
         self.q_per_kv = self.heads // self.kv_heads
         self.has_bias, self.window = bool(bias), int(window)

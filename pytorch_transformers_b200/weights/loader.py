@@ -38,8 +38,10 @@ class WeightError(RuntimeError):
         super().__init__("\n".join(lines))
 
 
-def load_weights(model, folder: str, name_rules: Optional[dict] = None) -> None:
-    """Read every parameter of ``model`` from the archive(s) in ``folder`` and bind them."""
+def load_weights(model, folder: str, name_rules: Optional[dict] = None, strict: bool = True) -> None:
+    """Read every parameter of ``model`` from the archive(s) in ``folder`` and bind them. With
+    ``strict=False`` tensors that the model does not ask for are reported as a warning instead of an
+    error (missing tensors and wrong shapes stay errors: the model could not run)."""
     rules = name_rules or {}
     prefix = rules.get("optional_prefix")
     ignore = tuple(rules.get("ignore_suffixes", ()))
@@ -69,6 +71,10 @@ def load_weights(model, folder: str, name_rules: Optional[dict] = None) -> None:
                 mismatched.append(f"{name}: stored as {e.dtype}, model wants an integer table")
             elif decl.role != "int" and e.dtype not in _FLOATS:
                 mismatched.append(f"{name}: stored as {e.dtype}, model wants floating point")
+        if unexpected and not strict and not missing and not mismatched:
+            import warnings
+            warnings.warn(f"{folder}: {len(unexpected)} tensors are not used by the model: " + ", ".join(sorted(unexpected)))
+            unexpected = []
         if missing or unexpected or mismatched:
             raise WeightError(folder, sorted(missing), sorted(unexpected), mismatched)
         tensors: Dict[str, torch.Tensor] = {}

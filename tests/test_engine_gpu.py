@@ -12,7 +12,7 @@ import tiny_models as tm
 pytestmark = pytest.mark.gpu
 
 CASES = {
-    "A": ("A", {}), "B": ("B", {}), "C": ("C", {}), "D": ("D", {}), "E": ("E", {}), "F": ("F", {}),
+    "A": ("A", {}), "B": ("B", {}), "C": ("C", {}), "D": ("D", {}), "E": ("E", {}), "F": ("F", {}), "G": ("G", {}),
     "A_sequential": ("A", {"parallel_attn": False}),
     "B_one_norm": ("B", {"num_ln_in_parallel_attn": 1}),
 }
@@ -67,7 +67,7 @@ def test_each_request_alone_and_whole(loaded, case, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("case", ["A", "B", "C", "D", "E", "F"])
+@pytest.mark.parametrize("case", ["A", "B", "C", "D", "E", "F", "G"])
 def test_last_32_tokens_one_by_one(loaded, case, dtype):
     L = loaded(case, dtype)
     cache = L.model.new_cache(192)
@@ -84,7 +84,7 @@ def test_last_32_tokens_one_by_one(loaded, case, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("case", ["A", "B", "C", "D", "E", "F"])
+@pytest.mark.parametrize("case", ["A", "B", "C", "D", "E", "F", "G"])
 def test_batches_of_unequal_lengths_with_slot_reuse(loaded, case, dtype):
     L = loaded(case, dtype)
     # 9 requests, batches of 3, a cache that holds one batch only: pages and slots are reused

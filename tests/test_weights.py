@@ -169,3 +169,24 @@ def test_random_weights_mode_writes_a_model_folder(tmp_path):
     assert torch.equal(m.head, wa["lm_head.weight"])
     # plain logits exist for the written model: the folder is a complete model
     assert plain.model_logits([1, 2, 3], ca, {k: v.double() for k, v in wa.items()}).shape == (3, 1000)
+
+
+def test_strict_false_only_forgives_unused_tensors(tmp_path):
+    cfg = tm.config_dict("A")
+    w = tm.make_weights(cfg, 0)
+    w["transformer.h.0.extra.weight"] = np.zeros((2, 2), np.float32)
+    folder = tm.write_model_folder(str(tmp_path / "extra"), cfg, w)
+    with pytest.raises(WeightError):
+        load_cpu(folder)
+    with pytest.warns(UserWarning, match="not used by the model"):
+        ptb.AutoModelForCausalLM.from_pretrained(folder, dtype="float32", device="cpu", strict=False)
+    del w["transformer.ln_f.bias"]
+    with pytest.raises(WeightError, match="missing"):
+        ptb.AutoModelForCausalLM.from_pretrained(tm.write_model_folder(str(tmp_path / "both"), cfg, w),
+                                                 dtype="float32", device="cpu", strict=False)
+
+
+def test_head_sizes_beyond_the_kernels_are_refused_when_the_model_is_built(tmp_path):
+    cfg = ptb.FalconConfig.from_dict(tm.config_dict("A", hidden_size=1040, num_attention_heads=2))   # head size 520
+    with pytest.raises(ValueError, match="head sizes from 1 to 256"):
+        ptb.AutoModelForCausalLM.from_config(cfg, device="cpu", dtype="float32")

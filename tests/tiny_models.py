@@ -56,8 +56,14 @@ TINY = {
               ffn_hidden_size=384, alibi=True, bias=True, layer_norm_epsilon=1e-5,
               max_position_embeddings=2048, tie_word_embeddings=False, activation="gelu",
               bos_token_id=0, eos_token_id=7),
+    # 11B-style at head size 128: grouped K/V (4 queries per group), one norm, rotary with a large theta
+    "G": dict(vocab_size=640, hidden_size=1024, num_hidden_layers=2, num_attention_heads=8,
+              num_kv_heads=2, new_decoder_architecture=True, num_ln_in_parallel_attn=1,
+              ffn_hidden_size=1536, alibi=False, bias=False, rope_theta=500042.0, layer_norm_epsilon=1e-5,
+              max_position_embeddings=8192, tie_word_embeddings=True, activation="gelu",
+              bos_token_id=11, eos_token_id=11),
 }
-SEEDS = {"A": 0, "B": 1, "C": 2, "D": 3, "E": 4, "F": 5}
+SEEDS = {"A": 0, "B": 1, "C": 2, "D": 3, "E": 4, "F": 5, "G": 6}
 
 
 def config_dict(name: str, **overrides) -> dict:
