@@ -177,11 +177,13 @@ def run_ours(args):
             sampler.__enter__()
         start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         torch.cuda.synchronize()
+        torch.cuda.profiler.start()   # a profiler started with --profile-from-start off sees the timed steps only
         start.record()
         for _ in range(steps):
             one()
         end.record()
         torch.cuda.synchronize()
+        torch.cuda.profiler.stop()
         if sampler:
             sampler.__exit__()
         ms = start.elapsed_time(end) / steps

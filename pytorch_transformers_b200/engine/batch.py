@@ -191,12 +191,12 @@ class StepContext:
 
     def rope(self, position_part):
         """(cos, sin) tables of this step's tokens for a rotary position part, computed once per step
-        and part on first use (the reference computes them once per forward pass too,
+        and set of constants (a part's ``rotation_key``; without one, per part) on first use (the reference computes them once per forward pass too,
         src/transformers/models/falcon/modeling_falcon.py:946); None for parts that do not rotate."""
         inv_freq = position_part.rotation() if position_part is not None else None
         if inv_freq is None:
             return None
-        key = id(position_part)
+        key = getattr(position_part, "rotation_key", None) or id(position_part)
         if key not in self._rope:
             self._rope[key] = K.rope_table(self.dev["tok_pos"], inv_freq)
         return self._rope[key]

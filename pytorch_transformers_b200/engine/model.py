@@ -191,7 +191,7 @@ class CausalLM:
         ctx.commit()
         return entry["out"].clone()   # the graph's own output buffer is rewritten by the next replay
 
-    TWO_STREAM_MAX_TOKENS = 16
+    TWO_STREAM_MAX_TOKENS = 32
 
     def forward(self, ctx: StepContext) -> torch.Tensor:
         k = self.build.kernels

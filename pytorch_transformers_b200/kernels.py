@@ -77,8 +77,9 @@ def lib():
                      "ptb_linear_f32", "ptb_split_rotate_store", "ptb_attention_generic", "ptb_sample",
                      "ptb_attention_generic_tile_rows", "ptb_attention_mma", "ptb_attention_mma_supports",
                      "ptb_skinny_linear", "ptb_skinny_linear_max_rows", "ptb_skinny_linear_k_multiple",
-                     "ptb_rope_table", "ptb_attention_decode", "ptb_stream_linear", "ptb_stream_linear_max_rows", "ptb_attention_tc", "ptb_attention_tc_supports",
-                     "ptb_attention_tc_tile_tokens"):
+                     "ptb_rope_table", "ptb_attention_decode", "ptb_attention_tc", "ptb_attention_tc_supports",
+                     "ptb_attention_tc_tile_tokens", "ptb_tc_linear", "ptb_tc_linear_max_rows",
+                     "ptb_tc_linear_k_multiple"):
             getattr(L, name).restype = ctypes.c_int
         _configured = True
     return L
@@ -374,43 +375,54 @@ def skinny_linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor]
     return y
 
 
-STREAM_MAX_ROWS = 16  # ptb_stream_linear_max_rows()
 _sm_count = {}
 
 
-def stream_linear_takes(rows: int, k: int) -> bool:
-    return 0 < rows <= STREAM_MAX_ROWS and k % 32 == 0
+TC_LINEAR_MAX_ROWS = 128   # ptb_tc_linear_max_rows()
+TC_LINEAR_K_MULTIPLE = 8   # ptb_tc_linear_k_multiple()
 
 
-def stream_linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None, act: str = "none",
-                  add: Optional[torch.Tensor] = None, out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
-    """act(x @ w.T + bias) + add for up to 16 rows of bfloat16 x; the weights go through a ring of
-    shared-memory stages filled by bulk asynchronous copies. Result bfloat16 or float32."""
+def tc_linear_takes(rows: int, k: int) -> bool:
+    return 0 < rows <= TC_LINEAR_MAX_ROWS and k % TC_LINEAR_K_MULTIPLE == 0
+
+
+def tc_linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None, act: str = "none",
+              add: Optional[torch.Tensor] = None, out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+    """act(x @ w.T + bias) + add for up to 128 rows of bfloat16 x on the tcgen05 tensor cores: the
+    weights stream once through shared memory (TMA), the sums stay in tensor memory, and bias,
+    activation and the sum with ``add`` happen in the float32 epilogue. Result bfloat16 or float32."""
     _need_cuda(x, w, bias, add)
     if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or (add is not None and add.dtype != torch.bfloat16):
-        raise KernelError("stream_linear takes bfloat16 x, w and add")
+        raise KernelError("tc_linear takes bfloat16 x, w and add")
     m, k = x.shape
     n = w.shape[0]
     if w.shape[1] != k or (add is not None and tuple(add.shape) != (m, n)):
-        raise KernelError(f"stream_linear: shapes x {list(x.shape)}, w {list(w.shape)} do not fit")
+        raise KernelError(f"tc_linear: shapes x {list(x.shape)}, w {list(w.shape)} do not fit")
+    if not x.is_contiguous() or not w.is_contiguous() or (add is not None and not add.is_contiguous()):
+        raise KernelError("tc_linear takes contiguous tensors")
     dev = x.device
     if dev not in _sm_count:
         _sm_count[dev] = torch.cuda.get_device_properties(dev).multi_processor_count
     y = torch.empty((m, n), dtype=out_dtype, device=dev)
     ybf, yf = (y, None) if out_dtype == torch.bfloat16 else (None, y)
-    _check(lib().ptb_stream_linear(_ptr(x), _ptr(w), _ptr(bias), _ptr(add), _ptr(ybf), _ptr(yf), m, n, k,
-                                   ACTIVATIONS[act], _sm_count[dev], _ptr(error_flag(dev)), _stream(x)),
-           "stream_linear")
+    _check(lib().ptb_tc_linear(_ptr(x), _ptr(w), _ptr(bias), _ptr(add), _ptr(ybf), _ptr(yf), m, n, k,
+                               ACTIVATIONS[act], _sm_count[dev], _ptr(error_flag(dev)), _stream(x)), "tc_linear")
     return y
 
 
-def matmul_nt(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
-    """Library matrix product x @ w.T for the bfloat16 path (cuBLAS through torch), where the
+def matmul_nt(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
+              add: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Library matrix product x @ w.T (+ add) for the bfloat16 path (cuBLAS through torch), where the
     reference's engine uses the same library. float32 inputs are refused: the float32 path has
     its own kernel (linear_f32)."""
     if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
         raise KernelError("matmul_nt is the bfloat16 library product; float32 goes through linear_f32")
     _need_cuda(x, w)
+    if add is not None:
+        # the library's own epilogue adds in float32 and rounds once (beta = 1)
+        if out_dtype not in (None, torch.bfloat16) or add.dtype != torch.bfloat16 or tuple(add.shape) != (x.shape[0], w.shape[0]):
+            raise KernelError("matmul_nt adds a bfloat16 tensor of the result's shape to a bfloat16 result")
+        return torch.addmm(add, x, w.t())
     if out_dtype is None or out_dtype == torch.bfloat16:
         return torch.mm(x, w.t())
     return torch.mm(x, w.t(), out_dtype=out_dtype)

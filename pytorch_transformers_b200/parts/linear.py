@@ -6,7 +6,8 @@ weight-streaming kernel, which also takes the bias, the activation and a tensor 
 residual) in its float32 epilogue. bfloat16 models with many rows (prompts) use the library
 matrix product that the reference's engine uses too (cuBLAS; ``FalconLinear``,
 src/transformers/models/falcon/modeling_falcon.py:67-72, multiplies and then adds the bias as a
-separate step), followed by hand-written kernels for bias, activation and sum, in float32.
+separate step); a tensor to add goes into that product's own float32 epilogue, and bias and
+activation, where a layer has them, are a hand-written kernel after it, in float32.
 """
 from __future__ import annotations
 
@@ -15,10 +16,12 @@ from typing import Optional
 import torch
 
 
-# Output width from which decode steps use stream_linear (the TMA ring) instead of skinny_linear. Off:
-# alone the ring is as fast as register loads (both meet the same per-launch ramp), but its 190 KB of
-# shared memory keep the other graph branch's kernels off the SM, and the whole step gets slower.
-STREAM_MIN_WIDTH = None
+# Rows up to which steps of more than a few tokens use tc_linear (TMA ring, tcgen05, accumulators
+# in tensor memory, bias / activation / residual in its epilogue) instead of the library product.
+# Off: alone it reads the weights at 3.1 to 5.3 TB/s where the library reaches 4.0 to 5.8 TB/s on the
+# same matrices (the profile of the weight-stream kernels has the table), and the fused epilogue does
+# not make up for it.
+TC_LINEAR_ROWS = None
 
 
 def linear(kernels, x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None,
@@ -28,13 +31,12 @@ def linear(kernels, x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.
         y = kernels.linear_f32(x, weight, bias, act)
         return y if add is None else kernels.residual(add, y)
     rows, k = x.shape
-    if (STREAM_MIN_WIDTH is not None and rows <= 8 and weight.shape[0] >= STREAM_MIN_WIDTH
-            and kernels.stream_linear_takes(rows, k)):
-        # wide outputs: the TMA ring keeps more bytes in flight than register loads can
-        return kernels.stream_linear(x, weight, bias, act, add)
     if kernels.skinny_linear_preferred(rows, k):
         return kernels.skinny_linear(x, weight, bias, act, add)
+    if TC_LINEAR_ROWS is not None and rows <= TC_LINEAR_ROWS and kernels.tc_linear_takes(rows, k):
+        return kernels.tc_linear(x, weight, bias, act, add)
+    if bias is None and act == "none":
+        return kernels.matmul_nt(x, weight, add=add)   # the sum with `add` in the product's own epilogue
     y = kernels.matmul_nt(x, weight)
-    if bias is not None or act != "none":
-        kernels.bias_act_(y, bias, act)
+    kernels.bias_act_(y, bias, act)
     return y if add is None else kernels.residual(add, y)

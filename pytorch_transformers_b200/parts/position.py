@@ -43,6 +43,8 @@ class RotaryPosition(NoPosition):
         if factor != 1.0:
             inv_freq = inv_freq / float(factor)
         self.inv_freq = inv_freq.to(torch.float32).to(build.device)
+        # layers whose rotation has the same constants share one table of angles per step
+        self.rotation_key = ("rotary", dim, float(theta), float(factor))
 
     def rotation(self):
         return self.inv_freq

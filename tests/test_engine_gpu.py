@@ -271,3 +271,27 @@ def test_long_prompt_batches_are_fed_in_several_steps(loaded, case):
         assert cut.sequences == whole.sequences
         for a, b in zip(cut.logits, whole.logits):
             torch.testing.assert_close(a, b, atol=1e-5, rtol=1e-4)
+
+
+@pytest.mark.parametrize("case", ["B", "E", "G"])
+def test_prompts_through_the_tensor_memory_linear_layer(loaded, case, monkeypatch):
+    """With the tcgen05 linear layer switched on for steps of 17 to 128 rows, prompts and batches of
+    that size give the plain implementation's logits (the switch is off by default: the library
+    product is faster)."""
+    from pytorch_transformers_b200 import kernels as K
+    from pytorch_transformers_b200.parts import linear as linear_mod
+    calls = []
+    real = K.tc_linear
+    monkeypatch.setattr(K, "tc_linear", lambda *a, **kw: (calls.append(a[0].shape[0]), real(*a, **kw))[1])
+    monkeypatch.setattr(linear_mod, "TC_LINEAR_ROWS", 128)
+    L = loaded(case, "bfloat16")
+    cache = L.model.new_cache(64 * 6)
+    lengths = [70, 20, 31]
+    reqs = tm.prompts(L.name, lengths, seed=21)
+    slots = [cache.open() for _ in reqs]
+    out = L.model.step(cache, slots, reqs, want="last")       # 121 rows in one step
+    for r, ids in enumerate(reqs):
+        close(out[r], L.plain_logits(ids)[-1], "bfloat16", f"{case} request {r}")
+    K.check_device_errors(out.device)
+    assert calls and all(16 < n <= 128 for n in calls)
+    cache.close_all()

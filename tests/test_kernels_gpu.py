@@ -149,6 +149,64 @@ def test_skinny_linear(K, m, n, k, act, bias, add, f32):
         torch.testing.assert_close(out.double().cpu(), ref, **tol(bf))
 
 
+@pytest.mark.parametrize("m", [1, 7, 16, 17, 33, 64, 100, 128])
+@pytest.mark.parametrize("n,k", [(100, 64), (4672, 4544), (71, 96), (18176 // 2, 4544), (333, 18176 // 4),
+                                 (4544, 1160), (129, 1024), (128, 8)])
+@pytest.mark.parametrize("act,bias,add,f32", [("none", False, False, False), ("gelu", True, False, False),
+                                               ("none", True, True, False), ("relu", False, True, True)])
+def test_tc_linear(K, m, n, k, act, bias, add, f32):
+    """The tcgen05 linear layer: every number of rows up to 128, widths that are no multiple of the
+    128-row tile or of the 64-wide k chunk, with and without the division of K over a cluster."""
+    bf = torch.bfloat16
+    x, w = rnd(m, k, dtype=bf, seed=1), rnd(n, k, dtype=bf, seed=2, scale=0.05)
+    b = rnd(n, seed=3) if bias else None
+    a = rnd(m, n, dtype=bf, seed=4) if add else None
+    assert K.tc_linear_takes(m, k)
+    ref = x.double().cpu() @ w.double().cpu().T
+    if bias:
+        ref = ref + b.double().cpu()
+    if act != "none":
+        ref = plain.activation(ref, act)
+    if add:
+        ref = ref + a.double().cpu()
+    out = K.tc_linear(x, w, b, act, a, out_dtype=torch.float32 if f32 else bf)
+    K.check_device_errors(x.device)
+    assert out.dtype == (torch.float32 if f32 else bf)
+    if f32:
+        torch.testing.assert_close(out.double().cpu(), ref, atol=1e-3, rtol=1e-4)
+    else:
+        torch.testing.assert_close(out.double().cpu(), ref, **tol(bf))
+
+
+def test_tc_linear_one_key_stands_out(K):
+    """A single large product far along K, in a block's last chunk, must arrive in the sum: one weight
+    row and one token get a matching spike at the last k."""
+    bf = torch.bfloat16
+    m, n, k = 48, 4544, 4544
+    x, w = rnd(m, k, dtype=bf, seed=1, scale=0.01), rnd(n, k, dtype=bf, seed=2, scale=0.01)
+    x[37, k - 1] = 8.0
+    w[4001, k - 1] = 4.0
+    out = K.tc_linear(x, w).float().cpu()
+    K.check_device_errors(x.device)
+    ref = (x.double().cpu() @ w.double().cpu().T).float()
+    assert abs(out[37, 4001] - 32.0) < 0.5
+    torch.testing.assert_close(out, ref, **tol(bf))
+
+
+def test_tc_linear_refuses_what_it_does_not_take(K):
+    from pytorch_transformers_b200.kernels import KernelError
+    assert K.lib().ptb_tc_linear_max_rows() == K.TC_LINEAR_MAX_ROWS
+    assert K.lib().ptb_tc_linear_k_multiple() == K.TC_LINEAR_K_MULTIPLE
+    assert not K.tc_linear_takes(129, 64) and not K.tc_linear_takes(4, 36)
+    bf = torch.bfloat16
+    with pytest.raises(KernelError):
+        K.tc_linear(rnd(129, 64, dtype=bf), rnd(16, 64, dtype=bf))
+    with pytest.raises(KernelError):
+        K.tc_linear(rnd(4, 36, dtype=bf), rnd(16, 36, dtype=bf))
+    with pytest.raises(KernelError):
+        K.tc_linear(rnd(4, 64), rnd(16, 64))
+
+
 def test_skinny_linear_refuses_what_it_does_not_take(K):
     from pytorch_transformers_b200.kernels import KernelError
     assert K.lib().ptb_skinny_linear_max_rows() == K.SKINNY_MAX_ROWS
@@ -162,36 +220,3 @@ def test_skinny_linear_refuses_what_it_does_not_take(K):
         K.skinny_linear(rnd(4, 64), rnd(16, 64))
 
 
-@pytest.mark.parametrize("m", [1, 5, 8, 9, 16])
-@pytest.mark.parametrize("n,k", [(100, 64), (4672, 4544), (71, 96), (18176 // 2, 4544), (33, 18176 // 4)])
-@pytest.mark.parametrize("act,bias,add,f32", [("none", False, False, False), ("gelu", True, False, False),
-                                               ("none", True, True, False), ("relu", False, True, True)])
-def test_stream_linear(K, m, n, k, act, bias, add, f32):
-    bf = torch.bfloat16
-    x, w = rnd(m, k, dtype=bf, seed=1), rnd(n, k, dtype=bf, seed=2, scale=0.05)
-    b = rnd(n, seed=3) if bias else None
-    a = rnd(m, n, dtype=bf, seed=4) if add else None
-    assert K.stream_linear_takes(m, k)
-    ref = x.double().cpu() @ w.double().cpu().T
-    if bias:
-        ref = ref + b.double().cpu()
-    if act != "none":
-        ref = plain.activation(ref, act)
-    if add:
-        ref = ref + a.double().cpu()
-    out = K.stream_linear(x, w, b, act, a, out_dtype=torch.float32 if f32 else bf)
-    K.check_device_errors("cuda")
-    if f32:
-        torch.testing.assert_close(out.double().cpu(), ref, atol=1e-3, rtol=1e-4)
-    else:
-        torch.testing.assert_close(out.double().cpu(), ref, **tol(bf))
-
-
-def test_stream_linear_refuses_what_it_does_not_take(K):
-    from pytorch_transformers_b200.kernels import KernelError
-    assert K.lib().ptb_stream_linear_max_rows() == K.STREAM_MAX_ROWS
-    assert not K.stream_linear_takes(17, 64) and not K.stream_linear_takes(4, 48)
-    with pytest.raises(KernelError):
-        K.stream_linear(rnd(17, 64, dtype=torch.bfloat16), rnd(16, 64, dtype=torch.bfloat16))
-    with pytest.raises(KernelError):
-        K.stream_linear(rnd(4, 48, dtype=torch.bfloat16), rnd(16, 48, dtype=torch.bfloat16))
