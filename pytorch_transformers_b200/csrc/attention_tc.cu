@@ -2,8 +2,8 @@
 // memory, for head size 64, bfloat16, causal, over the paged cache.
 //
 // One block = 128 consecutive new tokens of one sequence x one query head. 256 softmax threads: threads t
-// and t + 128 share query row t (tensor-memory lane t), each taking 32 of a page's 64 columns; they also
-// copy the pages. One more warp's first lane issues every matrix instruction. The roles meet only at
+// and t + 128 share query row t (tensor-memory lane t), each taking 32 of a page's 64 columns (TPR
+// threads per row; 1, 2 and 4 are correct); they also copy the pages. One more warp's first lane issues every matrix instruction. The roles meet only at
 // mbarriers (page landed, S written, P written, O updated): there is no block-wide barrier in the loop. Keys are walked one cache page (64 keys) at a time:
 //
 //   S = Q K^T      tcgen05.mma  M=128 N=64 K=64   A = Q  (shared, K-major, 128-byte swizzle)
@@ -25,6 +25,15 @@
 //
 // Two blocks fit on an SM (97 KB of shared memory and 256 columns of tensor memory each): while one
 // block's threads do softmax, the other's matrix instructions run.
+//
+// Measured on this kernel at 2,048 and 8,192 tokens (71 heads, one K/V head): one, two and four threads
+// per row take 165, 159 and 189 us at 2,048 tokens, so the softmax threads' arithmetic is not the limit;
+// a second P tile (softmax of page i + 1 no longer waits for O += P V of page i, at the price of one
+// page less of prefetch distance) took 164 us. A block is one chain of dependent steps per page
+// (about 1.5 us: tensor-memory load, maximum across the row's threads, exponentials, stores, fence,
+// arrival, issue, matrix instructions, completion), and an SM holds two such chains; the exponential
+// unit is busy a third of the time, the tensor pipe a sixth. More chains per SM (several heads of a
+// K/V group in one block, sharing the page copies) is the open step.
 #include "mma_common.cuh"
 #include "tc_common.cuh"
 
@@ -41,13 +50,16 @@ struct TcParams {
   float scale;
 };
 
-constexpr int SOFTMAX_THREADS = 2 * TQ;             // two threads per query row
+constexpr int TPR = 2;                              // threads per query row
+constexpr int COLS = KEYS / TPR;                    // columns of a page that a thread handles
+constexpr int SOFTMAX_THREADS = TPR * TQ;
 constexpr int BLOCK_THREADS = SOFTMAX_THREADS + 32;  // and one warp whose first lane issues the matrix instructions
 
 // barrier among the 64 threads of two warps (ids 1..4 are used)
-__device__ __forceinline__ void pair_sync(int id) { asm volatile("bar.sync %0, 64;\n" ::"r"(id) : "memory"); }
+// barrier among the TPR warps that share 32 query rows (ids 1..4 are used)
+__device__ __forceinline__ void row_sync(int id) { asm volatile("bar.sync %0, %1;\n" ::"r"(id), "n"(TPR * 32) : "memory"); }
 
-__global__ void __launch_bounds__(BLOCK_THREADS)
+__global__ void __launch_bounds__(BLOCK_THREADS, 2)
 attention_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_pool,
                     const __nv_bfloat16* __restrict__ v_pool, __nv_bfloat16* __restrict__ out, StepBatch sb,
                     const int* __restrict__ tile_seq, const int* __restrict__ tile_q0, TcParams p,
@@ -62,12 +74,12 @@ attention_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
   // barriers: [0], [1] S buffer written; [2] O updated; [3] P written; [4 ..] page landed, per stage
   uint64_t* bars = reinterpret_cast<uint64_t*>(p_tile + TILE_P_BYTES);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 4 + STAGES_TC);
-  float* pmax = reinterpret_cast<float*>(tmem_slot + 2);   // [2 buffers][2 halves][TQ]: partial row maxima
+  float* pmax = reinterpret_cast<float*>(tmem_slot + 2);   // [2 buffers][TPR parts][TQ]: partial row maxima
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const bool mma_warp = warp == SOFTMAX_THREADS / 32;
   const int row = tid & (TQ - 1);        // query row of a softmax thread (= its tensor-memory lane)
-  const int half = (tid >> 7) & 1;       // which 32 of the 64 columns of a page it handles
+  const int part = (tid >> 7) % TPR;     // which COLS of the 64 columns of a page it handles
   const int tile = blockIdx.x, h = blockIdx.y;
   const int qpk = p.heads / p.kv_heads;
   const int g = h / qpk;
@@ -135,38 +147,40 @@ attention_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
       constexpr uint32_t IDESC_PV = idesc_bf16(TQ, D, true);
       const uint64_t desc_q = smem_desc(smem_u32(q_tile), 16, 1024);
       const uint64_t desc_p = smem_desc(smem_u32(p_tile), 16, 1024);
-      auto issue_s = [&](int b) {  // S_b = Q K_b^T into S buffer b & 1
-        const uint64_t desc_k = smem_desc(smem_u32(k_ring + (b % STAGES_TC) * TILE_KV_BYTES), 16, 1024);
-#pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk)  // 16 dims = 32 bytes = 2 descriptor units along a swizzled row
-          tc_mma(tmem_base + (b & 1) * 64, desc_q + 2 * kk, desc_k + 2 * kk, IDESC_S, kk > 0 ? 1u : 0u);
+      const uint64_t desc_k0 = smem_desc(smem_u32(k_ring), 16, 1024);
+      const uint64_t desc_v0 = smem_desc(smem_u32(v_ring), 16, 1024);
+      constexpr uint64_t STAGE_UNITS = TILE_KV_BYTES >> 4;   // the address field counts 16-byte units
+      // S_b = Q K_b^T into S buffer b & 1; the page sits in stage `st`
+      auto issue_s = [&](int b, int st) {
+        tc_mma4<2, 2>(tmem_base + (b & 1) * 64, desc_q, desc_k0 + st * STAGE_UNITS, IDESC_S, 0u);
         tc_commit(bar_s + (b & 1) * 8);
       };
-      issue_s(0);   // page 0 was waited for before the block-wide barrier above
+      issue_s(0, 0);   // page 0 was waited for before the block-wide barrier above
+      int st = 0, st_next = 1 % STAGES_TC;   // stages of pages i and i + 1
       for (int i = 0; i < n_blocks && alive; ++i) {
         if (i + 1 < n_blocks) {
           // page i + 1 landed (all softmax threads said so); S_{i+1} runs under the softmax of page i.
           // Its S buffer held S_{i-1}, which every thread had read before it reported P_{i-1}.
-          alive = mbar_wait(bar_k + 8 * ((i + 1) % STAGES_TC), ((i + 1) / STAGES_TC) & 1, error_flag, 4);
+          alive = mbar_wait(bar_k + 8 * st_next, ((i + 1) / STAGES_TC) & 1, error_flag, 4);
           proxy_fence_async();
           tc_fence_after();
-          issue_s(i + 1);
+          issue_s(i + 1, st_next);
         }
-        // P_i is written and O is rescaled: O += P_i V_i
+        // P_i is written and O is rescaled: O += P_i V_i (16 keys: 32 bytes along P's rows, 2048 bytes
+        // down V's rows)
         if (alive) alive = mbar_wait(bar_p, i & 1, error_flag, 5);
         proxy_fence_async();
         tc_fence_after();
-        const uint64_t desc_v = smem_desc(smem_u32(v_ring + (i % STAGES_TC) * TILE_KV_BYTES), 16, 1024);
-#pragma unroll
-        for (int kk = 0; kk < KEYS / 16; ++kk)  // 16 keys: 32 bytes along P's rows, 2048 bytes down V's rows
-          tc_mma(tmem_o, desc_p + 2 * kk, desc_v + 128 * kk, IDESC_PV, (i > 0 || kk > 0) ? 1u : 0u);
+        tc_mma4<2, 128>(tmem_o, desc_p, desc_v0 + st * STAGE_UNITS, IDESC_PV, i > 0 ? 1u : 0u);
         tc_commit(bar_o);
+        st = st_next;
+        st_next = (st_next + 1 == STAGES_TC) ? 0 : st_next + 1;
       }
     }
   } else {
     // ------------------------------------------------------------ softmax threads
-    const uint32_t lane_addr = tmem_base + (uint32_t((warp & 3) * 32) << 16) + half * 32;  // this warp's lanes, its columns
-    const int pair_id = 1 + (warp & 3);
+    const uint32_t lane_addr = tmem_base + (uint32_t((warp & 3) * 32) << 16) + part * COLS;  // this warp's lanes, its columns
+    const int sync_id = 1 + (warp & 3);
     float m_run = -INFINITY, l_run = 0.f;   // running maximum of the raw scores, this thread's half of the sum
     const float sl2 = p.scale * 1.4426950408889634f;
     // page 0's arrival (the copies were waited for above)
@@ -175,8 +189,8 @@ attention_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
       // (1) this thread's 32 columns of its row of S_i
       if (alive) alive = mbar_wait(bar_s + (i & 1) * 8, (i >> 1) & 1, error_flag, 1);
       tc_fence_after();
-      float s[32];
-      tmem_ld32(lane_addr + (i & 1) * 64, s);
+      float s[COLS];
+      tmem_ld<COLS>(lane_addr + (i & 1) * 64, s);
       // (2) page i + 1: this thread's copies have landed; tell the issuing thread
       if (i + 1 < n_blocks) {
         cp_async_wait<1>();
@@ -186,21 +200,23 @@ attention_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
       // (3) maximum of the visible scores; only pages that reach past some row's position need the test
       float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
       if (i * KEYS + KEYS - 1 > past + q0 || !row_ok) {   // first part is uniform over the block
-        const int visible = row_pos - i * KEYS - half * 32;   // columns j <= visible are seen by this row
+        const int visible = row_pos - i * KEYS - part * COLS;   // columns j <= visible are seen by this row
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
+        for (int j = 0; j < COLS; ++j) {
           s[j] = (j <= visible) ? s[j] : -INFINITY;
           mx[j & 3] = fmaxf(mx[j & 3], s[j]);
         }
       } else {
 #pragma unroll
-        for (int j = 0; j < 32; ++j) mx[j & 3] = fmaxf(mx[j & 3], s[j]);
+        for (int j = 0; j < COLS; ++j) mx[j & 3] = fmaxf(mx[j & 3], s[j]);
       }
-      const float m_half = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
-      float* pm = pmax + (i & 1) * 2 * TQ;
-      pm[half * TQ + row] = m_half;
-      pair_sync(pair_id);   // the two warps that share these 32 rows
-      const float m_blk = fmaxf(m_half, pm[(half ^ 1) * TQ + row]);
+      const float m_part = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+      float* pm = pmax + (i & 1) * TPR * TQ;
+      pm[part * TQ + row] = m_part;
+      row_sync(sync_id);   // the warps that share these 32 rows
+      float m_blk = m_part;
+#pragma unroll
+      for (int o = 1; o < TPR; ++o) m_blk = fmaxf(m_blk, pm[((part + o) % TPR) * TQ + row]);
       const float m_new = fmaxf(m_run, m_blk);
       const float corr = (m_run == -INFINITY) ? 0.f : fast_exp2((m_run - m_new) * sl2);
       const bool moved = (m_new != m_run) && (m_run != -INFINITY);
@@ -214,18 +230,18 @@ attention_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
       load_block(i + 3);
       // (5) rescale this thread's 32 columns of its row of O if any row of the warp moved its maximum
       if (i > 0 && __any_sync(0xffffffffu, moved)) {
-        float o[32];
-        tmem_ld32(lane_addr + 128, o);
+        float o[COLS];
+        tmem_ld<COLS>(lane_addr + 128, o);
 #pragma unroll
-        for (int j = 0; j < 32; ++j) o[j] *= corr;
-        tmem_st32(lane_addr + 128, o);
+        for (int j = 0; j < COLS; ++j) o[j] *= corr;
+        tmem_st<COLS>(lane_addr + 128, o);
         tmem_st_wait();
       }
       l_run *= corr;
       // (6) P = exp2(S - max) as bfloat16 into the swizzled P tile: row, chunks 4 half .. 4 half + 3
       float ls[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < COLS / 8; ++c) {
         uint32_t w[4];
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
@@ -234,7 +250,7 @@ attention_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
           ls[e] += a + b;
           w[e] = pack_bf16(a, b);
         }
-        *reinterpret_cast<uint4*>(p_tile + swz<KEYS>(row, half * 4 + c)) = make_uint4(w[0], w[1], w[2], w[3]);
+        *reinterpret_cast<uint4*>(p_tile + swz<KEYS>(row, part * (COLS / 8) + c)) = make_uint4(w[0], w[1], w[2], w[3]);
       }
       l_run += (ls[0] + ls[1]) + (ls[2] + ls[3]);   // this thread's half of the row sum
       proxy_fence_async();
@@ -242,19 +258,22 @@ attention_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
       mbar_arrive(bar_p);   // (7) the issuing thread starts O += P V when all 256 have arrived
     }
     cp_async_wait<0>();
-    // the two halves of every row sum meet
-    pmax[half * TQ + row] = l_run;
-    pair_sync(pair_id);
-    const float l_row = l_run + pmax[(half ^ 1) * TQ + row];
+    // the parts of every row sum meet, in the buffer that the last page did not use, in one order
+    float* pl = pmax + (n_blocks & 1) * TPR * TQ;
+    pl[part * TQ + row] = l_run;
+    row_sync(sync_id);
+    float l_row = 0.f;
+#pragma unroll
+    for (int o = 0; o < TPR; ++o) l_row += pl[o * TQ + row];
     if (alive) alive = mbar_wait(bar_o, (n_blocks - 1) & 1, error_flag, 3);
     tc_fence_after();
     const float inv = l_row > 0.f ? 1.f / l_row : 0.f;
-    __nv_bfloat16* dst = out + (size_t(start + q0 + row) * p.heads + h) * D + half * 32;
-    float o[32];
-    tmem_ld32(lane_addr + 128, o);
+    __nv_bfloat16* dst = out + (size_t(start + q0 + row) * p.heads + h) * D + part * COLS;
+    float o[COLS];
+    tmem_ld<COLS>(lane_addr + 128, o);
     if (row_ok) {
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < COLS / 8; ++c) {
         uint32_t w[4];
 #pragma unroll
         for (int e = 0; e < 4; ++e) w[e] = pack_bf16(o[c * 8 + 2 * e] * inv, o[c * 8 + 2 * e + 1] * inv);
@@ -282,7 +301,7 @@ PTB_API int ptb_attention_tc(const void* q, const void* k_pool, const void* v_po
   if (n_tiles <= 0) return PTB_OK;
   if (head_dim != D || heads <= 0 || kv_heads <= 0 || heads % kv_heads != 0 || heads > 65535 || error_flag == nullptr)
     return PTB_ERR_SIZE;
-  const size_t smem = 1024 + TILE_Q_BYTES + 2 * STAGES_TC * TILE_KV_BYTES + TILE_P_BYTES + 128 + 4 * TQ * sizeof(float);
+  const size_t smem = 1024 + TILE_Q_BYTES + 2 * STAGES_TC * TILE_KV_BYTES + TILE_P_BYTES + 128 + 2 * TPR * TQ * sizeof(float);
   static bool configured = false;
   if (!configured) {
     if (cudaFuncSetAttribute(attention_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess)

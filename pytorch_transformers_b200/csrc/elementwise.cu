@@ -148,12 +148,126 @@ __global__ void norm_kernel(const T* __restrict__ x, const T* __restrict__ adden
   }
 }
 
+// The same for bfloat16 rows that move in 16-byte words, with the row in registers: thread t holds
+// the words t, t + 256, ... (VPT of them), so there is no pass through shared memory and a block
+// needs only the two reductions. 256 threads: rows up to 2048 * VPT values.
+constexpr int NORM_REG_THREADS = 256;
+__device__ __forceinline__ void load_f32x8(const float* __restrict__ p, float (&v)[8]) {   // p 16-byte aligned
+  const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+  v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+template <int VPT>
+__global__ void __launch_bounds__(NORM_REG_THREADS)
+norm_bf16_reg_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ addend,
+                     __nv_bfloat16* __restrict__ sum_out, const float* __restrict__ gain1,
+                     const float* __restrict__ bias1, __nv_bfloat16* __restrict__ y1,
+                     const float* __restrict__ gain2, const float* __restrict__ bias2,
+                     __nv_bfloat16* __restrict__ y2, int width, float eps, int kind) {
+  __shared__ float scratch[32];
+  const size_t base = size_t(blockIdx.x) * width;
+  const int nvec = width / 8;
+  const uint4* xv = reinterpret_cast<const uint4*>(x + base);
+  const uint4* av = addend ? reinterpret_cast<const uint4*>(addend + base) : nullptr;
+  uint4* sv = addend ? reinterpret_cast<uint4*>(sum_out + base) : nullptr;
+  float f[VPT][8];
+  uint4 raw[VPT], rawa[VPT];
+#pragma unroll
+  for (int v = 0; v < VPT; ++v) {   // all loads first: they are in flight together
+    const int i = threadIdx.x + v * NORM_REG_THREADS;
+    raw[v] = i < nvec ? xv[i] : make_uint4(0, 0, 0, 0);
+    rawa[v] = (av && i < nvec) ? av[i] : make_uint4(0, 0, 0, 0);
+  }
+  float s = 0.f;
+#pragma unroll
+  for (int v = 0; v < VPT; ++v) {
+    const int i = threadIdx.x + v * NORM_REG_THREADS;
+    unpack_bf16x8(raw[v], f[v]);
+    if (av) {
+      float g[8];
+      unpack_bf16x8(rawa[v], g);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) f[v][e] += g[e];
+      const uint4 r = pack_bf16x8(f[v]);
+      if (i < nvec) sv[i] = r;
+      unpack_bf16x8(r, f[v]);
+    }
+#pragma unroll
+    for (int e = 0; e < 8; ++e) s += f[v][e];
+  }
+  float mean = 0.f;
+  if (kind == 0) mean = block_sum(s, scratch) / float(width);
+  float q = 0.f;
+#pragma unroll
+  for (int v = 0; v < VPT; ++v) {
+    if (threadIdx.x + v * NORM_REG_THREADS < nvec) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const float c = f[v][e] - mean;
+        q += c * c;
+      }
+    }
+  }
+  const float var = block_sum(q, scratch) / float(width);
+  const float rstd = 1.0f / sqrtf(var + eps);
+  uint4* o1 = reinterpret_cast<uint4*>(y1 + base);
+  uint4* o2 = gain2 ? reinterpret_cast<uint4*>(y2 + base) : nullptr;
+#pragma unroll
+  for (int v = 0; v < VPT; ++v) {
+    const int i = threadIdx.x + v * NORM_REG_THREADS;
+    if (i >= nvec) continue;
+    float n[8], a[8], gb[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) n[e] = (f[v][e] - mean) * rstd;
+    load_f32x8(gain1 + i * 8, gb);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) a[e] = n[e] * gb[e];
+    if (bias1) {
+      load_f32x8(bias1 + i * 8, gb);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) a[e] += gb[e];
+    }
+    o1[i] = pack_bf16x8(a);
+    if (o2) {
+      load_f32x8(gain2 + i * 8, gb);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) a[e] = n[e] * gb[e];
+      if (bias2) {
+        load_f32x8(bias2 + i * 8, gb);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) a[e] += gb[e];
+      }
+      o2[i] = pack_bf16x8(a);
+    }
+  }
+}
+
+template <int VPT>
+void launch_norm_reg(const void* x, const void* addend, void* sum_out, const float* gain1, const float* bias1, void* y1,
+                     const float* gain2, const float* bias2, void* y2, int n, int width, float eps, int kind,
+                     cudaStream_t stream) {
+  norm_bf16_reg_kernel<VPT><<<n, NORM_REG_THREADS, 0, stream>>>(
+      (const __nv_bfloat16*)x, (const __nv_bfloat16*)addend, (__nv_bfloat16*)sum_out, gain1, bias1,
+      (__nv_bfloat16*)y1, gain2, bias2, (__nv_bfloat16*)y2, width, eps, kind);
+}
+
 PTB_API int ptb_norm(int dtype, const void* x, const void* addend, void* sum_out, const float* gain1,
                      const float* bias1, void* y1, const float* gain2, const float* bias2, void* y2, int n, int width,
                      float eps, int kind, cudaStream_t stream) {
   if (n <= 0) return PTB_OK;
   if (width <= 0 || kind < 0 || kind > 1) return PTB_ERR_SIZE;
   if ((addend == nullptr) != (sum_out == nullptr)) return PTB_ERR_SIZE;
+  const bool all16 = aligned16(x) && aligned16(y1) && aligned16(gain1) && (!bias1 || aligned16(bias1)) &&
+                     (!addend || (aligned16(addend) && aligned16(sum_out))) &&
+                     (!gain2 || (aligned16(y2) && aligned16(gain2) && (!bias2 || aligned16(bias2))));
+  if (dtype == PTB_BF16 && width % 8 == 0 && width <= 2048 * 8 && all16) {
+    const int vpt = (width / 8 + NORM_REG_THREADS - 1) / NORM_REG_THREADS;
+    if (vpt <= 1) launch_norm_reg<1>(x, addend, sum_out, gain1, bias1, y1, gain2, bias2, y2, n, width, eps, kind, stream);
+    else if (vpt <= 2) launch_norm_reg<2>(x, addend, sum_out, gain1, bias1, y1, gain2, bias2, y2, n, width, eps, kind, stream);
+    else if (vpt <= 4) launch_norm_reg<4>(x, addend, sum_out, gain1, bias1, y1, gain2, bias2, y2, n, width, eps, kind, stream);
+    else launch_norm_reg<8>(x, addend, sum_out, gain1, bias1, y1, gain2, bias2, y2, n, width, eps, kind, stream);
+    return launch_status();
+  }
   const size_t smem = size_t(width) * sizeof(float);
   if (smem > 200 * 1024) return PTB_ERR_SIZE;
   const int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);

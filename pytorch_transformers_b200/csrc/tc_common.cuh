@@ -7,6 +7,10 @@
 #include "mma_common.cuh"
 
 constexpr uint32_t WAIT_LIMIT = 1u << 20;
+// Time hint for one try_wait: the hardware may park the thread this long instead of returning "not
+// yet" at once, so waiting threads leave the issue slots to the working ones. A wait gives up after
+// WAIT_LIMIT tries: some seconds at most.
+constexpr uint32_t WAIT_SUSPEND_NS = 2000;
 
 // ---- shared-memory matrix descriptor (sm_100): start address, leading and stride byte offsets in
 // 16-byte units, version 1, layout type 2 = 128-byte swizzle
@@ -27,9 +31,9 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}\n"
-      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+      : "=r"(ok) : "r"(bar), "r"(parity), "r"(WAIT_SUSPEND_NS) : "memory");
   return ok != 0;
 }
 // bounded wait: false (and the error flag raised) if the barrier did not complete in time
@@ -112,10 +116,12 @@ __device__ __forceinline__ void tmem_ld8(uint32_t taddr, float (&v)[8]) {
 #pragma unroll
   for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[i]);
 }
-// D (+)= A B over 64 values of k between K-major 128-byte-swizzled tiles: four matrix instructions
-// of 16 k each (32 bytes = 2 descriptor units along a swizzled row), the first one overwriting D
-// when `accumulate` is 0. One asm block: the issuing thread's instruction count per tile matters,
-// it is the one thread that feeds the tensor core.
+// D (+)= A B over 64 values of k: four matrix instructions of 16 k each, the first one overwriting D
+// when `accumulate` is 0. From one instruction to the next the A descriptor advances by A_STEP and
+// the B descriptor by B_STEP units of 16 bytes: 2 along a 128-byte-swizzled K-major row (16 k = 32
+// bytes), 128 down the rows of an MN-major tile (16 rows of 128 bytes). One asm block: the issuing
+// thread's instruction count per tile matters, it is the one thread that feeds the tensor core.
+template <int A_STEP = 2, int B_STEP = 2>
 __device__ __forceinline__ void tc_mma4(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
                                         uint32_t accumulate) {
   asm volatile(
@@ -123,11 +129,55 @@ __device__ __forceinline__ void tc_mma4(uint32_t d_tmem, uint64_t a_desc, uint64
       "setp.ne.b32 p, %4, 0;\n\t"
       "setp.eq.b32 q, %3, %3;\n\t"
       "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t"
-      "add.u64 a, %1, 2;\n\tadd.u64 b, %2, 2;\n\t"
+      "add.u64 a, %1, %5;\n\tadd.u64 b, %2, %6;\n\t"
       "tcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, q;\n\t"
-      "add.u64 a, %1, 4;\n\tadd.u64 b, %2, 4;\n\t"
+      "add.u64 a, a, %5;\n\tadd.u64 b, b, %6;\n\t"
       "tcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, q;\n\t"
-      "add.u64 a, %1, 6;\n\tadd.u64 b, %2, 6;\n\t"
+      "add.u64 a, a, %5;\n\tadd.u64 b, b, %6;\n\t"
       "tcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, q;\n\t}\n"
-      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "n"(A_STEP), "n"(B_STEP) : "memory");
+}
+
+// N consecutive columns of this thread's lane, N = 16 or 32
+template <int N> __device__ __forceinline__ void tmem_ld(uint32_t taddr, float (&v)[N]);
+template <> __device__ __forceinline__ void tmem_ld<32>(uint32_t taddr, float (&v)[32]) { tmem_ld32(taddr, v); }
+template <> __device__ __forceinline__ void tmem_ld<16>(uint32_t taddr, float (&v)[16]) {
+  uint32_t r[16];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];\n"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+template <int N> __device__ __forceinline__ void tmem_st(uint32_t taddr, const float (&v)[N]);
+template <> __device__ __forceinline__ void tmem_st<32>(uint32_t taddr, const float (&v)[32]) { tmem_st32(taddr, v); }
+template <> __device__ __forceinline__ void tmem_st<16>(uint32_t taddr, const float (&v)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};\n"
+      ::"r"(taddr), "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])),
+        "r"(__float_as_uint(v[3])), "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])),
+        "r"(__float_as_uint(v[6])), "r"(__float_as_uint(v[7])), "r"(__float_as_uint(v[8])),
+        "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])), "r"(__float_as_uint(v[11])),
+        "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])),
+        "r"(__float_as_uint(v[15]))
+      : "memory");
+}
+template <> __device__ __forceinline__ void tmem_ld<64>(uint32_t taddr, float (&v)[64]) {
+  float a[32], b[32];
+  tmem_ld32(taddr, a);
+  tmem_ld32(taddr + 32, b);
+#pragma unroll
+  for (int i = 0; i < 32; ++i) { v[i] = a[i]; v[32 + i] = b[i]; }
+}
+template <> __device__ __forceinline__ void tmem_st<64>(uint32_t taddr, const float (&v)[64]) {
+  float a[32], b[32];
+#pragma unroll
+  for (int i = 0; i < 32; ++i) { a[i] = v[i]; b[i] = v[32 + i]; }
+  tmem_st32(taddr, a);
+  tmem_st32(taddr + 32, b);
 }

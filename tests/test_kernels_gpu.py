@@ -46,7 +46,8 @@ def test_gather_rows(K, dtype, width):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("rows,width,eps", [(1, 64, 1e-5), (5, 96, 1e-6), (3, 4544, 1e-5), (2, 8192, 1e-5),
-                                            (4, 1001, 1e-3), (2, 20000, 1e-5)])
+                                            (4, 1001, 1e-3), (2, 20000, 1e-5), (300, 4544, 1e-5), (2, 16384, 1e-5),
+                                            (2, 16392, 1e-5), (7, 2056, 1e-5)])
 def test_layernorm_and_pair(K, dtype, rows, width, eps):
     x = rnd(rows, width, dtype=dtype, scale=3.0) + 0.5
     g1, b1 = rnd(width, seed=1) + 1, rnd(width, seed=2)
