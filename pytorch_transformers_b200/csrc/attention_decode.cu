@@ -60,22 +60,6 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ fused, __nv_bfloat16* 
   const float* rs = rope_sin ? rope_sin + size_t(tok) * p.rot_pairs : nullptr;
   const int P = rc ? p.rot_pairs : 0;          // pairs (e, e + P) are rotated for e < P
 
-  // rotated value of element e of a fused row (query head or key)
-  auto rotated = [&](const __nv_bfloat16* row, int e) -> float {
-    const float v = __bfloat162float(row[e]);
-    if (e < P) {
-      float a, b;
-      rotate_pair(v, __bfloat162float(row[e + P]), rc[e], rs[e], a, b);
-      return a;
-    }
-    if (e < 2 * P) {
-      float a, b;
-      rotate_pair(__bfloat162float(row[e - P]), v, rc[e - P], rs[e - P], a, b);
-      return b;
-    }
-    return v;
-  };
-
   bool row_ok[2];
   int row_head[2];
 #pragma unroll
@@ -89,24 +73,6 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ fused, __nv_bfloat16* 
     for (int i = 0; i < 2; ++i)
       if (row_ok[i]) slope[i] = alibi_slopes[g * qpk + h0 + row_head[i]];
   }
-  // Q fragments: rotated, rounded to bfloat16 as the stored queries of the three-kernel path are
-  uint32_t qa[D / 16][4];
-#pragma unroll
-  for (int kk = 0; kk < D / 16; ++kk) {
-#pragma unroll
-    for (int i = 0; i < 2; ++i) {
-      uint32_t lo = 0u, hi = 0u;
-      if (row_ok[i]) {
-        const __nv_bfloat16* qr = frow + size_t(h0 + row_head[i]) * D;
-        const int e = kk * 16 + t4 * 2;
-        lo = pack_bf16(rotated(qr, e), rotated(qr, e + 1));
-        hi = pack_bf16(rotated(qr, e + 8), rotated(qr, e + 9));
-      }
-      qa[kk][i] = lo;
-      qa[kk][2 + i] = hi;
-    }
-  }
-
   // pages of this block
   int kb_first = 0;
   if (p.window > 0) kb_first = max(0, pos - p.window + 1) / KEYS;
@@ -118,14 +84,69 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ fused, __nv_bfloat16* 
   const int* pages = sb.pages + size_t(seq) * sb.pages_stride;
   const int n_mine = max(0, kb_end - kb_begin);
 
-  // the new token's key and value go to the cache once per (sequence, K/V head)
-  const __nv_bfloat16* krow = frow + size_t(qpk) * D;
+  auto issue = [&](int i) {  // copy page kb_begin + i into stage i % STAGES (or nothing), one group
+    if (i < n_mine) {
+      const int page = pages[kb_begin + i];
+      const uint32_t dst = smem_base + (i % STAGES) * 2 * TILE_BYTES;
+      load_page<D>(dst, k_pool + kv_offset(page, g, 0, p.kv_heads, D), tid, nthreads);
+      load_page<D>(dst + TILE_BYTES, v_pool + kv_offset(page, g, 0, p.kv_heads, D), tid, nthreads);
+    }
+    cp_async_commit();
+  };
+  for (int i = 0; i < STAGES - 1; ++i) issue(i);   // the first pages travel while the token's row is prepared
+
+  // The token's row of the fused projection, staged after the page ring: rows 0 .. hpk - 1 the query
+  // heads of this chunk, row hpk its key, row hpk + 1 its value; 16-byte copies, then the rotation in
+  // place (pairs (e, e + P)), rounded to bfloat16 as the stored queries of the three-kernel path are.
+  __nv_bfloat16* rowbuf = reinterpret_cast<__nv_bfloat16*>(smem_raw + size_t(STAGES) * 2 * TILE_BYTES);
+  float* cs = reinterpret_cast<float*>(rowbuf + size_t(p.hpk + 2) * D);   // cos[P], sin[P]
+  {
+    const uint4* src_q = reinterpret_cast<const uint4*>(frow + size_t(h0) * D);
+    const uint4* src_kv = reinterpret_cast<const uint4*>(frow + size_t(qpk) * D);
+    uint4* dst_q = reinterpret_cast<uint4*>(rowbuf);
+    uint4* dst_kv = reinterpret_cast<uint4*>(rowbuf + size_t(p.hpk) * D);
+    for (int i = tid; i < head_valid * (D / 8); i += nthreads) dst_q[i] = src_q[i];
+    for (int i = tid; i < 2 * (D / 8); i += nthreads) dst_kv[i] = src_kv[i];
+    for (int e = tid; e < P; e += nthreads) {
+      cs[e] = rc[e];
+      cs[P + e] = rs[e];
+    }
+  }
+  __syncthreads();
+  for (int idx = tid; idx < (head_valid + 1) * P; idx += nthreads) {
+    const int r = idx / P, e = idx % P;
+    __nv_bfloat16* row = rowbuf + size_t(r < head_valid ? r : p.hpk) * D;
+    float ra, rb;
+    rotate_pair(__bfloat162float(row[e]), __bfloat162float(row[e + P]), cs[e], cs[P + e], ra, rb);
+    row[e] = __float2bfloat16_rn(ra);
+    row[e + P] = __float2bfloat16_rn(rb);
+  }
+  __syncthreads();
+  const __nv_bfloat16* krow = rowbuf + size_t(p.hpk) * D;   // rotated key, value
   const __nv_bfloat16* vrow = krow + D;
+  // Q fragments
+  uint32_t qa[D / 16][4];
+#pragma unroll
+  for (int kk = 0; kk < D / 16; ++kk) {
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      uint32_t lo = 0u, hi = 0u;
+      if (row_ok[i]) {
+        const __nv_bfloat16* qr = rowbuf + size_t(row_head[i]) * D + kk * 16 + t4 * 2;
+        lo = *reinterpret_cast<const uint32_t*>(qr);
+        hi = *reinterpret_cast<const uint32_t*>(qr + 8);
+      }
+      qa[kk][i] = lo;
+      qa[kk][2 + i] = hi;
+    }
+  }
+
+  // the new token's key and value go to the cache once per (sequence, K/V head)
   const bool covers_new = n_mine > 0 && kb_end == kb_last + 1;
   if (p.write_cache && chunk == 0 && covers_new) {
     const size_t off = kv_offset(pages[kb_last], g, pos % KEYS, p.kv_heads, D);
     for (int e = tid; e < D; e += nthreads) {
-      k_pool[off + e] = __float2bfloat16_rn(rotated(krow, e));
+      k_pool[off + e] = krow[e];
       v_pool[off + e] = vrow[e];
     }
   }
@@ -136,16 +157,6 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ fused, __nv_bfloat16* 
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
   const float sl2 = p.scale * 1.4426950408889634f;
 
-  auto issue = [&](int i) {  // copy page kb_begin + i into stage i % STAGES (or nothing), one group
-    if (i < n_mine) {
-      const int page = pages[kb_begin + i];
-      const uint32_t dst = smem_base + (i % STAGES) * 2 * TILE_BYTES;
-      load_page<D>(dst, k_pool + kv_offset(page, g, 0, p.kv_heads, D), tid, nthreads);
-      load_page<D>(dst + TILE_BYTES, v_pool + kv_offset(page, g, 0, p.kv_heads, D), tid, nthreads);
-    }
-    cp_async_commit();
-  };
-  for (int i = 0; i < STAGES - 1; ++i) issue(i);
   for (int i = 0; i < n_mine; ++i) {
     const int kb = kb_begin + i;
     issue(i + STAGES - 1);
@@ -158,7 +169,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ fused, __nv_bfloat16* 
       const int r = pos % KEYS;
       for (int e = tid; e < D; e += nthreads) {
         const uint32_t o2 = swz<D>(r, e >> 3) + (e & 7) * 2;
-        *reinterpret_cast<__nv_bfloat16*>(kt + o2) = __float2bfloat16_rn(rotated(krow, e));
+        *reinterpret_cast<__nv_bfloat16*>(kt + o2) = krow[e];
         *reinterpret_cast<__nv_bfloat16*>(kt + TILE_BYTES + o2) = vrow[e];
       }
       __syncthreads();
@@ -176,19 +187,33 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ fused, __nv_bfloat16* 
       }
     }
     float m_blk[2] = {-INFINITY, -INFINITY};
+    // a page that every row sees whole, without a bias: scale and maximum only (rows past the valid
+    // heads have zero queries; their numbers are never written)
+    const bool whole_page = kb < kb_last && !alibi_slopes && (p.window == 0 || kb * KEYS > pos - p.window);
+    if (whole_page) {
 #pragma unroll
-    for (int j = 0; j < KEYS / 8; ++j) {
+      for (int j = 0; j < KEYS / 8; ++j) {
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int i2 = e >> 1;
-        const int key_pos = kb * KEYS + j * 8 + t4 * 2 + (e & 1);
-        bool visible = row_ok[i2] && key_pos <= pos;
-        if (p.window > 0) visible = visible && key_pos > pos - p.window;
-        float v = s[j][e];
-        if (alibi_slopes) v += alibi_bias(slope[i2], key_pos);
-        v = visible ? v * sl2 : -INFINITY;
-        s[j][e] = v;
-        m_blk[i2] = fmaxf(m_blk[i2], v);
+        for (int e = 0; e < 4; ++e) {
+          s[j][e] *= sl2;
+          m_blk[e >> 1] = fmaxf(m_blk[e >> 1], s[j][e]);
+        }
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < KEYS / 8; ++j) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int i2 = e >> 1;
+          const int key_pos = kb * KEYS + j * 8 + t4 * 2 + (e & 1);
+          bool visible = row_ok[i2] && key_pos <= pos;
+          if (p.window > 0) visible = visible && key_pos > pos - p.window;
+          float v = s[j][e];
+          if (alibi_slopes) v += alibi_bias(slope[i2], key_pos);
+          v = visible ? v * sl2 : -INFINITY;
+          s[j][e] = v;
+          m_blk[i2] = fmaxf(m_blk[i2], v);
+        }
       }
     }
     float corr[2];
@@ -308,7 +333,9 @@ int launch_decode(const void* fused, void* k_pool, void* v_pool, void* out, cons
                   int warps, cudaStream_t stream) {
   const int qpk = p.heads / p.kv_heads;
   const int chunks = (qpk + p.hpk - 1) / p.hpk;
-  size_t smem = size_t(STAGES) * 2 * KEYS * D * 2;
+  // page ring, then the token's row (query heads of the chunk, key, value) and its cos/sin
+  const size_t ring = size_t(STAGES) * 2 * KEYS * D * 2;
+  size_t smem = ring + size_t(p.hpk + 2) * D * 2 + size_t(D) * sizeof(float);
   const size_t join = size_t(warps) * 16 * (D + 2) * sizeof(float);  // partial results reuse the ring
   if (join > smem) smem = join;
   static size_t configured = 0;
@@ -357,7 +384,7 @@ PTB_API int ptb_attention_decode(const void* fused, void* k_pool, void* v_pool, 
   if (heads <= 0 || kv_heads <= 0 || heads % kv_heads != 0 || warps < 1 || warps > 8 || hpk < 1 ||
       hpk > warps * 16 || rot_pairs < 0 || 2 * rot_pairs > head_dim)
     return PTB_ERR_SIZE;
-  if (n_splits != 1 && n_splits != 2 && n_splits != 4 && n_splits != 8) return PTB_ERR_SIZE;
+  if (n_splits < 1 || n_splits > 8) return PTB_ERR_SIZE;   // a cluster holds at most 8 blocks
   if ((rope_cos == nullptr) != (rope_sin == nullptr)) return PTB_ERR_SIZE;
   const int qpk = heads / kv_heads;
   const int chunks = (qpk + hpk - 1) / hpk;
