@@ -1,5 +1,7 @@
 // Prompt attention on the fifth-generation tensor cores (tcgen05) with the accumulators in tensor
-// memory, for head size 64, bfloat16, causal, over the paged cache.
+// memory, for head sizes 64 and 128, bfloat16, causal, over the paged cache. The description below
+// is for head size 64; with 128 the tiles of Q, K and V are two blocks of 64 dims, S takes two groups
+// of matrix instructions, O two (one per 64 dims of the output), and one block fits on an SM.
 //
 // One block = 128 consecutive new tokens of one sequence x one query head. 256 softmax threads: threads t
 // and t + 128 share query row t (tensor-memory lane t), each taking 32 of a page's 64 columns (TPR
@@ -40,11 +42,24 @@
 namespace {
 
 constexpr int TQ = 128;          // query rows per block
-constexpr int D = 64;            // head size
 constexpr int STAGES_TC = 4;
-constexpr int TILE_Q_BYTES = TQ * D * 2;       // 16 KB
-constexpr int TILE_KV_BYTES = KEYS * D * 2;    // 8 KB
 constexpr int TILE_P_BYTES = TQ * KEYS * 2;    // 16 KB
+// Tiles of D = 64 or 128 dims are kept as D / 64 blocks of [rows][64 dims], one after another, each
+// block with the 128-byte swizzle: the layout that the matrix descriptors name for K-major operands
+// (Q, K: a block per 64 values of the contraction) and for the MN-major V (a block per 64 dims of
+// the output). Byte offset of 16-byte chunk `c` of row `row`:
+template <int ROWS> __device__ __forceinline__ uint32_t swz_tc(int row, int c) {
+  return uint32_t((c >> 3) * (ROWS * 128) + row * 128 + (((c & 7) ^ (row & 7)) << 4));
+}
+// copy one page [KEYS][D] (contiguous in global memory) into such a tile
+template <int D>
+__device__ __forceinline__ void load_page_tc(uint32_t smem_tile, const __nv_bfloat16* page, int tid, int nthreads) {
+  constexpr int CHUNKS = D / 8;
+  for (int i = tid; i < KEYS * CHUNKS; i += nthreads) {
+    const int row = i / CHUNKS, c = i % CHUNKS;
+    cp_async16(smem_tile + swz_tc<KEYS>(row, c), page + size_t(row) * D + c * 8);
+  }
+}
 struct TcParams {
   int heads, kv_heads;
   float scale;
@@ -55,11 +70,11 @@ constexpr int COLS = KEYS / TPR;                    // columns of a page that a 
 constexpr int SOFTMAX_THREADS = TPR * TQ;
 constexpr int BLOCK_THREADS = SOFTMAX_THREADS + 32;  // and one warp whose first lane issues the matrix instructions
 
-// barrier among the 64 threads of two warps (ids 1..4 are used)
 // barrier among the TPR warps that share 32 query rows (ids 1..4 are used)
 __device__ __forceinline__ void row_sync(int id) { asm volatile("bar.sync %0, %1;\n" ::"r"(id), "n"(TPR * 32) : "memory"); }
 
-__global__ void __launch_bounds__(BLOCK_THREADS, 2)
+template <int D>
+__global__ void __launch_bounds__(BLOCK_THREADS, D == 64 ? 2 : 1)
 attention_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_pool,
                     const __nv_bfloat16* __restrict__ v_pool, __nv_bfloat16* __restrict__ out, StepBatch sb,
                     const int* __restrict__ tile_seq, const int* __restrict__ tile_q0, TcParams p,
@@ -67,9 +82,12 @@ attention_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
   extern __shared__ unsigned char smem_dyn[];
   // 1024-byte alignment: the swizzle pattern is a function of address bits 4..9
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
-  unsigned char* q_tile = smem;                                       // 16 KB
-  unsigned char* k_ring = q_tile + TILE_Q_BYTES;                      // STAGES_TC x 8 KB
-  unsigned char* v_ring = k_ring + STAGES_TC * TILE_KV_BYTES;         // STAGES_TC x 8 KB
+  constexpr int TILE_Q_BYTES = TQ * D * 2;       // 16 or 32 KB
+  constexpr int TILE_KV_BYTES = KEYS * D * 2;    // 8 or 16 KB
+  constexpr int COLS_O = D / TPR;                // columns of O that a thread rescales and writes
+  unsigned char* q_tile = smem;
+  unsigned char* k_ring = q_tile + TILE_Q_BYTES;                      // STAGES_TC pages
+  unsigned char* v_ring = k_ring + STAGES_TC * TILE_KV_BYTES;         // STAGES_TC pages
   unsigned char* p_tile = v_ring + STAGES_TC * TILE_KV_BYTES;         // 16 KB
   // barriers: [0], [1] S buffer written; [2] O updated; [3] P written; [4 ..] page landed, per stage
   uint64_t* bars = reinterpret_cast<uint64_t*>(p_tile + TILE_P_BYTES);
@@ -110,10 +128,10 @@ attention_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
     if (b < n_blocks) {
       const int page = pages[b];
       const int st = b % STAGES_TC;
-      load_page<D>(smem_u32(k_ring + st * TILE_KV_BYTES), k_pool + kv_offset(page, g, 0, p.kv_heads, D), tid,
-                   SOFTMAX_THREADS);
-      load_page<D>(smem_u32(v_ring + st * TILE_KV_BYTES), v_pool + kv_offset(page, g, 0, p.kv_heads, D), tid,
-                   SOFTMAX_THREADS);
+      load_page_tc<D>(smem_u32(k_ring + st * TILE_KV_BYTES), k_pool + kv_offset(page, g, 0, p.kv_heads, D), tid,
+                      SOFTMAX_THREADS);
+      load_page_tc<D>(smem_u32(v_ring + st * TILE_KV_BYTES), v_pool + kv_offset(page, g, 0, p.kv_heads, D), tid,
+                      SOFTMAX_THREADS);
     }
     cp_async_commit();
   };
@@ -123,9 +141,9 @@ attention_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
     for (int i = tid; i < TQ * (D / 8); i += SOFTMAX_THREADS) {
       const int r = i / (D / 8), c = i % (D / 8);
       if (r < tok_valid)
-        cp_async16(qs + swz<D>(r, c), q + (size_t(start + q0 + r) * p.heads + h) * D + c * 8);
+        cp_async16(qs + swz_tc<TQ>(r, c), q + (size_t(start + q0 + r) * p.heads + h) * D + c * 8);
       else
-        *reinterpret_cast<uint4*>(q_tile + swz<D>(r, c)) = make_uint4(0, 0, 0, 0);
+        *reinterpret_cast<uint4*>(q_tile + swz_tc<TQ>(r, c)) = make_uint4(0, 0, 0, 0);
     }
     load_block(0);  // group 0 also holds the Q tile
     load_block(1);
@@ -137,22 +155,26 @@ attention_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
   __syncthreads();        // barriers, tensor memory, Q and page 0 are ready for everyone
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tmem_o = tmem_base + 128;   // S buffers at columns [0, 64) and [64, 128), O at [128, 192)
+  const uint32_t tmem_o = tmem_base + 128;   // S buffers at columns [0, 64) and [64, 128), O at [128, 128 + D)
   bool alive = true;  // false after a wait ran out: keep going without waiting, results are void
 
   if (mma_warp) {
     // ------------------------------------------------------------ the thread that issues matrix instructions
     if (lane == 0) {
       constexpr uint32_t IDESC_S = idesc_bf16(TQ, KEYS, false);
-      constexpr uint32_t IDESC_PV = idesc_bf16(TQ, D, true);
+      constexpr uint32_t IDESC_PV = idesc_bf16(TQ, 64, true);   // 64 dims of the output per instruction
       const uint64_t desc_q = smem_desc(smem_u32(q_tile), 16, 1024);
       const uint64_t desc_p = smem_desc(smem_u32(p_tile), 16, 1024);
       const uint64_t desc_k0 = smem_desc(smem_u32(k_ring), 16, 1024);
       const uint64_t desc_v0 = smem_desc(smem_u32(v_ring), 16, 1024);
       constexpr uint64_t STAGE_UNITS = TILE_KV_BYTES >> 4;   // the address field counts 16-byte units
+      constexpr uint64_t Q_BLOCK = (TQ * 128) >> 4, KV_BLOCK = (KEYS * 128) >> 4;   // blocks of 64 dims
       // S_b = Q K_b^T into S buffer b & 1; the page sits in stage `st`
       auto issue_s = [&](int b, int st) {
-        tc_mma4<2, 2>(tmem_base + (b & 1) * 64, desc_q, desc_k0 + st * STAGE_UNITS, IDESC_S, 0u);
+#pragma unroll
+        for (int blk = 0; blk < D / 64; ++blk)
+          tc_mma4<2, 2>(tmem_base + (b & 1) * 64, desc_q + blk * Q_BLOCK, desc_k0 + st * STAGE_UNITS + blk * KV_BLOCK,
+                        IDESC_S, blk > 0 ? 1u : 0u);
         tc_commit(bar_s + (b & 1) * 8);
       };
       issue_s(0, 0);   // page 0 was waited for before the block-wide barrier above
@@ -171,7 +193,10 @@ attention_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
         if (alive) alive = mbar_wait(bar_p, i & 1, error_flag, 5);
         proxy_fence_async();
         tc_fence_after();
-        tc_mma4<2, 128>(tmem_o, desc_p, desc_v0 + st * STAGE_UNITS, IDESC_PV, i > 0 ? 1u : 0u);
+#pragma unroll
+        for (int blk = 0; blk < D / 64; ++blk)
+          tc_mma4<2, 128>(tmem_o + blk * 64, desc_p, desc_v0 + st * STAGE_UNITS + blk * KV_BLOCK, IDESC_PV,
+                          i > 0 ? 1u : 0u);
         tc_commit(bar_o);
         st = st_next;
         st_next = (st_next + 1 == STAGES_TC) ? 0 : st_next + 1;
@@ -180,6 +205,7 @@ attention_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
   } else {
     // ------------------------------------------------------------ softmax threads
     const uint32_t lane_addr = tmem_base + (uint32_t((warp & 3) * 32) << 16) + part * COLS;  // this warp's lanes, its columns
+    const uint32_t o_addr = tmem_base + (uint32_t((warp & 3) * 32) << 16) + 128 + part * COLS_O;   // its columns of O
     const int sync_id = 1 + (warp & 3);
     float m_run = -INFINITY, l_run = 0.f;   // running maximum of the raw scores, this thread's half of the sum
     const float sl2 = p.scale * 1.4426950408889634f;
@@ -230,11 +256,14 @@ attention_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
       load_block(i + 3);
       // (5) rescale this thread's 32 columns of its row of O if any row of the warp moved its maximum
       if (i > 0 && __any_sync(0xffffffffu, moved)) {
-        float o[COLS];
-        tmem_ld<COLS>(lane_addr + 128, o);
 #pragma unroll
-        for (int j = 0; j < COLS; ++j) o[j] *= corr;
-        tmem_st<COLS>(lane_addr + 128, o);
+        for (int c0 = 0; c0 < COLS_O; c0 += 32) {
+          float o[32];
+          tmem_ld32(o_addr + c0, o);
+#pragma unroll
+          for (int j = 0; j < 32; ++j) o[j] *= corr;
+          tmem_st32(o_addr + c0, o);
+        }
         tmem_st_wait();
       }
       l_run *= corr;
@@ -268,16 +297,19 @@ attention_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
     if (alive) alive = mbar_wait(bar_o, (n_blocks - 1) & 1, error_flag, 3);
     tc_fence_after();
     const float inv = l_row > 0.f ? 1.f / l_row : 0.f;
-    __nv_bfloat16* dst = out + (size_t(start + q0 + row) * p.heads + h) * D + part * COLS;
-    float o[COLS];
-    tmem_ld<COLS>(lane_addr + 128, o);
-    if (row_ok) {
+    __nv_bfloat16* dst = out + (size_t(start + q0 + row) * p.heads + h) * D + part * COLS_O;
 #pragma unroll
-      for (int c = 0; c < COLS / 8; ++c) {
-        uint32_t w[4];
+    for (int c0 = 0; c0 < COLS_O; c0 += 32) {
+      float o[32];
+      tmem_ld32(o_addr + c0, o);
+      if (row_ok) {
 #pragma unroll
-        for (int e = 0; e < 4; ++e) w[e] = pack_bf16(o[c * 8 + 2 * e] * inv, o[c * 8 + 2 * e + 1] * inv);
-        *reinterpret_cast<uint4*>(dst + c * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+        for (int c = 0; c < 4; ++c) {
+          uint32_t w[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) w[e] = pack_bf16(o[c * 8 + 2 * e] * inv, o[c * 8 + 2 * e + 1] * inv);
+          *reinterpret_cast<uint4*>(dst + c0 + c * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+        }
       }
     }
   }
@@ -289,30 +321,42 @@ attention_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
 
 }  // namespace
 
-PTB_API int ptb_attention_tc_supports(int head_dim) { return head_dim == D ? 1 : 0; }
+PTB_API int ptb_attention_tc_supports(int head_dim) { return (head_dim == 64 || head_dim == 128) ? 1 : 0; }
 PTB_API int ptb_attention_tc_tile_tokens() { return TQ; }
 
+namespace {
+template <int D>
+int launch_tc(const void* q, const void* k_pool, const void* v_pool, void* out, const StepBatch& sb,
+              const int* tile_seq, const int* tile_q0, int n_tiles, const TcParams& p, int* error_flag,
+              cudaStream_t stream) {
+  const size_t smem = 1024 + TQ * D * 2 + 2 * STAGES_TC * KEYS * D * 2 + TILE_P_BYTES + 128 + 2 * TPR * TQ * sizeof(float);
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(attention_tc_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess)
+      return PTB_ERR_LAUNCH;
+    configured = true;
+  }
+  dim3 grid(n_tiles, p.heads);
+  attention_tc_kernel<D><<<grid, BLOCK_THREADS, smem, stream>>>(
+      (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, (__nv_bfloat16*)out, sb,
+      tile_seq, tile_q0, p, error_flag);
+  return launch_status();
+}
+}  // namespace
+
 // Causal attention of prompt tiles of 128 tokens (tile_seq / tile_q0 as for the other attention
-// kernels, 128 tokens per tile), bfloat16, head size 64, no bias, no window. `error_flag` is a device
-// int that stays 0 unless a bounded wait inside the kernel ran out.
+// kernels, 128 tokens per tile), bfloat16, head size 64 or 128, no bias, no window. `error_flag` is a
+// device int that stays 0 unless a bounded wait inside the kernel ran out.
 PTB_API int ptb_attention_tc(const void* q, const void* k_pool, const void* v_pool, void* out, const StepBatch* sb,
                              const int* tile_seq, const int* tile_q0, int n_tiles, int heads, int kv_heads,
                              int head_dim, float scale, int* error_flag, cudaStream_t stream) {
   if (n_tiles <= 0) return PTB_OK;
-  if (head_dim != D || heads <= 0 || kv_heads <= 0 || heads % kv_heads != 0 || heads > 65535 || error_flag == nullptr)
+  if ((head_dim != 64 && head_dim != 128) || heads <= 0 || kv_heads <= 0 || heads % kv_heads != 0 || heads > 65535 ||
+      error_flag == nullptr)
     return PTB_ERR_SIZE;
-  const size_t smem = 1024 + TILE_Q_BYTES + 2 * STAGES_TC * TILE_KV_BYTES + TILE_P_BYTES + 128 + 2 * TPR * TQ * sizeof(float);
-  static bool configured = false;
-  if (!configured) {
-    if (cudaFuncSetAttribute(attention_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess)
-      return PTB_ERR_LAUNCH;
-    configured = true;
-  }
   TcParams p;
   p.heads = heads; p.kv_heads = kv_heads; p.scale = scale;
-  dim3 grid(n_tiles, heads);
-  attention_tc_kernel<<<grid, BLOCK_THREADS, smem, stream>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool,
-                                                  (const __nv_bfloat16*)v_pool, (__nv_bfloat16*)out, *sb, tile_seq,
-                                                  tile_q0, p, error_flag);
-  return launch_status();
+  if (head_dim == 64)
+    return launch_tc<64>(q, k_pool, v_pool, out, *sb, tile_seq, tile_q0, n_tiles, p, error_flag, stream);
+  return launch_tc<128>(q, k_pool, v_pool, out, *sb, tile_seq, tile_q0, n_tiles, p, error_flag, stream);
 }

@@ -266,7 +266,7 @@ def attention_tc_supports(head_dim: int) -> bool:
 def attention_tc(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, batch: StepBatchC,
                  tile_seq: torch.Tensor, tile_q0: torch.Tensor, n_tiles: int, kv_heads: int, scale: float):
     """Causal prompt attention on tcgen05 tensor cores with accumulators in tensor memory: bfloat16,
-    head size 64, tiles of 128 tokens, no bias, no window. Returns [tokens, heads * head_dim]."""
+    head size 64 or 128, tiles of 128 tokens, no bias, no window. Returns [tokens, heads * head_dim]."""
     _need_cuda(q, k_pool, v_pool, tile_seq, tile_q0)
     if q.dtype != torch.bfloat16:
         raise KernelError("attention_tc takes bfloat16 tensors")

@@ -161,13 +161,16 @@ def test_rope_table_equals_in_kernel_angles(K):
 @pytest.mark.parametrize("heads,kv", [(1, 1), (3, 1), (71, 1), (8, 2), (4, 4)])
 @pytest.mark.parametrize("news,pasts", [([128], [0]), ([65], [0]), ([129, 300, 70], [0, 0, 0]), ([200, 66], [130, 63]),
                                         ([1000], [0])])
-def test_tc_prompts(K, heads, kv, news, pasts):
-    assert K.lib().ptb_attention_tc_tile_tokens() == K.TC_TILE_TOKENS and K.attention_tc_supports(64)
-    out, ref = attention_case(K, BF, heads, kv, 64, pasts=pasts, news=news, position="rotary", seed=11, tc=True)
+@pytest.mark.parametrize("d", [64, 128])
+def test_tc_prompts(K, heads, kv, news, pasts, d):
+    assert K.lib().ptb_attention_tc_tile_tokens() == K.TC_TILE_TOKENS and K.attention_tc_supports(d)
+    assert not K.attention_tc_supports(96) and not K.attention_tc_supports(256)
+    out, ref = attention_case(K, BF, heads, kv, d, pasts=pasts, news=news, position="rotary", seed=11, tc=True)
     torch.testing.assert_close(out, ref, **tol(BF))
 
 
-def test_tc_far_key(K):
-    out, ref = attention_case(K, BF, 2, 1, 64, pasts=[0, 0], news=[70, 700], position="none", seed=5,
+@pytest.mark.parametrize("d", [64, 128])
+def test_tc_far_key(K, d):
+    out, ref = attention_case(K, BF, 2, 1, d, pasts=[0, 0], news=[70, 700], position="none", seed=5,
                               needle=(1, 3), tc=True)
     torch.testing.assert_close(out, ref, **tol(BF))
