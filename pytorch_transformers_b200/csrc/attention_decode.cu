@@ -32,8 +32,13 @@ struct DecodeParams {
   float scale;
 };
 
-template <int D>
-__global__ void __launch_bounds__(256)
+// KS: the 64 keys of a page are divided among KS groups of warps (KS = 1, 2 or 4). A group keeps its
+// own running maximum, sum and output over its share of the keys of every page, like a block of a
+// split set does over its pages, and the groups' results meet in the same join. A step of single
+// tokens is a chain of dependent work per page and warp; with few query heads per K/V head (one
+// warp of rows) this is what puts more warps on the chain's pages.
+template <int D, int KS>
+__global__ void __launch_bounds__(D == 64 ? 320 : 256)
 attention_decode_kernel(const __nv_bfloat16* __restrict__ fused, __nv_bfloat16* __restrict__ k_pool,
                         __nv_bfloat16* __restrict__ v_pool, __nv_bfloat16* __restrict__ out, StepBatch sb, const float* __restrict__ rope_cos, const float* __restrict__ rope_sin,
                         const float* __restrict__ alibi_slopes, DecodeParams p) {
@@ -41,7 +46,12 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ fused, __nv_bfloat16* 
   constexpr int TILE_BYTES = KEYS * D * 2;
   const uint32_t smem_base = smem_u32(smem_raw);  // stage s: K at s * 2 * TILE_BYTES, V right after
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nthreads = blockDim.x;
-  const int rows_total = 16 * (nthreads >> 5);
+  const int row_warps = (nthreads >> 5) / KS;
+  const int rows_total = 16 * row_warps;
+  const int rb = warp % row_warps;             // which 16 rows (query heads) this warp holds
+  const int kp = warp / row_warps;             // which share of a page's keys it takes
+  constexpr int NT = KEYS / 8 / KS;            // 8-key tiles of S per warp and page
+  constexpr int KT = KEYS / 16 / KS;           // 16-key steps of P V per warp and page
   const int g4 = lane >> 2, t4 = lane & 3;
 
   const int seq = blockIdx.x;
@@ -64,7 +74,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ fused, __nv_bfloat16* 
   int row_head[2];
 #pragma unroll
   for (int i = 0; i < 2; ++i) {
-    row_head[i] = warp * 16 + g4 + 8 * i;
+    row_head[i] = rb * 16 + g4 + 8 * i;
     row_ok[i] = row_head[i] < head_valid;
   }
   float slope[2] = {0.f, 0.f};
@@ -174,14 +184,14 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ fused, __nv_bfloat16* 
       }
       __syncthreads();
     }
-    float s[KEYS / 8][4];
+    float s[NT][4];
 #pragma unroll
-    for (int j = 0; j < KEYS / 8; ++j) {
+    for (int j = 0; j < NT; ++j) {
       s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
 #pragma unroll
       for (int kk = 0; kk < D / 16; kk += 2) {
         uint32_t b0, b1, b2, b3;
-        ldmatrix_x4(b0, b1, b2, b3, ks + swz<D>(j * 8 + (lane & 7), 2 * kk + (lane >> 3)));
+        ldmatrix_x4(b0, b1, b2, b3, ks + swz<D>((kp * NT + j) * 8 + (lane & 7), 2 * kk + (lane >> 3)));
         mma_bf16(s[j], qa[kk], b0, b1);
         mma_bf16(s[j], qa[kk + 1], b2, b3);
       }
@@ -192,7 +202,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ fused, __nv_bfloat16* 
     const bool whole_page = kb < kb_last && !alibi_slopes && (p.window == 0 || kb * KEYS > pos - p.window);
     if (whole_page) {
 #pragma unroll
-      for (int j = 0; j < KEYS / 8; ++j) {
+      for (int j = 0; j < NT; ++j) {
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           s[j][e] *= sl2;
@@ -201,11 +211,11 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ fused, __nv_bfloat16* 
       }
     } else {
 #pragma unroll
-      for (int j = 0; j < KEYS / 8; ++j) {
+      for (int j = 0; j < NT; ++j) {
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           const int i2 = e >> 1;
-          const int key_pos = kb * KEYS + j * 8 + t4 * 2 + (e & 1);
+          const int key_pos = kb * KEYS + (kp * NT + j) * 8 + t4 * 2 + (e & 1);
           bool visible = row_ok[i2] && key_pos <= pos;
           if (p.window > 0) visible = visible && key_pos > pos - p.window;
           float v = s[j][e];
@@ -225,10 +235,10 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ fused, __nv_bfloat16* 
       corr[i2] = (m_run[i2] == -INFINITY) ? 0.f : fast_exp2(m_run[i2] - m_new);
       m_run[i2] = m_new;
     }
-    uint32_t pa[KEYS / 16][4];
+    uint32_t pa[KT][4];
     float l_blk[2] = {0.f, 0.f};
 #pragma unroll
-    for (int j = 0; j < KEYS / 8; ++j) {
+    for (int j = 0; j < NT; ++j) {
       float pv[4];
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
@@ -247,12 +257,12 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ fused, __nv_bfloat16* 
       o[j][2] *= corr[1]; o[j][3] *= corr[1];
     }
 #pragma unroll
-    for (int kk = 0; kk < KEYS / 16; ++kk) {
+    for (int kk = 0; kk < KT; ++kk) {
 #pragma unroll
       for (int j = 0; j < D / 8; j += 2) {
         uint32_t b0, b1, b2, b3;
         const int m = lane >> 3;
-        ldmatrix_x4_trans(b0, b1, b2, b3, vs + swz<D>(kk * 16 + (m & 1) * 8 + (lane & 7), j + (m >> 1)));
+        ldmatrix_x4_trans(b0, b1, b2, b3, vs + swz<D>((kp * KT + kk) * 16 + (m & 1) * 8 + (lane & 7), j + (m >> 1)));
         mma_bf16(o[j], pa[kk], b0, b1);
         mma_bf16(o[j + 1], pa[kk], b2, b3);
       }
@@ -267,7 +277,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ fused, __nv_bfloat16* 
   }
 
   __nv_bfloat16* out_tok = out + (size_t(tok) * p.heads + g * qpk + h0) * D;
-  if (p.n_splits == 1) {
+  if (p.n_splits == 1 && KS == 1) {
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
       if (!row_ok[i]) continue;
@@ -280,12 +290,13 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ fused, __nv_bfloat16* 
     return;
   }
   // partial results of this block, in its own shared memory (the page ring is no longer needed):
-  // po [rows_total][D] float32, then pml [rows_total][2]
+  // po [KS][rows_total][D] float32, then pml [KS][rows_total][2]
   float* po = reinterpret_cast<float*>(smem_raw);
-  float* pml = po + rows_total * D;
+  float* pml = po + KS * rows_total * D;
+  if (KS > 1) __syncthreads();   // every warp is past its last page: the ring may be overwritten
 #pragma unroll
   for (int i = 0; i < 2; ++i) {
-    const int r = row_head[i];
+    const int r = kp * rows_total + row_head[i];
 #pragma unroll
     for (int j = 0; j < D / 8; ++j)
       *reinterpret_cast<float2*>(po + size_t(r) * D + j * 8 + t4 * 2) = make_float2(o[j][2 * i], o[j][2 * i + 1]);
@@ -307,18 +318,23 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ fused, __nv_bfloat16* 
     float m = -INFINITY;
     for (int s = 0; s < n_splits; ++s) {
       const float* rml = cluster.map_shared_rank(pml, s);
-      m = fmaxf(m, rml[r * 2]);
+#pragma unroll
+      for (int k2 = 0; k2 < KS; ++k2) m = fmaxf(m, rml[(k2 * rows_total + r) * 2]);
     }
     float acc[VEC] = {0.f, 0.f, 0.f, 0.f};
     float l = 0.f;
-    for (int s = 0; s < n_splits; ++s) {
+    for (int s = 0; s < n_splits; ++s) {   // always in the same order: blocks of the split set, then key groups
       const float* rml = cluster.map_shared_rank(pml, s);
       const float* rpo = cluster.map_shared_rank(po, s);
-      const float ms = rml[r * 2];
-      const float w = (ms == -INFINITY) ? 0.f : exp2f(ms - m);
-      l += rml[r * 2 + 1] * w;
-      const float4 v = *reinterpret_cast<const float4*>(rpo + size_t(r) * D + d0);
-      acc[0] += v.x * w; acc[1] += v.y * w; acc[2] += v.z * w; acc[3] += v.w * w;
+#pragma unroll
+      for (int k2 = 0; k2 < KS; ++k2) {
+        const int rr = k2 * rows_total + r;
+        const float ms = rml[rr * 2];
+        const float w = (ms == -INFINITY) ? 0.f : exp2f(ms - m);
+        l += rml[rr * 2 + 1] * w;
+        const float4 v = *reinterpret_cast<const float4*>(rpo + size_t(rr) * D + d0);
+        acc[0] += v.x * w; acc[1] += v.y * w; acc[2] += v.z * w; acc[3] += v.w * w;
+      }
     }
     const float inv = l > 0.f ? 1.f / l : 0.f;
     __nv_bfloat16* dst = out_tok + size_t(r) * D + d0;
@@ -327,7 +343,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ fused, __nv_bfloat16* 
   cluster.sync();  // no block leaves while another still reads its shared memory
 }
 
-template <int D>
+template <int D, int KS>
 int launch_decode(const void* fused, void* k_pool, void* v_pool, void* out, const StepBatch& sb,
                   const float* rope_cos, const float* rope_sin, const float* slopes, const DecodeParams& p,
                   int warps, cudaStream_t stream) {
@@ -336,18 +352,18 @@ int launch_decode(const void* fused, void* k_pool, void* v_pool, void* out, cons
   // page ring, then the token's row (query heads of the chunk, key, value) and its cos/sin
   const size_t ring = size_t(STAGES) * 2 * KEYS * D * 2;
   size_t smem = ring + size_t(p.hpk + 2) * D * 2 + size_t(D) * sizeof(float);
-  const size_t join = size_t(warps) * 16 * (D + 2) * sizeof(float);  // partial results reuse the ring
+  const size_t join = size_t(KS) * warps * 16 * (D + 2) * sizeof(float);  // partial results reuse the ring
   if (join > smem) smem = join;
   static size_t configured = 0;
   if (smem > configured) {
-    if (cudaFuncSetAttribute(attention_decode_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) !=
+    if (cudaFuncSetAttribute(attention_decode_kernel<D, KS>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) !=
         cudaSuccess)
       return PTB_ERR_LAUNCH;
     configured = smem;
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(sb.n_seqs, p.kv_heads * chunks, p.n_splits);
-  cfg.blockDim = dim3(warps * 32);
+  cfg.blockDim = dim3(warps * KS * 32);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
@@ -357,7 +373,7 @@ int launch_decode(const void* fused, void* k_pool, void* v_pool, void* out, cons
   attr[0].val.clusterDim.z = p.n_splits;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  if (cudaLaunchKernelEx(&cfg, attention_decode_kernel<D>, (const __nv_bfloat16*)fused, (__nv_bfloat16*)k_pool,
+  if (cudaLaunchKernelEx(&cfg, attention_decode_kernel<D, KS>, (const __nv_bfloat16*)fused, (__nv_bfloat16*)k_pool,
                          (__nv_bfloat16*)v_pool, (__nv_bfloat16*)out, sb, rope_cos, rope_sin, slopes,
                          p) != cudaSuccess) {
     (void)cudaGetLastError();
@@ -372,12 +388,13 @@ int launch_decode(const void* fused, void* k_pool, void* v_pool, void* out, cons
 PTB_API int ptb_attention_decode_max_splits() { return 8; }
 
 // Every sequence of the step brings exactly one token. fused [n_seqs, kv_heads * (q_per_kv + 2) *
-// head_dim] bfloat16; out [n_seqs, heads * head_dim]. n_splits is 1, 2, 4 or 8. rope_cos/sin:
+// head_dim] bfloat16; out [n_seqs, heads * head_dim]. n_splits from 1 to 8; key_split 1, 2 or 4 groups
+// of `warps` warps each share the keys of every page (warps * key_split <= 10 for head size 64, 8 for 128). rope_cos/sin:
 // [n_seqs, rot_pairs] float32 tables for the step's tokens, or null for no rotation.
 PTB_API int ptb_attention_decode(const void* fused, void* k_pool, void* v_pool, void* out, const StepBatch* sb,
                                  const float* rope_cos, const float* rope_sin, int rot_pairs,
                                  const float* alibi_slopes, int heads, int kv_heads, int head_dim, int hpk,
-                                 int n_splits, int warps, float scale, int window, int write_cache,
+                                 int n_splits, int warps, int key_split, float scale, int window, int write_cache,
                                  cudaStream_t stream) {
   if (sb->n_seqs <= 0) return PTB_OK;
   if (sb->n_tokens != sb->n_seqs) return PTB_ERR_SIZE;
@@ -385,6 +402,8 @@ PTB_API int ptb_attention_decode(const void* fused, void* k_pool, void* v_pool, 
       hpk > warps * 16 || rot_pairs < 0 || 2 * rot_pairs > head_dim)
     return PTB_ERR_SIZE;
   if (n_splits < 1 || n_splits > 8) return PTB_ERR_SIZE;   // a cluster holds at most 8 blocks
+  if ((key_split != 1 && key_split != 2 && key_split != 4) || warps * key_split > (head_dim == 64 ? 10 : 8))
+    return PTB_ERR_SIZE;
   if ((rope_cos == nullptr) != (rope_sin == nullptr)) return PTB_ERR_SIZE;
   const int qpk = heads / kv_heads;
   const int chunks = (qpk + hpk - 1) / hpk;
@@ -392,12 +411,18 @@ PTB_API int ptb_attention_decode(const void* fused, void* k_pool, void* v_pool, 
   DecodeParams p;
   p.heads = heads; p.kv_heads = kv_heads; p.hpk = hpk; p.n_splits = n_splits; p.rot_pairs = rot_pairs;
   p.write_cache = write_cache; p.window = window; p.scale = scale;
-  switch (head_dim) {
-    case 64:
-      return launch_decode<64>(fused, k_pool, v_pool, out, *sb, rope_cos, rope_sin, alibi_slopes, p, warps, stream);
-    case 128:
-      return launch_decode<128>(fused, k_pool, v_pool, out, *sb, rope_cos, rope_sin, alibi_slopes, p, warps, stream);
-    default:
-      return PTB_ERR_SIZE;
+#define PTB_DECODE(DD, KK) \
+  return launch_decode<DD, KK>(fused, k_pool, v_pool, out, *sb, rope_cos, rope_sin, alibi_slopes, p, warps, stream)
+  if (head_dim == 64) {
+    if (key_split == 1) PTB_DECODE(64, 1);
+    if (key_split == 2) PTB_DECODE(64, 2);
+    PTB_DECODE(64, 4);
   }
+  if (head_dim == 128) {
+    if (key_split == 1) PTB_DECODE(128, 1);
+    if (key_split == 2) PTB_DECODE(128, 2);
+    PTB_DECODE(128, 4);
+  }
+#undef PTB_DECODE
+  return PTB_ERR_SIZE;
 }

@@ -36,8 +36,53 @@ __device__ __forceinline__ float act_f(float v, int act) {
   }
 }
 
+// steps c0 = first, first + stride, ... below `limit`; a step has the UNROLL chunks c0, c0 + apart,
+// c0 + 2 apart, ... in flight together (those past the last chunk are skipped)
+template <int MT, int NT, int UNROLL>
+__device__ __forceinline__ void sweep(float (&acc)[MT][NT][4], const __nv_bfloat16* const (&wrow)[MT][2],
+                                      const __nv_bfloat16* const (&xrow)[NT], const bool (&xok)[NT], int first,
+                                      int limit, int stride, int apart, int chunks) {
+  for (int c0 = first; c0 < limit; c0 += stride) {
+    uint4 wa[UNROLL][MT][2];
+    uint4 xb[UNROLL][NT];
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      const int c = c0 + u * apart;
+      if (c < chunks) {
+#pragma unroll
+        for (int i = 0; i < MT; ++i) {
+          wa[u][i][0] = ld_stream16(wrow[i][0] + size_t(c) * KC);
+          wa[u][i][1] = ld_stream16(wrow[i][1] + size_t(c) * KC);
+        }
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      const int c = c0 + u * apart;
+      if (c < chunks) {
+#pragma unroll
+        for (int j = 0; j < NT; ++j)
+          xb[u][j] = xok[j] ? *reinterpret_cast<const uint4*>(xrow[j] + size_t(c) * KC) : make_uint4(0, 0, 0, 0);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      if (c0 + u * apart < chunks) {
+#pragma unroll
+        for (int i = 0; i < MT; ++i)
+#pragma unroll
+          for (int j = 0; j < NT; ++j) {
+            // the thread's 8 k values: .x .y feed the first mma (as k pairs 2t and 2t + 8), .z .w the second
+            mma16816(acc[i][j], wa[u][i][0].x, wa[u][i][1].x, wa[u][i][0].y, wa[u][i][1].y, xb[u][j].x, xb[u][j].y);
+            mma16816(acc[i][j], wa[u][i][0].z, wa[u][i][1].z, wa[u][i][0].w, wa[u][i][1].w, xb[u][j].z, xb[u][j].w);
+          }
+      }
+    }
+  }
+}
+
 // MT: 16-row weight tiles per block; NT: 8-row activation tiles (M <= 8 * NT)
-template <int MT, int NT>
+template <int MT, int NT, int UNROLL>
 __global__ void __launch_bounds__(WARPS * 32)
 skinny_linear_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
                      const float* __restrict__ bias, const __nv_bfloat16* __restrict__ add,
@@ -67,45 +112,14 @@ skinny_linear_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* _
     xrow[j] = x + size_t(xok[j] ? j * 8 + g : 0) * K + t * 8;
   }
 
+  // The warps take the 32-wide chunks of K in turn, UNROLL chunks at a time: at any moment the block
+  // reads WARPS * UNROLL consecutive chunks of every weight row (one stretch of a DRAM page). What
+  // is left after the last full round is dealt round the warps chunk by chunk, in one more step, so
+  // that no warp idles.
   const int chunks = K / KC;
-  constexpr int UNROLL = (MT == 1) ? 4 : 2;  // chunks in flight per warp
-  for (int c0 = warp * UNROLL; c0 < chunks; c0 += WARPS * UNROLL) {
-    uint4 wa[UNROLL][MT][2];
-    uint4 xb[UNROLL][NT];
-#pragma unroll
-    for (int u = 0; u < UNROLL; ++u) {
-      const int c = c0 + u;
-      if (c < chunks) {
-#pragma unroll
-        for (int i = 0; i < MT; ++i) {
-          wa[u][i][0] = ld_stream16(wrow[i][0] + size_t(c) * KC);
-          wa[u][i][1] = ld_stream16(wrow[i][1] + size_t(c) * KC);
-        }
-      }
-    }
-#pragma unroll
-    for (int u = 0; u < UNROLL; ++u) {
-      const int c = c0 + u;
-      if (c < chunks) {
-#pragma unroll
-        for (int j = 0; j < NT; ++j)
-          xb[u][j] = xok[j] ? *reinterpret_cast<const uint4*>(xrow[j] + size_t(c) * KC) : make_uint4(0, 0, 0, 0);
-      }
-    }
-#pragma unroll
-    for (int u = 0; u < UNROLL; ++u) {
-      if (c0 + u < chunks) {
-#pragma unroll
-        for (int i = 0; i < MT; ++i)
-#pragma unroll
-          for (int j = 0; j < NT; ++j) {
-            // the thread's 8 k values: .x .y feed the first mma (as k pairs 2t and 2t + 8), .z .w the second
-            mma16816(acc[i][j], wa[u][i][0].x, wa[u][i][1].x, wa[u][i][0].y, wa[u][i][1].y, xb[u][j].x, xb[u][j].y);
-            mma16816(acc[i][j], wa[u][i][0].z, wa[u][i][1].z, wa[u][i][0].w, wa[u][i][1].w, xb[u][j].z, xb[u][j].w);
-          }
-      }
-    }
-  }
+  const int full = chunks / (WARPS * UNROLL) * (WARPS * UNROLL);
+  sweep<MT, NT, UNROLL>(acc, wrow, xrow, xok, warp * UNROLL, full, WARPS * UNROLL, 1, chunks);
+  sweep<MT, NT, UNROLL>(acc, wrow, xrow, xok, full + warp, full + WARPS, WARPS, WARPS, chunks);
   // partial sums of the 8 warps -> shared memory: red[warp][weight row][activation row]
 #pragma unroll
   for (int i = 0; i < MT; ++i)
@@ -134,11 +148,11 @@ skinny_linear_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* _
   }
 }
 
-template <int MT, int NT>
+template <int MT, int NT, int U>
 int launch_skinny(const void* x, const void* w, const float* bias, const void* add, void* y_bf16, float* y_f32,
                   int M, int N, int K, int act, cudaStream_t stream) {
   const int grid = (N + 16 * MT - 1) / (16 * MT);
-  skinny_linear_kernel<MT, NT><<<grid, WARPS * 32, 0, stream>>>(
+  skinny_linear_kernel<MT, NT, U><<<grid, WARPS * 32, 0, stream>>>(
       (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, bias, (const __nv_bfloat16*)add, (__nv_bfloat16*)y_bf16,
       y_f32, M, N, K, act);
   return launch_status();
@@ -158,12 +172,15 @@ PTB_API int ptb_skinny_linear(const void* x, const void* w, const float* bias, c
   if (M > 32 || K <= 0 || K % KC != 0 || act < 0 || act > 3) return PTB_ERR_SIZE;
   if ((y_bf16 == nullptr) == (y_f32 == nullptr)) return PTB_ERR_SIZE;
   if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w)) & 15) return PTB_ERR_ALIGN;
-  // wide matrices: 32 weight rows per block halve the re-reads of x; narrow ones keep more blocks
+  // Tile height and chunks in flight per warp, from a sweep over the projections of Falcon-7B, 11B and
+  // 40B (each matrix alone, from HBM): wide matrices (many rows, short K) want 32 rows per block and
+  // four chunks in flight at up to 8 activation rows, 16 rows and two chunks at up to 16; the others
+  // 16 rows and four chunks.
   const bool wide = N >= 16 * 148 * 4;
-  if (M <= 8) return wide ? launch_skinny<2, 1>(x, w, bias, add, y_bf16, y_f32, M, N, K, act, stream)
-                          : launch_skinny<1, 1>(x, w, bias, add, y_bf16, y_f32, M, N, K, act, stream);
-  if (M <= 16) return wide ? launch_skinny<2, 2>(x, w, bias, add, y_bf16, y_f32, M, N, K, act, stream)
-                           : launch_skinny<1, 2>(x, w, bias, add, y_bf16, y_f32, M, N, K, act, stream);
-  return wide ? launch_skinny<2, 4>(x, w, bias, add, y_bf16, y_f32, M, N, K, act, stream)
-              : launch_skinny<1, 4>(x, w, bias, add, y_bf16, y_f32, M, N, K, act, stream);
+  if (M <= 8) return wide ? launch_skinny<2, 1, 4>(x, w, bias, add, y_bf16, y_f32, M, N, K, act, stream)
+                          : launch_skinny<1, 1, 4>(x, w, bias, add, y_bf16, y_f32, M, N, K, act, stream);
+  if (M <= 16) return wide ? launch_skinny<1, 2, 2>(x, w, bias, add, y_bf16, y_f32, M, N, K, act, stream)
+                           : launch_skinny<1, 2, 4>(x, w, bias, add, y_bf16, y_f32, M, N, K, act, stream);
+  return wide ? launch_skinny<2, 4, 2>(x, w, bias, add, y_bf16, y_f32, M, N, K, act, stream)
+              : launch_skinny<1, 4, 4>(x, w, bias, add, y_bf16, y_f32, M, N, K, act, stream);
 }

@@ -192,11 +192,27 @@ class CausalLM:
         return entry["out"].clone()   # the graph's own output buffer is rewritten by the next replay
 
     TWO_STREAM_MAX_TOKENS = 32
+    # Two streams pay while the mixer's kernels are small beside the feed-forward's weight stream.
+    # Once a layer's attention reads tens of megabytes of keys and values itself, it competes with
+    # that stream instead of hiding under it (measured: 4 MB a layer, Falcon-7B at batch 8, 2.83 ms
+    # against 3.54 ms in one stream; 17 MB, batch 32, 3.73 against 4.00; 34 MB, 40B at batch 8,
+    # 18.9 against 17.2; 67 MB, 11B at batch 8, 7.07 against 6.16).
+    TWO_STREAM_MAX_KV_BYTES = 24 << 20
+
+    def _two_streams(self, ctx: StepContext) -> bool:
+        if self.device.type != "cuda" or self.dtype != torch.bfloat16 or ctx.n_tokens > self.TWO_STREAM_MAX_TOKENS:
+            return False
+        lengths = [p + n for p, n in zip(ctx.past, ctx.new)]
+        per_layer = 0
+        for g in ctx.cache.groups:   # keys and values that one layer of this group reads in this step
+            keys = sum(min(t, g.need.window) if g.need.window else t for t in lengths)
+            per_layer = max(per_layer, keys * g.need.kv_heads * g.need.head_dim * 2 * g.k.element_size())
+        return per_layer <= self.TWO_STREAM_MAX_KV_BYTES
 
     def forward(self, ctx: StepContext) -> torch.Tensor:
         k = self.build.kernels
         ctx.begin_forward()
-        if self.device.type == "cuda" and ctx.n_tokens <= self.TWO_STREAM_MAX_TOKENS and self.dtype == torch.bfloat16:
+        if self._two_streams(ctx):
             if self._side_stream is None:
                 self._side_stream = torch.cuda.Stream(device=self.device)
             ctx.side_stream = self._side_stream

@@ -208,15 +208,23 @@ def attention_generic(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tenso
     return out
 
 
-DECODE_SPLITS = (1, 2, 4, 8)   # ptb_attention_decode: the blocks of a split set form one cluster
+DECODE_SPLITS = (1, 2, 3, 4, 5, 6, 7, 8)   # ptb_attention_decode: the blocks of a split set form one cluster
+DECODE_KEY_SPLITS = (1, 2, 4)              # groups of warps that share a page's keys
+
+
+def decode_max_warps(head_dim: int) -> int:
+    """Warps of a block of attention_decode: row warps times key groups."""
+    return 10 if head_dim == 64 else 8
 
 
 def attention_decode(fused: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, batch: StepBatchC, rope,
                      slopes: Optional[torch.Tensor], kv_heads: int, q_per_kv: int, head_dim: int, scale: float,
-                     window: int, heads_per_tile: int, warps: int, n_splits: int, write_cache: bool = True):
+                     window: int, heads_per_tile: int, warps: int, n_splits: int, write_cache: bool = True,
+                     key_split: int = 1):
     """One kernel for the attention of a step of single tokens: rotate q and k of each new token, put
-    k and v into the cache, attend over the cache (all heads of a K/V group in one tile, key pages
-    divided among ``n_splits`` blocks of one cluster, joined through distributed shared memory).
+    k and v into the cache, attend over the cache (all heads of a K/V group in one tile of ``warps``
+    x 16 rows, key pages divided among ``n_splits`` blocks of one cluster, the keys of a page among
+    ``key_split`` groups of warps, all joined through (distributed) shared memory).
     Returns [tokens, heads * head_dim]."""
     _need_cuda(fused, k_pool, v_pool, slopes)
     if fused.dtype != torch.bfloat16:
@@ -231,7 +239,7 @@ def attention_decode(fused: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Te
     pairs = 0 if cos is None else cos.shape[1]
     _check(lib().ptb_attention_decode(_ptr(fused), _ptr(k_pool), _ptr(v_pool), _ptr(out), ctypes.byref(batch),
                                       _ptr(cos), _ptr(sin), pairs, _ptr(slopes), heads, kv_heads, head_dim,
-                                      heads_per_tile, n_splits, warps, ctypes.c_float(scale), window,
+                                      heads_per_tile, n_splits, warps, key_split, ctypes.c_float(scale), window,
                                       1 if write_cache else 0, _stream(fused)), "attention_decode")
     return out
 

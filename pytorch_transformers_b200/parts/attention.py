@@ -74,7 +74,7 @@ class Attention(Part):
             splits = max(s for s in k.DECODE_SPLITS if s <= want)
             o = k.attention_decode(fused, k_pool, v_pool, batch, rope, slopes, self.kv_heads, self.q_per_kv,
                                    self.head_dim, self.scale, self.window, hpk, warps, splits,
-                                   write_cache=entry.writes_cache)
+                                   write_cache=entry.writes_cache, key_split=self._decode_key_split(warps))
         else:
             q = k.split_rotate_store(fused, k_pool, v_pool, batch, None, self.kv_heads, self.q_per_kv,
                                      self.head_dim, write_cache=entry.writes_cache, rope=rope)
@@ -82,15 +82,28 @@ class Attention(Part):
         return linear(k, o, self.p_out_weight, self.p_out_bias, add=add)
 
     def _decode_splits(self, ctx, hpk):
-        """Blocks per (sequence, head chunk) for steps of single tokens: enough to put about two
-        blocks on every SM, each with at least two pages of keys (measured: more, smaller blocks
-        are slower at batch 64, clusters of 8 are harder to place than clusters of 4)."""
+        """Blocks per (sequence, head chunk) for steps of single tokens: up to about two blocks on
+        every SM, each with at least two pages of keys (measured: more, smaller blocks are slower
+        at batch 64, and a second wave of blocks costs more than it brings)."""
         chunks = (self.q_per_kv + hpk - 1) // hpk
         blocks = ctx.n_seqs * self.kv_heads * chunks
         pages = ctx.pages_hint
         if self.window > 0:
             pages = min(pages, self.window // self.build.kernels.PAGE + 2)
-        return max(1, min((2 * 148 + blocks - 1) // blocks, pages // 2, 64))
+        return max(1, min((2 * 148) // blocks, pages // 2, 64))
+
+    def _decode_key_split(self, row_warps):
+        """Groups of warps that share the keys of a page in the decode kernel. With few query heads
+        per K/V head a block has one or two warps of rows, and each page is a chain of dependent
+        work for them; measured on 32 heads / 8 groups of size 128 (4 groups: 1.8 to 2 times
+        faster) and on 128 heads / 8 groups of size 64 (2 groups: up to 1.1 times). With the 71
+        heads of one group (5 warps of rows) more groups bring nothing."""
+        if row_warps >= 3:
+            return 1
+        groups = 4 if self.head_dim > 64 else 2
+        while groups > 1 and row_warps * groups > self.build.kernels.decode_max_warps(self.head_dim):
+            groups //= 2
+        return groups
 
     def attend(self, q, k_pool, v_pool, ctx, batch, slopes):
         k = self.build.kernels

@@ -118,11 +118,37 @@ def test_mma_refuses_what_it_does_not_take(K):
 # ------------------------------------------------------------------------------ one-kernel decode
 @pytest.mark.parametrize("heads,kv,d", MMA_SHAPES)
 @pytest.mark.parametrize("position", ["rotary", "alibi"])
-@pytest.mark.parametrize("splits", [1, 2, 4, 8])
+@pytest.mark.parametrize("splits", [1, 2, 3, 4, 7, 8])
 def test_fused_decode(K, heads, kv, d, position, splits):
     # new tokens at a page's last slot, its first slot, in the middle, as the second token, far out
     out, ref = attention_case(K, BF, heads, kv, d, pasts=[63, 64, 200, 1, 700, 127], news=[1] * 6,
                               position=position, seed=3, fused_decode=(None, splits))
+    torch.testing.assert_close(out, ref, **tol(BF))
+
+
+@pytest.mark.parametrize("heads,kv,d", MMA_SHAPES)
+@pytest.mark.parametrize("position", ["rotary", "alibi"])
+@pytest.mark.parametrize("splits,key_split", [(1, 2), (1, 4), (3, 2), (5, 4), (8, 2)])
+def test_fused_decode_keys_of_a_page_shared_among_warp_groups(K, heads, kv, d, position, splits, key_split):
+    qpk = heads // kv
+    if ((min(qpk, 128) + 15) // 16) * key_split > K.decode_max_warps(d):
+        pytest.skip("more warps than a block of this kernel takes")
+    out, ref = attention_case(K, BF, heads, kv, d, pasts=[63, 64, 200, 1, 700, 127], news=[1] * 6,
+                              position=position, seed=3, fused_decode=(None, splits, key_split))
+    torch.testing.assert_close(out, ref, **tol(BF))
+
+
+@pytest.mark.parametrize("key_pos,key_split", [(0, 2), (64 + 17, 4), (698, 4), (699, 2)])
+def test_fused_decode_far_key_with_key_groups(K, key_pos, key_split):
+    out, ref = attention_case(K, BF, 8, 2, 64, pasts=[0 + 5, 699], news=[1, 1], position="none", seed=5,
+                              needle=(1, key_pos), fused_decode=(None, 3, key_split))
+    torch.testing.assert_close(out, ref, **tol(BF))
+
+
+@pytest.mark.parametrize("window,key_split", [(1, 2), (5, 4), (65, 4), (100, 2)])
+def test_fused_decode_window_with_key_groups(K, window, key_split):
+    out, ref = attention_case(K, BF, 4, 2, 64, pasts=[300, 5, 64], news=[1, 1, 1], position="rotary", window=window,
+                              seed=7, fused_decode=(None, 2, key_split))
     torch.testing.assert_close(out, ref, **tol(BF))
 
 
