@@ -335,29 +335,54 @@ __device__ __forceinline__ float gelu_erf_for_bf16(float v) {
   return 0.5f * v * (1.0f + copysignf(erf_abs, v));
 }
 
-// the same, eight bfloat16 values per thread and step (width a multiple of 8, 16-byte aligned rows)
-__global__ void bias_act_bf16x8_kernel(uint4* __restrict__ y, const float* __restrict__ bias, size_t total8, int width,
-                                       int act) {
-  const size_t stride = size_t(gridDim.x) * blockDim.x;
-  for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total8; i += stride) {
-    float f[8];
-    unpack_bf16x8(y[i], f);
-    const int col = int((i * 8) % width);
+// the same, eight bfloat16 values per 16-byte word (width a multiple of 8, 16-byte aligned rows); a
+// thread takes two words per step, both loads in flight before the arithmetic of either. The
+// activation and the presence of a bias are compile-time: the loop holds no test and, without a
+// bias, no division for the column.
+template <int ACT, bool BIAS>
+__device__ __forceinline__ uint4 bias_act_word(uint4 word, const float* __restrict__ bias, size_t i, unsigned words_per_row) {
+  float f[8];
+  unpack_bf16x8(word, f);
+  if (BIAS) {
+    float b[8];
+    load_f32x8(bias + size_t(unsigned(i % words_per_row)) * 8, b);
 #pragma unroll
-    for (int e = 0; e < 8; ++e) {
-      const float v = bias ? f[e] + bias[col + e] : f[e];
-      f[e] = (act == 1) ? gelu_erf_for_bf16(v) : activate(v, act);
-    }
-    y[i] = pack_bf16x8(f);
+    for (int e = 0; e < 8; ++e) f[e] += b[e];
   }
+#pragma unroll
+  for (int e = 0; e < 8; ++e) f[e] = (ACT == 1) ? gelu_erf_for_bf16(f[e]) : activate(f[e], ACT);
+  return pack_bf16x8(f);
+}
+template <int ACT, bool BIAS>
+__global__ void __launch_bounds__(256)
+bias_act_bf16x8_kernel(uint4* __restrict__ y, const float* __restrict__ bias, size_t total8, unsigned words_per_row) {
+  const size_t stride = size_t(gridDim.x) * blockDim.x;
+  size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
+  for (; i + stride < total8; i += 2 * stride) {
+    const uint4 a = y[i], b = y[i + stride];
+    y[i] = bias_act_word<ACT, BIAS>(a, bias, i, words_per_row);
+    y[i + stride] = bias_act_word<ACT, BIAS>(b, bias, i + stride, words_per_row);
+  }
+  if (i < total8) y[i] = bias_act_word<ACT, BIAS>(y[i], bias, i, words_per_row);
+}
+template <int ACT>
+void launch_bias_act_x8(void* y, const float* bias, size_t total8, int width, cudaStream_t stream) {
+  const int grid = grid_for(total8, 256);
+  if (bias) bias_act_bf16x8_kernel<ACT, true><<<grid, 256, 0, stream>>>((uint4*)y, bias, total8, unsigned(width / 8));
+  else bias_act_bf16x8_kernel<ACT, false><<<grid, 256, 0, stream>>>((uint4*)y, bias, total8, unsigned(width / 8));
 }
 
 PTB_API int ptb_bias_act(int dtype, void* y, const float* bias, int rows, int width, int act, cudaStream_t stream) {
   const size_t total = size_t(rows) * width;
   if (total == 0) return PTB_OK;
   if (act < 0 || act > 3) return PTB_ERR_SIZE;
-  if (dtype == PTB_BF16 && width % 8 == 0 && aligned16(y)) {
-    bias_act_bf16x8_kernel<<<grid_for(total / 8, 256), 256, 0, stream>>>((uint4*)y, bias, total / 8, width, act);
+  if (dtype == PTB_BF16 && width % 8 == 0 && aligned16(y) && (!bias || aligned16(bias))) {
+    switch (act) {
+      case 0: launch_bias_act_x8<0>(y, bias, total / 8, width, stream); break;
+      case 1: launch_bias_act_x8<1>(y, bias, total / 8, width, stream); break;
+      case 2: launch_bias_act_x8<2>(y, bias, total / 8, width, stream); break;
+      default: launch_bias_act_x8<3>(y, bias, total / 8, width, stream); break;
+    }
     return launch_status();
   }
   const int threads = 256;
