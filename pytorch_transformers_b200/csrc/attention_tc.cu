@@ -1,5 +1,6 @@
 // Prompt attention on the fifth-generation tensor cores (tcgen05) with the accumulators in tensor
-// memory, for head sizes 64 and 128, bfloat16, causal, over the paged cache. The description below
+// memory, for head sizes 64 and 128, bfloat16, causal, with or without per-head score slopes (ALiBi),
+// over the paged cache. The description below
 // is for head size 64; with 128 the tiles of Q, K and V are two blocks of 64 dims, S takes two groups
 // of matrix instructions, O two (one per 64 dims of the output), and one block fits on an SM.
 //
@@ -63,6 +64,7 @@ __device__ __forceinline__ void load_page_tc(uint32_t smem_tile, const __nv_bflo
 struct TcParams {
   int heads, kv_heads;
   float scale;
+  const float* slopes;   // per-head score slopes (ALiBi), or null
 };
 
 constexpr int TPR = 2;                              // threads per query row
@@ -73,7 +75,9 @@ constexpr int BLOCK_THREADS = SOFTMAX_THREADS + 32;  // and one warp whose first
 // barrier among the TPR warps that share 32 query rows (ids 1..4 are used)
 __device__ __forceinline__ void row_sync(int id) { asm volatile("bar.sync %0, %1;\n" ::"r"(id), "n"(TPR * 32) : "memory"); }
 
-template <int D>
+// BIAS: a per-head slope times the key's position is added to the raw scores, formed in bfloat16 as
+// the reference forms it.
+template <int D, bool BIAS>
 __global__ void __launch_bounds__(BLOCK_THREADS, D == 64 ? 2 : 1)
 attention_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_pool,
                     const __nv_bfloat16* __restrict__ v_pool, __nv_bfloat16* __restrict__ out, StepBatch sb,
@@ -208,6 +212,7 @@ attention_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
     const uint32_t o_addr = tmem_base + (uint32_t((warp & 3) * 32) << 16) + 128 + part * COLS_O;   // its columns of O
     const int sync_id = 1 + (warp & 3);
     float m_run = -INFINITY, l_run = 0.f;   // running maximum of the raw scores, this thread's half of the sum
+    const float slope = BIAS ? p.slopes[h] : 0.f;
     const float sl2 = p.scale * 1.4426950408889634f;
     // page 0's arrival (the copies were waited for above)
     mbar_arrive(bar_k);
@@ -222,6 +227,10 @@ attention_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
         cp_async_wait<1>();
         proxy_fence_async();
         mbar_arrive(bar_k + 8 * ((i + 1) % STAGES_TC));
+      }
+      if (BIAS) {
+#pragma unroll
+        for (int j = 0; j < COLS; ++j) s[j] += alibi_bias(slope, i * KEYS + part * COLS + j);
       }
       // (3) maximum of the visible scores; only pages that reach past some row's position need the test
       float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
@@ -325,19 +334,19 @@ PTB_API int ptb_attention_tc_supports(int head_dim) { return (head_dim == 64 || 
 PTB_API int ptb_attention_tc_tile_tokens() { return TQ; }
 
 namespace {
-template <int D>
+template <int D, bool BIAS>
 int launch_tc(const void* q, const void* k_pool, const void* v_pool, void* out, const StepBatch& sb,
               const int* tile_seq, const int* tile_q0, int n_tiles, const TcParams& p, int* error_flag,
               cudaStream_t stream) {
   const size_t smem = 1024 + TQ * D * 2 + 2 * STAGES_TC * KEYS * D * 2 + TILE_P_BYTES + 128 + 2 * TPR * TQ * sizeof(float);
   static bool configured = false;
   if (!configured) {
-    if (cudaFuncSetAttribute(attention_tc_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess)
+    if (cudaFuncSetAttribute(attention_tc_kernel<D, BIAS>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess)
       return PTB_ERR_LAUNCH;
     configured = true;
   }
   dim3 grid(n_tiles, p.heads);
-  attention_tc_kernel<D><<<grid, BLOCK_THREADS, smem, stream>>>(
+  attention_tc_kernel<D, BIAS><<<grid, BLOCK_THREADS, smem, stream>>>(
       (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, (__nv_bfloat16*)out, sb,
       tile_seq, tile_q0, p, error_flag);
   return launch_status();
@@ -345,18 +354,21 @@ int launch_tc(const void* q, const void* k_pool, const void* v_pool, void* out, 
 }  // namespace
 
 // Causal attention of prompt tiles of 128 tokens (tile_seq / tile_q0 as for the other attention
-// kernels, 128 tokens per tile), bfloat16, head size 64 or 128, no bias, no window. `error_flag` is a
-// device int that stays 0 unless a bounded wait inside the kernel ran out.
+// kernels, 128 tokens per tile), bfloat16, head size 64 or 128, no window. `slopes`: per-head score
+// slopes [heads] float32 (already rounded to bfloat16 values), or null. `error_flag` is a device int
+// that stays 0 unless a bounded wait inside the kernel ran out.
 PTB_API int ptb_attention_tc(const void* q, const void* k_pool, const void* v_pool, void* out, const StepBatch* sb,
-                             const int* tile_seq, const int* tile_q0, int n_tiles, int heads, int kv_heads,
-                             int head_dim, float scale, int* error_flag, cudaStream_t stream) {
+                             const int* tile_seq, const int* tile_q0, int n_tiles, const float* slopes, int heads,
+                             int kv_heads, int head_dim, float scale, int* error_flag, cudaStream_t stream) {
   if (n_tiles <= 0) return PTB_OK;
   if ((head_dim != 64 && head_dim != 128) || heads <= 0 || kv_heads <= 0 || heads % kv_heads != 0 || heads > 65535 ||
       error_flag == nullptr)
     return PTB_ERR_SIZE;
   TcParams p;
-  p.heads = heads; p.kv_heads = kv_heads; p.scale = scale;
+  p.heads = heads; p.kv_heads = kv_heads; p.scale = scale; p.slopes = slopes;
   if (head_dim == 64)
-    return launch_tc<64>(q, k_pool, v_pool, out, *sb, tile_seq, tile_q0, n_tiles, p, error_flag, stream);
-  return launch_tc<128>(q, k_pool, v_pool, out, *sb, tile_seq, tile_q0, n_tiles, p, error_flag, stream);
+    return slopes ? launch_tc<64, true>(q, k_pool, v_pool, out, *sb, tile_seq, tile_q0, n_tiles, p, error_flag, stream)
+                  : launch_tc<64, false>(q, k_pool, v_pool, out, *sb, tile_seq, tile_q0, n_tiles, p, error_flag, stream);
+  return slopes ? launch_tc<128, true>(q, k_pool, v_pool, out, *sb, tile_seq, tile_q0, n_tiles, p, error_flag, stream)
+                : launch_tc<128, false>(q, k_pool, v_pool, out, *sb, tile_seq, tile_q0, n_tiles, p, error_flag, stream);
 }

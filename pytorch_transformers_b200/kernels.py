@@ -272,16 +272,18 @@ def attention_tc_supports(head_dim: int) -> bool:
 
 
 def attention_tc(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, batch: StepBatchC,
-                 tile_seq: torch.Tensor, tile_q0: torch.Tensor, n_tiles: int, kv_heads: int, scale: float):
+                 tile_seq: torch.Tensor, tile_q0: torch.Tensor, n_tiles: int, kv_heads: int, scale: float,
+                 slopes: Optional[torch.Tensor] = None):
     """Causal prompt attention on tcgen05 tensor cores with accumulators in tensor memory: bfloat16,
-    head size 64 or 128, tiles of 128 tokens, no bias, no window. Returns [tokens, heads * head_dim]."""
-    _need_cuda(q, k_pool, v_pool, tile_seq, tile_q0)
+    head size 64 or 128, tiles of 128 tokens, no window; ``slopes`` [heads] float32: per-head score
+    slopes (ALiBi). Returns [tokens, heads * head_dim]."""
+    _need_cuda(q, k_pool, v_pool, tile_seq, tile_q0, slopes)
     if q.dtype != torch.bfloat16:
         raise KernelError("attention_tc takes bfloat16 tensors")
     n, heads, head_dim = q.shape
     out = torch.empty((n, heads * head_dim), dtype=q.dtype, device=q.device)
     _check(lib().ptb_attention_tc(_ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), ctypes.byref(batch), _ptr(tile_seq),
-                                  _ptr(tile_q0), n_tiles, heads, kv_heads, head_dim, ctypes.c_float(scale),
+                                  _ptr(tile_q0), n_tiles, _ptr(slopes), heads, kv_heads, head_dim, ctypes.c_float(scale),
                                   _ptr(error_flag(q.device)), _stream(q)), "attention_tc")
     return out
 

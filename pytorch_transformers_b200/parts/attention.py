@@ -107,11 +107,11 @@ class Attention(Part):
 
     def attend(self, q, k_pool, v_pool, ctx, batch, slopes):
         k = self.build.kernels
-        if (q.dtype == self._bf16 and slopes is None and self.window == 0 and ctx.mma_tokens == k.TC_TILE_TOKENS
+        if (q.dtype == self._bf16 and self.window == 0 and ctx.mma_tokens == k.TC_TILE_TOKENS
                 and k.attention_tc_supports(self.head_dim)):
             # long prompts: tcgen05 tensor cores, accumulators in tensor memory
             return k.attention_tc(q, k_pool, v_pool, batch, ctx.dev["mtile_seq"], ctx.dev["mtile_q0"],
-                                  ctx.n_mma_tiles, self.kv_heads, self.scale)
+                                  ctx.n_mma_tiles, self.kv_heads, self.scale, slopes)
         if q.dtype == self._bf16 and k.attention_mma_supports(self.head_dim):
             return self._attend_mma(q, k_pool, v_pool, ctx, batch, slopes)
         return k.attention_generic(q, k_pool, v_pool, batch, ctx.dev["tile_seq"], ctx.dev["tile_q0"], ctx.n_tiles,

@@ -68,7 +68,7 @@ def attention_case(K, dtype, heads, kv_heads, d, pasts, news, position="rotary",
         if tc:
             assert ctx.mma_tokens == K.TC_TILE_TOKENS
             out = K.attention_tc(q, k_pool, v_pool, ctx.batch_c[gi], ctx.dev["mtile_seq"], ctx.dev["mtile_q0"],
-                                 ctx.n_mma_tiles, kv_heads, scale)
+                                 ctx.n_mma_tiles, kv_heads, scale, slopes)
             K.check_device_errors("cuda")
         elif mma is None:
             out = K.attention_generic(q, k_pool, v_pool, ctx.batch_c[gi], ctx.dev["tile_seq"], ctx.dev["tile_q0"],

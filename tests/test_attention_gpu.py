@@ -188,15 +188,17 @@ def test_rope_table_equals_in_kernel_angles(K):
 @pytest.mark.parametrize("news,pasts", [([128], [0]), ([65], [0]), ([129, 300, 70], [0, 0, 0]), ([200, 66], [130, 63]),
                                         ([1000], [0])])
 @pytest.mark.parametrize("d", [64, 128])
-def test_tc_prompts(K, heads, kv, news, pasts, d):
+@pytest.mark.parametrize("position", ["rotary", "alibi"])
+def test_tc_prompts(K, heads, kv, news, pasts, d, position):
     assert K.lib().ptb_attention_tc_tile_tokens() == K.TC_TILE_TOKENS and K.attention_tc_supports(d)
     assert not K.attention_tc_supports(96) and not K.attention_tc_supports(256)
-    out, ref = attention_case(K, BF, heads, kv, d, pasts=pasts, news=news, position="rotary", seed=11, tc=True)
+    out, ref = attention_case(K, BF, heads, kv, d, pasts=pasts, news=news, position=position, seed=11, tc=True)
     torch.testing.assert_close(out, ref, **tol(BF))
 
 
 @pytest.mark.parametrize("d", [64, 128])
-def test_tc_far_key(K, d):
-    out, ref = attention_case(K, BF, 2, 1, d, pasts=[0, 0], news=[70, 700], position="none", seed=5,
+@pytest.mark.parametrize("position", ["none", "alibi"])
+def test_tc_far_key(K, d, position):
+    out, ref = attention_case(K, BF, 2, 1, d, pasts=[0, 0], news=[70, 700], position=position, seed=5,
                               needle=(1, 3), tc=True)
     torch.testing.assert_close(out, ref, **tol(BF))
