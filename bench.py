@@ -123,9 +123,11 @@ def decode_bytes(c, layers, batch, context):
 
 
 def prefill_flops(c, layers, tokens):
-    h, nh, f, v = c["hidden_size"], c["num_attention_heads"], 4 * c["hidden_size"], c["vocab_size"]
+    h, nh, v = c["hidden_size"], c["num_attention_heads"], c["vocab_size"]
+    f = c.get("ffn_hidden_size") or 4 * h
+    kvh = c.get("num_kv_heads", 1) if c.get("new_decoder_architecture") else (1 if c.get("multi_query", True) else nh)
     d = h // nh
-    gemm = 2 * tokens * layers * ((nh + 2) * d * h + h * h + 2 * f * h)
+    gemm = 2 * tokens * layers * ((nh + 2 * kvh) * d * h + h * h + 2 * f * h)
     attn = layers * nh * 2 * 2 * d * tokens * (tokens + 1) / 2      # QK^T and PV over the causal half
     head = 2 * v * h
     return gemm + attn + head
@@ -207,8 +209,9 @@ def run_ours(args):
         return 0
 
     # ---- prefill of 2,048 tokens (one prompt) ----
-    cache = model.new_cache(PREFILL_TOKENS + 64)
-    p = prompts(1, PREFILL_TOKENS)
+    n_prefill = args.prefill_tokens if args.only == "prefill" else PREFILL_TOKENS
+    cache = model.new_cache(n_prefill + 64)
+    p = prompts(1, n_prefill)
     times = []
     for i in range(2 + 3):
         s = cache.open()
@@ -224,8 +227,9 @@ def run_ours(args):
     del cache
     pre_ms = statistics.median(times)
     if args.only == "prefill":
-        print(json.dumps({"only": "prefill", "layers": layers, "ms": round(pre_ms, 3),
-                          "TFLOPs": round(prefill_flops(FALCON_7B, layers, PREFILL_TOKENS) / pre_ms / 1e9, 1)}))
+        print(json.dumps({"only": "prefill", "shape": args.shape, "tokens": n_prefill, "layers": layers,
+                          "ms": round(pre_ms, 3),
+                          "TFLOPs": round(prefill_flops(shape, layers, n_prefill) / pre_ms / 1e9, 1)}))
         return 0
     pre_flops = prefill_flops(FALCON_7B, layers, PREFILL_TOKENS)
     prefill = {"value": round(PREFILL_TOKENS / pre_ms * 1e3, 1), "tokens": PREFILL_TOKENS, "ms": round(pre_ms, 3),
@@ -376,15 +380,17 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--only", default="", choices=["", "decode", "prefill"],
                     help="run one section only and print its numbers (for profilers)")
-    ap.add_argument("--shape", default="7b", choices=sorted(SHAPES), help="model shape for --only decode")
+    ap.add_argument("--shape", default="7b", choices=sorted(SHAPES), help="model shape for --only decode / prefill")
+    ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS, help="prompt length for --only prefill")
     ap.add_argument("--no-graphs", action="store_true", help="launch every kernel of a decode step itself")
     args = ap.parse_args()
     if args.gpus != 1:
         print(f"bench.py measures one GPU: this library is a single-GPU engine, --gpus {args.gpus} is not run")
         return 2
     args.warmup = max(3, args.warmup)
-    if args.shape != "7b" and args.only != "decode":
-        print("--shape other than 7b goes with --only decode (the headline is measured on the 7B shape)")
+    if (args.shape != "7b" or args.prefill_tokens != PREFILL_TOKENS) and not args.only:
+        print("--shape and --prefill-tokens go with --only decode / --only prefill (the headline is measured on "
+              "the 7B shape with a prefill of 2,048 tokens)")
         return 2
     if args.impl == "reference":
         return run_reference(args)

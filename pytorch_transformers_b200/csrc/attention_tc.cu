@@ -6,8 +6,10 @@
 //
 // One block = 128 consecutive new tokens of one sequence x one query head. 256 softmax threads: threads t
 // and t + 128 share query row t (tensor-memory lane t), each taking 32 of a page's 64 columns (TPR
-// threads per row; 1, 2 and 4 are correct); they also copy the pages. One more warp's first lane issues every matrix instruction. The roles meet only at
-// mbarriers (page landed, S written, P written, O updated): there is no block-wide barrier in the loop. Keys are walked one cache page (64 keys) at a time:
+// threads per row; 1, 2 and 4 are correct). One more warp's first lane issues every matrix
+// instruction, another warp's first lane asks the tensor memory accelerator for the pages. The roles
+// meet only at mbarriers (page landed, stage free, S written, P written, O updated): there is no
+// block-wide barrier in the loop. Keys are walked one cache page (64 keys) at a time:
 //
 //   S = Q K^T      tcgen05.mma  M=128 N=64 K=64   A = Q  (shared, K-major, 128-byte swizzle)
 //                                                 B = K page (shared, K-major, 128-byte swizzle)
@@ -19,24 +21,34 @@
 //   O += P V       tcgen05.mma  M=128 N=64 K=64   A = P, B = V page (shared, MN-major: head dims are
 //                                                 contiguous), D = O in tensor memory, columns [128, 192)
 //
-// The page tiles [64 keys][64 dims] bfloat16 are copied with cp.async into a four-stage ring, each
-// 16-byte chunk XOR-swizzled by its row, which is exactly the canonical 128-byte-swizzle layout that
-// the matrix descriptors name (K-major for Q, K and P; MN-major for V). Completion of the matrix
-// instructions is signalled through tcgen05.commit on mbarriers. Every wait on a barrier is bounded:
-// if it runs out, a flag in global memory is raised and the block carries on to its end (tensor memory
-// is freed on every path), so a fault in the pipeline shows as an error, never as a hang.
+// The page tiles [64 keys][64 dims] bfloat16 come by TMA (cp.async.bulk.tensor.2d over the cache pool
+// seen as rows of D values, 128-byte swizzle) into a four-stage ring: exactly the canonical layout that
+// the matrix descriptors name (K-major for Q, K and P; MN-major for V); a stage's mbarrier counts the
+// bytes, and tcgen05.commit after the O += P V that read a stage gives it back to the copy thread. The
+// softmax threads neither copy nor wait for copies (measured with clock stamps in the loop: of about
+// 3,000 cycles per page a softmax thread spent 900 on issuing its share of the copies and on waiting
+// for them, when the pages still came by cp.async). Completion of the matrix instructions is signalled
+// through tcgen05.commit on mbarriers. Every wait on a barrier is bounded: if it runs out, a flag in
+// global memory is raised and the block carries on to its end (tensor memory is freed on every path,
+// copies in flight are waited for), so a fault in the pipeline shows as an error, never as a hang.
 //
 // Two blocks fit on an SM (97 KB of shared memory and 256 columns of tensor memory each): while one
 // block's threads do softmax, the other's matrix instructions run.
 //
 // Measured on this kernel at 2,048 and 8,192 tokens (71 heads, one K/V head): one, two and four threads
 // per row take 165, 159 and 189 us at 2,048 tokens, so the softmax threads' arithmetic is not the limit;
-// a second P tile (softmax of page i + 1 no longer waits for O += P V of page i, at the price of one
-// page less of prefetch distance) took 164 us. A block is one chain of dependent steps per page
+// a second P tile (softmax of page i + 1 no longer waits for O += P V of page i) took 7 % longer, measured
+// twice, with the pages by cp.async and by TMA. A block is one chain of dependent steps per page
 // (about 1.5 us: tensor-memory load, maximum across the row's threads, exponentials, stores, fence,
 // arrival, issue, matrix instructions, completion), and an SM holds two such chains; the exponential
 // unit is busy a third of the time, the tensor pipe a sixth. More chains per SM (several heads of a
 // K/V group in one block, sharing the page copies) is the open step.
+#include <cudaTypedefs.h>
+
+#include <map>
+#include <mutex>
+#include <tuple>
+
 #include "mma_common.cuh"
 #include "tc_common.cuh"
 
@@ -52,15 +64,6 @@ constexpr int TILE_P_BYTES = TQ * KEYS * 2;    // 16 KB
 template <int ROWS> __device__ __forceinline__ uint32_t swz_tc(int row, int c) {
   return uint32_t((c >> 3) * (ROWS * 128) + row * 128 + (((c & 7) ^ (row & 7)) << 4));
 }
-// copy one page [KEYS][D] (contiguous in global memory) into such a tile
-template <int D>
-__device__ __forceinline__ void load_page_tc(uint32_t smem_tile, const __nv_bfloat16* page, int tid, int nthreads) {
-  constexpr int CHUNKS = D / 8;
-  for (int i = tid; i < KEYS * CHUNKS; i += nthreads) {
-    const int row = i / CHUNKS, c = i % CHUNKS;
-    cp_async16(smem_tile + swz_tc<KEYS>(row, c), page + size_t(row) * D + c * 8);
-  }
-}
 struct TcParams {
   int heads, kv_heads;
   float scale;
@@ -70,7 +73,9 @@ struct TcParams {
 constexpr int TPR = 2;                              // threads per query row
 constexpr int COLS = KEYS / TPR;                    // columns of a page that a thread handles
 constexpr int SOFTMAX_THREADS = TPR * TQ;
-constexpr int BLOCK_THREADS = SOFTMAX_THREADS + 32;  // and one warp whose first lane issues the matrix instructions
+// one more warp whose first lane issues the matrix instructions, and one whose first lane asks the
+// tensor memory accelerator for the pages
+constexpr int BLOCK_THREADS = SOFTMAX_THREADS + 64;
 
 // barrier among the TPR warps that share 32 query rows (ids 1..4 are used)
 __device__ __forceinline__ void row_sync(int id) { asm volatile("bar.sync %0, %1;\n" ::"r"(id), "n"(TPR * 32) : "memory"); }
@@ -82,6 +87,7 @@ __global__ void __launch_bounds__(BLOCK_THREADS, D == 64 ? 2 : 1)
 attention_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_pool,
                     const __nv_bfloat16* __restrict__ v_pool, __nv_bfloat16* __restrict__ out, StepBatch sb,
                     const int* __restrict__ tile_seq, const int* __restrict__ tile_q0, TcParams p,
+                    const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
                     int* __restrict__ error_flag) {
   extern __shared__ unsigned char smem_dyn[];
   // 1024-byte alignment: the swizzle pattern is a function of address bits 4..9
@@ -93,13 +99,15 @@ attention_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
   unsigned char* k_ring = q_tile + TILE_Q_BYTES;                      // STAGES_TC pages
   unsigned char* v_ring = k_ring + STAGES_TC * TILE_KV_BYTES;         // STAGES_TC pages
   unsigned char* p_tile = v_ring + STAGES_TC * TILE_KV_BYTES;         // 16 KB
-  // barriers: [0], [1] S buffer written; [2] O updated; [3] P written; [4 ..] page landed, per stage
+  // barriers: [0], [1] S buffer written; [2] O updated; [3] P written; then per stage: page landed,
+  // stage free again
   uint64_t* bars = reinterpret_cast<uint64_t*>(p_tile + TILE_P_BYTES);
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 4 + STAGES_TC);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 4 + 2 * STAGES_TC);
   float* pmax = reinterpret_cast<float*>(tmem_slot + 2);   // [2 buffers][TPR parts][TQ]: partial row maxima
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const bool mma_warp = warp == SOFTMAX_THREADS / 32;
+  const bool copy_warp = warp == SOFTMAX_THREADS / 32 + 1;
   const int row = tid & (TQ - 1);        // query row of a softmax thread (= its tensor-memory lane)
   const int part = (tid >> 7) % TPR;     // which COLS of the 64 columns of a page it handles
   const int tile = blockIdx.x, h = blockIdx.y;
@@ -115,32 +123,24 @@ attention_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
   const int* pages = sb.pages + size_t(seq) * sb.pages_stride;
 
   const uint32_t bar_s = smem_u32(&bars[0]), bar_o = smem_u32(&bars[2]), bar_p = smem_u32(&bars[3]);
-  const uint32_t bar_k = smem_u32(&bars[4]);
+  const uint32_t bar_k = smem_u32(&bars[4]), bar_free = smem_u32(&bars[4 + STAGES_TC]);
   if (tid == 0) {
     mbar_init(bar_s, 1);
     mbar_init(bar_s + 8, 1);
     mbar_init(bar_o, 1);
     mbar_init(bar_p, SOFTMAX_THREADS);
-    for (int s = 0; s < STAGES_TC; ++s) mbar_init(bar_k + 8 * s, SOFTMAX_THREADS);
+    for (int s = 0; s < STAGES_TC; ++s) {
+      mbar_init(bar_k + 8 * s, 1);      // the copy thread's expect_tx; the bytes complete it
+      mbar_init(bar_free + 8 * s, 1);   // tcgen05.commit after the stage's O += P V
+    }
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
   if (warp == 0) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(tmem_slot)), "r"(256));
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::);
   }
-  auto load_block = [&](int b) {  // softmax threads: page b into stage b % STAGES_TC; one commit group, maybe empty
-    if (b < n_blocks) {
-      const int page = pages[b];
-      const int st = b % STAGES_TC;
-      load_page_tc<D>(smem_u32(k_ring + st * TILE_KV_BYTES), k_pool + kv_offset(page, g, 0, p.kv_heads, D), tid,
-                      SOFTMAX_THREADS);
-      load_page_tc<D>(smem_u32(v_ring + st * TILE_KV_BYTES), v_pool + kv_offset(page, g, 0, p.kv_heads, D), tid,
-                      SOFTMAX_THREADS);
-    }
-    cp_async_commit();
-  };
-  if (!mma_warp) {
-    // Q tile: rows of the tile, zero beyond the valid tokens; then the first three pages
+  if (!mma_warp && !copy_warp) {
+    // Q tile: rows of the tile, zero beyond the valid tokens
     const uint32_t qs = smem_u32(q_tile);
     for (int i = tid; i < TQ * (D / 8); i += SOFTMAX_THREADS) {
       const int r = i / (D / 8), c = i % (D / 8);
@@ -149,20 +149,45 @@ attention_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
       else
         *reinterpret_cast<uint4*>(q_tile + swz_tc<TQ>(r, c)) = make_uint4(0, 0, 0, 0);
     }
-    load_block(0);  // group 0 also holds the Q tile
-    load_block(1);
-    load_block(2);
-    cp_async_wait<2>();   // Q and page 0 have landed (for this thread's copies)
+    cp_async_commit();
+    cp_async_wait<0>();
     proxy_fence_async();
   }
   tc_fence_before();
-  __syncthreads();        // barriers, tensor memory, Q and page 0 are ready for everyone
+  __syncthreads();        // barriers, tensor memory and Q are ready for everyone
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t tmem_o = tmem_base + 128;   // S buffers at columns [0, 64) and [64, 128), O at [128, 128 + D)
   bool alive = true;  // false after a wait ran out: keep going without waiting, results are void
 
-  if (mma_warp) {
+  if (copy_warp) {
+    // ------------------------------------------------------------ the thread that asks for the pages
+    // Page b goes into stage b % STAGES_TC as D / 64 boxes [64 keys x 64 dims] for K and for V, in
+    // the swizzled layout; the stage's barrier counts the bytes. A stage is free again when the
+    // O += P V that read it has completed (S of that page completed before it).
+    if (lane == 0) {
+      constexpr uint32_t PAGE_BYTES = 2 * TILE_KV_BYTES;
+      int issued = 0;
+      for (int b = 0; b < n_blocks; ++b) {
+        const int st = b % STAGES_TC;
+        if (b >= STAGES_TC && !mbar_wait(bar_free + 8 * st, ((b / STAGES_TC) - 1) & 1, error_flag, 6)) break;
+        const int y = (pages[b] * p.kv_heads + g) * KEYS;   // first row of the page in the pool seen as [rows][D]
+        const uint32_t full = bar_k + 8 * st;
+        mbar_expect_tx(full, PAGE_BYTES);
+#pragma unroll
+        for (int blk = 0; blk < D / 64; ++blk) {
+          tma_load_2d(smem_u32(k_ring + st * TILE_KV_BYTES + blk * (KEYS * 128)), &k_map, blk * 64, y, full);
+          tma_load_2d(smem_u32(v_ring + st * TILE_KV_BYTES + blk * (KEYS * 128)), &v_map, blk * 64, y, full);
+        }
+        issued = b + 1;
+      }
+      if (issued < n_blocks) {
+        // a wait ran out: what is in flight lands before the block ends (bounded waits again)
+        for (int b = max(0, issued - STAGES_TC); b < issued; ++b)
+          mbar_wait(bar_k + 8 * (b % STAGES_TC), (b / STAGES_TC) & 1, error_flag, 6);
+      }
+    }
+  } else if (mma_warp) {
     // ------------------------------------------------------------ the thread that issues matrix instructions
     if (lane == 0) {
       constexpr uint32_t IDESC_S = idesc_bf16(TQ, KEYS, false);
@@ -181,14 +206,15 @@ attention_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
                         IDESC_S, blk > 0 ? 1u : 0u);
         tc_commit(bar_s + (b & 1) * 8);
       };
-      issue_s(0, 0);   // page 0 was waited for before the block-wide barrier above
+      alive = mbar_wait(bar_k, 0, error_flag, 4);   // page 0 landed
+      tc_fence_after();
+      if (alive) issue_s(0, 0);
       int st = 0, st_next = 1 % STAGES_TC;   // stages of pages i and i + 1
       for (int i = 0; i < n_blocks && alive; ++i) {
         if (i + 1 < n_blocks) {
-          // page i + 1 landed (all softmax threads said so); S_{i+1} runs under the softmax of page i.
-          // Its S buffer held S_{i-1}, which every thread had read before it reported P_{i-1}.
+          // page i + 1 landed; S_{i+1} runs under the softmax of page i. Its S buffer held S_{i-1},
+          // which every thread had read before it reported P_{i-1}.
           alive = mbar_wait(bar_k + 8 * st_next, ((i + 1) / STAGES_TC) & 1, error_flag, 4);
-          proxy_fence_async();
           tc_fence_after();
           issue_s(i + 1, st_next);
         }
@@ -202,6 +228,7 @@ attention_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
           tc_mma4<2, 128>(tmem_o + blk * 64, desc_p, desc_v0 + st * STAGE_UNITS + blk * KV_BLOCK, IDESC_PV,
                           i > 0 ? 1u : 0u);
         tc_commit(bar_o);
+        tc_commit(bar_free + 8 * st);   // the copy thread may refill this stage
         st = st_next;
         st_next = (st_next + 1 == STAGES_TC) ? 0 : st_next + 1;
       }
@@ -214,20 +241,12 @@ attention_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
     float m_run = -INFINITY, l_run = 0.f;   // running maximum of the raw scores, this thread's half of the sum
     const float slope = BIAS ? p.slopes[h] : 0.f;
     const float sl2 = p.scale * 1.4426950408889634f;
-    // page 0's arrival (the copies were waited for above)
-    mbar_arrive(bar_k);
     for (int i = 0; i < n_blocks; ++i) {
       // (1) this thread's 32 columns of its row of S_i
       if (alive) alive = mbar_wait(bar_s + (i & 1) * 8, (i >> 1) & 1, error_flag, 1);
       tc_fence_after();
       float s[COLS];
       tmem_ld<COLS>(lane_addr + (i & 1) * 64, s);
-      // (2) page i + 1: this thread's copies have landed; tell the issuing thread
-      if (i + 1 < n_blocks) {
-        cp_async_wait<1>();
-        proxy_fence_async();
-        mbar_arrive(bar_k + 8 * ((i + 1) % STAGES_TC));
-      }
       if (BIAS) {
 #pragma unroll
         for (int j = 0; j < COLS; ++j) s[j] += alibi_bias(slope, i * KEYS + part * COLS + j);
@@ -257,13 +276,12 @@ attention_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
       const bool moved = (m_new != m_run) && (m_run != -INFINITY);
       m_run = m_new;
       const float m_off = (m_run == -INFINITY) ? 0.f : m_run * sl2;   // exp2(s * sl2 - m_off); exp2(-inf) = 0
-      // (4) the previous O += P V is complete: its page stage and the P tile are free, O may be touched
+      // (4) the previous O += P V is complete: the P tile is free, O may be touched
       if (i > 0) {
         if (alive) alive = mbar_wait(bar_o, (i - 1) & 1, error_flag, 2);
         tc_fence_after();
       }
-      load_block(i + 3);
-      // (5) rescale this thread's 32 columns of its row of O if any row of the warp moved its maximum
+      // (5) rescale this thread's columns of its row of O if any row of the warp moved its maximum
       if (i > 0 && __any_sync(0xffffffffu, moved)) {
 #pragma unroll
         for (int c0 = 0; c0 < COLS_O; c0 += 32) {
@@ -276,7 +294,7 @@ attention_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
         tmem_st_wait();
       }
       l_run *= corr;
-      // (6) P = exp2(S - max) as bfloat16 into the swizzled P tile: row, chunks 4 half .. 4 half + 3
+      // (6) P = exp2(S - max) as bfloat16 into the swizzled P tile: row, chunks 4 part .. 4 part + 3
       float ls[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int c = 0; c < COLS / 8; ++c) {
@@ -295,7 +313,6 @@ attention_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
       tc_fence_before();
       mbar_arrive(bar_p);   // (7) the issuing thread starts O += P V when all 256 have arrived
     }
-    cp_async_wait<0>();
     // the parts of every row sum meet, in the buffer that the last page did not use, in one order
     float* pl = pmax + (n_blocks & 1) * TPR * TQ;
     pl[part * TQ + row] = l_run;
@@ -334,10 +351,47 @@ PTB_API int ptb_attention_tc_supports(int head_dim) { return (head_dim == 64 || 
 PTB_API int ptb_attention_tc_tile_tokens() { return TQ; }
 
 namespace {
+// a pool of one cache entry, [pages][kv_heads][64 keys][D], seen as rows of D values: boxes of 64 keys x
+// 64 dims land in the 128-byte-swizzle layout. Pools do not move: a map per pool is made once and kept.
+const CUtensorMap* pool_map(const void* pool, int pool_pages, int kv_heads, int d) {
+  struct Key {
+    const void* p; long long rows; int d;
+    bool operator<(const Key& o) const { return std::tie(p, rows, d) < std::tie(o.p, o.rows, o.d); }
+  };
+  static std::map<Key, CUtensorMap> cache;
+  static std::mutex mu;
+  static PFN_cuTensorMapEncodeTiled_v12000 encode = nullptr;
+  std::lock_guard<std::mutex> lock(mu);
+  if (!encode) {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult qr;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qr) != cudaSuccess ||
+        qr != cudaDriverEntryPointSuccess)
+      return nullptr;
+    encode = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(fn);
+  }
+  const Key key{pool, (long long)pool_pages * kv_heads * KEYS, d};
+  auto it = cache.find(key);
+  if (it != cache.end()) return &it->second;
+  CUtensorMap m;
+  const cuuint64_t dims[2] = {cuuint64_t(d), cuuint64_t(key.rows)};
+  const cuuint64_t strides[1] = {cuuint64_t(d) * 2};
+  const cuuint32_t box[2] = {64, cuuint32_t(KEYS)};
+  const cuuint32_t elem[2] = {1, 1};
+  if (encode(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(pool), dims, strides, box, elem,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+    return nullptr;
+  return &cache.emplace(key, m).first->second;
+}
+
 template <int D, bool BIAS>
-int launch_tc(const void* q, const void* k_pool, const void* v_pool, void* out, const StepBatch& sb,
+int launch_tc(const void* q, const void* k_pool, const void* v_pool, int pool_pages, void* out, const StepBatch& sb,
               const int* tile_seq, const int* tile_q0, int n_tiles, const TcParams& p, int* error_flag,
               cudaStream_t stream) {
+  const CUtensorMap* km = pool_map(k_pool, pool_pages, p.kv_heads, D);
+  const CUtensorMap* vm = pool_map(v_pool, pool_pages, p.kv_heads, D);
+  if (km == nullptr || vm == nullptr) return PTB_ERR_LAUNCH;
   const size_t smem = 1024 + TQ * D * 2 + 2 * STAGES_TC * KEYS * D * 2 + TILE_P_BYTES + 128 + 2 * TPR * TQ * sizeof(float);
   static bool configured = false;
   if (!configured) {
@@ -348,27 +402,30 @@ int launch_tc(const void* q, const void* k_pool, const void* v_pool, void* out, 
   dim3 grid(n_tiles, p.heads);
   attention_tc_kernel<D, BIAS><<<grid, BLOCK_THREADS, smem, stream>>>(
       (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, (__nv_bfloat16*)out, sb,
-      tile_seq, tile_q0, p, error_flag);
+      tile_seq, tile_q0, p, *km, *vm, error_flag);
   return launch_status();
 }
 }  // namespace
 
 // Causal attention of prompt tiles of 128 tokens (tile_seq / tile_q0 as for the other attention
-// kernels, 128 tokens per tile), bfloat16, head size 64 or 128, no window. `slopes`: per-head score
+// kernels, 128 tokens per tile), bfloat16, head size 64 or 128, no window. k_pool / v_pool: the pools of
+// one cache entry, [pool_pages][kv_heads][64][head_dim]. `slopes`: per-head score
 // slopes [heads] float32 (already rounded to bfloat16 values), or null. `error_flag` is a device int
 // that stays 0 unless a bounded wait inside the kernel ran out.
-PTB_API int ptb_attention_tc(const void* q, const void* k_pool, const void* v_pool, void* out, const StepBatch* sb,
+PTB_API int ptb_attention_tc(const void* q, const void* k_pool, const void* v_pool, int pool_pages, void* out,
+                             const StepBatch* sb,
                              const int* tile_seq, const int* tile_q0, int n_tiles, const float* slopes, int heads,
                              int kv_heads, int head_dim, float scale, int* error_flag, cudaStream_t stream) {
   if (n_tiles <= 0) return PTB_OK;
+  if (pool_pages <= 0 || (reinterpret_cast<uintptr_t>(k_pool) | reinterpret_cast<uintptr_t>(v_pool)) & 15) return PTB_ERR_ALIGN;
   if ((head_dim != 64 && head_dim != 128) || heads <= 0 || kv_heads <= 0 || heads % kv_heads != 0 || heads > 65535 ||
       error_flag == nullptr)
     return PTB_ERR_SIZE;
   TcParams p;
   p.heads = heads; p.kv_heads = kv_heads; p.scale = scale; p.slopes = slopes;
   if (head_dim == 64)
-    return slopes ? launch_tc<64, true>(q, k_pool, v_pool, out, *sb, tile_seq, tile_q0, n_tiles, p, error_flag, stream)
-                  : launch_tc<64, false>(q, k_pool, v_pool, out, *sb, tile_seq, tile_q0, n_tiles, p, error_flag, stream);
-  return slopes ? launch_tc<128, true>(q, k_pool, v_pool, out, *sb, tile_seq, tile_q0, n_tiles, p, error_flag, stream)
-                : launch_tc<128, false>(q, k_pool, v_pool, out, *sb, tile_seq, tile_q0, n_tiles, p, error_flag, stream);
+    return slopes ? launch_tc<64, true>(q, k_pool, v_pool, pool_pages, out, *sb, tile_seq, tile_q0, n_tiles, p, error_flag, stream)
+                  : launch_tc<64, false>(q, k_pool, v_pool, pool_pages, out, *sb, tile_seq, tile_q0, n_tiles, p, error_flag, stream);
+  return slopes ? launch_tc<128, true>(q, k_pool, v_pool, pool_pages, out, *sb, tile_seq, tile_q0, n_tiles, p, error_flag, stream)
+                : launch_tc<128, false>(q, k_pool, v_pool, pool_pages, out, *sb, tile_seq, tile_q0, n_tiles, p, error_flag, stream);
 }

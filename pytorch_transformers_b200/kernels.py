@@ -282,7 +282,9 @@ def attention_tc(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, ba
         raise KernelError("attention_tc takes bfloat16 tensors")
     n, heads, head_dim = q.shape
     out = torch.empty((n, heads * head_dim), dtype=q.dtype, device=q.device)
-    _check(lib().ptb_attention_tc(_ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), ctypes.byref(batch), _ptr(tile_seq),
+    if not k_pool.is_contiguous() or not v_pool.is_contiguous() or k_pool.shape != v_pool.shape:
+        raise KernelError("attention_tc takes the contiguous K and V pools of one cache entry")
+    _check(lib().ptb_attention_tc(_ptr(q), _ptr(k_pool), _ptr(v_pool), k_pool.shape[0], _ptr(out), ctypes.byref(batch), _ptr(tile_seq),
                                   _ptr(tile_q0), n_tiles, _ptr(slopes), heads, kv_heads, head_dim, ctypes.c_float(scale),
                                   _ptr(error_flag(q.device)), _stream(q)), "attention_tc")
     return out
