@@ -16,14 +16,17 @@
 //                                                 D = S in tensor memory, two buffers of 64 columns: the
 //                                                 product for the next page runs under this page's softmax
 //   softmax        each thread reads its row of S with tcgen05.ld, masks, keeps the running maximum and
-//                  sum in float32, rescales its row of O in tensor memory when the maximum moved, and
-//                  writes P = exp2(S - max) as bfloat16 into shared memory (K-major, swizzled)
-//   O += P V       tcgen05.mma  M=128 N=64 K=64   A = P, B = V page (shared, MN-major: head dims are
-//                                                 contiguous), D = O in tensor memory, columns [128, 192)
+//                  sum in float32, rescales its row of O in tensor memory when the maximum moved (only
+//                  then it waits for the previous page's O += P V), and writes P = exp2(S - max) as
+//                  bfloat16 pairs back into tensor memory with tcgen05.st (columns of its own, two
+//                  buffers for even and odd pages)
+//   O += P V       tcgen05.mma  M=128 N=64 K=64   A = P read from tensor memory, B = V page (shared,
+//                                                 MN-major: head dims are contiguous), D = O in tensor
+//                                                 memory, columns [128, 192)
 //
 // The page tiles [64 keys][64 dims] bfloat16 come by TMA (cp.async.bulk.tensor.2d over the cache pool
 // seen as rows of D values, 128-byte swizzle) into a four-stage ring: exactly the canonical layout that
-// the matrix descriptors name (K-major for Q, K and P; MN-major for V); a stage's mbarrier counts the
+// the matrix descriptors name (K-major for Q and K; MN-major for V); a stage's mbarrier counts the
 // bytes, and tcgen05.commit after the O += P V that read a stage gives it back to the copy thread. The
 // softmax threads neither copy nor wait for copies (measured with clock stamps in the loop: of about
 // 3,000 cycles per page a softmax thread spent 900 on issuing its share of the copies and on waiting
@@ -32,13 +35,16 @@
 // global memory is raised and the block carries on to its end (tensor memory is freed on every path,
 // copies in flight are waited for), so a fault in the pipeline shows as an error, never as a hang.
 //
-// Two blocks fit on an SM (97 KB of shared memory and 256 columns of tensor memory each): while one
-// block's threads do softmax, the other's matrix instructions run.
+// Two blocks fit on an SM (81 KB of shared memory and 256 columns of tensor memory each): while one
+// block's threads do softmax, the other's matrix instructions run. Threads of a block may be a page
+// apart, which is why "P written" and "O updated" have a barrier each for even and for odd pages: an
+// arrival for page i + 1 must not count for page i.
 //
 // Measured on this kernel at 2,048 and 8,192 tokens (71 heads, one K/V head): one, two and four threads
 // per row take 165, 159 and 189 us at 2,048 tokens, so the softmax threads' arithmetic is not the limit;
-// a second P tile (softmax of page i + 1 no longer waits for O += P V of page i) took 7 % longer, measured
-// twice, with the pages by cp.async and by TMA. A block is one chain of dependent steps per page
+// a second P tile in shared memory (softmax of page i + 1 no longer waits for O += P V of page i) took
+// 7 % longer, measured twice; P in tensor memory instead (no shared-memory stores, no proxy fence, the
+// same freedom) is 2 to 5 % faster than P in shared memory. A block is one chain of dependent steps per page
 // (about 1.5 us: tensor-memory load, maximum across the row's threads, exponentials, stores, fence,
 // arrival, issue, matrix instructions, completion), and an SM holds two such chains; the exponential
 // unit is busy a third of the time, the tensor pipe a sixth. More chains per SM (several heads of a
@@ -56,7 +62,6 @@ namespace {
 
 constexpr int TQ = 128;          // query rows per block
 constexpr int STAGES_TC = 4;
-constexpr int TILE_P_BYTES = TQ * KEYS * 2;    // 16 KB
 // Tiles of D = 64 or 128 dims are kept as D / 64 blocks of [rows][64 dims], one after another, each
 // block with the 128-byte swizzle: the layout that the matrix descriptors name for K-major operands
 // (Q, K: a block per 64 values of the contraction) and for the MN-major V (a block per 64 dims of
@@ -95,14 +100,16 @@ attention_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
   constexpr int TILE_Q_BYTES = TQ * D * 2;       // 16 or 32 KB
   constexpr int TILE_KV_BYTES = KEYS * D * 2;    // 8 or 16 KB
   constexpr int COLS_O = D / TPR;                // columns of O that a thread rescales and writes
+  // tensor memory: S of even and odd pages at columns [0, 64) and [64, 128), O at [128, 128 + D), then P
+  // of even and odd pages, 64 keys as bfloat16 pairs in 32 columns each
+  constexpr uint32_t TMEM_P = 128 + D, TMEM_COLS = (D == 64) ? 256 : 512;
   unsigned char* q_tile = smem;
   unsigned char* k_ring = q_tile + TILE_Q_BYTES;                      // STAGES_TC pages
   unsigned char* v_ring = k_ring + STAGES_TC * TILE_KV_BYTES;         // STAGES_TC pages
-  unsigned char* p_tile = v_ring + STAGES_TC * TILE_KV_BYTES;         // 16 KB
   // barriers: [0], [1] S buffer written; [2] O updated; [3] P written; then per stage: page landed,
   // stage free again
-  uint64_t* bars = reinterpret_cast<uint64_t*>(p_tile + TILE_P_BYTES);
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 4 + 2 * STAGES_TC);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(v_ring + STAGES_TC * TILE_KV_BYTES);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 6 + 2 * STAGES_TC);
   float* pmax = reinterpret_cast<float*>(tmem_slot + 2);   // [2 buffers][TPR parts][TQ]: partial row maxima
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -123,11 +130,16 @@ attention_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
   const int* pages = sb.pages + size_t(seq) * sb.pages_stride;
 
   const uint32_t bar_s = smem_u32(&bars[0]), bar_o = smem_u32(&bars[2]), bar_p = smem_u32(&bars[3]);
+  // O updated and P written for odd pages (bar_o, bar_p: even pages). A thread may be a page ahead of
+  // another one: arrivals for page i + 1 must not count for page i.
+  const uint32_t bar_o2 = smem_u32(&bars[4 + 2 * STAGES_TC]), bar_p2 = smem_u32(&bars[5 + 2 * STAGES_TC]);
   const uint32_t bar_k = smem_u32(&bars[4]), bar_free = smem_u32(&bars[4 + STAGES_TC]);
   if (tid == 0) {
     mbar_init(bar_s, 1);
     mbar_init(bar_s + 8, 1);
     mbar_init(bar_o, 1);
+    mbar_init(bar_o2, 1);
+    mbar_init(bar_p2, SOFTMAX_THREADS);
     mbar_init(bar_p, SOFTMAX_THREADS);
     for (int s = 0; s < STAGES_TC; ++s) {
       mbar_init(bar_k + 8 * s, 1);      // the copy thread's expect_tx; the bytes complete it
@@ -136,7 +148,7 @@ attention_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
   if (warp == 0) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(tmem_slot)), "r"(256));
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS));
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::);
   }
   if (!mma_warp && !copy_warp) {
@@ -193,7 +205,6 @@ attention_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
       constexpr uint32_t IDESC_S = idesc_bf16(TQ, KEYS, false);
       constexpr uint32_t IDESC_PV = idesc_bf16(TQ, 64, true);   // 64 dims of the output per instruction
       const uint64_t desc_q = smem_desc(smem_u32(q_tile), 16, 1024);
-      const uint64_t desc_p = smem_desc(smem_u32(p_tile), 16, 1024);
       const uint64_t desc_k0 = smem_desc(smem_u32(k_ring), 16, 1024);
       const uint64_t desc_v0 = smem_desc(smem_u32(v_ring), 16, 1024);
       constexpr uint64_t STAGE_UNITS = TILE_KV_BYTES >> 4;   // the address field counts 16-byte units
@@ -220,14 +231,13 @@ attention_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
         }
         // P_i is written and O is rescaled: O += P_i V_i (16 keys: 32 bytes along P's rows, 2048 bytes
         // down V's rows)
-        if (alive) alive = mbar_wait(bar_p, i & 1, error_flag, 5);
-        proxy_fence_async();
+        if (alive) alive = mbar_wait((i & 1) ? bar_p2 : bar_p, (i >> 1) & 1, error_flag, 5);
         tc_fence_after();
 #pragma unroll
         for (int blk = 0; blk < D / 64; ++blk)
-          tc_mma4<2, 128>(tmem_o + blk * 64, desc_p, desc_v0 + st * STAGE_UNITS + blk * KV_BLOCK, IDESC_PV,
-                          i > 0 ? 1u : 0u);
-        tc_commit(bar_o);
+          tc_mma4_ts<128>(tmem_o + blk * 64, tmem_base + TMEM_P + (i & 1) * 32, desc_v0 + st * STAGE_UNITS + blk * KV_BLOCK,
+                          IDESC_PV, i > 0 ? 1u : 0u);
+        tc_commit((i & 1) ? bar_o2 : bar_o);
         tc_commit(bar_free + 8 * st);   // the copy thread may refill this stage
         st = st_next;
         st_next = (st_next + 1 == STAGES_TC) ? 0 : st_next + 1;
@@ -276,13 +286,11 @@ attention_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
       const bool moved = (m_new != m_run) && (m_run != -INFINITY);
       m_run = m_new;
       const float m_off = (m_run == -INFINITY) ? 0.f : m_run * sl2;   // exp2(s * sl2 - m_off); exp2(-inf) = 0
-      // (4) the previous O += P V is complete: the P tile is free, O may be touched
-      if (i > 0) {
-        if (alive) alive = mbar_wait(bar_o, (i - 1) & 1, error_flag, 2);
-        tc_fence_after();
-      }
-      // (5) rescale this thread's columns of its row of O if any row of the warp moved its maximum
+      // (4) rescale this thread's columns of its row of O if any row of the warp moved its maximum;
+      // only then this warp waits for the previous page's O += P V
       if (i > 0 && __any_sync(0xffffffffu, moved)) {
+        if (alive) alive = mbar_wait(((i - 1) & 1) ? bar_o2 : bar_o, ((i - 1) >> 1) & 1, error_flag, 2);
+        tc_fence_after();
 #pragma unroll
         for (int c0 = 0; c0 < COLS_O; c0 += 32) {
           float o[32];
@@ -295,23 +303,24 @@ attention_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
       }
       l_run *= corr;
       // (6) P = exp2(S - max) as bfloat16 into the swizzled P tile: row, chunks 4 part .. 4 part + 3
+      static_assert(COLS == 32, "P goes to tensor memory 16 packed columns per thread");
       float ls[4] = {0.f, 0.f, 0.f, 0.f};
+      uint32_t w[16];
 #pragma unroll
-      for (int c = 0; c < COLS / 8; ++c) {
-        uint32_t w[4];
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const float a = fast_exp2(fmaf(s[c * 8 + 2 * e], sl2, -m_off));
-          const float b = fast_exp2(fmaf(s[c * 8 + 2 * e + 1], sl2, -m_off));
-          ls[e] += a + b;
-          w[e] = pack_bf16(a, b);
-        }
-        *reinterpret_cast<uint4*>(p_tile + swz<KEYS>(row, part * (COLS / 8) + c)) = make_uint4(w[0], w[1], w[2], w[3]);
+      for (int e = 0; e < 16; ++e) {
+        const float a = fast_exp2(fmaf(s[2 * e], sl2, -m_off));
+        const float b = fast_exp2(fmaf(s[2 * e + 1], sl2, -m_off));
+        ls[e & 3] += a + b;
+        w[e] = pack_bf16(a, b);
       }
+      // P of even / odd pages has its own columns: keys 2c, 2c + 1 in column c. This buffer was read
+      // by the O += P V of two pages ago, which is complete: S of this page was committed after it was
+      // issued, and a commit covers every matrix instruction issued before it.
+      tmem_st16_u32(tmem_base + (uint32_t((warp & 3) * 32) << 16) + TMEM_P + (i & 1) * 32 + part * 16, w);
+      tmem_st_wait();
       l_run += (ls[0] + ls[1]) + (ls[2] + ls[3]);   // this thread's half of the row sum
-      proxy_fence_async();
       tc_fence_before();
-      mbar_arrive(bar_p);   // (7) the issuing thread starts O += P V when all 256 have arrived
+      mbar_arrive((i & 1) ? bar_p2 : bar_p);   // (7) the issuing thread starts O += P V when all 256 have arrived
     }
     // the parts of every row sum meet, in the buffer that the last page did not use, in one order
     float* pl = pmax + (n_blocks & 1) * TPR * TQ;
@@ -320,7 +329,7 @@ attention_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
     float l_row = 0.f;
 #pragma unroll
     for (int o = 0; o < TPR; ++o) l_row += pl[o * TQ + row];
-    if (alive) alive = mbar_wait(bar_o, (n_blocks - 1) & 1, error_flag, 3);
+    if (alive) alive = mbar_wait(((n_blocks - 1) & 1) ? bar_o2 : bar_o, ((n_blocks - 1) >> 1) & 1, error_flag, 3);
     tc_fence_after();
     const float inv = l_row > 0.f ? 1.f / l_row : 0.f;
     __nv_bfloat16* dst = out + (size_t(start + q0 + row) * p.heads + h) * D + part * COLS_O;
@@ -342,7 +351,7 @@ attention_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
   tc_fence_before();
   __syncthreads();
   if (warp == 0)
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(256));
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(TMEM_COLS));
 }
 
 }  // namespace
@@ -392,7 +401,7 @@ int launch_tc(const void* q, const void* k_pool, const void* v_pool, int pool_pa
   const CUtensorMap* km = pool_map(k_pool, pool_pages, p.kv_heads, D);
   const CUtensorMap* vm = pool_map(v_pool, pool_pages, p.kv_heads, D);
   if (km == nullptr || vm == nullptr) return PTB_ERR_LAUNCH;
-  const size_t smem = 1024 + TQ * D * 2 + 2 * STAGES_TC * KEYS * D * 2 + TILE_P_BYTES + 128 + 2 * TPR * TQ * sizeof(float);
+  const size_t smem = 1024 + TQ * D * 2 + 2 * STAGES_TC * KEYS * D * 2 + 128 + 2 * TPR * TQ * sizeof(float);
   static bool configured = false;
   if (!configured) {
     if (cudaFuncSetAttribute(attention_tc_kernel<D, BIAS>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess)

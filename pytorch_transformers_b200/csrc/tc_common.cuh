@@ -181,3 +181,31 @@ template <> __device__ __forceinline__ void tmem_st<64>(uint32_t taddr, const fl
   tmem_st32(taddr, a);
   tmem_st32(taddr + 32, b);
 }
+
+// The same with A read from tensor memory (bfloat16 pairs packed into 32-bit columns, row = lane): from
+// one instruction to the next A advances by 8 columns (16 k), the B descriptor by B_STEP units.
+template <int B_STEP>
+__device__ __forceinline__ void tc_mma4_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                           uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t.reg .b64 b;\n\t.reg .b32 a;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "setp.eq.b32 q, %3, %3;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t"
+      "add.u32 a, %1, 8;\n\tadd.u64 b, %2, %5;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [a], b, %3, q;\n\t"
+      "add.u32 a, a, 8;\n\tadd.u64 b, b, %5;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [a], b, %3, q;\n\t"
+      "add.u32 a, a, 8;\n\tadd.u64 b, b, %5;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [a], b, %3, q;\n\t}\n"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate), "n"(B_STEP) : "memory");
+}
+// 16 consecutive columns of this thread's lane from 16 registers
+__device__ __forceinline__ void tmem_st16_u32(uint32_t taddr, const uint32_t (&v)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};\n"
+      ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]),
+        "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])
+      : "memory");
+}
