@@ -4,9 +4,9 @@
 // is for head size 64; with 128 the tiles of Q, K and V are two blocks of 64 dims, S takes two groups
 // of matrix instructions, O two (one per 64 dims of the output), and one block fits on an SM.
 //
-// One block = 128 consecutive new tokens of one sequence x one query head. 256 softmax threads: threads t
-// and t + 128 share query row t (tensor-memory lane t), each taking 32 of a page's 64 columns (TPR
-// threads per row; 1, 2 and 4 are correct). One more warp's first lane issues every matrix
+// One block = 128 consecutive new tokens of one sequence x one query head. 128 softmax threads, one per
+// query row (tensor-memory lane t = row t; TPR threads per row: 1, 2 and 4 are correct, with 2 or 4
+// the threads of a row split a page's 64 columns). One more warp's first lane issues every matrix
 // instruction, another warp's first lane asks the tensor memory accelerator for the pages. The roles
 // meet only at mbarriers (page landed, stage free, S written, P written, O updated): there is no
 // block-wide barrier in the loop. Keys are walked one cache page (64 keys) at a time:
@@ -41,7 +41,11 @@
 // arrival for page i + 1 must not count for page i.
 //
 // Measured on this kernel at 2,048 and 8,192 tokens (71 heads, one K/V head): one, two and four threads
-// per row take 165, 159 and 189 us at 2,048 tokens, so the softmax threads' arithmetic is not the limit;
+// per row took 165, 159 and 189 us at 2,048 tokens while the softmax threads still copied the pages and
+// wrote P to shared memory; now one thread per row is 2 to 3 % ahead of two (136 against 140 us). Clock
+// stamps in the loop (cycles per page, of about 2,500): the exponentials and the packing to bfloat16 750
+// (two blocks share the SM's 16 transcendental lanes: that is their full rate), the wait for S 500, the
+// rescaling test 350, mask and maximum 280, loads and stores of tensor memory 330;
 // a second P tile in shared memory (softmax of page i + 1 no longer waits for O += P V of page i) took
 // 7 % longer, measured twice; P in tensor memory instead (no shared-memory stores, no proxy fence, the
 // same freedom) is 2 to 5 % faster than P in shared memory. A block is one chain of dependent steps per page
@@ -75,7 +79,7 @@ struct TcParams {
   const float* slopes;   // per-head score slopes (ALiBi), or null
 };
 
-constexpr int TPR = 2;                              // threads per query row
+constexpr int TPR = 1;                              // threads per query row
 constexpr int COLS = KEYS / TPR;                    // columns of a page that a thread handles
 constexpr int SOFTMAX_THREADS = TPR * TQ;
 // one more warp whose first lane issues the matrix instructions, and one whose first lane asks the
@@ -303,11 +307,11 @@ attention_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
       }
       l_run *= corr;
       // (6) P = exp2(S - max) as bfloat16 into the swizzled P tile: row, chunks 4 part .. 4 part + 3
-      static_assert(COLS == 32, "P goes to tensor memory 16 packed columns per thread");
+      static_assert(COLS == 32 || COLS == 64, "P goes to tensor memory 16 or 32 packed columns per thread");
       float ls[4] = {0.f, 0.f, 0.f, 0.f};
-      uint32_t w[16];
+      uint32_t w[COLS / 2];
 #pragma unroll
-      for (int e = 0; e < 16; ++e) {
+      for (int e = 0; e < COLS / 2; ++e) {
         const float a = fast_exp2(fmaf(s[2 * e], sl2, -m_off));
         const float b = fast_exp2(fmaf(s[2 * e + 1], sl2, -m_off));
         ls[e & 3] += a + b;
@@ -316,7 +320,8 @@ attention_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
       // P of even / odd pages has its own columns: keys 2c, 2c + 1 in column c. This buffer was read
       // by the O += P V of two pages ago, which is complete: S of this page was committed after it was
       // issued, and a commit covers every matrix instruction issued before it.
-      tmem_st16_u32(tmem_base + (uint32_t((warp & 3) * 32) << 16) + TMEM_P + (i & 1) * 32 + part * 16, w);
+      const uint32_t p_addr = tmem_base + (uint32_t((warp & 3) * 32) << 16) + TMEM_P + (i & 1) * 32 + part * (COLS / 2);
+      tmem_st_u32<COLS / 2>(p_addr, w);
       tmem_st_wait();
       l_run += (ls[0] + ls[1]) + (ls[2] + ls[3]);   // this thread's half of the row sum
       tc_fence_before();
