@@ -173,8 +173,10 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ fused, __nv_bfloat16* 
     cp_async_wait<STAGES - 1>();
     __syncthreads();
     const uint32_t ks = smem_base + (i % STAGES) * 2 * TILE_BYTES, vs = ks + TILE_BYTES;
-    if (kb == kb_last) {
-      // the new token's row, from registers of this block rather than from the cache
+    if (kb == kb_last && p.write_cache) {
+      // the new token's row, from this block's staging rather than from the cache (another block
+      // may still be writing it there). A layer that only reads another layer's cache finds the row
+      // in the cache: the owner wrote it earlier in the step.
       unsigned char* kt = smem_raw + (i % STAGES) * 2 * TILE_BYTES;
       const int r = pos % KEYS;
       for (int e = tid; e < D; e += nthreads) {
