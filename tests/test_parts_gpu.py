@@ -447,3 +447,109 @@ def test_toy_architecture_with_a_routed_feed_forward_and_other_position_encoding
     cache.check()
     gen = model.generate([reqs[1]], max_new_tokens=3, eos_token_id=None)
     assert len(gen[0]) == len(reqs[1]) + 3
+
+
+# ------------------------------------------------ a third toy: a layer with all keys and a layer with a window
+def _register_toy_window():
+    import pytorch_transformers_b200 as ptb
+    from pytorch_transformers_b200.config.base import ModelConfig
+    from pytorch_transformers_b200.parts import ModelSpec, PartSpec, ScheduleEntry
+
+    @dataclasses.dataclass
+    class ToyWindowConfig(ModelConfig):
+        model_type: ClassVar[str] = "toy_window"
+        vocab_size: int = 97
+        hidden_size: int = 128
+        heads: int = 2
+        window: int = 40
+
+    def spec(cfg):
+        h, d = cfg.hidden_size, cfg.hidden_size // cfg.heads
+
+        def norm(name):
+            return PartSpec("norm", "rmsnorm", {"size": h, "eps": 1e-6}, names={"weight": name + ".weight"})
+
+        def block(i, window):
+            attn = PartSpec("mixer", "attention", {"hidden": h, "heads": cfg.heads, "kv_heads": 1, "head_dim": d,
+                                                   "window": window},
+                            children={"position": PartSpec("position", "rotary", {"head_dim": d, "theta": 1000.0})},
+                            names={"qkv.weight": f"l{i}.qkv.weight", "out.weight": f"l{i}.out.weight"})
+            ff = PartSpec("feed_forward", "dense", {"hidden": h, "inner": 96, "activation": "relu"},
+                          names={"up.weight": f"l{i}.up.weight", "down.weight": f"l{i}.down.weight"})
+            return PartSpec("block", "sequential", children={"norm_mixer": norm(f"l{i}.n1"), "norm_ff": norm(f"l{i}.n2"),
+                                                             "mixer": attn, "feed_forward": ff})
+
+        return ModelSpec(cfg.vocab_size, h, "embed.weight", [block(0, 0), block(1, cfg.window)], norm("nf"), None,
+                         [ScheduleEntry(0, 0), ScheduleEntry(1, 1)])
+
+    ptb.register_architecture("toy_window", ("ToyWindowForCausalLM",), ToyWindowConfig, spec)
+    return ToyWindowConfig
+
+
+def toy_window_plain(ids, w, cfg):
+    h, nh = cfg.hidden_size, cfg.heads
+    d = h // nh
+    c = {"num_attention_heads": nh, "hidden_size": h, "new_decoder_architecture": False, "multi_query": True,
+         "num_kv_heads": 1}
+    inv = 1.0 / (1000.0 ** (torch.arange(0, d, 2, dtype=torch.int64).float() / d))
+
+    def rms(x, name):
+        return x / torch.sqrt((x ** 2).mean(-1, keepdim=True) + 1e-6) * w[name + ".weight"]
+
+    def attn(a, i, window):
+        q, k, v = plain.split_heads(a @ w[f"l{i}.qkv.weight"].T, c)
+        pos = torch.arange(a.shape[0])
+        q, k = plain.rotary(q, pos, inv), plain.rotary(k, pos, inv)
+        s = a.shape[0]
+        out = torch.empty(s, nh, d, dtype=a.dtype)
+        seen = pos[None, :] <= pos[:, None]
+        if window:
+            seen = seen & (pos[None, :] > pos[:, None] - window)     # the query's own position and window - 1 before it
+        for hh in range(nh):
+            scores = (q[:, hh] @ k[:, 0].T) / math.sqrt(d)
+            out[:, hh] = torch.softmax(scores.masked_fill(~seen, float("-inf")), -1) @ v[:, 0]
+        return out.reshape(s, h) @ w[f"l{i}.out.weight"].T
+
+    x = w["embed.weight"][torch.tensor(ids)]
+    for i, window in ((0, 0), (1, cfg.window)):
+        x = x + attn(rms(x, f"l{i}.n1"), i, window)
+        m = rms(x, f"l{i}.n2")
+        x = x + torch.relu(m @ w[f"l{i}.up.weight"].T) @ w[f"l{i}.down.weight"].T
+    return rms(x, "nf") @ w["embed.weight"].T
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_toy_architecture_with_a_full_and_a_windowed_layer(tmp_path, dtype):
+    """Two storage groups in one cache: the first layer keeps all keys, the second a window of 40 (no
+    multiple of the page), whose pages behind the window go back to the pool while the sequences grow.
+    Prompts longer than the window, batches of unequal lengths, 100 single-token steps on a cache that
+    would not hold the windowed layer's keys without the release."""
+    import pytorch_transformers_b200 as ptb
+    Config = _register_toy_window()
+    cfg = Config()
+    folder = ptb.write_random_model(cfg, seed=9, folder=str(tmp_path / "toy_window"), dtype=getattr(torch, dtype))
+    model = ptb.AutoModelForCausalLM.from_pretrained(folder, dtype=dtype)
+    _, w = plain.load_folder(folder, torch.float64)
+    tol = dict(atol=2e-5, rtol=1e-4) if dtype == "float32" else dict(atol=3e-2, rtol=3e-2)
+    g = torch.Generator().manual_seed(4)
+    reqs = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (230, 45, 131)]
+    refs = [toy_window_plain(ids, w, cfg) for ids in reqs]
+    cache = model.new_cache(64 * 8)
+    kinds = sorted(grp.need.kind for grp in cache.groups)
+    assert kinds == ["full", "window"]
+    slots = [cache.open() for _ in reqs]
+    heads = [130, 5, 31]
+    out = model.step(cache, slots, [r[:n] for r, n in zip(reqs, heads)], want="last")
+    live, t = list(range(3)), 0
+    while live:
+        for row, i in enumerate(live):
+            torch.testing.assert_close(out[row].double().cpu(), refs[i][heads[i] + t - 1], **tol)
+        live = [i for i in live if heads[i] + t < len(reqs[i])]
+        if not live:
+            break
+        out = model.step(cache, [slots[i] for i in live], [[reqs[i][heads[i] + t]] for i in live], want="last")
+        t += 1
+        window_group = next(grp for grp in cache.groups if grp.need.kind == "window")
+        assert window_group.pool.in_use <= 2 * len(live) + 1      # a window of 40 spans at most two pages
+    cache.close_all()
+    cache.check()
