@@ -152,8 +152,9 @@ def run_ours(args):
     def prompts(n, length):
         return torch.randint(0, cfg.vocab_size, (n, length), generator=gen).tolist()
 
-    def decode_run(batch, steps, warmup, sample_clocks=False):
-        """Prefill `batch` prompts of CONTEXT tokens, then time `steps` decode steps."""
+    def decode_run(batch, steps, warmup, sample_clocks=False, context=CONTEXT):
+        """Prefill `batch` prompts of `context` tokens, then time `steps` decode steps."""
+        CONTEXT = context
         total = CONTEXT + steps + warmup + 1
         cache = model.new_cache(batch * ((total + 63) // 64 * 64))
         slots = [cache.open() for _ in range(batch)]
@@ -199,9 +200,10 @@ def run_ours(args):
     if args.no_graphs:
         model.use_graphs = False
     if args.only == "decode":
-        ms, launches, ctx_mid, _ = decode_run(args.batch, args.steps, args.warmup)
+        ms, launches, ctx_mid, _ = decode_run(args.batch, args.steps, args.warmup, context=args.context)
         kv_bytes = args.batch * ctx_mid * layers * 2 * cfg.kv_heads_eff * cfg.head_dim * 2
-        print(json.dumps({"only": "decode", "shape": args.shape, "batch": args.batch, "layers": layers,
+        print(json.dumps({"only": "decode", "shape": args.shape, "batch": args.batch, "context": args.context,
+                          "layers": layers,
                           "ms_per_step": round(ms, 4), "launches_per_step": launches / args.steps,
                           "GBps": round((model.weight_bytes() - (0 if cfg.tie_word_embeddings else
                                                                 cfg.vocab_size * cfg.hidden_size * 2) + kv_bytes)
@@ -382,14 +384,15 @@ def main():
                     help="run one section only and print its numbers (for profilers)")
     ap.add_argument("--shape", default="7b", choices=sorted(SHAPES), help="model shape for --only decode / prefill")
     ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS, help="prompt length for --only prefill")
+    ap.add_argument("--context", type=int, default=CONTEXT, help="cached tokens per sequence for --only decode")
     ap.add_argument("--no-graphs", action="store_true", help="launch every kernel of a decode step itself")
     args = ap.parse_args()
     if args.gpus != 1:
         print(f"bench.py measures one GPU: this library is a single-GPU engine, --gpus {args.gpus} is not run")
         return 2
     args.warmup = max(3, args.warmup)
-    if (args.shape != "7b" or args.prefill_tokens != PREFILL_TOKENS) and not args.only:
-        print("--shape and --prefill-tokens go with --only decode / --only prefill (the headline is measured on "
+    if (args.shape != "7b" or args.prefill_tokens != PREFILL_TOKENS or args.context != CONTEXT) and not args.only:
+        print("--shape, --context and --prefill-tokens go with --only decode / --only prefill (the headline is measured on "
               "the 7B shape with a prefill of 2,048 tokens)")
         return 2
     if args.impl == "reference":

@@ -3,6 +3,11 @@
 // tensor memory accelerator's tiled copies.
 #pragma once
 #include <cuda.h>
+#include <cudaTypedefs.h>
+
+#include <map>
+#include <mutex>
+#include <tuple>
 
 #include "mma_common.cuh"
 
@@ -223,3 +228,39 @@ __device__ __forceinline__ void tmem_st32_u32(uint32_t taddr, const uint32_t (&v
 template <int N> __device__ __forceinline__ void tmem_st_u32(uint32_t taddr, const uint32_t (&v)[N]);
 template <> __device__ __forceinline__ void tmem_st_u32<16>(uint32_t taddr, const uint32_t (&v)[16]) { tmem_st16_u32(taddr, v); }
 template <> __device__ __forceinline__ void tmem_st_u32<32>(uint32_t taddr, const uint32_t (&v)[32]) { tmem_st32_u32(taddr, v); }
+
+// ---- host side
+// a pool of one cache entry, [pages][kv_heads][64 keys][D], seen as rows of D values: boxes of 64 keys x
+// 64 dims land in the 128-byte-swizzle layout. Pools do not move: a map per pool is made once and kept.
+inline const CUtensorMap* pool_map(const void* pool, int pool_pages, int kv_heads, int d) {
+  struct Key {
+    const void* p; long long rows; int d;
+    bool operator<(const Key& o) const { return std::tie(p, rows, d) < std::tie(o.p, o.rows, o.d); }
+  };
+  static std::map<Key, CUtensorMap> cache;
+  static std::mutex mu;
+  static PFN_cuTensorMapEncodeTiled_v12000 encode = nullptr;
+  std::lock_guard<std::mutex> lock(mu);
+  if (!encode) {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult qr;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qr) != cudaSuccess ||
+        qr != cudaDriverEntryPointSuccess)
+      return nullptr;
+    encode = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(fn);
+  }
+  const Key key{pool, (long long)pool_pages * kv_heads * KEYS, d};
+  auto it = cache.find(key);
+  if (it != cache.end()) return &it->second;
+  CUtensorMap m;
+  const cuuint64_t dims[2] = {cuuint64_t(d), cuuint64_t(key.rows)};
+  const cuuint64_t strides[1] = {cuuint64_t(d) * 2};
+  const cuuint32_t box[2] = {64, cuuint32_t(KEYS)};
+  const cuuint32_t elem[2] = {1, 1};
+  if (encode(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(pool), dims, strides, box, elem,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+    return nullptr;
+  return &cache.emplace(key, m).first->second;
+}
+

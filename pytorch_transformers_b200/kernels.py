@@ -79,7 +79,7 @@ def lib():
                      "ptb_skinny_linear", "ptb_skinny_linear_max_rows", "ptb_skinny_linear_k_multiple",
                      "ptb_rope_table", "ptb_attention_decode", "ptb_attention_tc", "ptb_attention_tc_supports",
                      "ptb_attention_tc_tile_tokens", "ptb_tc_linear", "ptb_tc_linear_max_rows",
-                     "ptb_tc_linear_k_multiple"):
+                     "ptb_tc_linear_k_multiple", "ptb_attention_decode_tc", "ptb_attention_decode_tc_supports"):
             getattr(L, name).restype = ctypes.c_int
         _configured = True
     return L
@@ -241,6 +241,38 @@ def attention_decode(fused: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Te
                                       _ptr(cos), _ptr(sin), pairs, _ptr(slopes), heads, kv_heads, head_dim,
                                       heads_per_tile, n_splits, warps, key_split, ctypes.c_float(scale), window,
                                       1 if write_cache else 0, _stream(fused)), "attention_decode")
+    return out
+
+
+def attention_decode_tc_supports(head_dim: int, q_per_kv: int) -> bool:
+    return bool(lib().ptb_attention_decode_tc_supports(int(head_dim), int(q_per_kv)))
+
+
+def attention_decode_tc(fused: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, batch: StepBatchC, rope,
+                        kv_heads: int, q_per_kv: int, head_dim: int, scale: float, n_splits: int,
+                        write_cache: bool = True):
+    """The attention of a step of single tokens on the tcgen05 tensor cores, for K/V heads that serve
+    33 to 128 query heads of size 64: the query heads of a group are the rows of one tile, S, P and O
+    live in tensor memory, pages come by TMA, ``n_splits`` blocks of one cluster share a sequence's
+    pages and join through distributed shared memory. No score bias, no window.
+    Returns [tokens, heads * head_dim]."""
+    _need_cuda(fused, k_pool, v_pool)
+    if fused.dtype != torch.bfloat16:
+        raise KernelError("attention_decode_tc takes bfloat16 tensors")
+    n = fused.shape[0]
+    heads = kv_heads * q_per_kv
+    if fused.shape[1] != kv_heads * (q_per_kv + 2) * head_dim:
+        raise KernelError(f"fused projection has width {fused.shape[1]}, expected "
+                          f"{kv_heads * (q_per_kv + 2) * head_dim}")
+    if not k_pool.is_contiguous() or not v_pool.is_contiguous() or k_pool.shape != v_pool.shape:
+        raise KernelError("attention_decode_tc takes the contiguous K and V pools of one cache entry")
+    out = torch.empty((n, heads * head_dim), dtype=fused.dtype, device=fused.device)
+    cos, sin = rope if rope is not None else (None, None)
+    pairs = 0 if cos is None else cos.shape[1]
+    _check(lib().ptb_attention_decode_tc(_ptr(fused), _ptr(k_pool), _ptr(v_pool), k_pool.shape[0], _ptr(out),
+                                         ctypes.byref(batch), _ptr(cos), _ptr(sin), pairs, heads, kv_heads, head_dim,
+                                         n_splits, ctypes.c_float(scale), 1 if write_cache else 0,
+                                         _ptr(error_flag(fused.device)), _stream(fused)), "attention_decode_tc")
     return out
 
 

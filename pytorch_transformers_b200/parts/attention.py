@@ -72,6 +72,15 @@ class Attention(Part):
             warps = (hpk + 15) // 16
             want = self._decode_splits(ctx, hpk)
             splits = max(s for s in k.DECODE_SPLITS if s <= want)
+            if (slopes is None and self.window == 0 and getattr(ctx, "side_stream", None) is None
+                    and k.attention_decode_tc_supports(self.head_dim, self.q_per_kv)):
+                # many query heads on a K/V head: they are the rows of one tcgen05 tile. Not while the
+                # feed-forward streams its weights on the other graph branch: this kernel's 100 KB of
+                # shared memory would keep those blocks off the SMs (measured: 3.34 ms against 2.81 ms
+                # per step at batch 8), where the mma.sync kernel's 58 KB fit beside them
+                o = k.attention_decode_tc(fused, k_pool, v_pool, batch, rope, self.kv_heads, self.q_per_kv,
+                                          self.head_dim, self.scale, splits, write_cache=entry.writes_cache)
+                return linear(k, o, self.p_out_weight, self.p_out_bias, add=add)
             o = k.attention_decode(fused, k_pool, v_pool, batch, rope, slopes, self.kv_heads, self.q_per_kv,
                                    self.head_dim, self.scale, self.window, hpk, warps, splits,
                                    write_cache=entry.writes_cache, key_split=self._decode_key_split(warps))

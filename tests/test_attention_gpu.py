@@ -152,6 +152,35 @@ def test_fused_decode_window_with_key_groups(K, window, key_split):
     torch.testing.assert_close(out, ref, **tol(BF))
 
 
+# ------------------------------------------------------------------------------ one-kernel decode on tcgen05
+@pytest.mark.parametrize("heads,kv", [(71, 1), (128, 1), (33, 1), (80, 2), (132, 4)])
+@pytest.mark.parametrize("position", ["rotary", "none"])
+@pytest.mark.parametrize("splits", [1, 2, 3, 8])
+def test_fused_decode_tc(K, heads, kv, position, splits):
+    assert K.attention_decode_tc_supports(64, heads // kv)
+    assert not K.attention_decode_tc_supports(64, 32) and not K.attention_decode_tc_supports(128, 64)
+    assert not K.attention_decode_tc_supports(64, 129)
+    # new tokens at a page's last slot, its first slot, in the middle, as the second token, far out
+    out, ref = attention_case(K, BF, heads, kv, 64, pasts=[63, 64, 200, 1, 700, 127], news=[1] * 6,
+                              position=position, seed=3, fused_decode=("tc", splits))
+    torch.testing.assert_close(out, ref, **tol(BF))
+
+
+@pytest.mark.parametrize("key_pos", [0, 64, 698, 699])
+def test_fused_decode_tc_far_key_and_own_key(K, key_pos):
+    out, ref = attention_case(K, BF, 71, 1, 64, pasts=[0 + 5, 699], news=[1, 1], position="none", seed=5,
+                              needle=(1, key_pos), fused_decode=("tc", 4))
+    torch.testing.assert_close(out, ref, **tol(BF))
+
+
+def test_fused_decode_tc_repeated_steps(K):
+    # three single-token steps in a row on the same cache: each step's key must be in the cache for the next
+    for seed in (1, 2):
+        out, ref = attention_case(K, BF, 71, 1, 64, pasts=[300, 65, 5], news=[1, 1, 1], position="rotary", seed=seed,
+                                  fused_decode=("tc", 2))
+        torch.testing.assert_close(out, ref, **tol(BF))
+
+
 @pytest.mark.parametrize("hpk", [16, 32, None])
 def test_fused_decode_head_chunks_and_repeated_launches(K, hpk):
     # 71 heads in chunks of 16 or 32: several blocks share a K/V head; launched twice so that the
