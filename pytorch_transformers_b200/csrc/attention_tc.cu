@@ -5,8 +5,8 @@
 // of matrix instructions, O two (one per 64 dims of the output), and one block fits on an SM.
 //
 // One block = 128 consecutive new tokens of one sequence x one query head. 128 softmax threads, one per
-// query row (tensor-memory lane t = row t; TPR threads per row: 1, 2 and 4 are correct, with 2 or 4
-// the threads of a row split a page's 64 columns). One more warp's first lane issues every matrix
+// query row (tensor-memory lane t = row t; TPR threads per row: 1 or 2; with 2 the
+// threads of a row split a page's 64 columns). One more warp's first lane issues every matrix
 // instruction, another warp's first lane asks the tensor memory accelerator for the pages. The roles
 // meet only at mbarriers (page landed, stage free, S written, P written, O updated): there is no
 // block-wide barrier in the loop. Keys are walked one cache page (64 keys) at a time:

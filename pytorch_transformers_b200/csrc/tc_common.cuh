@@ -143,48 +143,15 @@ __device__ __forceinline__ void tc_mma4(uint32_t d_tmem, uint64_t a_desc, uint64
       ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "n"(A_STEP), "n"(B_STEP) : "memory");
 }
 
-// N consecutive columns of this thread's lane, N = 16 or 32
+// N consecutive columns of this thread's lane, N = 32 or 64
 template <int N> __device__ __forceinline__ void tmem_ld(uint32_t taddr, float (&v)[N]);
 template <> __device__ __forceinline__ void tmem_ld<32>(uint32_t taddr, float (&v)[32]) { tmem_ld32(taddr, v); }
-template <> __device__ __forceinline__ void tmem_ld<16>(uint32_t taddr, float (&v)[16]) {
-  uint32_t r[16];
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];\n"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-      : "r"(taddr));
-  asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
-#pragma unroll
-  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
-}
-template <int N> __device__ __forceinline__ void tmem_st(uint32_t taddr, const float (&v)[N]);
-template <> __device__ __forceinline__ void tmem_st<32>(uint32_t taddr, const float (&v)[32]) { tmem_st32(taddr, v); }
-template <> __device__ __forceinline__ void tmem_st<16>(uint32_t taddr, const float (&v)[16]) {
-  asm volatile(
-      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
-      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};\n"
-      ::"r"(taddr), "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])),
-        "r"(__float_as_uint(v[3])), "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])),
-        "r"(__float_as_uint(v[6])), "r"(__float_as_uint(v[7])), "r"(__float_as_uint(v[8])),
-        "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])), "r"(__float_as_uint(v[11])),
-        "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])),
-        "r"(__float_as_uint(v[15]))
-      : "memory");
-}
 template <> __device__ __forceinline__ void tmem_ld<64>(uint32_t taddr, float (&v)[64]) {
   float a[32], b[32];
   tmem_ld32(taddr, a);
   tmem_ld32(taddr + 32, b);
 #pragma unroll
   for (int i = 0; i < 32; ++i) { v[i] = a[i]; v[32 + i] = b[i]; }
-}
-template <> __device__ __forceinline__ void tmem_st<64>(uint32_t taddr, const float (&v)[64]) {
-  float a[32], b[32];
-#pragma unroll
-  for (int i = 0; i < 32; ++i) { a[i] = v[i]; b[i] = v[32 + i]; }
-  tmem_st32(taddr, a);
-  tmem_st32(taddr + 32, b);
 }
 
 // The same with A read from tensor memory (bfloat16 pairs packed into 32-bit columns, row = lane): from
