@@ -86,11 +86,15 @@ template <int MT, int NT, int UNROLL>
 __global__ void __launch_bounds__(WARPS * 32)
 skinny_linear_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
                      const float* __restrict__ bias, const __nv_bfloat16* __restrict__ add,
-                     __nv_bfloat16* __restrict__ y_bf16, float* __restrict__ y_f32, int M, int N, int K, int act) {
+                     __nv_bfloat16* __restrict__ y_bf16, float* __restrict__ y_f32, int M, int N, int K, int act,
+                     int ksplit, float* __restrict__ scratch, int* __restrict__ tickets) {
   __shared__ float red[WARPS][MT * 16][NT * 8 + 1];
+  __shared__ int is_last;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int g = lane >> 2, t = lane & 3;
-  const int n0 = blockIdx.x * (16 * MT);
+  // ksplit blocks share a tile of weight rows, each with a share of K
+  const int rank = blockIdx.x % ksplit, tile = blockIdx.x / ksplit;
+  const int n0 = tile * (16 * MT);
   float acc[MT][NT][4];
 #pragma unroll
   for (int i = 0; i < MT; ++i)
@@ -116,10 +120,12 @@ skinny_linear_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* _
   // reads WARPS * UNROLL consecutive chunks of every weight row (one stretch of a DRAM page). What
   // is left after the last full round is dealt round the warps chunk by chunk, in one more step, so
   // that no warp idles.
-  const int chunks = K / KC;
-  const int full = chunks / (WARPS * UNROLL) * (WARPS * UNROLL);
-  sweep<MT, NT, UNROLL>(acc, wrow, xrow, xok, warp * UNROLL, full, WARPS * UNROLL, 1, chunks);
-  sweep<MT, NT, UNROLL>(acc, wrow, xrow, xok, full + warp, full + WARPS, WARPS, WARPS, chunks);
+  const int chunks_all = K / KC;
+  const int per_block = (chunks_all + ksplit - 1) / ksplit;
+  const int c_begin = min(chunks_all, rank * per_block), chunks = min(chunks_all, c_begin + per_block);
+  const int full = (chunks - c_begin) / (WARPS * UNROLL) * (WARPS * UNROLL);
+  sweep<MT, NT, UNROLL>(acc, wrow, xrow, xok, c_begin + warp * UNROLL, c_begin + full, WARPS * UNROLL, 1, chunks);
+  sweep<MT, NT, UNROLL>(acc, wrow, xrow, xok, c_begin + full + warp, c_begin + full + WARPS, WARPS, WARPS, chunks);
   // partial sums of the 8 warps -> shared memory: red[warp][weight row][activation row]
 #pragma unroll
   for (int i = 0; i < MT; ++i)
@@ -131,6 +137,31 @@ skinny_linear_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* _
       red[warp][i * 16 + g + 8][j * 8 + 2 * t + 1] = acc[i][j][3];
     }
   __syncthreads();
+  constexpr int TILE_ELEMS = MT * 16 * NT * 8;
+  if (ksplit > 1) {
+    // This block's partial sums go to its slot of the scratch buffer; the block of the tile that
+    // arrives last (a ticket per tile, put back to zero by that block) sums the slots in the order
+    // of the blocks and runs the epilogue. No atomics on values: the result does not depend on who
+    // arrives when.
+    float* mine = scratch + (size_t(tile) * ksplit + rank) * TILE_ELEMS;
+    for (int idx = threadIdx.x; idx < TILE_ELEMS; idx += WARPS * 32) {
+      const int r = idx % (MT * 16), m = idx / (MT * 16);
+      float v = 0.f;
+#pragma unroll
+      for (int wi = 0; wi < WARPS; ++wi) v += red[wi][r][m];
+      mine[idx] = v;
+    }
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      const int arrived = atomicAdd(&tickets[tile], 1);
+      is_last = (arrived == ksplit - 1) ? 1 : 0;
+      if (is_last) tickets[tile] = 0;
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+  }
   // epilogue: thread -> (activation row m, weight row r); consecutive threads take consecutive r,
   // which are consecutive addresses of y
   for (int idx = threadIdx.x; idx < MT * 16 * NT * 8; idx += WARPS * 32) {
@@ -138,8 +169,12 @@ skinny_linear_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* _
     const int n = n0 + r;
     if (m >= M || n >= N) continue;
     float v = 0.f;
+    if (ksplit > 1) {
+      for (int b = 0; b < ksplit; ++b) v += __ldcg(scratch + (size_t(tile) * ksplit + b) * TILE_ELEMS + idx);
+    } else {
 #pragma unroll
-    for (int wi = 0; wi < WARPS; ++wi) v += red[wi][r][m];
+      for (int wi = 0; wi < WARPS; ++wi) v += red[wi][r][m];
+    }
     if (bias) v += bias[n];
     v = act_f(v, act);
     if (add) v += __bfloat162float(add[size_t(m) * N + n]);
@@ -148,14 +183,77 @@ skinny_linear_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* _
   }
 }
 
+// Blocks per tile of weight rows, each with a share of K. The blocks of a launch are all resident at
+// once and share the SMs' memory bandwidth, so the launch takes as long as the SM with the most blocks:
+// 512 tiles on 148 SMs are 3.46 a piece, some SMs get 4, and the launch takes 16 % longer than its share
+// of the bandwidth. Dividing K by 2, 3 or 4 changes the count to one that divides better (1,024 blocks:
+// 6.92 a piece, 7 at most: 1 %). Taken when it saves more than 3 %, every block keeps at least 16 full
+// rounds of its warps, and the caller has given scratch memory and tickets. Blocks with a short K are
+// slower per byte (measured: Falcon-11B's down projection, K = 16384, in 4 shares 30.8 us against 24.6
+// us undivided, although the shares divide evenly over the SMs; Falcon-40B's, K = 32768, in 2 shares 95
+// against 111 us).
+int k_split(int tiles, int chunks, int round) {
+  static int sms = 0;
+  if (sms == 0) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess ||
+        sms <= 0)
+      sms = 148;
+  }
+  auto excess = [&](int blocks) { return double((blocks + sms - 1) / sms) * sms / blocks; };
+  int best = 1;
+  double best_excess = excess(tiles);
+  for (int s = 2; s <= 4; ++s) {
+    if (chunks / s < 16 * round) break;
+    const double e = excess(tiles * s);
+    if (e < best_excess - 0.03) {
+      best = s;
+      best_excess = e;
+    }
+  }
+  return best;
+}
+
 template <int MT, int NT, int U>
 int launch_skinny(const void* x, const void* w, const float* bias, const void* add, void* y_bf16, float* y_f32,
-                  int M, int N, int K, int act, cudaStream_t stream) {
-  const int grid = (N + 16 * MT - 1) / (16 * MT);
-  skinny_linear_kernel<MT, NT, U><<<grid, WARPS * 32, 0, stream>>>(
+                  int M, int N, int K, int act, float* scratch, size_t scratch_floats, int* tickets, int n_tickets,
+                  size_t* need_floats, cudaStream_t stream) {
+  const int tiles = (N + 16 * MT - 1) / (16 * MT);
+  int ksplit = k_split(tiles, K / KC, WARPS * U);
+  const size_t need = ksplit > 1 ? size_t(tiles) * ksplit * (MT * 16 * NT * 8) : 0;
+  if (need_floats != nullptr) {   // a question, not a launch
+    *need_floats = need;
+    return PTB_OK;
+  }
+  if (scratch == nullptr || tickets == nullptr || scratch_floats < need || n_tickets < tiles) ksplit = 1;
+  skinny_linear_kernel<MT, NT, U><<<tiles * ksplit, WARPS * 32, 0, stream>>>(
       (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, bias, (const __nv_bfloat16*)add, (__nv_bfloat16*)y_bf16,
-      y_f32, M, N, K, act);
+      y_f32, M, N, K, act, ksplit, scratch, tickets);
   return launch_status();
+}
+
+int dispatch_skinny(const void* x, const void* w, const float* bias, const void* add, void* y_bf16, float* y_f32, int M,
+                    int N, int K, int act, float* scratch, size_t scratch_floats, int* tickets, int n_tickets,
+                    size_t* need_floats, cudaStream_t stream) {
+  // Tile height and chunks in flight per warp, from a sweep over the projections of Falcon-7B, 11B and
+  // 40B (each matrix alone, from HBM): wide matrices (many rows, short K) want 32 rows per block and
+  // four chunks in flight at up to 8 activation rows, 16 rows and two chunks at up to 16; the others
+  // 16 rows and four chunks.
+  const bool wide = N >= 16 * 148 * 4;
+#define PTB_SKINNY(MT, NT, U) \
+  return launch_skinny<MT, NT, U>(x, w, bias, add, y_bf16, y_f32, M, N, K, act, scratch, scratch_floats, tickets, \
+                                  n_tickets, need_floats, stream)
+  if (M <= 8) {
+    if (wide) PTB_SKINNY(2, 1, 4);
+    PTB_SKINNY(1, 1, 4);
+  }
+  if (M <= 16) {
+    if (wide) PTB_SKINNY(1, 2, 2);
+    PTB_SKINNY(1, 2, 4);
+  }
+  if (wide) PTB_SKINNY(2, 4, 2);
+  PTB_SKINNY(1, 4, 4);
+#undef PTB_SKINNY
 }
 
 }  // namespace
@@ -166,21 +264,24 @@ PTB_API int ptb_skinny_linear_k_multiple() { return KC; }
 
 // y = act(x w^T + bias) + add. x [M, K], w [N, K], add [M, N] bfloat16; bias float32 [N];
 // exactly one of y_bf16, y_f32 is given. M <= 32, K a multiple of 32, 16-byte aligned x and w.
+// scratch (float32, scratch_floats of them) and tickets (int32, n_tickets of them, all zero between
+// launches: the kernel puts them back) let the kernel divide K among several blocks per tile where that
+// balances the SMs; without them it does not divide. ptb_skinny_linear_scratch says how many floats a
+// launch would use.
 PTB_API int ptb_skinny_linear(const void* x, const void* w, const float* bias, const void* add, void* y_bf16,
-                              float* y_f32, int M, int N, int K, int act, cudaStream_t stream) {
+                              float* y_f32, int M, int N, int K, int act, float* scratch, size_t scratch_floats,
+                              int* tickets, int n_tickets, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return PTB_OK;
   if (M > 32 || K <= 0 || K % KC != 0 || act < 0 || act > 3) return PTB_ERR_SIZE;
   if ((y_bf16 == nullptr) == (y_f32 == nullptr)) return PTB_ERR_SIZE;
   if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w)) & 15) return PTB_ERR_ALIGN;
-  // Tile height and chunks in flight per warp, from a sweep over the projections of Falcon-7B, 11B and
-  // 40B (each matrix alone, from HBM): wide matrices (many rows, short K) want 32 rows per block and
-  // four chunks in flight at up to 8 activation rows, 16 rows and two chunks at up to 16; the others
-  // 16 rows and four chunks.
-  const bool wide = N >= 16 * 148 * 4;
-  if (M <= 8) return wide ? launch_skinny<2, 1, 4>(x, w, bias, add, y_bf16, y_f32, M, N, K, act, stream)
-                          : launch_skinny<1, 1, 4>(x, w, bias, add, y_bf16, y_f32, M, N, K, act, stream);
-  if (M <= 16) return wide ? launch_skinny<1, 2, 2>(x, w, bias, add, y_bf16, y_f32, M, N, K, act, stream)
-                           : launch_skinny<1, 2, 4>(x, w, bias, add, y_bf16, y_f32, M, N, K, act, stream);
-  return wide ? launch_skinny<2, 4, 2>(x, w, bias, add, y_bf16, y_f32, M, N, K, act, stream)
-              : launch_skinny<1, 4, 4>(x, w, bias, add, y_bf16, y_f32, M, N, K, act, stream);
+  return dispatch_skinny(x, w, bias, add, y_bf16, y_f32, M, N, K, act, scratch, scratch_floats, tickets, n_tickets,
+                         nullptr, stream);
+}
+
+PTB_API long long ptb_skinny_linear_scratch(int M, int N, int K) {
+  if (M <= 0 || N <= 0 || M > 32 || K <= 0 || K % KC != 0) return 0;
+  size_t need = 0;
+  dispatch_skinny(nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, M, N, K, 0, nullptr, 0, nullptr, 0, &need, nullptr);
+  return (long long)need;
 }

@@ -414,9 +414,37 @@ def skinny_linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor]
         raise KernelError(f"skinny_linear: shapes x {list(x.shape)}, w {list(w.shape)} do not fit")
     y = torch.empty((m, n), dtype=out_dtype, device=x.device)
     ybf, yf = (y, None) if out_dtype == torch.bfloat16 else (None, y)
+    # where the tiles of w do not divide evenly over the SMs the kernel divides K among several blocks per
+    # tile; their partial sums meet in scratch memory, a zeroed ticket per tile says who is last
+    need = _skinny_scratch_floats(m, n, k)
+    scratch = torch.empty(need, dtype=torch.float32, device=x.device) if need else None
+    tickets = _skinny_tickets(x.device) if need else None
     _check(lib().ptb_skinny_linear(_ptr(x), _ptr(w), _ptr(bias), _ptr(add), _ptr(ybf), _ptr(yf), m, n, k,
-                                   ACTIVATIONS[act], _stream(x)), "skinny_linear")
+                                   ACTIVATIONS[act], _ptr(scratch), ctypes.c_size_t(need), _ptr(tickets),
+                                   SKINNY_TICKETS if need else 0, _stream(x)), "skinny_linear")
     return y
+
+
+SKINNY_TICKETS = 8192
+_skinny_ticket_buffers = {}
+_skinny_scratch_cache = {}
+
+
+def _skinny_tickets(device) -> torch.Tensor:
+    """int32 zeros, one per tile of a launch; the kernel leaves them zero."""
+    device = torch.device(device)
+    if device not in _skinny_ticket_buffers:
+        _skinny_ticket_buffers[device] = torch.zeros(SKINNY_TICKETS, dtype=torch.int32, device=device)
+    return _skinny_ticket_buffers[device]
+
+
+def _skinny_scratch_floats(m: int, n: int, k: int) -> int:
+    key = (m, n, k)
+    if key not in _skinny_scratch_cache:
+        fn = lib().ptb_skinny_linear_scratch
+        fn.restype = ctypes.c_longlong
+        _skinny_scratch_cache[key] = int(fn(m, n, k))
+    return _skinny_scratch_cache[key]
 
 
 _sm_count = {}

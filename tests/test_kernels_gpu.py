@@ -208,6 +208,24 @@ def test_tc_linear_refuses_what_it_does_not_take(K):
         K.tc_linear(rnd(4, 64), rnd(16, 64))
 
 
+@pytest.mark.parametrize("m", [1, 8, 16])
+@pytest.mark.parametrize("n,k,shares", [(8192, 32768, 2), (4096, 65568, 4)])
+def test_skinny_linear_k_divided_among_blocks(K, m, n, k, shares):
+    """512 and 256 tiles of 16 rows do not divide evenly over 148 SMs and K is long enough: 2 and 4 blocks
+    per tile, partial sums through scratch memory, the last block by ticket runs the epilogue. Twice in a
+    row: the tickets must be back at zero. The second K leaves a ragged last round."""
+    bf = torch.bfloat16
+    assert K._skinny_scratch_floats(m, n, k) == (n // 16) * shares * 16 * (8 if m <= 8 else 16)
+    assert K._skinny_scratch_floats(m, 4544, 18176) == 0
+    x, w = rnd(m, k, dtype=bf, seed=1, scale=0.3), rnd(n, k, dtype=bf, seed=2, scale=0.05)
+    b, a = rnd(n, seed=3), rnd(m, n, dtype=bf, seed=4)
+    ref = plain.activation(x.double().cpu() @ w.double().cpu().T + b.double().cpu(), "gelu") + a.double().cpu()
+    for _ in range(2):
+        out = K.skinny_linear(x, w, b, "gelu", a)
+        torch.testing.assert_close(out.double().cpu(), ref, **tol(bf))
+    assert int(K._skinny_tickets(x.device).abs().sum()) == 0
+
+
 def test_skinny_linear_refuses_what_it_does_not_take(K):
     from pytorch_transformers_b200.kernels import KernelError
     assert K.lib().ptb_skinny_linear_max_rows() == K.SKINNY_MAX_ROWS
