@@ -126,3 +126,60 @@ def test_sampling_through_generate(tmp_path):
     # top_k=1 sampling is greedy
     assert model.generate(prompts, max_new_tokens=5, do_sample=True, top_k=1, eos_token_id=None) == \
         model.generate(prompts, max_new_tokens=5, eos_token_id=None)
+
+
+def draws_of_one_row(K, row, rows=4096, n_draws=64, **opt):
+    """rows x n_draws draws from one row of logits (each copy of the row has a stream of its own)."""
+    logits = row[None].expand(rows, -1).contiguous().cuda()
+    return select(K, logits, n_draws=n_draws, do_sample=True, **opt)
+
+
+def check_kept_set(toks, kept, exact_above=25.0):
+    """No token outside the plain filter's set; every token of the set that is expected at least
+    `exact_above` times is drawn; the rarest tenth of the set gets its share of the draws."""
+    allowed = torch.isfinite(kept)
+    counts = torch.bincount(toks.ravel(), minlength=kept.numel())
+    assert counts[~allowed].sum() == 0, torch.nonzero(counts * ~allowed).ravel()[:10]
+    p = torch.softmax(kept.double(), -1)
+    expected = p * toks.numel()
+    assert (counts[expected >= exact_above] > 0).all()
+    order = torch.argsort(p + (~allowed) * 2.0)          # allowed tokens first, rarest first
+    tail = order[: max(1, int(allowed.sum()) // 10)]
+    want = float(expected[tail].sum())
+    assert abs(float(counts[tail].sum()) - want) < 5 * want ** 0.5 + 3, (float(counts[tail].sum()), want)
+
+
+@pytest.mark.parametrize("vocab,scale,opt", [
+    (65024, 3.0, dict(top_k=50)),                      # the threads' maxima bound the candidates
+    (70001, 3.0, dict(top_k=50, top_p=0.8)),           # a width that is no multiple of four
+    (65024, 1.0, dict(top_k=2000)),                    # more candidates than the block holds
+    (2000, 0.3, dict(top_k=0, top_p=0.9)),             # flat: the cut lies far below the first candidates
+    (70001, 0.5, dict(top_k=0, top_p=0.9)),            # flat and wide: several narrowing passes
+    (65024, 6.0, dict(top_k=0, top_p=0.9)),            # peaked: the cut lies among the first candidates
+    (65024, 2.0, dict(top_k=3000, top_p=0.7)),         # top-p below a top-k that does not fit the block
+    (5000, 2.0, dict(top_k=0, min_p=0.05)),
+    (65024, 2.0, dict(top_k=0, temperature=0.7)),
+])
+def test_filters_on_wide_rows(K, vocab, scale, opt):
+    g = torch.Generator().manual_seed(vocab + int(scale * 10))
+    lg = torch.randn(vocab, generator=g) * scale
+    kept = lg / opt.get("temperature", 1.0)
+    if opt.get("top_k", 0) > 0:
+        kept = plain.top_k_filter(kept, opt["top_k"])
+    if opt.get("top_p", 1.0) < 1.0:
+        kept = plain.top_p_filter(kept, opt["top_p"])
+    if opt.get("min_p", 0.0) > 0.0:
+        pr = torch.softmax(kept, -1)
+        kept = kept.masked_fill(pr < opt["min_p"] * pr.max(), float("-inf"))
+    check_kept_set(draws_of_one_row(K, lg, **opt), kept)
+
+
+def test_top_k_keeps_all_ties_with_the_last_value_even_when_they_overflow_the_block(K):
+    g = torch.Generator().manual_seed(9)
+    lg = torch.rand(5000, generator=g)               # below 1
+    perm = torch.randperm(5000, generator=g)
+    lg[perm[:1500]] = 2.0
+    lg[perm[1500:1505]] = 3.0
+    toks = draws_of_one_row(K, lg, top_k=10)
+    check_kept_set(toks, plain.top_k_filter(lg, 10))
+    assert set(toks.ravel().tolist()) == set(perm[:1505].tolist())
