@@ -28,8 +28,10 @@ namespace {
 constexpr int STAGES = 3;
 
 struct DecodeParams {
-  int heads, kv_heads, hpk, n_splits, rot_pairs, write_cache, window;
+  int heads, kv_heads, hpk, n_splits, n_teams, rot_pairs, write_cache, window;
   float scale;
+  float* team_parts;   // [n_seqs][kv_heads * chunks][n_teams][hpk][D + 2] float32 when n_teams > 1
+  int* tickets;        // [n_seqs][kv_heads * chunks][n_splits], zero before and after the launch
 };
 
 // KS: the 64 keys of a page are divided among KS groups of warps (KS = 1, 2 or 4). A group keeps its
@@ -50,6 +52,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ fused, __nv_bfloat16* 
   const int rows_total = 16 * row_warps;
   const int rb = warp % row_warps;             // which 16 rows (query heads) this warp holds
   const int kp = warp / row_warps;             // which share of a page's keys it takes
+  constexpr int PART = D + 2;                  // floats of a row in the teams' workspace: output, maximum, sum
   constexpr int NT = KEYS / 8 / KS;            // 8-key tiles of S per warp and page
   constexpr int KT = KEYS / 16 / KS;           // 16-key steps of P V per warp and page
   const int g4 = lane >> 2, t4 = lane & 3;
@@ -60,7 +63,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ fused, __nv_bfloat16* 
   const int g = blockIdx.y / chunks;
   const int chunk = blockIdx.y % chunks;
   const int h0 = chunk * p.hpk;
-  const int split = blockIdx.z;
+  const int split = blockIdx.z % p.n_splits, team = blockIdx.z / p.n_splits;   // a cluster = consecutive z
   const int pos = sb.seq_past[seq];            // position of the new token
   const int tok = sb.seq_start[seq];           // its row in the step
   const int head_valid = min(p.hpk, qpk - h0);
@@ -88,9 +91,9 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ fused, __nv_bfloat16* 
   if (p.window > 0) kb_first = max(0, pos - p.window + 1) / KEYS;
   const int kb_last = pos / KEYS;               // page that holds the new token
   const int n_pages = kb_last + 1 - kb_first;
-  const int per_split = (n_pages + p.n_splits - 1) / p.n_splits;
-  const int kb_begin = kb_first + split * per_split;
-  const int kb_end = min(kb_last + 1, kb_begin + per_split);
+  const int n_sharers = p.n_splits * p.n_teams;
+  const int kb_begin = kb_first + int((long long)blockIdx.z * n_pages / n_sharers);
+  const int kb_end = kb_first + int((long long)(blockIdx.z + 1) * n_pages / n_sharers);
   const int* pages = sb.pages + size_t(seq) * sb.pages_stride;
   const int n_mine = max(0, kb_end - kb_begin);
 
@@ -279,7 +282,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ fused, __nv_bfloat16* 
   }
 
   __nv_bfloat16* out_tok = out + (size_t(tok) * p.heads + g * qpk + h0) * D;
-  if (p.n_splits == 1 && KS == 1) {
+  if (p.n_splits == 1 && KS == 1 && p.n_teams == 1) {
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
       if (!row_ok[i]) continue;
@@ -338,11 +341,68 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ fused, __nv_bfloat16* 
         acc[0] += v.x * w; acc[1] += v.y * w; acc[2] += v.z * w; acc[3] += v.w * w;
       }
     }
+    if (p.n_teams > 1) {
+      // the cluster's rows as they are, for the join of the teams
+      float* dst = p.team_parts + ((size_t(seq) * gridDim.y + blockIdx.y) * p.n_teams + team) * p.hpk * PART + size_t(r) * PART;
+      *reinterpret_cast<float2*>(dst + d0) = make_float2(acc[0], acc[1]);
+      *reinterpret_cast<float2*>(dst + d0 + 2) = make_float2(acc[2], acc[3]);
+      if (d0 == 0) *reinterpret_cast<float2*>(dst + D) = make_float2(m, l);
+      continue;
+    }
     const float inv = l > 0.f ? 1.f / l : 0.f;
     __nv_bfloat16* dst = out_tok + size_t(r) * D + d0;
     *reinterpret_cast<uint2*>(dst) = make_uint2(pack_bf16(acc[0] * inv, acc[1] * inv), pack_bf16(acc[2] * inv, acc[3] * inv));
   }
   cluster.sync();  // no block leaves while another still reads its shared memory
+  if (p.n_teams == 1) return;
+  // The teams' join: every block takes a ticket for its share of the rows (r % n_splits == split); the one
+  // that draws the last joins what the teams left, always in the order of the teams, and puts the
+  // counter back to zero.
+  __shared__ int s_last;
+  __threadfence();
+  __syncthreads();
+  int* ticket = p.tickets + (size_t(seq) * gridDim.y + blockIdx.y) * n_splits + split;
+  if (tid == 0) s_last = (atomicAdd(ticket, 1) == p.n_teams - 1) ? 1 : 0;
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  const float* parts = p.team_parts + (size_t(seq) * gridDim.y + blockIdx.y) * p.n_teams * p.hpk * PART;
+  for (int idx = tid; idx < my_rows * per_row; idx += nthreads) {
+    const int r = split + (idx / per_row) * n_splits;
+    const int d0 = (idx % per_row) * VEC;
+    // eight teams' loads in flight at a time: this block alone reads what all teams left
+    float m = -INFINITY;
+    for (int t0 = 0; t0 < p.n_teams; t0 += 8) {
+      float mt[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u)
+        mt[u] = (t0 + u < p.n_teams) ? __ldcg(parts + (size_t(t0 + u) * p.hpk + r) * PART + D) : -INFINITY;
+#pragma unroll
+      for (int u = 0; u < 8; ++u) m = fmaxf(m, mt[u]);
+    }
+    float acc[VEC] = {0.f, 0.f, 0.f, 0.f};
+    float l = 0.f;
+    for (int t0 = 0; t0 < p.n_teams; t0 += 8) {
+      float2 ml[8], v0[8], v1[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const float* pr = parts + (size_t(min(t0 + u, p.n_teams - 1)) * p.hpk + r) * PART;
+        ml[u] = __ldcg(reinterpret_cast<const float2*>(pr + D));
+        v0[u] = __ldcg(reinterpret_cast<const float2*>(pr + d0));
+        v1[u] = __ldcg(reinterpret_cast<const float2*>(pr + d0 + 2));
+      }
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const float w = (t0 + u >= p.n_teams || ml[u].x == -INFINITY) ? 0.f : exp2f(ml[u].x - m);
+        l += ml[u].y * w;
+        acc[0] += v0[u].x * w; acc[1] += v0[u].y * w; acc[2] += v1[u].x * w; acc[3] += v1[u].y * w;
+      }
+    }
+    const float inv = l > 0.f ? 1.f / l : 0.f;
+    __nv_bfloat16* dst = out_tok + size_t(r) * D + d0;
+    *reinterpret_cast<uint2*>(dst) = make_uint2(pack_bf16(acc[0] * inv, acc[1] * inv), pack_bf16(acc[2] * inv, acc[3] * inv));
+  }
+  if (tid == 0) *ticket = 0;
 }
 
 template <int D, int KS>
@@ -364,7 +424,7 @@ int launch_decode(const void* fused, void* k_pool, void* v_pool, void* out, cons
     configured = smem;
   }
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(sb.n_seqs, p.kv_heads * chunks, p.n_splits);
+  cfg.gridDim = dim3(sb.n_seqs, p.kv_heads * chunks, p.n_splits * p.n_teams);
   cfg.blockDim = dim3(warps * KS * 32);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
@@ -390,13 +450,17 @@ int launch_decode(const void* fused, void* k_pool, void* v_pool, void* out, cons
 PTB_API int ptb_attention_decode_max_splits() { return 8; }
 
 // Every sequence of the step brings exactly one token. fused [n_seqs, kv_heads * (q_per_kv + 2) *
-// head_dim] bfloat16; out [n_seqs, heads * head_dim]. n_splits from 1 to 8; key_split 1, 2 or 4 groups
+// head_dim] bfloat16; out [n_seqs, heads * head_dim]. n_teams clusters of n_splits (1 to 8) blocks share a
+// sequence's pages; more than one team needs `team_parts` (n_seqs * kv_heads * chunks * n_teams * hpk *
+// (head_dim + 2) floats) and `tickets` (n_seqs * kv_heads * chunks * n_splits ints, zero before the launch
+// and after it). key_split 1, 2 or 4 groups
 // of `warps` warps each share the keys of every page (warps * key_split <= 10 for head size 64, 8 for 128). rope_cos/sin:
 // [n_seqs, rot_pairs] float32 tables for the step's tokens, or null for no rotation.
 PTB_API int ptb_attention_decode(const void* fused, void* k_pool, void* v_pool, void* out, const StepBatch* sb,
                                  const float* rope_cos, const float* rope_sin, int rot_pairs,
                                  const float* alibi_slopes, int heads, int kv_heads, int head_dim, int hpk,
-                                 int n_splits, int warps, int key_split, float scale, int window, int write_cache,
+                                 int n_splits, int n_teams, int warps, int key_split, float scale, int window,
+                                 int write_cache, float* team_parts, size_t team_floats, int* tickets, int n_tickets,
                                  cudaStream_t stream) {
   if (sb->n_seqs <= 0) return PTB_OK;
   if (sb->n_tokens != sb->n_seqs) return PTB_ERR_SIZE;
@@ -409,10 +473,17 @@ PTB_API int ptb_attention_decode(const void* fused, void* k_pool, void* v_pool, 
   if ((rope_cos == nullptr) != (rope_sin == nullptr)) return PTB_ERR_SIZE;
   const int qpk = heads / kv_heads;
   const int chunks = (qpk + hpk - 1) / hpk;
-  if (kv_heads * chunks > 65535) return PTB_ERR_SIZE;
+  if (kv_heads * chunks > 65535 || n_teams < 1 || n_splits * n_teams > 65535) return PTB_ERR_SIZE;
+  if (n_teams > 1) {
+    const size_t groups = size_t(sb->n_seqs) * kv_heads * chunks;
+    if (team_parts == nullptr || tickets == nullptr || team_floats < groups * n_teams * hpk * (head_dim + 2) ||
+        size_t(n_tickets) < groups * n_splits || (reinterpret_cast<uintptr_t>(team_parts) & 7))
+      return PTB_ERR_SIZE;
+  }
   DecodeParams p;
-  p.heads = heads; p.kv_heads = kv_heads; p.hpk = hpk; p.n_splits = n_splits; p.rot_pairs = rot_pairs;
-  p.write_cache = write_cache; p.window = window; p.scale = scale;
+  p.heads = heads; p.kv_heads = kv_heads; p.hpk = hpk; p.n_splits = n_splits; p.n_teams = n_teams;
+  p.rot_pairs = rot_pairs; p.write_cache = write_cache; p.window = window; p.scale = scale;
+  p.team_parts = team_parts; p.tickets = tickets;
 #define PTB_DECODE(DD, KK) \
   return launch_decode<DD, KK>(fused, k_pool, v_pool, out, *sb, rope_cos, rope_sin, alibi_slopes, p, warps, stream)
   if (head_dim == 64) {

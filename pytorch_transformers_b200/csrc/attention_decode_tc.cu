@@ -23,6 +23,11 @@
 // barrier every block joins a share of the rows from all blocks' shared memory (distributed shared
 // memory) and writes them out: no workspace in global memory, no second launch.
 //
+// A long sequence in a small batch needs more blocks than a cluster holds: then `n_teams` clusters (teams)
+// share the sequence's pages. Each team leaves its joined rows (maximum, sum, unnormalised output) in a
+// workspace in global memory and takes a ticket; the block that draws the last ticket for its share of
+// the rows joins the teams, always in the order of the teams, and leaves the ticket counter at zero.
+//
 // Every wait on an mbarrier is bounded; when one runs out the block raises the error flag in global
 // memory and goes on to its end without waiting again (tensor memory is freed, the cluster barriers
 // are passed, copies in flight are waited for): a fault shows as an error, never as a hang.
@@ -48,16 +53,17 @@ template <int RS> __device__ __forceinline__ uint32_t swz_blk(int row, int c) {
 }
 
 struct DecodeTcParams {
-  int heads, kv_heads, n_splits, rot_pairs, write_cache;
+  int heads, kv_heads, n_splits, n_teams, rot_pairs, write_cache;
   float scale;
 };
+constexpr int PART = DD + 2;     // floats of a row in the teams' workspace: output, maximum, sum
 
 __global__ void __launch_bounds__(BLOCK_T, 2)
 attention_decode_tc_kernel(const __nv_bfloat16* __restrict__ fused, __nv_bfloat16* __restrict__ k_pool,
                            __nv_bfloat16* __restrict__ v_pool, __nv_bfloat16* __restrict__ out, StepBatch sb,
                            const float* __restrict__ rope_cos, const float* __restrict__ rope_sin, DecodeTcParams p,
                            const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
-                           int* __restrict__ error_flag) {
+                           float* __restrict__ team_parts, int* __restrict__ tickets, int* __restrict__ error_flag) {
   extern __shared__ unsigned char smem_dyn[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
   unsigned char* q_tile = smem;
@@ -76,7 +82,8 @@ attention_decode_tc_kernel(const __nv_bfloat16* __restrict__ fused, __nv_bfloat1
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const bool mma_warp = warp == SOFTMAX_T / 32, copy_warp = warp == SOFTMAX_T / 32 + 1;
-  const int seq = blockIdx.x, g = blockIdx.y, split = blockIdx.z;
+  const int seq = blockIdx.x, g = blockIdx.y;
+  const int split = blockIdx.z % p.n_splits, team = blockIdx.z / p.n_splits;   // a cluster = consecutive z
   const int qpk = p.heads / p.kv_heads;
   const int pos = sb.seq_past[seq];            // position of the new token
   const int tok = sb.seq_start[seq];           // its row in the step
@@ -88,10 +95,10 @@ attention_decode_tc_kernel(const __nv_bfloat16* __restrict__ fused, __nv_bfloat1
   // pages of this block
   const int kb_last = pos / KEYS;
   const int n_pages = kb_last + 1;
-  const int per_split = (n_pages + p.n_splits - 1) / p.n_splits;
-  const int kb_begin = split * per_split;
-  const int kb_end = min(n_pages, kb_begin + per_split);
-  const int n_mine = max(0, kb_end - kb_begin);
+  const int n_sharers = p.n_splits * p.n_teams;
+  const int kb_begin = int((long long)blockIdx.z * n_pages / n_sharers);
+  const int kb_end = int((long long)(blockIdx.z + 1) * n_pages / n_sharers);
+  const int n_mine = kb_end - kb_begin;
   const bool covers_new = n_mine > 0 && kb_end == n_pages;
 
   const uint32_t bar_s = smem_u32(&bars[0]), bar_o = smem_u32(&bars[2]), bar_p = smem_u32(&bars[4]);
@@ -243,7 +250,8 @@ attention_decode_tc_kernel(const __nv_bfloat16* __restrict__ fused, __nv_bfloat1
         for (int j = 0; j < KEYS; ++j) mx[j & 3] = fmaxf(mx[j & 3], s[j]);
       }
       const float m_blk = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
-      const float m_new = fmaxf(m_run, m_blk);
+      float m_new = fmaxf(m_run, m_blk);
+      if ((m_new - m_run) * sl2 <= RESCALE_LOG2) m_new = m_run;   // (false from -inf: the first scores set it)
       const float corr = (m_run == -INFINITY) ? 0.f : fast_exp2((m_run - m_new) * sl2);
       const bool moved = (m_new != m_run) && (m_run != -INFINITY);
       m_run = m_new;
@@ -292,7 +300,15 @@ attention_decode_tc_kernel(const __nv_bfloat16* __restrict__ fused, __nv_bfloat1
 #pragma unroll
         for (int j = 0; j < 32; ++j) o[j] = 0.f;
       }
-      if (p.n_splits == 1) {
+      if (p.n_splits == 1 && p.n_teams > 1) {
+        // a team of one block: its rows go to the workspace as they are
+        if (row < qpk) {
+          float* dst = team_parts + ((size_t(seq) * p.kv_heads + g) * p.n_teams + team) * qpk * PART + size_t(row) * PART;
+#pragma unroll
+          for (int j = 0; j < 32; j += 2) *reinterpret_cast<float2*>(dst + c0 + j) = make_float2(o[j], o[j + 1]);
+          if (c0 == 0) *reinterpret_cast<float2*>(dst + DD) = make_float2(m_run, l_run);
+        }
+      } else if (p.n_splits == 1) {
         if (row < qpk) {
           const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
 #pragma unroll
@@ -340,11 +356,69 @@ attention_decode_tc_kernel(const __nv_bfloat16* __restrict__ fused, __nv_bfloat1
         const float4 v = *reinterpret_cast<const float4*>(rpo + size_t(r) * DD + d0);
         acc[0] += v.x * wgt; acc[1] += v.y * wgt; acc[2] += v.z * wgt; acc[3] += v.w * wgt;
       }
+      if (p.n_teams > 1) {
+        float* dst = team_parts + ((size_t(seq) * p.kv_heads + g) * p.n_teams + team) * qpk * PART + size_t(r) * PART;
+        *reinterpret_cast<float2*>(dst + d0) = make_float2(acc[0], acc[1]);
+        *reinterpret_cast<float2*>(dst + d0 + 2) = make_float2(acc[2], acc[3]);
+        if (d0 == 0) *reinterpret_cast<float2*>(dst + DD) = make_float2(m, l);
+        continue;
+      }
       const float inv = l > 0.f ? 1.f / l : 0.f;
       __nv_bfloat16* dst = out + (size_t(tok) * p.heads + size_t(g) * qpk + r) * DD + d0;
       *reinterpret_cast<uint2*>(dst) = make_uint2(pack_bf16(acc[0] * inv, acc[1] * inv), pack_bf16(acc[2] * inv, acc[3] * inv));
     }
     cluster.sync();   // no block leaves while another still reads its shared memory
+  }
+  if (p.n_teams > 1) {
+    // the teams' join: the block with the last ticket for its share of the rows (r % n_splits == split)
+    __threadfence();
+    __syncthreads();
+    int* ticket = tickets + (size_t(seq) * p.kv_heads + g) * p.n_splits + split;
+    if (tid == 0) tmem_slot[1] = (atomicAdd(ticket, 1) == p.n_teams - 1) ? 1u : 0u;
+    __syncthreads();
+    if (tmem_slot[1]) {
+      __threadfence();
+      const float sl2 = p.scale * 1.4426950408889634f;
+      const float* parts = team_parts + (size_t(seq) * p.kv_heads + g) * p.n_teams * qpk * PART;
+      const int per_row = DD / 4;
+      const int my_rows = (qpk - split + p.n_splits - 1) / p.n_splits;
+      for (int idx = tid; idx < my_rows * per_row; idx += BLOCK_T) {
+        const int r = split + (idx / per_row) * p.n_splits;
+        const int d0 = (idx % per_row) * 4;
+        // eight teams' loads in flight at a time: this block alone reads what all teams left
+        float m = -INFINITY;
+        for (int t0 = 0; t0 < p.n_teams; t0 += 8) {
+          float mt[8];
+#pragma unroll
+          for (int u = 0; u < 8; ++u)
+            mt[u] = (t0 + u < p.n_teams) ? __ldcg(parts + (size_t(t0 + u) * qpk + r) * PART + DD) : -INFINITY;
+#pragma unroll
+          for (int u = 0; u < 8; ++u) m = fmaxf(m, mt[u]);
+        }
+        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+        float l = 0.f;
+        for (int t0 = 0; t0 < p.n_teams; t0 += 8) {
+          float2 ml[8], v0[8], v1[8];
+#pragma unroll
+          for (int u = 0; u < 8; ++u) {
+            const float* pr = parts + (size_t(min(t0 + u, p.n_teams - 1)) * qpk + r) * PART;
+            ml[u] = __ldcg(reinterpret_cast<const float2*>(pr + DD));
+            v0[u] = __ldcg(reinterpret_cast<const float2*>(pr + d0));
+            v1[u] = __ldcg(reinterpret_cast<const float2*>(pr + d0 + 2));
+          }
+#pragma unroll
+          for (int u = 0; u < 8; ++u) {   // always in the order of the teams
+            const float wgt = (t0 + u >= p.n_teams || ml[u].x == -INFINITY) ? 0.f : exp2f((ml[u].x - m) * sl2);
+            l += ml[u].y * wgt;
+            acc[0] += v0[u].x * wgt; acc[1] += v0[u].y * wgt; acc[2] += v1[u].x * wgt; acc[3] += v1[u].y * wgt;
+          }
+        }
+        const float inv = l > 0.f ? 1.f / l : 0.f;
+        __nv_bfloat16* dst = out + (size_t(tok) * p.heads + size_t(g) * qpk + r) * DD + d0;
+        *reinterpret_cast<uint2*>(dst) = make_uint2(pack_bf16(acc[0] * inv, acc[1] * inv), pack_bf16(acc[2] * inv, acc[3] * inv));
+      }
+      if (tid == 0) *ticket = 0;   // for the next launch
+    }
   }
   tc_fence_before();
   __syncthreads();
@@ -359,14 +433,33 @@ PTB_API int ptb_attention_decode_tc_supports(int head_dim, int q_per_kv) {
   return (head_dim == DD && q_per_kv > 32 && q_per_kv <= ROWS) ? 1 : 0;
 }
 
+static size_t decode_tc_smem() {
+  // Q tile, page ring, the token's row and its cos / sin, barriers; the join's partial results
+  // (ROWS x (DD + 2) float32) reuse the ring
+  return 1024 + TILE_Q + 2 * STAGES_D * TILE_KV + size_t(ROWS + 2) * DD * 2 + DD * sizeof(float) + 256;
+}
+static bool decode_tc_configure() {
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(attention_decode_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             int(decode_tc_smem())) != cudaSuccess)
+      return false;
+    configured = true;
+  }
+  return true;
+}
+
 // Every sequence of the step brings exactly one token. fused [n_seqs, kv_heads * (q_per_kv + 2) * 64]
 // bfloat16; k_pool / v_pool: the pools of one cache entry, [pool_pages][kv_heads][64][64]; out
-// [n_seqs, heads * 64]. n_splits from 1 to 8 blocks share a sequence's pages. rope_cos / rope_sin:
+// [n_seqs, heads * 64]. n_teams clusters of n_splits (1 to 8) blocks share a sequence's pages; more than
+// one team needs `team_parts` (n_seqs * kv_heads * n_teams * q_per_kv * 66 floats) and `tickets`
+// (n_seqs * kv_heads * n_splits ints, zero before the launch and after it). rope_cos / rope_sin:
 // [n_seqs, rot_pairs] float32 tables for the step's tokens, or null for no rotation. No score bias, no
 // window. `error_flag`: a device int that stays 0 unless a bounded wait inside the kernel ran out.
 PTB_API int ptb_attention_decode_tc(const void* fused, void* k_pool, void* v_pool, int pool_pages, void* out,
                                     const StepBatch* sb, const float* rope_cos, const float* rope_sin, int rot_pairs,
-                                    int heads, int kv_heads, int head_dim, int n_splits, float scale, int write_cache,
+                                    int heads, int kv_heads, int head_dim, int n_splits, int n_teams, float scale,
+                                    int write_cache, float* team_parts, size_t team_floats, int* tickets, int n_tickets,
                                     int* error_flag, cudaStream_t stream) {
   if (sb->n_seqs <= 0) return PTB_OK;
   if (sb->n_tokens != sb->n_seqs) return PTB_ERR_SIZE;
@@ -374,6 +467,13 @@ PTB_API int ptb_attention_decode_tc(const void* fused, void* k_pool, void* v_poo
     return PTB_ERR_SIZE;
   if (!ptb_attention_decode_tc_supports(head_dim, heads / kv_heads)) return PTB_ERR_SIZE;
   if (n_splits < 1 || n_splits > 8 || rot_pairs < 0 || 2 * rot_pairs > head_dim) return PTB_ERR_SIZE;
+  if (n_teams < 1 || n_splits * n_teams > 65535) return PTB_ERR_SIZE;
+  if (n_teams > 1) {
+    const size_t need = size_t(sb->n_seqs) * kv_heads * n_teams * (heads / kv_heads) * PART;
+    if (team_parts == nullptr || tickets == nullptr || team_floats < need ||
+        size_t(n_tickets) < size_t(sb->n_seqs) * kv_heads * n_splits || (reinterpret_cast<uintptr_t>(team_parts) & 7))
+      return PTB_ERR_SIZE;
+  }
   if ((rope_cos == nullptr) != (rope_sin == nullptr)) return PTB_ERR_SIZE;
   if (pool_pages <= 0 || ((reinterpret_cast<uintptr_t>(k_pool) | reinterpret_cast<uintptr_t>(v_pool) |
                            reinterpret_cast<uintptr_t>(fused)) & 15))
@@ -382,20 +482,12 @@ PTB_API int ptb_attention_decode_tc(const void* fused, void* k_pool, void* v_poo
   const CUtensorMap* vm = pool_map(v_pool, pool_pages, kv_heads, DD);
   if (km == nullptr || vm == nullptr) return PTB_ERR_LAUNCH;
   DecodeTcParams p;
-  p.heads = heads; p.kv_heads = kv_heads; p.n_splits = n_splits; p.rot_pairs = rot_pairs;
+  p.heads = heads; p.kv_heads = kv_heads; p.n_splits = n_splits; p.n_teams = n_teams; p.rot_pairs = rot_pairs;
   p.write_cache = write_cache; p.scale = scale;
-  // Q tile, page ring, the token's row and its cos / sin, barriers; the join's partial results
-  // (ROWS x (DD + 2) float32) reuse the ring
-  const size_t smem = 1024 + TILE_Q + 2 * STAGES_D * TILE_KV + size_t(ROWS + 2) * DD * 2 + DD * sizeof(float) + 256;
-  static bool configured = false;
-  if (!configured) {
-    if (cudaFuncSetAttribute(attention_decode_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) !=
-        cudaSuccess)
-      return PTB_ERR_LAUNCH;
-    configured = true;
-  }
+  const size_t smem = decode_tc_smem();
+  if (!decode_tc_configure()) return PTB_ERR_LAUNCH;
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(sb->n_seqs, kv_heads, n_splits);
+  cfg.gridDim = dim3(sb->n_seqs, kv_heads, n_splits * n_teams);
   cfg.blockDim = dim3(BLOCK_T);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
@@ -408,7 +500,7 @@ PTB_API int ptb_attention_decode_tc(const void* fused, void* k_pool, void* v_poo
   cfg.numAttrs = 1;
   if (cudaLaunchKernelEx(&cfg, attention_decode_tc_kernel, (const __nv_bfloat16*)fused, (__nv_bfloat16*)k_pool,
                          (__nv_bfloat16*)v_pool, (__nv_bfloat16*)out, *sb, rope_cos, rope_sin, p, *km, *vm,
-                         error_flag) != cudaSuccess) {
+                         team_parts, tickets, error_flag) != cudaSuccess) {
     (void)cudaGetLastError();
     return PTB_ERR_LAUNCH;
   }

@@ -279,7 +279,8 @@ attention_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
       float m_blk = m_part;
 #pragma unroll
       for (int o = 1; o < TPR; ++o) m_blk = fmaxf(m_blk, pm[((part + o) % TPR) * TQ + row]);
-      const float m_new = fmaxf(m_run, m_blk);
+      float m_new = fmaxf(m_run, m_blk);
+      if ((m_new - m_run) * sl2 <= RESCALE_LOG2) m_new = m_run;   // (false from -inf: the first scores set it)
       const float corr = (m_run == -INFINITY) ? 0.f : fast_exp2((m_run - m_new) * sl2);
       const bool moved = (m_new != m_run) && (m_run != -INFINITY);
       m_run = m_new;

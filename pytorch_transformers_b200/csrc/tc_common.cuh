@@ -11,6 +11,11 @@
 
 #include "mma_common.cuh"
 
+// Online softmax keeps each row's exponentials relative to a reference score. The reference follows the
+// row's maximum only when the maximum has grown by more than this many powers of two: until then P holds
+// values up to 2^8 (no loss in bfloat16, whose exponent carries them, nor in the float32 sums), and the
+// rescaling of O in tensor memory, which has to wait for the previous page's O += P V, is skipped.
+constexpr float RESCALE_LOG2 = 8.0f;
 constexpr uint32_t WAIT_LIMIT = 1u << 20;
 // Time hint for one try_wait: the hardware may park the thread this long instead of returning "not
 // yet" at once, so waiting threads leave the issue slots to the working ones. A wait gives up after

@@ -194,20 +194,26 @@ class CausalLM:
     TWO_STREAM_MAX_TOKENS = 32
     # Two streams pay while the mixer's kernels are small beside the feed-forward's weight stream.
     # Once a layer's attention reads tens of megabytes of keys and values itself, it competes with
-    # that stream instead of hiding under it (measured: 4 MB a layer, Falcon-7B at batch 8, 2.83 ms
-    # against 3.54 ms in one stream; 17 MB, batch 32, 3.73 against 4.00; 34 MB, 40B at batch 8,
-    # 18.9 against 17.2; 67 MB, 11B at batch 8, 7.07 against 6.16).
-    TWO_STREAM_MAX_KV_BYTES = 24 << 20
+    # that stream instead of hiding under it. Measured (two streams against one, ms per step):
+    # Falcon-7B, 4 MB a layer (batch 8) 2.83 / 3.54; 17 MB (batch 32) 3.73 / 4.00; 34 MB (batch 8 at
+    # 16,384 keys) 3.43 / 3.85; 42 MB (batch 10) 4.49 / 4.24. Falcon-40B, 34 MB (batch 8) 16.0 / 16.3.
+    # Heads of size 128 need the decode kernel's large page ring, which keeps the stream's blocks off
+    # the SMs earlier: Falcon-11B, 17 MB (batch 2) 5.39 / 5.55; 34 MB (batch 4) 7.80 / 5.80; 67 MB
+    # (batch 8) 7.07 / 6.16.
+    TWO_STREAM_MAX_KV_BYTES = 40 << 20
+    TWO_STREAM_MAX_KV_BYTES_WIDE_HEADS = 24 << 20
 
     def _two_streams(self, ctx: StepContext) -> bool:
         if self.device.type != "cuda" or self.dtype != torch.bfloat16 or ctx.n_tokens > self.TWO_STREAM_MAX_TOKENS:
             return False
         lengths = [p + n for p, n in zip(ctx.past, ctx.new)]
-        per_layer = 0
         for g in ctx.cache.groups:   # keys and values that one layer of this group reads in this step
             keys = sum(min(t, g.need.window) if g.need.window else t for t in lengths)
-            per_layer = max(per_layer, keys * g.need.kv_heads * g.need.head_dim * 2 * g.k.element_size())
-        return per_layer <= self.TWO_STREAM_MAX_KV_BYTES
+            per_layer = keys * g.need.kv_heads * g.need.head_dim * 2 * g.k.element_size()
+            limit = self.TWO_STREAM_MAX_KV_BYTES if g.need.head_dim <= 64 else self.TWO_STREAM_MAX_KV_BYTES_WIDE_HEADS
+            if per_layer > limit:
+                return False
+        return True
 
     def forward(self, ctx: StepContext) -> torch.Tensor:
         k = self.build.kernels

@@ -220,11 +220,12 @@ def decode_max_warps(head_dim: int) -> int:
 def attention_decode(fused: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, batch: StepBatchC, rope,
                      slopes: Optional[torch.Tensor], kv_heads: int, q_per_kv: int, head_dim: int, scale: float,
                      window: int, heads_per_tile: int, warps: int, n_splits: int, write_cache: bool = True,
-                     key_split: int = 1):
+                     key_split: int = 1, n_teams: int = 1):
     """One kernel for the attention of a step of single tokens: rotate q and k of each new token, put
     k and v into the cache, attend over the cache (all heads of a K/V group in one tile of ``warps``
     x 16 rows, key pages divided among ``n_splits`` blocks of one cluster, the keys of a page among
-    ``key_split`` groups of warps, all joined through (distributed) shared memory).
+    ``key_split`` groups of warps, all joined through (distributed) shared memory; ``n_teams`` such
+    clusters share the pages of a long sequence and join through a workspace in global memory).
     Returns [tokens, heads * head_dim]."""
     _need_cuda(fused, k_pool, v_pool, slopes)
     if fused.dtype != torch.bfloat16:
@@ -237,10 +238,21 @@ def attention_decode(fused: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Te
     out = torch.empty((n, heads * head_dim), dtype=fused.dtype, device=fused.device)
     cos, sin = rope if rope is not None else (None, None)
     pairs = 0 if cos is None else cos.shape[1]
+    parts = tickets = None
+    part_floats = 0
+    if n_teams > 1:
+        groups = n * kv_heads * ((q_per_kv + heads_per_tile - 1) // heads_per_tile)
+        if groups * n_splits > DECODE_TICKETS:
+            raise KernelError("attention_decode: too many (sequence, head chunk, split) triples for the ticket buffer")
+        part_floats = groups * n_teams * heads_per_tile * (head_dim + 2)
+        parts = torch.empty(part_floats, dtype=torch.float32, device=fused.device)
+        tickets = _decode_tickets(fused.device)
     _check(lib().ptb_attention_decode(_ptr(fused), _ptr(k_pool), _ptr(v_pool), _ptr(out), ctypes.byref(batch),
                                       _ptr(cos), _ptr(sin), pairs, _ptr(slopes), heads, kv_heads, head_dim,
-                                      heads_per_tile, n_splits, warps, key_split, ctypes.c_float(scale), window,
-                                      1 if write_cache else 0, _stream(fused)), "attention_decode")
+                                      heads_per_tile, n_splits, n_teams, warps, key_split, ctypes.c_float(scale),
+                                      window, 1 if write_cache else 0, _ptr(parts), ctypes.c_size_t(part_floats),
+                                      _ptr(tickets), DECODE_TICKETS if n_teams > 1 else 0, _stream(fused)),
+           "attention_decode")
     return out
 
 
@@ -250,11 +262,12 @@ def attention_decode_tc_supports(head_dim: int, q_per_kv: int) -> bool:
 
 def attention_decode_tc(fused: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, batch: StepBatchC, rope,
                         kv_heads: int, q_per_kv: int, head_dim: int, scale: float, n_splits: int,
-                        write_cache: bool = True):
+                        write_cache: bool = True, n_teams: int = 1):
     """The attention of a step of single tokens on the tcgen05 tensor cores, for K/V heads that serve
     33 to 128 query heads of size 64: the query heads of a group are the rows of one tile, S, P and O
     live in tensor memory, pages come by TMA, ``n_splits`` blocks of one cluster share a sequence's
-    pages and join through distributed shared memory. No score bias, no window.
+    pages and join through distributed shared memory; ``n_teams`` such clusters share the pages of a
+    long sequence and join through a workspace in global memory. No score bias, no window.
     Returns [tokens, heads * head_dim]."""
     _need_cuda(fused, k_pool, v_pool)
     if fused.dtype != torch.bfloat16:
@@ -269,11 +282,33 @@ def attention_decode_tc(fused: torch.Tensor, k_pool: torch.Tensor, v_pool: torch
     out = torch.empty((n, heads * head_dim), dtype=fused.dtype, device=fused.device)
     cos, sin = rope if rope is not None else (None, None)
     pairs = 0 if cos is None else cos.shape[1]
+    parts = tickets = None
+    part_floats = 0
+    if n_teams > 1:
+        if n * kv_heads * n_splits > DECODE_TICKETS:
+            raise KernelError("attention_decode_tc: too many (sequence, K/V head, split) triples for the ticket buffer")
+        part_floats = n * kv_heads * n_teams * q_per_kv * (head_dim + 2)
+        parts = torch.empty(part_floats, dtype=torch.float32, device=fused.device)
+        tickets = _decode_tickets(fused.device)
     _check(lib().ptb_attention_decode_tc(_ptr(fused), _ptr(k_pool), _ptr(v_pool), k_pool.shape[0], _ptr(out),
                                          ctypes.byref(batch), _ptr(cos), _ptr(sin), pairs, heads, kv_heads, head_dim,
-                                         n_splits, ctypes.c_float(scale), 1 if write_cache else 0,
+                                         n_splits, n_teams, ctypes.c_float(scale), 1 if write_cache else 0,
+                                         _ptr(parts), ctypes.c_size_t(part_floats), _ptr(tickets),
+                                         DECODE_TICKETS if n_teams > 1 else 0,
                                          _ptr(error_flag(fused.device)), _stream(fused)), "attention_decode_tc")
     return out
+
+
+DECODE_TICKETS = 8192
+_decode_ticket_buffers = {}
+
+
+def _decode_tickets(device) -> torch.Tensor:
+    """int32 zeros, one per (sequence, K/V head, split) of a launch; the kernel leaves them zero."""
+    device = torch.device(device)
+    if device not in _decode_ticket_buffers:
+        _decode_ticket_buffers[device] = torch.zeros(DECODE_TICKETS, dtype=torch.int32, device=device)
+    return _decode_ticket_buffers[device]
 
 
 _error_flags = {}

@@ -72,18 +72,27 @@ class Attention(Part):
             warps = (hpk + 15) // 16
             want = self._decode_splits(ctx, hpk)
             splits = max(s for s in k.DECODE_SPLITS if s <= want)
-            if (slopes is None and self.window == 0 and getattr(ctx, "side_stream", None) is None
-                    and k.attention_decode_tc_supports(self.head_dim, self.q_per_kv)):
+            tc = (slopes is None and self.window == 0 and getattr(ctx, "side_stream", None) is None
+                  and k.attention_decode_tc_supports(self.head_dim, self.q_per_kv))
+            # beside the feed-forward's weight stream (two graph branches) the attention only has to stay
+            # off the critical path, and its blocks take SMs from the stream: 128 blocks at most
+            if getattr(ctx, "side_stream", None) is not None:
+                chunks = (self.q_per_kv + hpk - 1) // hpk
+                want = min(want, max(1, 128 // (ctx.n_seqs * self.kv_heads * chunks)))
+            teams = self._decode_teams(ctx, want, 4)
+            if tc:
                 # many query heads on a K/V head: they are the rows of one tcgen05 tile. Not while the
                 # feed-forward streams its weights on the other graph branch: this kernel's 100 KB of
                 # shared memory would keep those blocks off the SMs (measured: 3.34 ms against 2.81 ms
                 # per step at batch 8), where the mma.sync kernel's 58 KB fit beside them
                 o = k.attention_decode_tc(fused, k_pool, v_pool, batch, rope, self.kv_heads, self.q_per_kv,
-                                          self.head_dim, self.scale, splits, write_cache=entry.writes_cache)
+                                          self.head_dim, self.scale, splits, write_cache=entry.writes_cache,
+                                          n_teams=teams)
                 return linear(k, o, self.p_out_weight, self.p_out_bias, add=add)
             o = k.attention_decode(fused, k_pool, v_pool, batch, rope, slopes, self.kv_heads, self.q_per_kv,
                                    self.head_dim, self.scale, self.window, hpk, warps, splits,
-                                   write_cache=entry.writes_cache, key_split=self._decode_key_split(warps))
+                                   write_cache=entry.writes_cache, key_split=self._decode_key_split(warps),
+                                   n_teams=teams)
         else:
             q = k.split_rotate_store(fused, k_pool, v_pool, batch, None, self.kv_heads, self.q_per_kv,
                                      self.head_dim, write_cache=entry.writes_cache, rope=rope)
@@ -96,10 +105,24 @@ class Attention(Part):
         at batch 64, and a second wave of blocks costs more than it brings)."""
         chunks = (self.q_per_kv + hpk - 1) // hpk
         blocks = ctx.n_seqs * self.kv_heads * chunks
+        return max(1, min((2 * 148) // blocks, self._decode_pages(ctx) // 2, 64))
+
+    def _decode_pages(self, ctx):
         pages = ctx.pages_hint
         if self.window > 0:
             pages = min(pages, self.window // self.build.kernels.PAGE + 2)
-        return max(1, min((2 * 148) // blocks, pages // 2, 64))
+        return pages
+
+    def _decode_teams(self, ctx, want, min_pages):
+        """Clusters of blocks per (sequence, head chunk) in the decode kernels. A cluster holds 8 blocks;
+        long sequences in a small batch need more to fill the SMs, each block with ``min_pages`` pages
+        at least. Measured at 16,384 keys, 71 heads on one K/V head: batch 1, 8 x 8 blocks 18 us
+        against 57 us for 8 (mma.sync kernel; 18 against 35 us for the tcgen05 kernel); batch 8,
+        8 x 4 blocks 29 against 57 us (26 against 35 us). At 2,048 keys more than one cluster a
+        sequence brings nothing. Falcon-7B's step at batch 1 and 16,384 keys: 2.65 ms against 3.64 ms."""
+        if want <= 8:
+            return 1
+        return max(1, min(want, self._decode_pages(ctx) // min_pages) // 8)
 
     def _decode_key_split(self, row_warps):
         """Groups of warps that share the keys of a page in the decode kernel. With few query heads

@@ -56,19 +56,20 @@ def attention_case(K, dtype, heads, kv_heads, d, pasts, news, position="rotary",
         ctx = StepContext(cache, [s for s, _ in live], toks, 1, [[] for _ in live], K.generic_tile_rows())
         x = torch.cat([fused[i][r[0]:r[1]] for i, (_, r) in zip(idx, live)]).to(dtype).cuda().contiguous()
         if fused_decode is not None and ctx.mma_tokens == 1:
-            # fused_decode = (heads per tile or None, splits[, key groups]): the one-kernel decode path
+            # fused_decode = (heads per tile or None, splits[, key groups[, teams]]): the one-kernel decode path
             rope = K.rope_table(ctx.dev["tok_pos"], inv_freq) if inv_freq is not None else None
             hpk = fused_decode[0] or min(qpk, 128)
             if fused_decode[0] == "tc":
-                # fused_decode = ("tc", splits): the tcgen05 form of the one-kernel decode path
+                # fused_decode = ("tc", splits[, teams]): the tcgen05 form of the one-kernel decode path
                 out = K.attention_decode_tc(x, k_pool, v_pool, ctx.batch_c[gi], rope, kv_heads, qpk, d, scale,
-                                            fused_decode[1])
+                                            fused_decode[1], n_teams=fused_decode[2] if len(fused_decode) > 2 else 1)
                 K.check_device_errors("cuda")
                 ctx.commit()
                 return out, idx
             out = K.attention_decode(x, k_pool, v_pool, ctx.batch_c[gi], rope, slopes, kv_heads, qpk, d, scale,
                                      window, hpk, (hpk + 15) // 16, fused_decode[1],
-                                     key_split=fused_decode[2] if len(fused_decode) > 2 else 1)
+                                     key_split=fused_decode[2] if len(fused_decode) > 2 else 1,
+                                     n_teams=fused_decode[3] if len(fused_decode) > 3 else 1)
             ctx.commit()
             return out, idx
         q = K.split_rotate_store(x, k_pool, v_pool, ctx.batch_c[gi], inv_freq, kv_heads, qpk, d)

@@ -166,6 +166,24 @@ def test_fused_decode_tc(K, heads, kv, position, splits):
     torch.testing.assert_close(out, ref, **tol(BF))
 
 
+@pytest.mark.parametrize("heads,kv", [(71, 1), (80, 2)])
+@pytest.mark.parametrize("splits,teams", [(1, 2), (1, 5), (2, 3), (4, 4), (8, 2)])
+def test_fused_decode_tc_teams_of_clusters(K, heads, kv, splits, teams):
+    # several clusters share a sequence's pages and join through the workspace; sequences with fewer pages
+    # than blocks leave some blocks without pages; launched twice, so the tickets must have been put back
+    for seed in (3, 4):
+        out, ref = attention_case(K, BF, heads, kv, 64, pasts=[63, 64, 200, 1, 1500, 127], news=[1] * 6,
+                                  position="rotary", seed=seed, fused_decode=("tc", splits, teams))
+        torch.testing.assert_close(out, ref, **tol(BF))
+
+
+@pytest.mark.parametrize("key_pos", [0, 64, 1400, 1499])
+def test_fused_decode_tc_teams_far_key_and_own_key(K, key_pos):
+    out, ref = attention_case(K, BF, 71, 1, 64, pasts=[0 + 5, 1499], news=[1, 1], position="none", seed=5,
+                              needle=(1, key_pos), fused_decode=("tc", 2, 4))
+    torch.testing.assert_close(out, ref, **tol(BF))
+
+
 @pytest.mark.parametrize("key_pos", [0, 64, 698, 699])
 def test_fused_decode_tc_far_key_and_own_key(K, key_pos):
     out, ref = attention_case(K, BF, 71, 1, 64, pasts=[0 + 5, 699], news=[1, 1], position="none", seed=5,
@@ -189,6 +207,32 @@ def test_fused_decode_head_chunks_and_repeated_launches(K, hpk):
         out, ref = attention_case(K, BF, 71, 1, 64, pasts=[300, 65, 5], news=[1, 1, 1], position="rotary", seed=seed,
                                   fused_decode=(hpk, 4))
         torch.testing.assert_close(out, ref, **tol(BF))
+
+
+@pytest.mark.parametrize("heads,kv,d,hpk,key_split", [(71, 1, 64, None, 1), (71, 1, 64, 32, 1), (32, 8, 128, None, 4),
+                                                      (8, 2, 64, None, 2), (128, 8, 64, None, 2)])
+@pytest.mark.parametrize("splits,teams", [(1, 3), (2, 2), (4, 5), (8, 2)])
+@pytest.mark.parametrize("position", ["rotary", "alibi"])
+def test_fused_decode_teams_of_clusters(K, heads, kv, d, hpk, key_split, splits, teams, position):
+    # several clusters share a sequence's pages and join through the workspace; short sequences leave
+    # blocks without pages; launched twice, so the tickets must have been put back
+    for seed in (3, 4):
+        out, ref = attention_case(K, BF, heads, kv, d, pasts=[63, 64, 200, 1, 1500, 127], news=[1] * 6,
+                                  position=position, seed=seed, fused_decode=(hpk, splits, key_split, teams))
+        torch.testing.assert_close(out, ref, **tol(BF))
+
+
+@pytest.mark.parametrize("key_pos", [0, 64, 1400, 1499])
+def test_fused_decode_teams_far_key_and_own_key(K, key_pos):
+    out, ref = attention_case(K, BF, 71, 1, 64, pasts=[0 + 5, 1499], news=[1, 1], position="none", seed=5,
+                              needle=(1, key_pos), fused_decode=(None, 2, 1, 4))
+    torch.testing.assert_close(out, ref, **tol(BF))
+
+
+def test_fused_decode_teams_with_window(K):
+    out, ref = attention_case(K, BF, 4, 2, 64, pasts=[900, 5, 64], news=[1, 1, 1], position="rotary", window=300,
+                              seed=7, fused_decode=(None, 2, 2, 3))
+    torch.testing.assert_close(out, ref, **tol(BF))
 
 
 @pytest.mark.parametrize("key_pos", [0, 64, 698, 699])

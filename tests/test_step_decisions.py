@@ -56,15 +56,33 @@ def fake_step(batch, context, kv_heads, head_dim, tokens_per_seq=1, window=0):
 def test_second_stream_only_while_the_layers_key_value_read_is_small():
     model = SimpleNamespace(device=torch.device("cuda"), dtype=torch.bfloat16,
                             TWO_STREAM_MAX_TOKENS=CausalLM.TWO_STREAM_MAX_TOKENS,
-                            TWO_STREAM_MAX_KV_BYTES=CausalLM.TWO_STREAM_MAX_KV_BYTES)
+                            TWO_STREAM_MAX_KV_BYTES=CausalLM.TWO_STREAM_MAX_KV_BYTES,
+                            TWO_STREAM_MAX_KV_BYTES_WIDE_HEADS=CausalLM.TWO_STREAM_MAX_KV_BYTES_WIDE_HEADS)
     rule = lambda ctx: CausalLM._two_streams(model, ctx)
     assert rule(fake_step(8, 2048, 1, 64))            # Falcon-7B, batch 8: 4 MB a layer
     assert rule(fake_step(32, 2048, 1, 64))           # batch 32: 17 MB
     assert not rule(fake_step(64, 2048, 1, 64))       # more than 32 tokens
     assert not rule(fake_step(8, 2048, 8, 128))       # Falcon-11B, batch 8: 67 MB
     assert rule(fake_step(1, 2048, 8, 128))           # batch 1: 8 MB
-    assert not rule(fake_step(8, 2048, 8, 64))        # Falcon-40B, batch 8: 34 MB
+    assert rule(fake_step(8, 2048, 8, 64))            # Falcon-40B, batch 8: 34 MB
+    assert rule(fake_step(8, 16384, 1, 64))           # Falcon-7B, batch 8 at 16,384 keys: 34 MB
+    assert not rule(fake_step(10, 16384, 1, 64))      # 42 MB
+    assert not rule(fake_step(4, 2048, 8, 128))       # Falcon-11B, batch 4: 34 MB, but heads of size 128
+    assert rule(fake_step(2, 2048, 8, 128))           # 17 MB
     assert rule(fake_step(8, 100000, 8, 64, window=1024))   # a window bounds what a layer reads
     assert not rule(fake_step(2, 10, 1, 64, tokens_per_seq=40))
     model.dtype = torch.float32
     assert not rule(fake_step(8, 2048, 1, 64))
+
+
+def test_teams_of_clusters_for_long_sequences_in_small_batches():
+    falcon_7b = attention(71, 1, 64)
+    def teams(n_seqs, pages):
+        ctx = SimpleNamespace(n_seqs=n_seqs, pages_hint=pages)
+        return falcon_7b._decode_teams(ctx, falcon_7b._decode_splits(ctx, 71), 4)
+    assert teams(8, 33) == 1         # 2,048 keys: one cluster of 8 blocks, four pages each
+    assert teams(64, 33) == 1
+    assert teams(8, 257) == 4        # 16,384 keys, batch 8: 8 x 32 blocks fill the device once
+    assert teams(1, 257) == 8        # batch 1: four pages a block at least
+    assert teams(1, 129) == 4
+    assert teams(64, 257) == 1       # a large batch fills the device by itself
