@@ -425,15 +425,24 @@ SKINNY_MAX_ROWS = 32   # ptb_skinny_linear_max_rows()
 SKINNY_K_MULTIPLE = 32  # ptb_skinny_linear_k_multiple()
 
 
-SKINNY_BEST_ROWS = 16   # beyond this the library product is faster (measured on B200)
+# Beyond this the library product is faster. Measured on B200 inside Falcon-7B's step, skinny_linear
+# against the library, ms: 9 rows 3.35 / 3.46, 12 rows 3.40 / 3.49, 16 rows 3.51 / 3.22 (each matrix alone
+# the library is ahead from 9 rows on, 10.3 against 11.5 us on the 42 MB matrices, but beside the other
+# graph branch's kernels its blocks leave less room).
+SKINNY_BEST_ROWS = 12
+# A matrix of the vocabulary's height runs alone in the step, and there the library reads it faster from
+# 8 rows on (591 MB: 87.0 against 94.6 us at 8 rows, 87 against 108 us at 9).
+SKINNY_TALL_ROWS = 32768
+SKINNY_BEST_ROWS_TALL = 7
 
 
 def skinny_linear_takes(rows: int, k: int) -> bool:
     return 0 < rows <= SKINNY_MAX_ROWS and k % SKINNY_K_MULTIPLE == 0
 
 
-def skinny_linear_preferred(rows: int, k: int) -> bool:
-    return 0 < rows <= SKINNY_BEST_ROWS and k % SKINNY_K_MULTIPLE == 0
+def skinny_linear_preferred(rows: int, k: int, n: int = 0) -> bool:
+    best = SKINNY_BEST_ROWS_TALL if n >= SKINNY_TALL_ROWS else SKINNY_BEST_ROWS
+    return 0 < rows <= best and k % SKINNY_K_MULTIPLE == 0
 
 
 def skinny_linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None, act: str = "none",

@@ -31,7 +31,7 @@ def linear(kernels, x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.
         y = kernels.linear_f32(x, weight, bias, act)
         return y if add is None else kernels.residual(add, y)
     rows, k = x.shape
-    if kernels.skinny_linear_preferred(rows, k):
+    if kernels.skinny_linear_preferred(rows, k, weight.shape[0]):
         return kernels.skinny_linear(x, weight, bias, act, add)
     if TC_LINEAR_ROWS is not None and rows <= TC_LINEAR_ROWS and kernels.tc_linear_takes(rows, k):
         return kernels.tc_linear(x, weight, bias, act, add)

@@ -61,7 +61,8 @@ def test_second_stream_only_while_the_layers_key_value_read_is_small():
     rule = lambda ctx: CausalLM._two_streams(model, ctx)
     assert rule(fake_step(8, 2048, 1, 64))            # Falcon-7B, batch 8: 4 MB a layer
     assert rule(fake_step(32, 2048, 1, 64))           # batch 32: 17 MB
-    assert not rule(fake_step(64, 2048, 1, 64))       # more than 32 tokens
+    assert rule(fake_step(48, 2048, 1, 64))           # batch 48: 25 MB
+    assert not rule(fake_step(64, 2048, 1, 64))       # more than 48 tokens
     assert not rule(fake_step(8, 2048, 8, 128))       # Falcon-11B, batch 8: 67 MB
     assert rule(fake_step(1, 2048, 8, 128))           # batch 1: 8 MB
     assert rule(fake_step(8, 2048, 8, 64))            # Falcon-40B, batch 8: 34 MB
