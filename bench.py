@@ -133,7 +133,118 @@ def prefill_flops(c, layers, tokens):
     return gemm + attn + head
 
 
+def run_sample(args):
+    """Device time of the selection kernel for the ways of sampling, `--batch` rows of the 7B vocabulary,
+    20 launches captured in a CUDA graph (no host time); rows of scale 3 are flat, of scale 6 peaked."""
+    import torch
+
+    from pytorch_transformers_b200 import kernels
+
+    torch.cuda.set_device(0)
+    rows, vocab = args.batch, SHAPES["7b"]["vocab_size"]
+    gen = torch.Generator(device="cuda").manual_seed(0)
+    base = torch.randn(rows, vocab, device="cuda", generator=gen)
+    work = torch.empty_like(base)
+    out = torch.empty(rows, dtype=torch.int32, device="cuda")
+    streams = torch.arange(rows, dtype=torch.int64, device="cuda")
+    counters = torch.zeros(rows, dtype=torch.int64, device="cuda")
+    cases = {"greedy": (3.0, dict(do_sample=False)), "temperature": (3.0, dict(do_sample=True, temperature=0.8)),
+             "top_k 50": (3.0, dict(do_sample=True, top_k=50)),
+             "top_k 50 top_p 0.9": (3.0, dict(do_sample=True, top_k=50, top_p=0.9, temperature=0.7)),
+             "top_k 2000": (3.0, dict(do_sample=True, top_k=2000)),
+             "top_p 0.9 peaked": (6.0, dict(do_sample=True, top_p=0.9)),
+             "top_p 0.9 flat": (3.0, dict(do_sample=True, top_p=0.9)), "min_p 0.05": (3.0, dict(do_sample=True, min_p=0.05))}
+    result = {"only": "sample", "rows": rows, "vocab": vocab, "unit": "us per launch"}
+    side = torch.cuda.Stream()
+    for name, (scale, opt) in cases.items():
+        logits = base * scale
+        launch = lambda: kernels.sample(logits, work, out, seed=1, streams=streams, counters=counters, **opt)
+        with torch.cuda.stream(side):
+            for _ in range(3):
+                launch()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                for _ in range(20):
+                    launch()
+            graph.replay()
+            t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            t0.record()
+            for _ in range(5):
+                graph.replay()
+            t1.record()
+        torch.cuda.synchronize()
+        result[name] = round(t0.elapsed_time(t1) * 10.0, 1)   # ms for 100 launches -> us for one
+    print(json.dumps(result))
+    return 0
+
+
+def run_decode_attention(args):
+    """Device time of the two decode attention kernels alone (20 launches in a CUDA graph), `--batch`
+    sequences of `--context` cached keys with the heads of `--shape`, for blocks a cluster x clusters a
+    sequence."""
+    import math
+
+    import torch
+
+    import pytorch_transformers_b200 as ptb
+    from pytorch_transformers_b200 import kernels as K
+    from pytorch_transformers_b200.cache.paged import Cache
+    from pytorch_transformers_b200.engine.batch import StepContext
+    from pytorch_transformers_b200.parts.base import CacheNeed
+
+    torch.cuda.set_device(0)
+    cfg = ptb.FalconConfig.from_dict(SHAPES[args.shape])
+    kv, d, qpk, rows, keys = cfg.kv_heads_eff, cfg.head_dim, cfg.q_per_kv, args.batch, args.context
+    cache = Cache([(0, CacheNeed("full", kv, d, 0), None)], rows * (keys + 64), torch.bfloat16, "cuda")
+    slots = [cache.open() for _ in range(rows)]
+    for slot in slots:
+        cache.reserve(slot, keys)
+        cache.commit(slot, keys)
+    k_pool, v_pool, group = cache.entry_storage(0)
+    k_pool.normal_()
+    v_pool.normal_()
+    ctx = StepContext(cache, slots, [[0]] * rows, 1, [[]] * rows, K.generic_tile_rows())
+    fused = torch.randn(rows, kv * (qpk + 2) * d, device="cuda", dtype=torch.bfloat16)
+    rope = K.rope_table(ctx.dev["tok_pos"], (1.0 / (10000 ** (torch.arange(0, d, 2).float() / d))).cuda())
+    hpk = min(qpk, 128)
+    warps, scale, batch = (hpk + 15) // 16, 1 / math.sqrt(d), ctx.batch_c[group]
+    key_split = 1 if warps >= 3 else min(4 if d > 64 else 2, K.decode_max_warps(d) // warps)
+    result = {"only": "decode-attention", "shape": args.shape, "batch": rows, "context": keys, "unit": "us per launch"}
+    side = torch.cuda.Stream()
+    for splits, teams in ((1, 1), (4, 1), (8, 1), (8, 2), (8, 4), (8, 8), (4, 8), (1, 32)):
+        if splits * teams * 2 > keys // 64 + 1:
+            continue
+        launches = {"mma": lambda: K.attention_decode(fused, k_pool, v_pool, batch, rope, None, kv, qpk, d, scale, 0, hpk,
+                                                      warps, splits, key_split=key_split, n_teams=teams)}
+        if K.attention_decode_tc_supports(d, qpk):
+            launches["tcgen05"] = lambda: K.attention_decode_tc(fused, k_pool, v_pool, batch, rope, kv, qpk, d, scale,
+                                                                splits, n_teams=teams)
+        for name, launch in launches.items():
+            with torch.cuda.stream(side):
+                for _ in range(3):
+                    launch()
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=side):
+                    for _ in range(20):
+                        launch()
+                graph.replay()
+                t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                t0.record()
+                for _ in range(5):
+                    graph.replay()
+                t1.record()
+            torch.cuda.synchronize()
+            result[f"{name} {splits}x{teams}"] = round(t0.elapsed_time(t1) * 10.0, 1)
+    K.check_device_errors("cuda:0")
+    print(json.dumps(result))
+    return 0
+
+
 def run_ours(args):
+    if args.only == "sample":
+        return run_sample(args)
+    if args.only == "decode-attention":
+        return run_decode_attention(args)
     import torch
 
     import pytorch_transformers_b200 as ptb
@@ -380,7 +491,7 @@ def main():
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration's (0: all)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--only", default="", choices=["", "decode", "prefill"],
+    ap.add_argument("--only", default="", choices=["", "decode", "prefill", "sample", "decode-attention"],
                     help="run one section only and print its numbers (for profilers)")
     ap.add_argument("--shape", default="7b", choices=sorted(SHAPES), help="model shape for --only decode / prefill")
     ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS, help="prompt length for --only prefill")
