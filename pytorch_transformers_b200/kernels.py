@@ -431,9 +431,10 @@ SKINNY_K_MULTIPLE = 32  # ptb_skinny_linear_k_multiple()
 # graph branch's kernels its blocks leave less room).
 SKINNY_BEST_ROWS = 12
 # A matrix of the vocabulary's height runs alone in the step, and there the library reads it faster from
-# 8 rows on (591 MB: 87.0 against 94.6 us at 8 rows, 87 against 108 us at 9).
+# 5 rows on (591 MB, float32 out: 89.7 against 90.3 us at 1 row, 91.0 / 90.5 at 4, 92.3 / 86.7 at 6,
+# 92.7 / 86.9 at 8, 108 / 87 at 9).
 SKINNY_TALL_ROWS = 32768
-SKINNY_BEST_ROWS_TALL = 7
+SKINNY_BEST_ROWS_TALL = 4
 
 
 def skinny_linear_takes(rows: int, k: int) -> bool:
