@@ -5,24 +5,23 @@
 // of matrix instructions, O two (one per 64 dims of the output), and one block fits on an SM.
 //
 // One block = 128 consecutive new tokens of one sequence x one query head. 128 softmax threads, one per
-// query row (tensor-memory lane t = row t; TPR threads per row: 1 or 2; with 2 the
-// threads of a row split a page's 64 columns). One more warp's first lane issues every matrix
+// query row (tensor-memory lane t = row t). One more warp's first lane issues every matrix
 // instruction, another warp's first lane asks the tensor memory accelerator for the pages. The roles
 // meet only at mbarriers (page landed, stage free, S written, P written, O updated): there is no
 // block-wide barrier in the loop. Keys are walked one cache page (64 keys) at a time:
 //
 //   S = Q K^T      tcgen05.mma  M=128 N=64 K=64   A = Q  (shared, K-major, 128-byte swizzle)
 //                                                 B = K page (shared, K-major, 128-byte swizzle)
-//                                                 D = S in tensor memory, two buffers of 64 columns: the
-//                                                 product for the next page runs under this page's softmax
+//                                                 D = S in tensor memory, three buffers of 64 columns:
+//                                                 the products of the next two pages run under this
+//                                                 page's softmax
 //   softmax        each thread reads its row of S with tcgen05.ld, masks, keeps the running maximum and
 //                  sum in float32, rescales its row of O in tensor memory when the maximum moved (only
 //                  then it waits for the previous page's O += P V), and writes P = exp2(S - max) as
-//                  bfloat16 pairs back into tensor memory with tcgen05.st (columns of its own, two
-//                  buffers for even and odd pages)
+//                  bfloat16 pairs back into tensor memory with tcgen05.st, in place of its row of S
 //   O += P V       tcgen05.mma  M=128 N=64 K=64   A = P read from tensor memory, B = V page (shared,
 //                                                 MN-major: head dims are contiguous), D = O in tensor
-//                                                 memory, columns [128, 192)
+//                                                 memory, columns [192, 256)
 //
 // The page tiles [64 keys][64 dims] bfloat16 come by TMA (cp.async.bulk.tensor.2d over the cache pool
 // seen as rows of D values, 128-byte swizzle) into a four-stage ring: exactly the canonical layout that
@@ -37,8 +36,8 @@
 //
 // Two blocks fit on an SM (81 KB of shared memory and 256 columns of tensor memory each): while one
 // block's threads do softmax, the other's matrix instructions run. Threads of a block may be a page
-// apart, which is why "P written" and "O updated" have a barrier each for even and for odd pages: an
-// arrival for page i + 1 must not count for page i.
+// or two apart, which is why "P written" has a barrier per S buffer and "O updated" one each for even and
+// odd pages: an arrival for a later page must not count for page i.
 //
 // Measured on this kernel at 2,048 and 8,192 tokens (71 heads, one K/V head): one, two and four threads
 // per row took 165, 159 and 189 us at 2,048 tokens while the softmax threads still copied the pages and
@@ -47,7 +46,10 @@
 // (two blocks share the SM's 16 transcendental lanes: that is their full rate), the wait for S 500, the
 // rescaling test 350, mask and maximum 280, loads and stores of tensor memory 330. Rescaling O only when a
 // row's maximum has grown by more than 2^8 (RESCALE_LOG2) brought 136 to 121 us and 1,229 to 1,060 us at
-// 8,192 tokens (575 TFLOP/s of causal flops); a cap of 128 registers (small spills) cost 10 %;
+// 8,192 tokens (575 TFLOP/s of causal flops); a third S buffer with P in place of S (S two pages ahead:
+// the softmax no longer waits for a product that could only be issued when the slowest warp had
+// finished the page before) 121 to 118 us and 1,060 to 1,028 us; a cap of 128 registers (small spills)
+// cost 10 %;
 // a second P tile in shared memory (softmax of page i + 1 no longer waits for O += P V of page i) took
 // 7 % longer, measured twice; P in tensor memory instead (no shared-memory stores, no proxy fence, the
 // same freedom) is 2 to 5 % faster than P in shared memory. A block is one chain of dependent steps per page
@@ -100,16 +102,21 @@ attention_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
   constexpr int TILE_Q_BYTES = TQ * D * 2;       // 16 or 32 KB
   constexpr int TILE_KV_BYTES = KEYS * D * 2;    // 8 or 16 KB
   constexpr int COLS_O = D / TPR;                // columns of O that a thread rescales and writes
-  // tensor memory: S of even and odd pages at columns [0, 64) and [64, 128), O at [128, 128 + D), then P
-  // of even and odd pages, 64 keys as bfloat16 pairs in 32 columns each
-  constexpr uint32_t TMEM_P = 128 + D, TMEM_COLS = (D == 64) ? 256 : 512;
+  // tensor memory: three S buffers of 64 columns (page i uses buffer i % 3), O at [192, 192 + D). P of a
+  // page (64 keys as bfloat16 pairs, 32 columns) takes the place of its S: a thread has its row of S in
+  // registers before it writes its row of P, nobody else touches that row, and the S of three pages later
+  // is issued after the O += P V that reads this P (the tensor pipe runs in order). With three buffers S
+  // runs two pages ahead of the softmax, so the softmax does not wait for a matrix product that was
+  // issued only when the slowest warp finished the page before.
+  static_assert(TPR == 1, "P in place of S needs one thread per row");
+  constexpr uint32_t TMEM_O = 192, TMEM_COLS = (D == 64) ? 256 : 512;
   unsigned char* q_tile = smem;
   unsigned char* k_ring = q_tile + TILE_Q_BYTES;                      // STAGES_TC pages
   unsigned char* v_ring = k_ring + STAGES_TC * TILE_KV_BYTES;         // STAGES_TC pages
-  // barriers: [0], [1] S buffer written; [2] O updated; [3] P written; then per stage: page landed,
-  // stage free again
+  // barriers: [0..2] S buffer written; [3], [4] O updated (even / odd pages); [5..7] P written (page % 3);
+  // then per stage: page landed, stage free again
   uint64_t* bars = reinterpret_cast<uint64_t*>(v_ring + STAGES_TC * TILE_KV_BYTES);
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 6 + 2 * STAGES_TC);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8 + 2 * STAGES_TC);
   float* pmax = reinterpret_cast<float*>(tmem_slot + 2);   // [2 buffers][TPR parts][TQ]: partial row maxima
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -129,18 +136,19 @@ attention_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
   const int n_blocks = last_pos / KEYS + 1;
   const int* pages = sb.pages + size_t(seq) * sb.pages_stride;
 
-  const uint32_t bar_s = smem_u32(&bars[0]), bar_o = smem_u32(&bars[2]), bar_p = smem_u32(&bars[3]);
-  // O updated and P written for odd pages (bar_o, bar_p: even pages). A thread may be a page ahead of
-  // another one: arrivals for page i + 1 must not count for page i.
-  const uint32_t bar_o2 = smem_u32(&bars[4 + 2 * STAGES_TC]), bar_p2 = smem_u32(&bars[5 + 2 * STAGES_TC]);
-  const uint32_t bar_k = smem_u32(&bars[4]), bar_free = smem_u32(&bars[4 + STAGES_TC]);
+  // A thread may be two pages ahead of another one (S of page i + 2 is issued before P of page i is
+  // complete, S of page i + 3 only after it): arrivals for pages i + 1 and i + 2 must not count for page
+  // i, hence a "P written" barrier per S buffer. "O updated" is waited for one page back only.
+  const uint32_t bar_s = smem_u32(&bars[0]), bar_o = smem_u32(&bars[3]), bar_o2 = smem_u32(&bars[4]);
+  const uint32_t bar_p = smem_u32(&bars[5]);
+  const uint32_t bar_k = smem_u32(&bars[8]), bar_free = smem_u32(&bars[8 + STAGES_TC]);
   if (tid == 0) {
-    mbar_init(bar_s, 1);
-    mbar_init(bar_s + 8, 1);
+    for (int b = 0; b < 3; ++b) {
+      mbar_init(bar_s + 8 * b, 1);
+      mbar_init(bar_p + 8 * b, SOFTMAX_THREADS);
+    }
     mbar_init(bar_o, 1);
     mbar_init(bar_o2, 1);
-    mbar_init(bar_p2, SOFTMAX_THREADS);
-    mbar_init(bar_p, SOFTMAX_THREADS);
     for (int s = 0; s < STAGES_TC; ++s) {
       mbar_init(bar_k + 8 * s, 1);      // the copy thread's expect_tx; the bytes complete it
       mbar_init(bar_free + 8 * s, 1);   // tcgen05.commit after the stage's O += P V
@@ -169,7 +177,7 @@ attention_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
   __syncthreads();        // barriers, tensor memory and Q are ready for everyone
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tmem_o = tmem_base + 128;   // S buffers at columns [0, 64) and [64, 128), O at [128, 128 + D)
+  const uint32_t tmem_o = tmem_base + TMEM_O;
   bool alive = true;  // false after a wait ran out: keep going without waiting, results are void
 
   if (copy_warp) {
@@ -209,54 +217,59 @@ attention_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
       const uint64_t desc_v0 = smem_desc(smem_u32(v_ring), 16, 1024);
       constexpr uint64_t STAGE_UNITS = TILE_KV_BYTES >> 4;   // the address field counts 16-byte units
       constexpr uint64_t Q_BLOCK = (TQ * 128) >> 4, KV_BLOCK = (KEYS * 128) >> 4;   // blocks of 64 dims
-      // S_b = Q K_b^T into S buffer b & 1; the page sits in stage `st`
-      auto issue_s = [&](int b, int st) {
+      // S_b = Q K_b^T into S buffer `buf`; the page sits in stage b % STAGES_TC
+      auto issue_s = [&](int b, int buf) {
+        const int st = b % STAGES_TC;
 #pragma unroll
         for (int blk = 0; blk < D / 64; ++blk)
-          tc_mma4<2, 2>(tmem_base + (b & 1) * 64, desc_q + blk * Q_BLOCK, desc_k0 + st * STAGE_UNITS + blk * KV_BLOCK,
+          tc_mma4<2, 2>(tmem_base + buf * 64, desc_q + blk * Q_BLOCK, desc_k0 + st * STAGE_UNITS + blk * KV_BLOCK,
                         IDESC_S, blk > 0 ? 1u : 0u);
-        tc_commit(bar_s + (b & 1) * 8);
+        tc_commit(bar_s + buf * 8);
       };
-      alive = mbar_wait(bar_k, 0, error_flag, 4);   // page 0 landed
-      tc_fence_after();
-      if (alive) issue_s(0, 0);
-      int st = 0, st_next = 1 % STAGES_TC;   // stages of pages i and i + 1
+      // S of the first two pages
+      for (int b = 0; b < 2 && b < n_blocks && alive; ++b) {
+        alive = mbar_wait(bar_k + 8 * b, 0, error_flag, 4);
+        tc_fence_after();
+        if (alive) issue_s(b, b);
+      }
+      int buf = 0, phase = 0;   // S buffer of page i (i % 3) and the parity of its barriers ((i / 3) & 1)
       for (int i = 0; i < n_blocks && alive; ++i) {
-        if (i + 1 < n_blocks) {
-          // page i + 1 landed; S_{i+1} runs under the softmax of page i. Its S buffer held S_{i-1},
-          // which every thread had read before it reported P_{i-1}.
-          alive = mbar_wait(bar_k + 8 * st_next, ((i + 1) / STAGES_TC) & 1, error_flag, 4);
+        if (i + 2 < n_blocks) {
+          // page i + 2 landed; S_{i+2} goes where S_{i-1} and P_{i-1} were: every thread had read that S
+          // before it reported P_{i-1}, and the O += P_{i-1} V_{i-1} that reads the P was issued before
+          alive = mbar_wait(bar_k + 8 * ((i + 2) % STAGES_TC), ((i + 2) / STAGES_TC) & 1, error_flag, 4);
           tc_fence_after();
-          issue_s(i + 1, st_next);
+          issue_s(i + 2, buf == 0 ? 2 : buf - 1);
         }
         // P_i is written and O is rescaled: O += P_i V_i (16 keys: 32 bytes along P's rows, 2048 bytes
         // down V's rows)
-        if (alive) alive = mbar_wait((i & 1) ? bar_p2 : bar_p, (i >> 1) & 1, error_flag, 5);
+        if (alive) alive = mbar_wait(bar_p + buf * 8, phase, error_flag, 5);
         tc_fence_after();
+        const int st = i % STAGES_TC;
 #pragma unroll
         for (int blk = 0; blk < D / 64; ++blk)
-          tc_mma4_ts<128>(tmem_o + blk * 64, tmem_base + TMEM_P + (i & 1) * 32, desc_v0 + st * STAGE_UNITS + blk * KV_BLOCK,
+          tc_mma4_ts<128>(tmem_o + blk * 64, tmem_base + buf * 64, desc_v0 + st * STAGE_UNITS + blk * KV_BLOCK,
                           IDESC_PV, i > 0 ? 1u : 0u);
         tc_commit((i & 1) ? bar_o2 : bar_o);
         tc_commit(bar_free + 8 * st);   // the copy thread may refill this stage
-        st = st_next;
-        st_next = (st_next + 1 == STAGES_TC) ? 0 : st_next + 1;
+        if (++buf == 3) { buf = 0; phase ^= 1; }
       }
     }
   } else {
     // ------------------------------------------------------------ softmax threads
     const uint32_t lane_addr = tmem_base + (uint32_t((warp & 3) * 32) << 16) + part * COLS;  // this warp's lanes, its columns
-    const uint32_t o_addr = tmem_base + (uint32_t((warp & 3) * 32) << 16) + 128 + part * COLS_O;   // its columns of O
+    const uint32_t o_addr = tmem_base + (uint32_t((warp & 3) * 32) << 16) + TMEM_O + part * COLS_O;   // its columns of O
+    int buf = 0, phase = 0;   // S buffer of page i (i % 3) and the parity of its barriers ((i / 3) & 1)
     const int sync_id = 1 + (warp & 3);
     float m_run = -INFINITY, l_run = 0.f;   // running maximum of the raw scores, this thread's half of the sum
     const float slope = BIAS ? p.slopes[h] : 0.f;
     const float sl2 = p.scale * 1.4426950408889634f;
     for (int i = 0; i < n_blocks; ++i) {
       // (1) this thread's 32 columns of its row of S_i
-      if (alive) alive = mbar_wait(bar_s + (i & 1) * 8, (i >> 1) & 1, error_flag, 1);
+      if (alive) alive = mbar_wait(bar_s + buf * 8, phase, error_flag, 1);
       tc_fence_after();
       float s[COLS];
-      tmem_ld<COLS>(lane_addr + (i & 1) * 64, s);
+      tmem_ld<COLS>(lane_addr + buf * 64, s);
       if (BIAS) {
 #pragma unroll
         for (int j = 0; j < COLS; ++j) s[j] += alibi_bias(slope, i * KEYS + part * COLS + j);
@@ -314,15 +327,14 @@ attention_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
         ls[e & 3] += a + b;
         w[e] = pack_bf16(a, b);
       }
-      // P of even / odd pages has its own columns: keys 2c, 2c + 1 in column c. This buffer was read
-      // by the O += P V of two pages ago, which is complete: S of this page was committed after it was
-      // issued, and a commit covers every matrix instruction issued before it.
-      const uint32_t p_addr = tmem_base + (uint32_t((warp & 3) * 32) << 16) + TMEM_P + (i & 1) * 32 + part * (COLS / 2);
-      tmem_st_u32<COLS / 2>(p_addr, w);
+      // P in place of this page's S: keys 2c, 2c + 1 in column c of the buffer (this thread's row of S is in
+      // registers since the load above)
+      tmem_st_u32<COLS / 2>(lane_addr + buf * 64, w);
       tmem_st_wait();
       l_run += (ls[0] + ls[1]) + (ls[2] + ls[3]);   // this thread's half of the row sum
       tc_fence_before();
-      mbar_arrive((i & 1) ? bar_p2 : bar_p);   // (7) the issuing thread starts O += P V when all 256 have arrived
+      mbar_arrive(bar_p + buf * 8);   // (7) the issuing thread starts O += P V when all rows have arrived
+      if (++buf == 3) { buf = 0; phase ^= 1; }
     }
     // the parts of every row sum meet, in the buffer that the last page did not use, in one order
     float* pl = pmax + (n_blocks & 1) * TPR * TQ;
@@ -369,7 +381,7 @@ int launch_tc(const void* q, const void* k_pool, const void* v_pool, int pool_pa
   const CUtensorMap* km = pool_map(k_pool, pool_pages, p.kv_heads, D);
   const CUtensorMap* vm = pool_map(v_pool, pool_pages, p.kv_heads, D);
   if (km == nullptr || vm == nullptr) return PTB_ERR_LAUNCH;
-  const size_t smem = 1024 + TQ * D * 2 + 2 * STAGES_TC * KEYS * D * 2 + 128 + 2 * TPR * TQ * sizeof(float);
+  const size_t smem = 1024 + TQ * D * 2 + 2 * STAGES_TC * KEYS * D * 2 + 192 + 2 * TPR * TQ * sizeof(float);
   static bool configured = false;
   if (!configured) {
     if (cudaFuncSetAttribute(attention_tc_kernel<D, BIAS>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess)
