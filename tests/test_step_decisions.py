@@ -87,3 +87,12 @@ def test_teams_of_clusters_for_long_sequences_in_small_batches():
     assert teams(1, 257) == 8        # batch 1: four pages a block at least
     assert teams(1, 129) == 4
     assert teams(64, 257) == 1       # a large batch fills the device by itself
+
+
+def test_rows_that_go_to_the_skinny_linear_kernel():
+    assert kernels.skinny_linear_preferred(8, 4544, 4672)
+    assert kernels.skinny_linear_preferred(12, 4544, 18176)
+    assert not kernels.skinny_linear_preferred(13, 4544, 18176)       # the library from 13 rows on
+    assert kernels.skinny_linear_preferred(4, 4544, 65024)            # the head: up to 4 rows
+    assert not kernels.skinny_linear_preferred(8, 4544, 65024)
+    assert not kernels.skinny_linear_preferred(8, 4544 + 8, 4672)     # K must be a multiple of 32
