@@ -315,7 +315,7 @@ sample_kernel(const float* __restrict__ logits, float* __restrict__ work, int* _
 #pragma unroll
     for (int c = 0; c < 4; ++c) {
       y[c] = x[c] * inv_t;
-      if (4 * j + c < V) vmax = fmaxf(vmax, y[c]);
+      vmax = fmaxf(vmax, y[c]);   // (what lies past the row's end was loaded as -inf)
     }
     store_group(w, rv, j, y);
   });
@@ -338,23 +338,33 @@ sample_kernel(const float* __restrict__ logits, float* __restrict__ work, int* _
   // Candidates are gathered in any order (a slot from a counter) and then sorted by (value, token), so what
   // follows does not depend on the order of arrival.
   uint32_t bound = 0u;  // keys >= bound are candidates
-  auto gather = [&](long long above, long long upto) -> int {   // the tokens with above < key <= upto
+  auto gather = [&](uint32_t from, uint32_t upto) -> int {   // the tokens with from <= key <= upto
     __syncthreads();
     if (tid == 0) s_count = 0u;
     __syncthreads();
     sweep<4>(w, rv, 0, rv.groups, tid, ST, [&](int j, const float (&x)[4], bool ok) {
+      const int valid = ok ? min(4, V - 4 * j) : 0;   // tokens of this group inside the row
+      uint32_t key[4];
+      unsigned int mine = 0u;                          // bit c: token c of my group is a candidate
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
-        const uint32_t key = ordered_key(x[c]);
-        const bool is = ok && 4 * j + c < V && (long long)key > above && (long long)key <= upto;
-        const unsigned int votes = __ballot_sync(0xffffffffu, is);
-        if (votes == 0u) continue;
-        unsigned int base = 0u;
-        if (lane == __ffs(votes) - 1) base = atomicAdd(&s_count, (unsigned int)__popc(votes));
-        base = __shfl_sync(0xffffffffu, base, __ffs(votes) - 1);
-        const unsigned int slot = base + __popc(votes & ((1u << lane) - 1u));
-        if (is && slot < (unsigned int)ST) s_cand[slot] = ((unsigned long long)key << 32) | (unsigned int)(4 * j + c);
+        key[c] = ordered_key(x[c]);
+        if (c < valid && key[c] >= from && key[c] <= upto) mine |= 1u << c;
       }
+      // candidates are rare: one vote per group of four tokens, and slots only where somebody has one
+      const unsigned int votes = __ballot_sync(0xffffffffu, mine != 0u);
+      if (votes == 0u) return;
+      const unsigned int n_mine = __popc(mine);
+      const unsigned int upto_me = warp_inclusive_scan_u(n_mine, lane);
+      unsigned int base = 0u;
+      if (lane == 31) base = atomicAdd(&s_count, upto_me);
+      unsigned int slot = __shfl_sync(0xffffffffu, base, 31) + upto_me - n_mine;
+#pragma unroll
+      for (int c = 0; c < 4; ++c)
+        if (mine & (1u << c)) {
+          if (slot < (unsigned int)ST) s_cand[slot] = ((unsigned long long)key[c] << 32) | (unsigned int)(4 * j + c);
+          ++slot;
+        }
     });
     __syncthreads();
     return (int)s_count;
@@ -368,9 +378,9 @@ sample_kernel(const float* __restrict__ logits, float* __restrict__ work, int* _
     __syncthreads();
     block_sort_ascending(tmax, ST);
     bound = ordered_key(tmax[ST - select]);
-    kept = gather((long long)bound - 1, 0xffffffffll);
+    kept = gather(bound, 0xffffffffu);
   } else if (select == 0 && V <= ST) {
-    kept = gather(-1, 0xffffffffll);
+    kept = gather(0u, 0xffffffffu);
   }
   if (select > 0 && kept > ST) {
     // too many (ties, or a top_k beyond the block): the exact key by radix selection, 12 + 12 + 8 bits
@@ -384,7 +394,7 @@ sample_kernel(const float* __restrict__ logits, float* __restrict__ work, int* _
     __syncthreads();
     radix_pass(w, rv, prefix, 0, 8, want, s_hist, s_scan_u, &s_pick, &s_above, &s_same);
     bound = prefix | s_pick;
-    kept = gather((long long)bound - 1, 0xffffffffll);
+    kept = gather(bound, 0xffffffffu);
   }
 
   if (kept <= ST) {
@@ -537,7 +547,7 @@ sample_kernel(const float* __restrict__ logits, float* __restrict__ work, int* _
     }
     uint32_t cut = (uint32_t)hi;
     if (c_hi - c_lo <= (unsigned int)ST) {
-      const int inside = gather(lo, hi);
+      const int inside = gather((uint32_t)(lo + 1), (uint32_t)hi);
       int n2 = 32;
       while (n2 < inside) n2 <<= 1;
       for (int i = inside + tid; i < n2; i += ST) s_cand[i] = 0ull;
@@ -559,7 +569,9 @@ sample_kernel(const float* __restrict__ logits, float* __restrict__ work, int* _
   }
   // probabilities below min_p times the largest one go: exp(v - vmax) < min_p
   const float min_p = p.min_p;
+  const bool unfiltered = floor_key == 0u && !(min_p > 0.f);
   auto mass_of = [&](float x) {
+    if (unfiltered) return expf(x - vmax);   // (the same for the whole block)
     if (ordered_key(x) < floor_key) return 0.f;
     const float e = expf(x - vmax);
     return (min_p > 0.f && e < min_p && x != vmax) ? 0.f : e;
