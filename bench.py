@@ -105,28 +105,35 @@ class ClockSampler:
         return {"sm_mhz": int(statistics.median(mhz)), "sm_max_mhz": max(mx), "reasons": sorted(reasons)}
 
 
+def shape_sizes(c):
+    """(hidden, heads, K/V heads, head size, feed-forward width, vocabulary) of a shape dictionary."""
+    h, nh, v = c["hidden_size"], c["num_attention_heads"], c["vocab_size"]
+    f = c.get("ffn_hidden_size") or 4 * h
+    kvh = c.get("num_kv_heads", 1) if c.get("new_decoder_architecture") else (1 if c.get("multi_query", True) else nh)
+    return h, nh, kvh, h // nh, f, v
+
+
 def falcon_param_count(c, layers):
-    h, nh, f, v = c["hidden_size"], c["num_attention_heads"], 4 * c["hidden_size"], c["vocab_size"]
-    d = h // nh
-    per_layer = (nh + 2) * d * h + h * h + 2 * f * h + 2 * h
+    """Weights that a step reads: the layers' matrices and norm vectors and the head matrix (tied or not,
+    it is read once; of the embedding table a step reads a row per token). Also the count of one layer."""
+    h, nh, kvh, d, f, v = shape_sizes(c)
+    norms = 2 if (c.get("new_decoder_architecture") and c.get("num_ln_in_parallel_attn", 2) != 1) or \
+        not (c.get("new_decoder_architecture") or c.get("parallel_attn", True)) else 1
+    per_layer = (nh + 2 * kvh) * d * h + h * h + 2 * f * h + norms * 2 * h
     return layers * per_layer + v * h + 2 * h, per_layer
 
 
 def decode_bytes(c, layers, batch, context):
-    """Bytes a decode step has to read: every weight it uses once (the tied table serves as head)
-    and the cached keys and values of the live requests, in bfloat16."""
-    h, nh = c["hidden_size"], c["num_attention_heads"]
-    d = h // nh
+    """Bytes a decode step has to read: every weight it uses once and the cached keys and values of the
+    live requests, in bfloat16."""
+    h, nh, kvh, d, f, v = shape_sizes(c)
     params, _ = falcon_param_count(c, layers)
-    kv = batch * context * layers * 2 * d * 2      # one K/V head
+    kv = batch * context * layers * 2 * kvh * d * 2
     return 2 * params + kv
 
 
 def prefill_flops(c, layers, tokens):
-    h, nh, v = c["hidden_size"], c["num_attention_heads"], c["vocab_size"]
-    f = c.get("ffn_hidden_size") or 4 * h
-    kvh = c.get("num_kv_heads", 1) if c.get("new_decoder_architecture") else (1 if c.get("multi_query", True) else nh)
-    d = h // nh
+    h, nh, kvh, d, f, v = shape_sizes(c)
     gemm = 2 * tokens * layers * ((nh + 2 * kvh) * d * h + h * h + 2 * f * h)
     attn = layers * nh * 2 * 2 * d * tokens * (tokens + 1) / 2      # QK^T and PV over the causal half
     head = 2 * v * h
