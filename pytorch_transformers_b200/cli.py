@@ -11,6 +11,7 @@ tokenizer.json and the ``tokenizers`` wheel is importable.
     python -m pytorch_transformers_b200.cli random-model --config config.json --seed 0 --out DIR
     python -m pytorch_transformers_b200.cli replay --model DIR --dtype float32 --out DIR --max-tokens N < steps
     python -m pytorch_transformers_b200.cli env
+    python -m pytorch_transformers_b200.cli bench -- --steps 20
 """
 from __future__ import annotations
 
@@ -184,11 +185,43 @@ class EnvCommand(BaseCommand):
         return 0
 
 
-def main(argv: Optional[List[str]] = None) -> int:
+class BenchCommand(BaseCommand):
+    """Runs the repository's benchmark (bench.py beside the package) with the arguments given after
+    ``bench``; the reference keeps its benchmark outside the package too (benchmark/llama.py)."""
+
+    @staticmethod
+    def register_subcommand(sub) -> None:
+        p = sub.add_parser("bench", help="run bench.py of the checkout (arguments are passed on)")
+        p.add_argument("bench_args", nargs=argparse.REMAINDER, help="arguments of bench.py, e.g. --steps 20")
+        p.set_defaults(func=BenchCommand)
+
+    def __init__(self, args):
+        self.args = args
+
+    @staticmethod
+    def script() -> str:
+        return os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "bench.py")
+
+    def run(self) -> int:
+        import subprocess
+        path = self.script()
+        if not os.path.isfile(path):
+            raise SystemExit(f"bench: {path} does not exist (the benchmark lives in the source checkout, not in an "
+                             "installed package)")
+        rest = [a for a in self.args.bench_args if a != "--"]
+        return subprocess.call([sys.executable, path] + rest)
+
+
+def build_parser() -> argparse.ArgumentParser:
     parser = argparse.ArgumentParser("pytorch_transformers_b200 CLI tool", usage="ptb200-cli <command> [<args>]")
     sub = parser.add_subparsers(help="commands")
-    for cmd in (RunGenerationCommand, RandomModelCommand, ReplayCommand, EnvCommand):
+    for cmd in (RunGenerationCommand, RandomModelCommand, ReplayCommand, EnvCommand, BenchCommand):
         cmd.register_subcommand(sub)
+    return parser
+
+
+def main(argv: Optional[List[str]] = None) -> int:
+    parser = build_parser()
     args = parser.parse_args(argv)
     if not hasattr(args, "func"):
         parser.print_help()

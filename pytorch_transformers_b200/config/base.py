@@ -13,7 +13,10 @@ import json
 import os
 from typing import Any, ClassVar, Dict, Optional, Tuple
 
+from ..utils import logging as log
+
 CONFIG_NAME = "config.json"  # src/transformers/utils/__init__.py:263
+_logger = log.get_logger(__name__)
 
 
 class ConfigError(ValueError):
@@ -62,6 +65,8 @@ class ModelConfig:
             kwargs["architectures"] = tuple(kwargs["architectures"])
         cfg = cls(**kwargs)
         cfg.extra = extra
+        if extra:
+            _logger.debug("%s keeps config keys that it has no field for: %s", cls.__name__, ", ".join(sorted(extra)))
         return cfg
 
     @classmethod

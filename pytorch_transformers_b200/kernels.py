@@ -79,7 +79,8 @@ def lib():
                      "ptb_skinny_linear", "ptb_skinny_linear_max_rows", "ptb_skinny_linear_k_multiple",
                      "ptb_rope_table", "ptb_attention_decode", "ptb_attention_tc", "ptb_attention_tc_supports",
                      "ptb_attention_tc_tile_tokens", "ptb_tc_linear", "ptb_tc_linear_max_rows",
-                     "ptb_tc_linear_k_multiple", "ptb_attention_decode_tc", "ptb_attention_decode_tc_supports"):
+                     "ptb_tc_linear_k_multiple", "ptb_attention_decode_tc", "ptb_attention_decode_tc_supports",
+                     "ptb_fill_normal"):
             getattr(L, name).restype = ctypes.c_int
         _configured = True
     return L
@@ -141,6 +142,18 @@ def to_float(x: torch.Tensor) -> torch.Tensor:
     out = torch.empty(x.shape, dtype=torch.float32, device=x.device)
     _check(lib().ptb_to_float(_dtype_code(x), _ptr(x), _ptr(out), ctypes.c_longlong(x.numel()), _stream(x)),
            "to_float")
+    return out
+
+
+def fill_normal(out: torch.Tensor, key: int, std: float, offset: float = 0.0, first: int = 0,
+                round_bf16: bool = False) -> torch.Tensor:
+    """out.flatten()[i] = offset + std * z(key, first + i): the device twin of weights/generator.py, bit for
+    bit. ``round_bf16`` rounds a float32 tensor's values to what a bfloat16 tensor would hold."""
+    _need_cuda(out)
+    _check(lib().ptb_fill_normal(_dtype_code(out), _ptr(out), ctypes.c_ulonglong(out.numel()),
+                                 ctypes.c_ulonglong(first), ctypes.c_ulonglong(key & (2 ** 64 - 1)),
+                                 ctypes.c_double(std), ctypes.c_double(offset), 1 if round_bf16 else 0,
+                                 _stream(out)), "fill_normal")
     return out
 
 

@@ -20,6 +20,9 @@ import time
 from concurrent.futures import ThreadPoolExecutor
 from typing import List, Optional
 
+from .utils import logging as log
+
+_logger = log.get_logger(__name__)
 _HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(_HERE, "csrc")
 LIB_NAME = "libptb200_kernels.so"
@@ -81,7 +84,8 @@ def _writable_dir() -> str:
 
 
 def _say(msg: str) -> None:
-    print(f"[pytorch_transformers_b200] {msg}", file=sys.stderr, flush=True)
+    # progress of a compilation that may take a minute: shown at the default verbosity too
+    log.always(_logger, msg)
 
 
 def _compile_one(nvcc: str, src: str, obj: str, verbose_ptxas: bool) -> str:

@@ -17,7 +17,10 @@ from typing import Dict, List, Optional
 
 import torch
 
+from ..utils import logging as log
 from .safetensors_io import open_checkpoint
+
+_logger = log.get_logger(__name__)
 
 _FLOATS = (torch.float32, torch.bfloat16, torch.float16, torch.float64)
 
@@ -72,8 +75,8 @@ def load_weights(model, folder: str, name_rules: Optional[dict] = None, strict: 
             elif decl.role != "int" and e.dtype not in _FLOATS:
                 mismatched.append(f"{name}: stored as {e.dtype}, model wants floating point")
         if unexpected and not strict and not missing and not mismatched:
-            import warnings
-            warnings.warn(f"{folder}: {len(unexpected)} tensors are not used by the model: " + ", ".join(sorted(unexpected)))
+            _logger.warning("%s: %d tensors are not used by the model: %s", folder, len(unexpected),
+                            ", ".join(sorted(unexpected)))
             unexpected = []
         if missing or unexpected or mismatched:
             raise WeightError(folder, sorted(missing), sorted(unexpected), mismatched)

@@ -178,8 +178,16 @@ def test_strict_false_only_forgives_unused_tensors(tmp_path):
     folder = tm.write_model_folder(str(tmp_path / "extra"), cfg, w)
     with pytest.raises(WeightError):
         load_cpu(folder)
-    with pytest.warns(UserWarning, match="not used by the model"):
+    import io
+    import logging
+    seen = io.StringIO()
+    handler = logging.StreamHandler(seen)
+    logging.getLogger("pytorch_transformers_b200").addHandler(handler)
+    try:
         ptb.AutoModelForCausalLM.from_pretrained(folder, dtype="float32", device="cpu", strict=False)
+    finally:
+        logging.getLogger("pytorch_transformers_b200").removeHandler(handler)
+    assert "not used by the model" in seen.getvalue() and "transformer.h.0.extra.weight" in seen.getvalue()
     del w["transformer.ln_f.bias"]
     with pytest.raises(WeightError, match="missing"):
         ptb.AutoModelForCausalLM.from_pretrained(tm.write_model_folder(str(tmp_path / "both"), cfg, w),
