@@ -42,7 +42,7 @@ FALCON_40B = dict(vocab_size=65024, hidden_size=8192, num_hidden_layers=60, num_
 SHAPES = {"7b": FALCON_7B, "11b": FALCON_11B, "40b": FALCON_40B}
 CONTEXT = 2048
 PREFILL_TOKENS = 2048
-FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
 
 def peaks():
@@ -50,7 +50,9 @@ def peaks():
     if os.path.isfile(path):
         try:
             raw = json.load(open(path))
-            return {"hbm_gbs": float(raw["hbm_gbs"]), "bf16_tflops": float(raw["bf16_tflops"]), "source": "measured"}
+            return {"hbm_gbs": float(raw["hbm_gbs"]), "bf16_tflops": float(raw["bf16_tflops"]),
+                    "bf16_tflops_sustained": float(raw.get("bf16_tflops_sustained") or raw["bf16_tflops"]),
+                    "source": "measured"}
         except Exception:
             pass
     return dict(FALLBACK_PEAKS, source="fallback")
@@ -103,6 +105,16 @@ class ClockSampler:
         if not mhz:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
         return {"sm_mhz": int(statistics.median(mhz)), "sm_max_mhz": max(mx), "reasons": sorted(reasons)}
+
+
+def workload_config(layers, batch):
+    """What is run, in the same words for both arms: the layer sizes of Falcon-7B, the batch, the context."""
+    h, nh, kvh, d, f, v = shape_sizes(FALCON_7B)
+    return {"model": "falcon-7b-shape", "layers": layers, "layers_of_config": FALCON_7B["num_hidden_layers"],
+            "hidden": h, "heads": nh, "kv_heads": kvh, "head_dim": d, "ffn": f, "vocab": v, "global_batch": batch,
+            "seq_len": CONTEXT, "prompt_tokens": CONTEXT, "weights": "random seed 0", "tokens": "uniform seed 0",
+            "parallelism": "none", "sampling": "greedy",
+            "l2": "inputs larger than L2 (all weights read per step)"}
 
 
 def shape_sizes(c):
@@ -210,7 +222,7 @@ def run_decode_attention(args):
     k_pool, v_pool, group = cache.entry_storage(0)
     k_pool.normal_()
     v_pool.normal_()
-    ctx = StepContext(cache, slots, [[0]] * rows, 1, [[]] * rows, K.generic_tile_rows())
+    ctx = StepContext(cache, slots, [[0]] * rows, 1, [[]] * rows)
     fused = torch.randn(rows, kv * (qpk + 2) * d, device="cuda", dtype=torch.bfloat16)
     rope = K.rope_table(ctx.dev["tok_pos"], (1.0 / (10000 ** (torch.arange(0, d, 2).float() / d))).cuda())
     hpk = min(qpk, 128)
@@ -247,11 +259,132 @@ def run_decode_attention(args):
     return 0
 
 
+def prefill_flops_ragged(c, layers, lengths):
+    """Flops of one ragged prefill of prompts of the given lengths (logits for each prompt's last token)."""
+    h, nh, kvh, d, f, v = shape_sizes(c)
+    total = sum(lengths)
+    gemm = 2 * total * layers * ((nh + 2 * kvh) * d * h + h * h + 2 * f * h)
+    attn = sum(layers * nh * 2 * 2 * d * n * (n + 1) / 2 for n in lengths)
+    return gemm + attn + len(lengths) * 2 * v * h
+
+
+# BASELINE's runs of the two larger shapes: prompts of seeded uniform lengths in one generate() call
+BASELINE_RUNS = {"11b": {"prompts": 8, "shortest": 512, "longest": 8192, "steps": 128},
+                 "40b": {"prompts": 16, "shortest": 64, "longest": 2048, "steps": 256}}
+
+
+def run_config(args, model, cfg, layers, pk):
+    """`--only config --shape 11b|40b`: the run that BASELINE names for the shape, through generate():
+    prompts of unequal lengths in one ragged prefill (fed in steps of at most 16,384 tokens), then one
+    token each for the given number of steps. Device time from CUDA events recorded as each step's tokens
+    reach the host; bytes of a decode step from the lengths the sequences really have at mid-run."""
+    import torch
+    run = BASELINE_RUNS[args.shape]
+    gen = torch.Generator().manual_seed(0)
+    n, steps = run["prompts"], args.decode_steps or run["steps"]
+    lengths = torch.randint(run["shortest"], run["longest"] + 1, (n,), generator=gen).tolist()
+    prompts = [torch.randint(0, cfg.vocab_size, (length,), generator=gen).tolist() for length in lengths]
+    marks = []
+
+    def on_token(r, tok):
+        if r == n - 1:
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record()
+            marks.append((ev, time.perf_counter()))
+
+    def once():
+        marks.clear()
+        torch.cuda.synchronize()
+        start = torch.cuda.Event(enable_timing=True)
+        start.record()
+        t0 = time.perf_counter()
+        model.generate(prompts, max_new_tokens=steps, eos_token_id=None, max_batch_size=n, on_token=on_token)
+        torch.cuda.synchronize()
+        return start, t0
+
+    once()                      # sizes the cache, captures the graphs of the decode steps
+    with ClockSampler() as sampler:
+        start, t0 = once()
+    prefill_ms = start.elapsed_time(marks[0][0])
+    decode_ms = marks[0][0].elapsed_time(marks[-1][0]) / (len(marks) - 1)
+    wall_ms = (marks[-1][1] - marks[0][1]) / (len(marks) - 1) * 1e3
+    shape = SHAPES[args.shape]
+    h, nh, kvh, d, f, v = shape_sizes(shape)
+    params, _ = falcon_param_count(shape, layers)
+    mid = sum(lengths) + n * (1 + steps / 2)                       # cached tokens at the middle step
+    step_bytes = 2 * params + mid * layers * 2 * kvh * d * 2
+    flops = prefill_flops_ragged(shape, layers, lengths)
+    print(json.dumps({
+        "only": "config", "shape": args.shape, "layers": layers, "layers_of_config": shape["num_hidden_layers"],
+        "prompts": n, "prompt_lengths": lengths, "prompt_tokens": sum(lengths), "decode_steps": steps,
+        "decode": {"tokens_per_s": round(n / decode_ms * 1e3, 1), "ms_per_step": round(decode_ms, 4),
+                   "ms_per_step_wall": round(wall_ms, 4), "bytes_per_step": int(step_bytes),
+                   "achieved_GBps": round(step_bytes / decode_ms / 1e6, 1),
+                   "frac": round(step_bytes / decode_ms / 1e6 / pk["hbm_gbs"], 4)},
+        "prefill": {"tokens_per_s": round(sum(lengths) / prefill_ms * 1e3, 1), "ms": round(prefill_ms, 2),
+                    "TFLOPs": round(flops / prefill_ms / 1e9, 1),
+                    "frac": round(flops / prefill_ms / 1e9 / pk["bf16_tflops"], 4),
+                    "frac_sustained": round(flops / prefill_ms / 1e9 / pk["bf16_tflops_sustained"], 4)},
+        "peaks": pk["source"], "clocks": sampler.summary()}))
+    return 0
+
+
+def run_linear(args):
+    """`--only linear --rows R`: device time of one linear layer of `--shape` at R rows, for the three ways
+    the library has of running it: the weight-streaming kernel (up to 32 rows), the library product
+    (cuBLAS through torch) and the tcgen05 kernel (up to 128 rows). 20 launches in a CUDA graph go round
+    enough copies of the matrix that every launch reads its weights from HBM, not from L2."""
+    import torch
+
+    from pytorch_transformers_b200 import kernels as K
+
+    torch.cuda.set_device(0)
+    h, nh, kvh, d, f, v = shape_sizes(SHAPES[args.shape])
+    rows = args.rows
+    shapes = {"qkv": ((nh + 2 * kvh) * d, h), "out": (h, nh * d), "up": (f, h), "down": (h, f), "head": (v, h)}
+    x_cache = {}
+    result = {"only": "linear", "shape": args.shape, "rows": rows, "unit": "us per launch (GB/s of the matrix)"}
+    side = torch.cuda.Stream()
+    for name, (n, k) in shapes.items():
+        copies = max(2, -(-(300 << 20) // (n * k * 2)))
+        ws = [torch.randn(n, k, device="cuda", dtype=torch.bfloat16) * 0.02 for _ in range(copies)]
+        x = x_cache.setdefault(k, torch.randn(rows, k, device="cuda", dtype=torch.bfloat16))
+        ways = {"library": lambda w: K.matmul_nt(x, w)}
+        if K.skinny_linear_takes(rows, k):
+            ways["skinny"] = lambda w: K.skinny_linear(x, w)
+        if K.tc_linear_takes(rows, k):
+            ways["tcgen05"] = lambda w: K.tc_linear(x, w)
+        for way, launch in ways.items():
+            with torch.cuda.stream(side):
+                for i in range(3):
+                    launch(ws[i % copies])
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=side):
+                    for i in range(20):
+                        launch(ws[i % copies])
+                graph.replay()
+                t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                t0.record()
+                for _ in range(5):
+                    graph.replay()
+                t1.record()
+            torch.cuda.synchronize()
+            us = t0.elapsed_time(t1) * 10.0
+            result[f"{name} {way}"] = [round(us, 1), round(n * k * 2 / us / 1e3)]
+        del ws
+        torch.cuda.empty_cache()
+    K.check_device_errors("cuda:0")
+    print(json.dumps(result))
+    return 0
+
+
 def run_ours(args):
     if args.only == "sample":
         return run_sample(args)
     if args.only == "decode-attention":
         return run_decode_attention(args)
+    if args.only == "linear":
+        return run_linear(args)
     import torch
 
     import pytorch_transformers_b200 as ptb
@@ -285,9 +418,13 @@ def run_ours(args):
         toks = sel.select(model.step(cache, slots, [[1]] * batch, want="last"), list(range(batch)), 0)
 
         def one():
+            # as the generation loop does it: the selection runs on the device while the host builds the
+            # next step, which then only waits for its tokens
             nonlocal toks
             logits = model.step(cache, slots, [[t] for t in toks], want="last")
-            toks = sel.select(logits, list(range(batch)), 0)
+            pending = sel.begin(logits, list(range(batch)), 0)
+            model.prepare_next(cache, slots)
+            toks = sel.finish(pending)
 
         for _ in range(warmup):
             one()
@@ -317,6 +454,8 @@ def run_ours(args):
 
     if args.no_graphs:
         model.use_graphs = False
+    if args.only == "config":
+        return run_config(args, model, cfg, layers, pk)
     if args.only == "decode":
         ms, launches, ctx_mid, _ = decode_run(args.batch, args.steps, args.warmup, context=args.context)
         kv_bytes = args.batch * ctx_mid * layers * 2 * cfg.kv_heads_eff * cfg.head_dim * 2
@@ -353,7 +492,8 @@ def run_ours(args):
         return 0
     pre_flops = prefill_flops(FALCON_7B, layers, PREFILL_TOKENS)
     prefill = {"value": round(PREFILL_TOKENS / pre_ms * 1e3, 1), "tokens": PREFILL_TOKENS, "ms": round(pre_ms, 3),
-               "frac": round(pre_flops / (pre_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
+               "frac": round(pre_flops / (pre_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4),
+               "frac_sustained": round(pre_flops / (pre_ms * 1e-3) / (pk["bf16_tflops_sustained"] * 1e12), 4)}
 
     # ---- headline: decode at batch 8 ----
     batch = args.batch
@@ -364,10 +504,14 @@ def run_ours(args):
     roofline = {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
                 "frac": round(achieved / pk["hbm_gbs"], 4), "peaks": pk["source"]}
 
-    points = {}
+    points, points_roofline = {}, {}
     for b in (1, 64):
-        pms, _, _, _ = decode_run(b, max(8, args.steps // 2), 3)
+        pms, _, pctx, _ = decode_run(b, max(8, args.steps // 2), 3)
         points[f"decode_b{b}"] = round(b / pms * 1e3, 1)
+        pbytes = decode_bytes(FALCON_7B, layers, b, pctx)
+        points_roofline[f"decode_b{b}"] = {"ms_per_step": round(pms, 4), "bytes": int(pbytes),
+                                           "achieved": round(pbytes / (pms * 1e-3) / 1e9, 1),
+                                           "frac": round(pbytes / (pms * 1e-3) / 1e9 / pk["hbm_gbs"], 4)}
 
     # ---- end to end through generate(): host token lists in, host token lists out ----
     n_new = args.steps + args.warmup
@@ -395,12 +539,11 @@ def run_ours(args):
         "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms, 4),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "impl": "ours",
-        "config": {"model": "falcon-7b-shape", "layers": layers, "layers_of_config": FALCON_7B["num_hidden_layers"],
-                   "hidden": 4544, "heads": 71, "kv_heads": 1, "head_dim": 64, "ffn": 18176, "vocab": 65024,
-                   "global_batch": batch, "seq_len": CONTEXT, "prompt_tokens": CONTEXT, "weights": "random seed 0",
-                   "tokens": "uniform seed 0", "parallelism": "none", "sampling": "greedy on device",
-                   "l2": "inputs larger than L2 (all weights read per step)", "cache_page": 64},
-        "prefill": prefill, "roofline": roofline, "points": points, "e2e": e2e, "gpu_launches": launches,
+        "config": workload_config(layers, batch),
+        "notes": {"sampling": "greedy, on the device", "cache_page": 64, "decode_steps": "CUDA graphs",
+                  "timing": "CUDA events around K steps"},
+        "prefill": prefill, "roofline": roofline, "points": points, "points_roofline": points_roofline, "e2e": e2e,
+        "gpu_launches": launches,
         "clocks": clocks,
     }
     print(json.dumps(out), flush=True)
@@ -479,10 +622,9 @@ def run_reference(args):
                "value": round(batch / ms * 1e3, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
                "warmup": args.warmup, "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak",
                "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-               "config": {"model": "falcon-7b-shape", "layers": layers,
-                          "layers_of_config": FALCON_7B["num_hidden_layers"], "global_batch": batch,
-                          "seq_len": CONTEXT, "attention": "sdpa (reference default)", "cache": "DynamicCache",
-                          "timing": "generate(W+K) minus generate(W), CUDA events"},
+               "config": workload_config(layers, batch),
+               "notes": {"sampling": "greedy", "attention": "sdpa (reference default)", "cache": "DynamicCache",
+                         "timing": "generate(W+K) minus generate(W), CUDA events"},
                "e2e": e2e, "gpu_launches": 0, "clocks": sampler.summary()}
         print(json.dumps(out), flush=True)
     except Exception as e:  # noqa: BLE001
@@ -498,11 +640,14 @@ def main():
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration's (0: all)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--only", default="", choices=["", "decode", "prefill", "sample", "decode-attention"],
+    ap.add_argument("--only", default="", choices=["", "decode", "prefill", "sample", "decode-attention", "config", "linear"],
                     help="run one section only and print its numbers (for profilers)")
     ap.add_argument("--shape", default="7b", choices=sorted(SHAPES), help="model shape for --only decode / prefill")
     ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS, help="prompt length for --only prefill")
     ap.add_argument("--context", type=int, default=CONTEXT, help="cached tokens per sequence for --only decode")
+    ap.add_argument("--rows", type=int, default=8, help="rows of the activation for --only linear")
+    ap.add_argument("--decode-steps", type=int, default=0,
+                    help="decode steps of --only config (0: the number BASELINE gives for the shape)")
     ap.add_argument("--no-graphs", action="store_true", help="launch every kernel of a decode step itself")
     args = ap.parse_args()
     if args.gpus != 1:
@@ -512,6 +657,9 @@ def main():
     if (args.shape != "7b" or args.prefill_tokens != PREFILL_TOKENS or args.context != CONTEXT) and not args.only:
         print("--shape, --context and --prefill-tokens go with --only decode / --only prefill (the headline is measured on "
               "the 7B shape with a prefill of 2,048 tokens)")
+        return 2
+    if args.only == "config" and args.shape not in BASELINE_RUNS:
+        print("--only config runs BASELINE's configurations of the larger shapes: --shape 11b or --shape 40b")
         return 2
     if args.impl == "reference":
         return run_reference(args)

@@ -68,6 +68,7 @@ class Cache:
         self.max_slots = int(max_slots) if max_slots is not None else max(1, min(self.num_pages, 4096))
         self.slots = IdPool(self.max_slots, "sequence slot")
         self.records: Dict[int, SequenceRecord] = {}
+        self.epoch = 0   # counts opened and closed sequences: what was planned for an earlier epoch is stale
         self.state_entries: Dict[int, int] = {}
         self.state: Optional[torch.Tensor] = None
         widths = [(e, s.numel) for e, _, s in needs if s is not None and s.numel > 0]
@@ -83,6 +84,7 @@ class Cache:
     # ------------------------------------------------------------------ sequences
     def open(self) -> int:
         (slot,) = self.slots.take(1)
+        self.epoch += 1
         self.records[slot] = SequenceRecord(len(self.groups))
         if self.state_width:
             self.state[slot].zero_()
@@ -147,6 +149,7 @@ class Cache:
         for gi, g in enumerate(self.groups):
             g.pool.give_back([p for p in rec.pages[gi] if p >= 0])
         del self.records[slot]
+        self.epoch += 1
         self.slots.give_back([slot])
 
     def close_all(self) -> None:

@@ -104,17 +104,24 @@ attention_decode_tc_kernel(const __nv_bfloat16* __restrict__ fused, __nv_bfloat1
   const uint32_t bar_s = smem_u32(&bars[0]), bar_o = smem_u32(&bars[2]), bar_p = smem_u32(&bars[4]);
   const uint32_t bar_k = smem_u32(&bars[6]), bar_free = smem_u32(&bars[6 + STAGES_D]);
   const uint32_t bar_new = smem_u32(&bars[6 + 2 * STAGES_D]), bar_q = smem_u32(&bars[7 + 2 * STAGES_D]);
+  // Warps whose 32 rows all lie past the group's heads take no part in the softmax: they would spend a
+  // quarter or half of the exponential unit's time on rows that nobody reads. Their rows of P and O in
+  // tensor memory hold whatever was there; a row of the products depends on its own row of P only.
+  const int active_warps = (qpk + 31) / 32;
+  // The usual rotation (the halves of the head, or none) is done in registers, a thread per head; any
+  // other number of rotated pairs goes the general way through shared memory.
+  const bool in_registers = P == DD / 2 || P == 0;
   if (tid == 0) {
     for (int b = 0; b < 2; ++b) {
       mbar_init(bar_s + 8 * b, 1);
       mbar_init(bar_o + 8 * b, 1);
-      mbar_init(bar_p + 8 * b, SOFTMAX_T);
+      mbar_init(bar_p + 8 * b, uint32_t(active_warps) * 32);
     }
     for (int s = 0; s < STAGES_D; ++s) {
       mbar_init(bar_k + 8 * s, 1);
       mbar_init(bar_free + 8 * s, 1);
     }
-    mbar_init(bar_new, SOFTMAX_T);
+    mbar_init(bar_new, in_registers ? 1 : SOFTMAX_T);
     mbar_init(bar_q, SOFTMAX_T);
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
@@ -131,7 +138,65 @@ attention_decode_tc_kernel(const __nv_bfloat16* __restrict__ fused, __nv_bfloat1
   bool alive = true;
   auto softmax_sync = [] { asm volatile("bar.sync 1, %0;\n" ::"n"(SOFTMAX_T) : "memory"); };   // the 128 softmax threads
 
-  if (!copy_warp && !mma_warp) {
+  if (!copy_warp && !mma_warp && in_registers) {
+    // thread t = query head t: its 64 values come straight from the fused projection into registers,
+    // are rotated there (pairs (e, e + 32), the angles from the step's table) and go into the swizzled Q
+    // tile; rows past the group's heads are zero
+    uint4 raw[DD / 8];
+#pragma unroll
+    for (int c = 0; c < DD / 8; ++c)
+      raw[c] = tid < qpk ? *reinterpret_cast<const uint4*>(frow + size_t(tid) * DD + c * 8) : make_uint4(0, 0, 0, 0);
+    if (P > 0 && tid < qpk) {
+      const float* cosr = rope_cos + size_t(tok) * p.rot_pairs;
+      const float* sinr = rope_sin + size_t(tok) * p.rot_pairs;
+#pragma unroll
+      for (int c = 0; c < DD / 16; ++c) {
+        float a[8], b[8], cv[8], sv[8];
+        unpack_bf16x8(raw[c], a);
+        unpack_bf16x8(raw[c + DD / 16], b);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          cv[j] = __ldg(cosr + c * 8 + j);
+          sv[j] = __ldg(sinr + c * 8 + j);
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) rotate_pair(a[j], b[j], cv[j], sv[j], a[j], b[j]);
+        raw[c] = pack_bf16x8(a);
+        raw[c + DD / 16] = pack_bf16x8(b);
+      }
+    }
+#pragma unroll
+    for (int c = 0; c < DD / 8; ++c) *reinterpret_cast<uint4*>(q_tile + swz_blk<ROWS>(tid, c)) = raw[c];
+    proxy_fence_async();
+    mbar_arrive(bar_q);
+  } else if (mma_warp && in_registers && covers_new && p.write_cache) {
+    // the token's key (rotated) and value go to the cache from the block that covers the token's page:
+    // lanes 0..3 take the key's pairs of 16-byte chunks, lanes 4..11 the value's chunks; the copy thread
+    // asks for that page only after these writes (made visible to the TMA's proxy)
+    const __nv_bfloat16* krow = frow + size_t(qpk) * DD;
+    const size_t off = kv_offset(pages[kb_last], g, pos % KEYS, p.kv_heads, DD);
+    if (lane < DD / 16) {
+      float a[8], b[8];
+      unpack_bf16x8(*reinterpret_cast<const uint4*>(krow + lane * 8), a);
+      unpack_bf16x8(*reinterpret_cast<const uint4*>(krow + DD / 2 + lane * 8), b);
+      if (P > 0) {
+        const float* cosr = rope_cos + size_t(tok) * p.rot_pairs;
+        const float* sinr = rope_sin + size_t(tok) * p.rot_pairs;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) rotate_pair(a[j], b[j], __ldg(cosr + lane * 8 + j), __ldg(sinr + lane * 8 + j), a[j], b[j]);
+      }
+      *reinterpret_cast<uint4*>(k_pool + off + lane * 8) = pack_bf16x8(a);
+      *reinterpret_cast<uint4*>(k_pool + off + DD / 2 + lane * 8) = pack_bf16x8(b);
+    } else if (lane < DD / 16 + DD / 8) {
+      const int c = lane - DD / 16;
+      *reinterpret_cast<uint4*>(v_pool + off + c * 8) = *reinterpret_cast<const uint4*>(krow + DD + c * 8);
+    }
+    __threadfence();
+    asm volatile("fence.proxy.async;\n" ::: "memory");
+    __syncwarp();
+    if (lane == 0) mbar_arrive(bar_new);
+  }
+  if (!copy_warp && !mma_warp && !in_registers) {
     // stage the token's row: 16-byte copies of the group's queries, key, value; the rotation's cos / sin
     const uint4* src = reinterpret_cast<const uint4*>(frow);
     uint4* dst = reinterpret_cast<uint4*>(rowbuf);
@@ -225,7 +290,7 @@ attention_decode_tc_kernel(const __nv_bfloat16* __restrict__ fused, __nv_bfloat1
         st_next = (st_next + 1 == STAGES_D) ? 0 : st_next + 1;
       }
     }
-  } else {
+  } else if (warp < active_warps) {
     // ------------------------------------------------------------ softmax threads: row = query head
     const int row = tid;
     const uint32_t lane_base = tmem_base + (uint32_t(warp * 32) << 16);
@@ -343,18 +408,32 @@ attention_decode_tc_kernel(const __nv_bfloat16* __restrict__ fused, __nv_bfloat1
     for (int idx = tid; idx < my_rows * per_row; idx += BLOCK_T) {
       const int r = split + (idx / per_row) * n_splits;
       const int d0 = (idx % per_row) * 4;
+      // all blocks' values first (the loads from the other blocks' shared memory are in flight together),
+      // then the sums, always in the order of the blocks
+      float2 ml[8];
+      float4 vs[8];
+#pragma unroll
+      for (int s = 0; s < 8; ++s) {
+        if (s < n_splits) {
+          ml[s] = *reinterpret_cast<const float2*>(cluster.map_shared_rank(pml, s) + r * 2);
+          vs[s] = *reinterpret_cast<const float4*>(cluster.map_shared_rank(po, s) + size_t(r) * DD + d0);
+        } else {
+          ml[s] = make_float2(-INFINITY, 0.f);
+          vs[s] = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+      }
       float m = -INFINITY;
-      for (int s = 0; s < n_splits; ++s) m = fmaxf(m, cluster.map_shared_rank(pml, s)[r * 2]);
+#pragma unroll
+      for (int s = 0; s < 8; ++s) m = fmaxf(m, ml[s].x);
       float acc[4] = {0.f, 0.f, 0.f, 0.f};
       float l = 0.f;
-      for (int s = 0; s < n_splits; ++s) {   // always in the order of the blocks
-        const float* rml = cluster.map_shared_rank(pml, s);
-        const float* rpo = cluster.map_shared_rank(po, s);
-        const float ms = rml[r * 2];
-        const float wgt = (ms == -INFINITY) ? 0.f : exp2f((ms - m) * sl2);
-        l += rml[r * 2 + 1] * wgt;
-        const float4 v = *reinterpret_cast<const float4*>(rpo + size_t(r) * DD + d0);
-        acc[0] += v.x * wgt; acc[1] += v.y * wgt; acc[2] += v.z * wgt; acc[3] += v.w * wgt;
+#pragma unroll
+      for (int s = 0; s < 8; ++s) {
+        if (s < n_splits) {
+          const float wgt = (ml[s].x == -INFINITY) ? 0.f : exp2f((ml[s].x - m) * sl2);
+          l += ml[s].y * wgt;
+          acc[0] += vs[s].x * wgt; acc[1] += vs[s].y * wgt; acc[2] += vs[s].z * wgt; acc[3] += vs[s].w * wgt;
+        }
       }
       if (p.n_teams > 1) {
         float* dst = team_parts + ((size_t(seq) * p.kv_heads + g) * p.n_teams + team) * qpk * PART + size_t(r) * PART;

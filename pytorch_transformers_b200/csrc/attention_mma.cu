@@ -8,6 +8,7 @@
 // page), double-buffered through shared memory with cp.async into a 16-byte XOR swizzle that makes
 // the ldmatrix reads conflict-free. With n_splits > 1 the pages of a sequence are divided among
 // gridDim.z blocks which write unnormalised partial results; attention_mma_reduce joins them.
+#include <mutex>
 #include "mma_common.cuh"
 
 namespace {
@@ -306,12 +307,20 @@ int launch_mma(const void* q, const void* k_pool, const void* v_pool, void* out,
   const int qpk = p.heads / p.kv_heads;
   const int chunks = (qpk + p.hpk - 1) / p.hpk;
   const size_t smem = size_t(2) * 2 * KEYS * D * 2;  // two stages of (K, V)
-  static size_t configured = 48 * 1024;  // raised once per head size, never inside a stream capture's replay
-  if (smem > configured) {
-    if (cudaFuncSetAttribute(attention_mma_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) !=
-        cudaSuccess)
-      return PTB_ERR_LAUNCH;
-    configured = smem;
+  // the kernel's limit of dynamic shared memory is raised once per device and head size (a function
+  // attribute belongs to the device's context), by whichever thread comes first
+  {
+    static std::mutex mutex;
+    static bool configured[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return PTB_ERR_LAUNCH;
+    std::lock_guard<std::mutex> lock(mutex);
+    if (smem > 48 * 1024 && !configured[dev]) {
+      if (cudaFuncSetAttribute(attention_mma_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) !=
+          cudaSuccess)
+        return PTB_ERR_LAUNCH;
+      configured[dev] = true;
+    }
   }
   dim3 grid(n_tiles, p.kv_heads * chunks, p.n_splits);
   const bool partial = p.n_splits > 1;
@@ -431,7 +440,10 @@ PTB_API int ptb_attention_mma_fixed_scratch(const void* q, const void* k_pool, c
                                             int head_dim, int hpk, int tokens_per_tile, int n_splits, int warps,
                                             float scale, int window, cudaStream_t stream) {
   if (n_tiles <= 0) return PTB_OK;
-  if (heads <= 0 || kv_heads <= 0 || heads % kv_heads != 0 || hpk < 1 || warps < 1 || n_splits < 1)
+  // every size is checked before the workspace is counted, so that the count cannot overflow
+  if (heads <= 0 || kv_heads <= 0 || heads % kv_heads != 0 || hpk < 1 || warps < 1 || warps > 8 || n_splits < 1 ||
+      n_splits > 65535 || tokens_per_tile < 1 || hpk * tokens_per_tile > warps * 16 ||
+      !ptb_attention_mma_supports(head_dim))
     return PTB_ERR_SIZE;
   const long long need =
       ptb_attention_mma_scratch_floats(n_tiles, heads, kv_heads, hpk, n_splits, warps, head_dim);

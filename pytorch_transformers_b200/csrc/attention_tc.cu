@@ -27,9 +27,7 @@
 // seen as rows of D values, 128-byte swizzle) into a four-stage ring: exactly the canonical layout that
 // the matrix descriptors name (K-major for Q and K; MN-major for V); a stage's mbarrier counts the
 // bytes, and tcgen05.commit after the O += P V that read a stage gives it back to the copy thread. The
-// softmax threads neither copy nor wait for copies (measured with clock stamps in the loop: of about
-// 3,000 cycles per page a softmax thread spent 900 on issuing its share of the copies and on waiting
-// for them, when the pages still came by cp.async). Completion of the matrix instructions is signalled
+// softmax threads neither copy nor wait for copies. Completion of the matrix instructions is signalled
 // through tcgen05.commit on mbarriers. Every wait on a barrier is bounded: if it runs out, a flag in
 // global memory is raised and the block carries on to its end (tensor memory is freed on every path,
 // copies in flight are waited for), so a fault in the pipeline shows as an error, never as a hang.
@@ -39,24 +37,12 @@
 // or two apart, which is why "P written" has a barrier per S buffer and "O updated" one each for even and
 // odd pages: an arrival for a later page must not count for page i.
 //
-// Measured on this kernel at 2,048 and 8,192 tokens (71 heads, one K/V head): one, two and four threads
-// per row took 165, 159 and 189 us at 2,048 tokens while the softmax threads still copied the pages and
-// wrote P to shared memory; now one thread per row is 2 to 3 % ahead of two (136 against 140 us). Clock
-// stamps in the loop (cycles per page, of about 2,500): the exponentials and the packing to bfloat16 750
-// (two blocks share the SM's 16 transcendental lanes: that is their full rate), the wait for S 500, the
-// rescaling test 350, mask and maximum 280, loads and stores of tensor memory 330. Rescaling O only when a
-// row's maximum has grown by more than 2^8 (RESCALE_LOG2) brought 136 to 121 us and 1,229 to 1,060 us at
-// 8,192 tokens (575 TFLOP/s of causal flops); a third S buffer with P in place of S (S two pages ahead:
-// the softmax no longer waits for a product that could only be issued when the slowest warp had
-// finished the page before) 121 to 118 us and 1,060 to 1,028 us; a cap of 128 registers (small spills)
-// cost 10 %;
-// a second P tile in shared memory (softmax of page i + 1 no longer waits for O += P V of page i) took
-// 7 % longer, measured twice; P in tensor memory instead (no shared-memory stores, no proxy fence, the
-// same freedom) is 2 to 5 % faster than P in shared memory. A block is one chain of dependent steps per page
-// (about 1.5 us: tensor-memory load, maximum across the row's threads, exponentials, stores, fence,
-// arrival, issue, matrix instructions, completion), and an SM holds two such chains; the exponential
-// unit is busy a third of the time, the tensor pipe a sixth. More chains per SM (several heads of a
-// K/V group in one block, sharing the page copies) is the open step.
+// Decisions that rest on measurements (2,048 tokens, 71 heads on one K/V head; the profile of this kernel
+// has the series): one softmax thread per row (2 to 3 % ahead of two); O is rescaled only when a row's
+// maximum has grown by more than 2^8 (136 -> 121 us); three S buffers with P in place of S (121 -> 118 us);
+// P in tensor memory rather than in shared memory (2 to 5 %); no cap on registers (a cap of 128 cost
+// 10 %). A block is one chain of dependent steps per page (about 1.5 us) and an SM holds two such chains:
+// the exponential unit is busy a third of the time, the tensor pipe a sixth.
 #include "mma_common.cuh"
 #include "tc_common.cuh"
 
@@ -124,7 +110,10 @@ attention_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
   const bool copy_warp = warp == SOFTMAX_THREADS / 32 + 1;
   const int row = tid & (TQ - 1);        // query row of a softmax thread (= its tensor-memory lane)
   const int part = (tid >> 7) % TPR;     // which COLS of the 64 columns of a page it handles
-  const int tile = blockIdx.x, h = blockIdx.y;
+  // heads are the fast index of the grid: the blocks of one tile start together (they read the same
+  // pages), and tiles come in the order of the list, which the caller sorts by falling key count so that
+  // the longest chains start first and the short ones fill the end
+  const int tile = blockIdx.y, h = blockIdx.x;
   const int qpk = p.heads / p.kv_heads;
   const int g = h / qpk;
   const int seq = tile_seq[tile], q0 = tile_q0[tile];
@@ -388,7 +377,7 @@ int launch_tc(const void* q, const void* k_pool, const void* v_pool, int pool_pa
       return PTB_ERR_LAUNCH;
     configured = true;
   }
-  dim3 grid(n_tiles, p.heads);
+  dim3 grid(p.heads, n_tiles);
   attention_tc_kernel<D, BIAS><<<grid, BLOCK_THREADS, smem, stream>>>(
       (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, (__nv_bfloat16*)out, sb,
       tile_seq, tile_q0, p, *km, *vm, error_flag);
@@ -407,7 +396,7 @@ PTB_API int ptb_attention_tc(const void* q, const void* k_pool, const void* v_po
                              int kv_heads, int head_dim, float scale, int* error_flag, cudaStream_t stream) {
   if (n_tiles <= 0) return PTB_OK;
   if (pool_pages <= 0 || (reinterpret_cast<uintptr_t>(k_pool) | reinterpret_cast<uintptr_t>(v_pool)) & 15) return PTB_ERR_ALIGN;
-  if ((head_dim != 64 && head_dim != 128) || heads <= 0 || kv_heads <= 0 || heads % kv_heads != 0 || heads > 65535 ||
+  if ((head_dim != 64 && head_dim != 128) || heads <= 0 || kv_heads <= 0 || heads % kv_heads != 0 || n_tiles > 65535 ||
       error_flag == nullptr)
     return PTB_ERR_SIZE;
   TcParams p;

@@ -19,6 +19,32 @@ enum {
   PTB_ERR_ALIGN = 4,      // a pointer or a row size that is not aligned as the kernel needs
 };
 
+// Activations, by the codes that every entry point with an `act` argument takes. This is the one table:
+// a new activation is an entry here, a case in apply_activation and a name in kernels.ACTIVATIONS.
+enum { PTB_ACT_NONE = 0, PTB_ACT_GELU_ERF = 1, PTB_ACT_GELU_TANH = 2, PTB_ACT_RELU = 3, PTB_ACT_COUNT = 4 };
+inline bool activation_known(int act) { return act >= 0 && act < PTB_ACT_COUNT; }
+__device__ __forceinline__ float apply_activation(float v, int act) {
+  switch (act) {
+    case PTB_ACT_GELU_ERF: return 0.5f * v * (1.0f + erff(v * 0.70710678118654752440f));
+    case PTB_ACT_GELU_TANH: return 0.5f * v * (1.0f + tanhf(0.79788456080286535588f * (v + 0.044715f * v * v * v)));
+    case PTB_ACT_RELU: return fmaxf(v, 0.f);
+    default: return v;
+  }
+}
+
+// multiprocessors of the current device (asked once per process and device)
+inline int sm_count() {
+  static int sms[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  if (sms[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    sms[dev] = n;
+  }
+  return sms[dev];
+}
+
 // tokens of a cache page; a sequence holds whole pages
 constexpr int PTB_PAGE = 64;
 

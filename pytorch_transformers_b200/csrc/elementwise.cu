@@ -3,10 +3,10 @@
 // activations are float32 or bfloat16 (template T); gains, biases are float32 vectors.
 #include "common.cuh"
 
-// blocks of a grid-stride launch: enough to cover `total`, at most 16 per SM of a 148-SM device
+// blocks of a grid-stride launch: enough to cover `total`, at most 16 per SM
 static int grid_for(size_t total, int threads) {
-  const size_t want = (total + threads - 1) / threads;
-  return int(want < size_t(148 * 16) ? want : size_t(148 * 16));
+  const size_t want = (total + threads - 1) / threads, most = size_t(sm_count()) * 16;
+  return int(want < most ? want : most);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -297,15 +297,7 @@ PTB_API int ptb_norm(int dtype, const void* x, const void* addend, void* sum_out
 }
 
 // ------------------------------------------------------------------------------------------------
-// Activations. 0 none, 1 GELU (erf form), 2 GELU (tanh form), 3 ReLU.
-__device__ __forceinline__ float activate(float v, int act) {
-  switch (act) {
-    case 1: return 0.5f * v * (1.0f + erff(v * 0.70710678118654752440f));
-    case 2: return 0.5f * v * (1.0f + tanhf(0.79788456080286535588f * (v + 0.044715f * v * v * v)));
-    case 3: return fmaxf(v, 0.f);
-    default: return v;
-  }
-}
+// Bias and activation (codes and formulas: apply_activation in common.cuh).
 
 // y[r, c] = act(y[r, c] + bias[c]) in place (bias may be null).
 template <typename T>
@@ -314,7 +306,7 @@ __global__ void bias_act_kernel(T* __restrict__ y, const float* __restrict__ bia
   for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
     float v = to_f(y[i]);
     if (bias) v += bias[i % width];
-    y[i] = from_f<T>(activate(v, act));
+    y[i] = from_f<T>(apply_activation(v, act));
   }
 }
 
@@ -337,10 +329,11 @@ __device__ __forceinline__ float gelu_erf_for_bf16(float v) {
 
 // the same, eight bfloat16 values per 16-byte word (width a multiple of 8, 16-byte aligned rows); a
 // thread takes two words per step, both loads in flight before the arithmetic of either. The
-// activation and the presence of a bias are compile-time: the loop holds no test and, without a
-// bias, no division for the column.
-template <int ACT, bool BIAS>
-__device__ __forceinline__ uint4 bias_act_word(uint4 word, const float* __restrict__ bias, size_t i, unsigned words_per_row) {
+// presence of a bias is compile-time (without one the loop holds no division for the column), and
+// so is the erf GELU with its cheaper form (FAST_GELU); every other activation goes by its code.
+template <bool FAST_GELU, bool BIAS>
+__device__ __forceinline__ uint4 bias_act_word(uint4 word, const float* __restrict__ bias, size_t i, unsigned words_per_row,
+                                               int act) {
   float f[8];
   unpack_bf16x8(word, f);
   if (BIAS) {
@@ -350,39 +343,37 @@ __device__ __forceinline__ uint4 bias_act_word(uint4 word, const float* __restri
     for (int e = 0; e < 8; ++e) f[e] += b[e];
   }
 #pragma unroll
-  for (int e = 0; e < 8; ++e) f[e] = (ACT == 1) ? gelu_erf_for_bf16(f[e]) : activate(f[e], ACT);
+  for (int e = 0; e < 8; ++e) f[e] = FAST_GELU ? gelu_erf_for_bf16(f[e]) : apply_activation(f[e], act);
   return pack_bf16x8(f);
 }
-template <int ACT, bool BIAS>
+template <bool FAST_GELU, bool BIAS>
 __global__ void __launch_bounds__(256)
-bias_act_bf16x8_kernel(uint4* __restrict__ y, const float* __restrict__ bias, size_t total8, unsigned words_per_row) {
+bias_act_bf16x8_kernel(uint4* __restrict__ y, const float* __restrict__ bias, size_t total8, unsigned words_per_row,
+                       int act) {
   const size_t stride = size_t(gridDim.x) * blockDim.x;
   size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
   for (; i + stride < total8; i += 2 * stride) {
     const uint4 a = y[i], b = y[i + stride];
-    y[i] = bias_act_word<ACT, BIAS>(a, bias, i, words_per_row);
-    y[i + stride] = bias_act_word<ACT, BIAS>(b, bias, i + stride, words_per_row);
+    y[i] = bias_act_word<FAST_GELU, BIAS>(a, bias, i, words_per_row, act);
+    y[i + stride] = bias_act_word<FAST_GELU, BIAS>(b, bias, i + stride, words_per_row, act);
   }
-  if (i < total8) y[i] = bias_act_word<ACT, BIAS>(y[i], bias, i, words_per_row);
+  if (i < total8) y[i] = bias_act_word<FAST_GELU, BIAS>(y[i], bias, i, words_per_row, act);
 }
-template <int ACT>
-void launch_bias_act_x8(void* y, const float* bias, size_t total8, int width, cudaStream_t stream) {
+template <bool FAST_GELU>
+void launch_bias_act_x8(void* y, const float* bias, size_t total8, int width, int act, cudaStream_t stream) {
   const int grid = grid_for(total8, 256);
-  if (bias) bias_act_bf16x8_kernel<ACT, true><<<grid, 256, 0, stream>>>((uint4*)y, bias, total8, unsigned(width / 8));
-  else bias_act_bf16x8_kernel<ACT, false><<<grid, 256, 0, stream>>>((uint4*)y, bias, total8, unsigned(width / 8));
+  const unsigned words = unsigned(width / 8);
+  if (bias) bias_act_bf16x8_kernel<FAST_GELU, true><<<grid, 256, 0, stream>>>((uint4*)y, bias, total8, words, act);
+  else bias_act_bf16x8_kernel<FAST_GELU, false><<<grid, 256, 0, stream>>>((uint4*)y, bias, total8, words, act);
 }
 
 PTB_API int ptb_bias_act(int dtype, void* y, const float* bias, int rows, int width, int act, cudaStream_t stream) {
   const size_t total = size_t(rows) * width;
   if (total == 0) return PTB_OK;
-  if (act < 0 || act > 3) return PTB_ERR_SIZE;
+  if (!activation_known(act)) return PTB_ERR_SIZE;
   if (dtype == PTB_BF16 && width % 8 == 0 && aligned16(y) && (!bias || aligned16(bias))) {
-    switch (act) {
-      case 0: launch_bias_act_x8<0>(y, bias, total / 8, width, stream); break;
-      case 1: launch_bias_act_x8<1>(y, bias, total / 8, width, stream); break;
-      case 2: launch_bias_act_x8<2>(y, bias, total / 8, width, stream); break;
-      default: launch_bias_act_x8<3>(y, bias, total / 8, width, stream); break;
-    }
+    if (act == PTB_ACT_GELU_ERF) launch_bias_act_x8<true>(y, bias, total / 8, width, act, stream);
+    else launch_bias_act_x8<false>(y, bias, total / 8, width, act, stream);
     return launch_status();
   }
   const int threads = 256;

@@ -123,7 +123,8 @@ PTB_API int ptb_fill_normal(int dtype, void* out, unsigned long long count, unsi
   const size_t pairs = (size_t(count) + 2) / 2;
   const int threads = 256;
   const size_t want = (pairs + threads - 1) / threads;
-  const int blocks = int(want < size_t(148 * 32) ? want : size_t(148 * 32));
+  const size_t most = size_t(sm_count()) * 32;
+  const int blocks = int(want < most ? want : most);
   if (dtype == PTB_F32)
     fill_normal_kernel<float><<<blocks, threads, 0, stream>>>((float*)out, count, first, key, std, offset,
                                                               round_bf16_first);

@@ -10,14 +10,6 @@ namespace {
 constexpr int BM = 64, BN = 64, BK = 16;  // tile of the output and step along K
 constexpr int TM = 4, TN = 4;             // outputs per thread; 256 threads
 
-__device__ __forceinline__ float activate32(float v, int act) {
-  switch (act) {
-    case 1: return 0.5f * v * (1.0f + erff(v * 0.70710678118654752440f));
-    case 2: return 0.5f * v * (1.0f + tanhf(0.79788456080286535588f * (v + 0.044715f * v * v * v)));
-    case 3: return fmaxf(v, 0.f);
-    default: return v;
-  }
-}
 
 __global__ void __launch_bounds__(256) linear_f32_kernel(const float* __restrict__ x, const float* __restrict__ w,
                                                          const float* __restrict__ bias, float* __restrict__ y, int M,
@@ -80,7 +72,7 @@ __global__ void __launch_bounds__(256) linear_f32_kernel(const float* __restrict
       if (gn >= N) continue;
       float v = acc[i][j];
       if (bias) v += bias[gn];
-      y[size_t(gm) * N + gn] = activate32(v, act);
+      y[size_t(gm) * N + gn] = apply_activation(v, act);
     }
   }
 }
@@ -90,7 +82,7 @@ __global__ void __launch_bounds__(256) linear_f32_kernel(const float* __restrict
 PTB_API int ptb_linear_f32(const float* x, const float* w, const float* bias, float* y, int M, int N, int K, int act,
                            cudaStream_t stream) {
   if (M <= 0 || N <= 0) return PTB_OK;
-  if (K <= 0 || act < 0 || act > 3) return PTB_ERR_SIZE;
+  if (K <= 0 || !activation_known(act)) return PTB_ERR_SIZE;
   dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
   if (grid.y > 65535) return PTB_ERR_SIZE;
   linear_f32_kernel<<<grid, 256, 0, stream>>>(x, w, bias, y, M, N, K, act);

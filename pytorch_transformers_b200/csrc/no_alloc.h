@@ -2,10 +2,9 @@
 // pytorch-transformers leaves all memory management to PyTorch); it exists for callers of this
 // library's C interface that must not, or cannot, obtain device memory at call time:
 //
-//   * code that runs while a CUDA stream is being captured into a graph, where cudaMalloc and
-//     cudaFree are not allowed and an allocator that falls back to them would break the capture;
 //   * hosts that embed the library through its C symbols without PyTorch's caching allocator and
-//     run with a fixed device-memory budget that was handed out completely at start-up;
+//     run with a fixed device-memory budget that was handed out completely at start-up, so that a
+//     cudaMalloc in the middle of serving would fail or evict somebody;
 //   * latency-critical loops that may not take the driver's allocation lock (a cudaMalloc can stall
 //     behind another thread's context-wide operation for milliseconds).
 //
@@ -18,8 +17,11 @@
 //     library carries these 16 MiB until the process exits, used or not. A call whose partial results
 //     need more (see ptb_attention_mma_scratch_floats) is refused with PTB_ERR_FIXED_SCRATCH_TOO_SMALL
 //     and launches nothing; ptb_attention_mma_fixed_scratch_strerror gives the text.
-//   * The first call on a device looks up the array's device address (cudaGetSymbolAddress, with that
-//     device current) and remembers it per device. Make that first call outside any stream capture.
+//   * Set-up happens inside the first call on a device: it looks up the array's device address
+//     (cudaGetSymbolAddress, with that device current) and remembers it per device, and the first
+//     call on a device for a head size (64, 128) raises the kernel's shared-memory limit
+//     (cudaFuncSetAttribute). Both are guarded by mutexes. Make these first calls, one per device
+//     and head size, before any stream capture.
 //   * All calls on a device share the one array and find the previous call's contents in it. The
 //     kernels write every partial result they later read, so nothing needs clearing; but two calls
 //     whose kernels may run at the same time on one GPU (different streams, or graphs replayed

@@ -27,14 +27,6 @@ __device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1
   asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
                : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
-__device__ __forceinline__ float act_f(float v, int act) {
-  switch (act) {
-    case 1: return 0.5f * v * (1.0f + erff(v * 0.70710678118654752440f));
-    case 2: return 0.5f * v * (1.0f + tanhf(0.79788456080286535588f * (v + 0.044715f * v * v * v)));
-    case 3: return fmaxf(v, 0.f);
-    default: return v;
-  }
-}
 
 // steps c0 = first, first + stride, ... below `limit`; a step has the UNROLL chunks c0, c0 + apart,
 // c0 + 2 apart, ... in flight together (those past the last chunk are skipped)
@@ -176,7 +168,7 @@ skinny_linear_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* _
       for (int wi = 0; wi < WARPS; ++wi) v += red[wi][r][m];
     }
     if (bias) v += bias[n];
-    v = act_f(v, act);
+    v = apply_activation(v, act);
     if (add) v += __bfloat162float(add[size_t(m) * N + n]);
     if (y_f32) y_f32[size_t(m) * N + n] = v;
     else y_bf16[size_t(m) * N + n] = __float2bfloat16_rn(v);
@@ -186,20 +178,12 @@ skinny_linear_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* _
 // Blocks per tile of weight rows, each with a share of K. The blocks of a launch are all resident at
 // once and share the SMs' memory bandwidth, so the launch takes as long as the SM with the most blocks:
 // 512 tiles on 148 SMs are 3.46 a piece, some SMs get 4, and the launch takes 16 % longer than its share
-// of the bandwidth. Dividing K by 2, 3 or 4 changes the count to one that divides better (1,024 blocks:
-// 6.92 a piece, 7 at most: 1 %). Taken when it saves more than 3 %, every block keeps at least 16 full
-// rounds of its warps, and the caller has given scratch memory and tickets. Blocks with a short K are
-// slower per byte (measured: Falcon-11B's down projection, K = 16384, in 4 shares 30.8 us against 24.6
-// us undivided, although the shares divide evenly over the SMs; Falcon-40B's, K = 32768, in 2 shares 95
-// against 111 us).
+// of the bandwidth. Dividing K by 2, 3 or 4 changes the count to one that divides better. Taken when it
+// saves more than 3 %, every block keeps at least 16 full rounds of its warps (blocks with a short K are
+// slower per byte: K = 16384 in 4 shares 30.8 us against 24.6 us undivided; K = 32768 in 2 shares 95
+// against 111 us), and the caller has given scratch memory and tickets.
 int k_split(int tiles, int chunks, int round) {
-  static int sms = 0;
-  if (sms == 0) {
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess ||
-        sms <= 0)
-      sms = 148;
-  }
+  const int sms = sm_count();
   auto excess = [&](int blocks) { return double((blocks + sms - 1) / sms) * sms / blocks; };
   int best = 1;
   double best_excess = excess(tiles);
@@ -235,11 +219,11 @@ int launch_skinny(const void* x, const void* w, const float* bias, const void* a
 int dispatch_skinny(const void* x, const void* w, const float* bias, const void* add, void* y_bf16, float* y_f32, int M,
                     int N, int K, int act, float* scratch, size_t scratch_floats, int* tickets, int n_tickets,
                     size_t* need_floats, cudaStream_t stream) {
-  // Tile height and chunks in flight per warp, from a sweep over the projections of Falcon-7B, 11B and
-  // 40B (each matrix alone, from HBM): wide matrices (many rows, short K) want 32 rows per block and
-  // four chunks in flight at up to 8 activation rows, 16 rows and two chunks at up to 16; the others
-  // 16 rows and four chunks.
-  const bool wide = N >= 16 * 148 * 4;
+  // Tile height and chunks in flight per warp, from a sweep over matrices of 4,096 to 65,024 rows (each
+  // alone, from HBM): matrices with four tiles or more per SM (many rows, short K) want 32 rows per
+  // block and four chunks in flight at up to 8 activation rows, 16 rows and two chunks at up to 16;
+  // the others 16 rows and four chunks.
+  const bool wide = N >= 16 * sm_count() * 4;   // four 16-row tiles or more per SM
 #define PTB_SKINNY(MT, NT, U) \
   return launch_skinny<MT, NT, U>(x, w, bias, add, y_bf16, y_f32, M, N, K, act, scratch, scratch_floats, tickets, \
                                   n_tickets, need_floats, stream)
@@ -272,7 +256,7 @@ PTB_API int ptb_skinny_linear(const void* x, const void* w, const float* bias, c
                               float* y_f32, int M, int N, int K, int act, float* scratch, size_t scratch_floats,
                               int* tickets, int n_tickets, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return PTB_OK;
-  if (M > 32 || K <= 0 || K % KC != 0 || act < 0 || act > 3) return PTB_ERR_SIZE;
+  if (M > 32 || K <= 0 || K % KC != 0 || !activation_known(act)) return PTB_ERR_SIZE;
   if ((y_bf16 == nullptr) == (y_f32 == nullptr)) return PTB_ERR_SIZE;
   if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w)) & 15) return PTB_ERR_ALIGN;
   return dispatch_skinny(x, w, bias, add, y_bf16, y_f32, M, N, K, act, scratch, scratch_floats, tickets, n_tickets,

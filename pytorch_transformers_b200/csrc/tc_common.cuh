@@ -46,9 +46,10 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       : "=r"(ok) : "r"(bar), "r"(parity), "r"(WAIT_SUSPEND_NS) : "memory");
   return ok != 0;
 }
-// bounded wait: false (and the error flag raised) if the barrier did not complete in time
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* error_flag, int code) {
-  for (uint32_t i = 0; i < WAIT_LIMIT; ++i)
+// bounded wait: false (and the error flag raised) if the barrier did not complete within `limit` tries
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* error_flag, int code,
+                                          uint32_t limit = WAIT_LIMIT) {
+  for (uint32_t i = 0; i < limit; ++i)
     if (mbar_try_wait(bar, parity)) return true;
   atomicExch(error_flag, code);
   return false;

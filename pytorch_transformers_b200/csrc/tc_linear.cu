@@ -42,14 +42,6 @@ constexpr int W_STAGE_BYTES = WROWS_TC * KC_TC * 2;   // 16 KB
 constexpr int MAX_STAGES_TC = 4;
 constexpr int MAX_TOKENS_TC = 128;
 
-__device__ __forceinline__ float act_tc(float v, int act) {
-  switch (act) {
-    case 1: return 0.5f * v * (1.0f + erff(v * 0.70710678118654752440f));
-    case 2: return 0.5f * v * (1.0f + tanhf(0.79788456080286535588f * (v + 0.044715f * v * v * v)));
-    case 3: return fmaxf(v, 0.f);
-    default: return v;
-  }
-}
 __device__ __forceinline__ uint32_t cluster_rank() {
   uint32_t r;
   asm volatile("mov.u32 %0, %%cluster_ctarank;\n" : "=r"(r));
@@ -234,7 +226,7 @@ tc_linear_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constan
       for (int j = 0; j < 8; ++j) {
         const int t = t0 + g * 8 + j;
         if (t >= p.M) continue;
-        float o = act_tc(v[j] + b, p.act);
+        float o = apply_activation(v[j] + b, p.act);
         const size_t at = size_t(t) * p.N + n;
         if (add) o += __bfloat162float(add[at]);
         if (y_f32) y_f32[at] = o;
@@ -309,7 +301,7 @@ PTB_API int ptb_tc_linear_k_multiple() { return 8; }
 PTB_API int ptb_tc_linear(const void* x, const void* w, const float* bias, const void* add, void* y_bf16, float* y_f32,
                           int M, int N, int K, int act, int sms, int* error_flag, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return PTB_OK;
-  if (M > MAX_TOKENS_TC || K <= 0 || K % 8 != 0 || act < 0 || act > 3 || sms < 1 || error_flag == nullptr)
+  if (M > MAX_TOKENS_TC || K <= 0 || K % 8 != 0 || !activation_known(act) || sms < 1 || error_flag == nullptr)
     return PTB_ERR_SIZE;
   if ((y_bf16 == nullptr) == (y_f32 == nullptr)) return PTB_ERR_SIZE;
   if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w)) & 15) return PTB_ERR_ALIGN;

@@ -7,14 +7,21 @@ through ``StepBatch`` (csrc/common.cuh). The reference pads prompts on the left 
 ``attention_mask``, ``position_ids`` and ``cache_position`` tensors instead
 (src/transformers/generation/utils.py:349-481); here positions are arithmetic on lengths.
 
-The layout of the buffer depends only on the counts (tokens, sequences, wanted rows, tiles,
-width of the page tables). A step of single tokens whose counts equal an earlier one's can
-therefore reuse that step's device buffer: that is what lets a decode step be replayed as a
-CUDA graph (``static`` below).
+The step itself knows counts, positions and page tables only. What a kind of mixer needs
+beyond that for its kernels (lists of tiles, say) comes from the mixer's *planner*: an object
+with a ``plan_key`` and ``plan(ctx) -> StepPlan`` that the model collects from its parts. A
+plan's integer arrays travel in the same buffer and copy as the step's own, and its ``facts``
+(numbers that shape launches) are part of the layout.
+
+The layout of the buffer depends only on the counts (tokens, sequences, wanted rows, width of
+the page tables, and the plans' sizes and facts). A step of single tokens whose layout equals
+an earlier one's can therefore reuse that step's device buffer: that is what lets a decode
+step be replayed as a CUDA graph (``static`` below).
 """
 from __future__ import annotations
 
-from typing import Dict, List, Optional, Sequence, Tuple
+import dataclasses
+from typing import Any, Dict, List, Optional, Sequence, Tuple
 
 import numpy as np
 import torch
@@ -66,16 +73,28 @@ class StepError(ValueError):
     """A step that cannot be run as asked (bad slot, empty token list, token id out of range...)."""
 
 
+@dataclasses.dataclass
+class StepPlan:
+    """What one planner adds to a step: ``arrays`` (name -> integer array, copied to the device with the
+    step's own arrays and found in ``dev`` afterwards) and ``facts`` (name -> int, numbers that shape the
+    kernels' launches and therefore belong to the step's layout)."""
+    arrays: Dict[str, Any] = dataclasses.field(default_factory=dict)
+    facts: Dict[str, int] = dataclasses.field(default_factory=dict)
+    dev: Dict[str, torch.Tensor] = dataclasses.field(default_factory=dict)
+
+
 class StepContext:
     """Everything a part may read about the running step.
 
     ``slots``, ``new``, ``past``: per sequence, on the host. ``dev[name]``: int32 device arrays
-    (tokens, tok_seq, tok_pos, seq_start, seq_new, seq_past, slots, logits_at, the tile lists and
-    one page table per storage group). ``batch_c[group]``: the StepBatch struct for the kernels.
+    (tokens, tok_seq, tok_pos, seq_start, seq_new, seq_past, slots, logits_at and one page table
+    per storage group). ``batch_c[group]``: the StepBatch struct for the kernels.
+    ``plans[plan_key]``: the StepPlan of each planner the step was built with.
     """
 
     def __init__(self, cache: Cache, slots: Sequence[int], token_lists: Sequence[Sequence[int]], vocab_size: int,
-                 want: Sequence[Sequence[int]], tile_rows: int, page_bucket: int = 0, defer: bool = False):
+                 want: Sequence[Sequence[int]], planners: Sequence[Any] = (), page_bucket: int = 0,
+                 defer: bool = False):
         if len(slots) != len(token_lists) or len(slots) != len(want):
             raise StepError("slots, token lists and wanted positions must have one item per sequence")
         if len(slots) == 0:
@@ -113,15 +132,12 @@ class StepContext:
                 logits_at.append(int(seq_start[b]) + int(i))
         self.n_wanted = len(logits_at)
 
-        # tiles of the general attention kernel: (sequence, first row) every `tile_rows` rows
-        tile_seq, tile_q0 = self._tiles(tile_rows)
-        self.n_tiles = len(tile_seq)
-        # tiles of the tensor-core attention kernel: one token per tile when every sequence brings
-        # a single token (all heads of a K/V group share the tile), else 16, 64 or 128 tokens
-        longest = max(self.new)
-        self.mma_tokens = 1 if longest == 1 else (16 if longest <= 16 else (64 if longest <= 64 else 128))
-        mtile_seq, mtile_q0 = self._tiles(self.mma_tokens)
-        self.n_mma_tiles = len(mtile_seq)
+        # what the mixers' planners add (parts that share a plan_key share one plan); they see the
+        # counts and positions above, and run before anything is reserved
+        self.plans: Dict[str, StepPlan] = {}
+        for planner in planners:
+            if planner.plan_key not in self.plans:
+                self.plans[planner.plan_key] = planner.plan(self)
 
         # page tables, one per storage group, padded to the longest (or to a whole bucket)
         cache.reserve_all(list(zip(self.slots, self.new)))
@@ -141,11 +157,12 @@ class StepContext:
 
         parts = {"tokens": tokens, "tok_seq": tok_seq, "tok_pos": tok_pos, "seq_start": seq_start[:-1],
                  "seq_new": np.asarray(self.new), "seq_past": np.asarray(self.past),
-                 "slots": np.asarray(self.slots), "logits_at": np.asarray(logits_at, dtype=np.int64),
-                 "tile_seq": np.asarray(tile_seq), "tile_q0": np.asarray(tile_q0),
-                 "mtile_seq": np.asarray(mtile_seq), "mtile_q0": np.asarray(mtile_q0)}
+                 "slots": np.asarray(self.slots), "logits_at": np.asarray(logits_at, dtype=np.int64)}
         for gi, tab in enumerate(tables):
             parts[f"pages{gi}"] = tab.reshape(-1)
+        for key, plan in self.plans.items():
+            for name, arr in plan.arrays.items():
+                parts[f"plan.{key}.{name}"] = np.asarray(arr)
         offsets, total = {}, 0
         for name, arr in parts.items():
             offsets[name] = (total, arr.size)
@@ -155,8 +172,10 @@ class StepContext:
             o, n = offsets[name]
             packed[o:o + n] = arr
         self.host = {name: packed[o:o + n] for name, (o, n) in offsets.items()}
-        self.layout_key = (self.n_tokens, self.n_seqs, self.n_wanted, self.n_tiles, self.n_mma_tiles,
-                           self.mma_tokens, self.table_widths)
+        self.layout_key = (self.n_tokens, self.n_seqs, self.n_wanted, self.table_widths,
+                           tuple((key, tuple(sorted(plan.facts.items())),
+                                  tuple((n, np.asarray(a).size) for n, a in plan.arrays.items()))
+                                 for key, plan in sorted(self.plans.items())))
         self.h2d_bytes = packed.nbytes
         self.packed_size = packed.size
         self._packed, self._offsets, self._tables = packed, offsets, tables
@@ -164,6 +183,17 @@ class StepContext:
         self.batch_c: List[K.StepBatchC] = []
         if not defer:
             self.bind()
+
+    def set_tokens(self, token_lists: Sequence[Sequence[int]], vocab_size: int) -> None:
+        """Put other token ids into a step that was built ahead of time with placeholders (same counts);
+        before ``bind``."""
+        if [len(t) for t in token_lists] != self.new:
+            raise StepError("the tokens do not fit the step that was prepared")
+        tokens = np.fromiter((t for lst in token_lists for t in lst), dtype=np.int64, count=self.n_tokens)
+        if tokens.min() < 0 or tokens.max() >= vocab_size:
+            bad = int(tokens[(tokens < 0) | (tokens >= vocab_size)][0])
+            raise StepError(f"token id {bad} is outside the vocabulary 0..{vocab_size - 1}")
+        self.host["tokens"][:] = tokens
 
     def bind(self, static: Optional[torch.Tensor] = None) -> None:
         """Copy the index arrays to the device: into a new buffer, or into ``static`` (a buffer of
@@ -173,6 +203,8 @@ class StepContext:
             raise StepError("the static step buffer does not fit this step's layout")
         dev = _RING.stage(packed, self.cache.device, into=static)
         self.dev = {name: dev[o:o + n] for name, (o, n) in offsets.items()}
+        for key, plan in self.plans.items():
+            plan.dev = {name: self.dev[f"plan.{key}.{name}"] for name in plan.arrays}
         self.packed_dev = dev
         self.batch_c = []
         for gi, tab in enumerate(tables):
@@ -201,7 +233,15 @@ class StepContext:
             self._rope[key] = K.rope_table(self.dev["tok_pos"], inv_freq)
         return self._rope[key]
 
-    def _tiles(self, rows: int):
+    def plan(self, plan_key: str) -> StepPlan:
+        try:
+            return self.plans[plan_key]
+        except KeyError:
+            raise StepError(f"this step was built without the plan {plan_key!r}: pass the mixer's planner() to "
+                            f"StepContext (plans of this step: {', '.join(sorted(self.plans)) or 'none'})") from None
+
+    def tiles(self, rows: int):
+        """(sequence, first token) of every tile of ``rows`` consecutive new tokens of one sequence."""
         seqs, firsts = [], []
         for b, n in enumerate(self.new):
             for q0 in range(0, n, rows):

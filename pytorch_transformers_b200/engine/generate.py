@@ -23,10 +23,12 @@ class Stepper(Protocol):
     def open(self) -> int: ...
     def close(self, slot: int) -> None: ...
     def step(self, slots: Sequence[int], token_lists: Sequence[Sequence[int]]): ...
+    # optional: prepare(slots) builds the next step of one token each ahead of time
 
 
 class Selector(Protocol):
     def select(self, logits, request_ids, step, histories=None, suppress_stop=False) -> List[int]: ...
+    # optional: begin(...) launches the selection, finish(handle) waits for its tokens
 
 
 @dataclasses.dataclass
@@ -60,6 +62,8 @@ def run_generation(stepper: Stepper, selector: Selector, prompts: Sequence[Seque
     stop = set(options.eos_ids())
     min_new = int(options.min_new_tokens or 0)
     results = [RequestResult(prompt=list(p), tokens=[]) for p in prompts]
+    # a stepper that can prepare a step ahead and a selector that can run without the host waiting
+    can_overlap = all(hasattr(selector, n) for n in ("begin", "finish")) and hasattr(stepper, "prepare")
     for batch in plan_batches(len(prompts), max_batch):
         held = set()
         live = []
@@ -73,8 +77,16 @@ def run_generation(stepper: Stepper, selector: Selector, prompts: Sequence[Seque
                 req_ids = [r for r, _ in live]
                 histories = ([results[r].prompt + results[r].tokens for r in req_ids]
                              if options.repetition_penalty != 1.0 else None)
-                chosen = selector.select(logits, req_ids, t, histories=histories,
-                                         suppress_stop=bool(stop) and t < min_new)
+                if can_overlap and t + 1 < budget:
+                    # the selection runs on the device; meanwhile the host builds the next step of one
+                    # token each for the sequences that are live now (used if none of them ends here)
+                    pending = selector.begin(logits, req_ids, t, histories=histories,
+                                             suppress_stop=bool(stop) and t < min_new)
+                    stepper.prepare([s for _, s in live])
+                    chosen = selector.finish(pending)
+                else:
+                    chosen = selector.select(logits, req_ids, t, histories=histories,
+                                             suppress_stop=bool(stop) and t < min_new)
                 still = []
                 for row, ((r, slot), tok) in enumerate(zip(live, chosen)):
                     res = results[r]

@@ -46,6 +46,15 @@ class CausalLM:
         self.use_graphs = all(p.graph_safe for top in self.blocks + [self.final_norm] for p in top.walk())
         self.last_h2d_bytes = 0
         self._side_stream = None
+        # what the parts ask of every step: their planners (one per plan_key) and the mixers' word on streams
+        self.planners, seen = [], set()
+        for top in self.blocks + [self.final_norm]:
+            for part in top.walk():
+                planner = part.planner()
+                if planner is not None and planner.plan_key not in seen:
+                    seen.add(planner.plan_key)
+                    self.planners.append(planner)
+        self._mixers = [b.children["mixer"] for b in self.blocks if "mixer" in b.children]
 
     # ------------------------------------------------------------------ parameters
     def param_table(self) -> Dict[str, Tuple[Optional[Part], str, ParamDecl]]:
@@ -142,9 +151,20 @@ class CausalLM:
             else:
                 raise StepError(f"want must be 'last', 'all', 'none' or lists of positions, got {want!r}")
         single = all(len(t) == 1 for t in token_lists) and all(list(w) == [0] for w in want)
+        prepared = cache.__dict__.pop("_prepared_step", None)     # whatever was prepared is used now or never
         if single and self.use_graphs and self.device.type == "cuda":
-            return self._step_graph(cache, slots, token_lists, want)
-        ctx = StepContext(cache, slots, token_lists, self.spec.vocab_size, want, K.generic_tile_rows())
+            ctx = None
+            if prepared is not None:
+                owner, epoch, ahead = prepared
+                if (owner == id(self) and epoch == cache.epoch and ahead.slots == [int(s) for s in slots]
+                        and ahead.past == [cache.length(s) for s in ahead.slots]):
+                    ahead.set_tokens(token_lists, self.spec.vocab_size)
+                    ctx = ahead
+            if ctx is None:
+                ctx = StepContext(cache, slots, token_lists, self.spec.vocab_size, want, self.planners,
+                                  page_bucket=self.GRAPH_PAGE_BUCKET, defer=True)
+            return self._step_graph(cache, ctx)
+        ctx = StepContext(cache, slots, token_lists, self.spec.vocab_size, want, self.planners)
         self.last_h2d_bytes = ctx.h2d_bytes     # index arrays copied to the device for this step
         logits = self.forward(ctx)
         ctx.commit()
@@ -158,9 +178,26 @@ class CausalLM:
     GRAPH_PAGE_BUCKET = 16
     MAX_GRAPHS = 16
 
-    def _step_graph(self, cache: Cache, slots, token_lists, want) -> torch.Tensor:
-        ctx = StepContext(cache, slots, token_lists, self.spec.vocab_size, want, K.generic_tile_rows(),
-                          page_bucket=self.GRAPH_PAGE_BUCKET, defer=True)
+    def prepare_next(self, cache: Cache, slots: Sequence[int]) -> bool:
+        """Build ahead of time the step that will give each of ``slots`` one more token, while the device
+        is still busy with the step before: positions, page tables (pages are reserved now) and plans
+        need no token ids. The next ``step`` on this cache uses it if it is that step (same slots, same
+        lengths, no sequence opened or closed since) and only puts the tokens in; any other step drops
+        it. Returns whether a step was prepared (not without graphs, not when the cache is full)."""
+        from ..cache.pool import CacheFull
+        cache.__dict__.pop("_prepared_step", None)
+        if not (self.use_graphs and self.device.type == "cuda") or len(slots) == 0:
+            return False
+        one = [[0]] * len(slots)
+        try:
+            ahead = StepContext(cache, slots, one, self.spec.vocab_size, one, self.planners,
+                                page_bucket=self.GRAPH_PAGE_BUCKET, defer=True)
+        except CacheFull:
+            return False
+        cache.__dict__["_prepared_step"] = (id(self), cache.epoch, ahead)
+        return True
+
+    def _step_graph(self, cache: Cache, ctx: StepContext) -> torch.Tensor:
         # graphs live on the cache they were captured for (they hold pointers into its storage)
         graphs = cache.__dict__.setdefault("_step_graphs", {})
         key = (id(self), ctx.layout_key)
@@ -168,52 +205,40 @@ class CausalLM:
         if entry is None:
             static = torch.empty(ctx.packed_size, dtype=torch.int32, device=self.device)
             ctx.bind(static)
-            # one plain run on a side stream first: lazy initialisations must not be captured
-            side = torch.cuda.Stream(device=self.device)
-            side.wait_stream(torch.cuda.current_stream(self.device))
-            with torch.cuda.stream(side):
-                self.forward(ctx)
-            torch.cuda.current_stream(self.device).wait_stream(side)
+            # The first step of a layout runs plainly, and its result is what is returned: lazy
+            # initialisations (and one-time set-up inside the library) happen here, outside the capture.
+            # The capture that follows records the same launches without running them, so the step's
+            # work, a mixer's update of its per-sequence state included, is done exactly once.
+            first = self.forward(ctx)
             graph = torch.cuda.CUDAGraph()
             before = K.launches
             with torch.cuda.graph(graph):
                 out = self.forward(ctx)
-            # kernels of this library that one replay launches (for the launch count of benchmarks)
+            # kernels of this library that one replay launches (for the launch count of benchmarks);
+            # the capture itself launched nothing
             entry = {"static": static, "graph": graph, "out": out, "launches": K.launches - before}
+            K.launches = before
             while len(graphs) >= self.MAX_GRAPHS:
                 graphs.pop(next(iter(graphs)))
             graphs[key] = entry
-        else:
-            ctx.bind(entry["static"])
+            self.last_h2d_bytes = ctx.h2d_bytes
+            ctx.commit()
+            return first
+        ctx.bind(entry["static"])
         self.last_h2d_bytes = ctx.h2d_bytes
         entry["graph"].replay()
         K.launches += entry["launches"]
         ctx.commit()
         return entry["out"].clone()   # the graph's own output buffer is rewritten by the next replay
 
-    TWO_STREAM_MAX_TOKENS = 48   # Falcon-7B, two streams against one: batch 40 4.04 / 4.41 ms, 48 4.19 / 4.49, 64 4.44 / 4.25
-    # Two streams pay while the mixer's kernels are small beside the feed-forward's weight stream.
-    # Once a layer's attention reads tens of megabytes of keys and values itself, it competes with
-    # that stream instead of hiding under it. Measured (two streams against one, ms per step):
-    # Falcon-7B, 4 MB a layer (batch 8) 2.83 / 3.54; 17 MB (batch 32) 3.73 / 4.00; 34 MB (batch 8 at
-    # 16,384 keys) 3.43 / 3.85; 42 MB (batch 10) 4.49 / 4.24. Falcon-40B, 34 MB (batch 8) 16.0 / 16.3.
-    # Heads of size 128 need the decode kernel's large page ring, which keeps the stream's blocks off
-    # the SMs earlier: Falcon-11B, 17 MB (batch 2) 5.39 / 5.55; 34 MB (batch 4) 7.80 / 5.80; 67 MB
-    # (batch 8) 7.07 / 6.16.
-    TWO_STREAM_MAX_KV_BYTES = 40 << 20
-    TWO_STREAM_MAX_KV_BYTES_WIDE_HEADS = 24 << 20
-
     def _two_streams(self, ctx: StepContext) -> bool:
-        if self.device.type != "cuda" or self.dtype != torch.bfloat16 or ctx.n_tokens > self.TWO_STREAM_MAX_TOKENS:
+        """Mixer and feed-forward of a parallel block as two branches: only for steps of few rows (whose
+        linear layers are weight streams), and only if every mixer of the model says that its work in
+        this step is small beside such a stream (Part.runs_beside)."""
+        k = self.build.kernels
+        if self.device.type != "cuda" or ctx.n_tokens > k.WEIGHT_STREAM_MAX_ROWS or not self._mixers:
             return False
-        lengths = [p + n for p, n in zip(ctx.past, ctx.new)]
-        for g in ctx.cache.groups:   # keys and values that one layer of this group reads in this step
-            keys = sum(min(t, g.need.window) if g.need.window else t for t in lengths)
-            per_layer = keys * g.need.kv_heads * g.need.head_dim * 2 * g.k.element_size()
-            limit = self.TWO_STREAM_MAX_KV_BYTES if g.need.head_dim <= 64 else self.TWO_STREAM_MAX_KV_BYTES_WIDE_HEADS
-            if per_layer > limit:
-                return False
-        return True
+        return all(m.runs_beside(ctx) for m in self._mixers)
 
     def forward(self, ctx: StepContext) -> torch.Tensor:
         k = self.build.kernels

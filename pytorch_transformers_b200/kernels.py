@@ -15,6 +15,7 @@ import torch
 from . import native
 
 PAGE = 64  # tokens of a cache page (PTB_PAGE in csrc/common.cuh)
+# names (src/transformers/activations.py:200-228) -> the codes of csrc/common.cuh, the kernels' one table
 ACTIVATIONS = {"none": 0, "gelu": 1, "gelu_new": 2, "gelu_pytorch_tanh": 2, "relu": 3}
 NORM_KINDS = {"layernorm": 0, "rmsnorm": 1}
 _ERRORS = {1: "unknown dtype code", 2: "a size that the kernel does not take", 3: "the CUDA launch failed",
@@ -80,7 +81,7 @@ def lib():
                      "ptb_rope_table", "ptb_attention_decode", "ptb_attention_tc", "ptb_attention_tc_supports",
                      "ptb_attention_tc_tile_tokens", "ptb_tc_linear", "ptb_tc_linear_max_rows",
                      "ptb_tc_linear_k_multiple", "ptb_attention_decode_tc", "ptb_attention_decode_tc_supports",
-                     "ptb_fill_normal"):
+                     "ptb_fill_normal", "ptb_selftest_bounded_wait"):
             getattr(L, name).restype = ctypes.c_int
         _configured = True
     return L
@@ -252,19 +253,20 @@ def attention_decode(fused: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Te
     cos, sin = rope if rope is not None else (None, None)
     pairs = 0 if cos is None else cos.shape[1]
     parts = tickets = None
-    part_floats = 0
+    part_floats = n_tickets = 0
     if n_teams > 1:
         groups = n * kv_heads * ((q_per_kv + heads_per_tile - 1) // heads_per_tile)
         if groups * n_splits > DECODE_TICKETS:
             raise KernelError("attention_decode: too many (sequence, head chunk, split) triples for the ticket buffer")
         part_floats = groups * n_teams * heads_per_tile * (head_dim + 2)
         parts = torch.empty(part_floats, dtype=torch.float32, device=fused.device)
-        tickets = _decode_tickets(fused.device)
+        n_tickets = groups * n_splits
+        tickets = _tickets(n_tickets, fused.device)
     _check(lib().ptb_attention_decode(_ptr(fused), _ptr(k_pool), _ptr(v_pool), _ptr(out), ctypes.byref(batch),
                                       _ptr(cos), _ptr(sin), pairs, _ptr(slopes), heads, kv_heads, head_dim,
                                       heads_per_tile, n_splits, n_teams, warps, key_split, ctypes.c_float(scale),
                                       window, 1 if write_cache else 0, _ptr(parts), ctypes.c_size_t(part_floats),
-                                      _ptr(tickets), DECODE_TICKETS if n_teams > 1 else 0, _stream(fused)),
+                                      _ptr(tickets), n_tickets, _stream(fused)),
            "attention_decode")
     return out
 
@@ -296,32 +298,46 @@ def attention_decode_tc(fused: torch.Tensor, k_pool: torch.Tensor, v_pool: torch
     cos, sin = rope if rope is not None else (None, None)
     pairs = 0 if cos is None else cos.shape[1]
     parts = tickets = None
-    part_floats = 0
+    part_floats = n_tickets = 0
     if n_teams > 1:
         if n * kv_heads * n_splits > DECODE_TICKETS:
             raise KernelError("attention_decode_tc: too many (sequence, K/V head, split) triples for the ticket buffer")
         part_floats = n * kv_heads * n_teams * q_per_kv * (head_dim + 2)
         parts = torch.empty(part_floats, dtype=torch.float32, device=fused.device)
-        tickets = _decode_tickets(fused.device)
+        n_tickets = n * kv_heads * n_splits
+        tickets = _tickets(n_tickets, fused.device)
     _check(lib().ptb_attention_decode_tc(_ptr(fused), _ptr(k_pool), _ptr(v_pool), k_pool.shape[0], _ptr(out),
                                          ctypes.byref(batch), _ptr(cos), _ptr(sin), pairs, heads, kv_heads, head_dim,
                                          n_splits, n_teams, ctypes.c_float(scale), 1 if write_cache else 0,
-                                         _ptr(parts), ctypes.c_size_t(part_floats), _ptr(tickets),
-                                         DECODE_TICKETS if n_teams > 1 else 0,
+                                         _ptr(parts), ctypes.c_size_t(part_floats), _ptr(tickets), n_tickets,
                                          _ptr(error_flag(fused.device)), _stream(fused)), "attention_decode_tc")
     return out
 
 
-DECODE_TICKETS = 8192
-_decode_ticket_buffers = {}
+DECODE_TICKETS = 8192      # most (sequence, K/V head, split) triples of one decode attention launch
+TICKET_ARENA = 1 << 18     # int32 words per device
+_ticket_arenas = {}
 
 
-def _decode_tickets(device) -> torch.Tensor:
-    """int32 zeros, one per (sequence, K/V head, split) of a launch; the kernel leaves them zero."""
+def _tickets(n: int, device) -> torch.Tensor:
+    """``n`` int32 zeros for a launch whose blocks count their arrivals; the kernel leaves them zero.
+    Two launches that run at the same time (the two branches of a block, side by side in one graph)
+    must not count in the same words, so every launch takes the next stretch of a zeroed arena, which
+    wraps around after tens of launches; launches that far apart in a stream or a graph depend on
+    one another and never overlap. The arena is allocated at a device's first launch, which is never
+    inside a stream capture (a captured step has run once plainly before)."""
     device = torch.device(device)
-    if device not in _decode_ticket_buffers:
-        _decode_ticket_buffers[device] = torch.zeros(DECODE_TICKETS, dtype=torch.int32, device=device)
-    return _decode_ticket_buffers[device]
+    arena = _ticket_arenas.get(device)
+    if arena is None:
+        arena = _ticket_arenas[device] = [torch.zeros(TICKET_ARENA, dtype=torch.int32, device=device), 0]
+    n = (n + 31) // 32 * 32
+    if n > TICKET_ARENA:
+        raise KernelError(f"a launch asks for {n} tickets, more than the arena's {TICKET_ARENA}")
+    if arena[1] + n > TICKET_ARENA:
+        arena[1] = 0
+    out = arena[0][arena[1]:arena[1] + n]
+    arena[1] += n
+    return out
 
 
 _error_flags = {}
@@ -345,6 +361,18 @@ def check_device_errors(device) -> None:
         if code != 0:
             flag.zero_()
             raise KernelError(f"a kernel gave up waiting inside its pipeline (code {code}): its results are void")
+
+
+def selftest_bounded_wait(device, tries: int = 1000) -> torch.Tensor:
+    """Launch a kernel that waits, at most ``tries`` times, on a barrier at which nobody arrives: the wait
+    runs out and raises the device's error flag, as a tcgen05 kernel does whose copy never lands.
+    Returns an int32 word that the kernel sets to 1 when it gave up. ``check_device_errors`` then raises."""
+    device = torch.device(device)
+    gave_up = torch.zeros(1, dtype=torch.int32, device=device)
+    _check(lib().ptb_selftest_bounded_wait(int(tries), _ptr(error_flag(device)), _ptr(gave_up),
+                                           ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)),
+           "selftest_bounded_wait")
+    return gave_up
 
 
 def attention_tc_supports(head_dim: int) -> bool:
@@ -438,14 +466,11 @@ SKINNY_MAX_ROWS = 32   # ptb_skinny_linear_max_rows()
 SKINNY_K_MULTIPLE = 32  # ptb_skinny_linear_k_multiple()
 
 
-# Beyond this the library product is faster. Measured on B200 inside Falcon-7B's step, skinny_linear
-# against the library, ms: 9 rows 3.35 / 3.46, 12 rows 3.40 / 3.49, 16 rows 3.51 / 3.22 (each matrix alone
-# the library is ahead from 9 rows on, 10.3 against 11.5 us on the 42 MB matrices, but beside the other
-# graph branch's kernels its blocks leave less room).
+# Rows beyond which the library product is faster inside a step (12 rows: 3.40 against 3.49 ms a step;
+# 16 rows: 3.51 against 3.22).
 SKINNY_BEST_ROWS = 12
-# A matrix of the vocabulary's height runs alone in the step, and there the library reads it faster from
-# 5 rows on (591 MB, float32 out: 89.7 against 90.3 us at 1 row, 91.0 / 90.5 at 4, 92.3 / 86.7 at 6,
-# 92.7 / 86.9 at 8, 108 / 87 at 9).
+# A matrix of tens of thousands of rows (the vocabulary's) runs alone in the step, and there the library
+# reads it faster from 5 rows on (591 MB, float32 out, 8 rows: 92.7 against 86.9 us).
 SKINNY_TALL_ROWS = 32768
 SKINNY_BEST_ROWS_TALL = 4
 
@@ -476,24 +501,15 @@ def skinny_linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor]
     # tile; their partial sums meet in scratch memory, a zeroed ticket per tile says who is last
     need = _skinny_scratch_floats(m, n, k)
     scratch = torch.empty(need, dtype=torch.float32, device=x.device) if need else None
-    tickets = _skinny_tickets(x.device) if need else None
+    n_tickets = (n + 15) // 16 if need else 0        # a ticket per tile of weight rows; tiles have 16 rows or more
+    tickets = _tickets(n_tickets, x.device) if need else None
     _check(lib().ptb_skinny_linear(_ptr(x), _ptr(w), _ptr(bias), _ptr(add), _ptr(ybf), _ptr(yf), m, n, k,
                                    ACTIVATIONS[act], _ptr(scratch), ctypes.c_size_t(need), _ptr(tickets),
-                                   SKINNY_TICKETS if need else 0, _stream(x)), "skinny_linear")
+                                   n_tickets, _stream(x)), "skinny_linear")
     return y
 
 
-SKINNY_TICKETS = 8192
-_skinny_ticket_buffers = {}
 _skinny_scratch_cache = {}
-
-
-def _skinny_tickets(device) -> torch.Tensor:
-    """int32 zeros, one per tile of a launch; the kernel leaves them zero."""
-    device = torch.device(device)
-    if device not in _skinny_ticket_buffers:
-        _skinny_ticket_buffers[device] = torch.zeros(SKINNY_TICKETS, dtype=torch.int32, device=device)
-    return _skinny_ticket_buffers[device]
 
 
 def _skinny_scratch_floats(m: int, n: int, k: int) -> int:
@@ -506,6 +522,34 @@ def _skinny_scratch_floats(m: int, n: int, k: int) -> int:
 
 
 _sm_count = {}
+
+
+def sm_count(device) -> int:
+    """Multiprocessors of ``device`` (148 on a B200); without a CUDA device, the B200's count."""
+    device = torch.device(device)
+    if device.type != "cuda" or not torch.cuda.is_available():
+        return 148
+    if device not in _sm_count:
+        _sm_count[device] = torch.cuda.get_device_properties(device).multi_processor_count
+    return _sm_count[device]
+
+
+# A step of few tokens is bound by the read of the weights, and a mixer's small kernels can hide under
+# the feed-forward's weight stream on a second stream. Two limits say how long that pays:
+# rows of the step (beyond them the linear layers are no longer pure weight streams; two branches
+# against one at 48 rows: 4.19 against 4.49 ms a step, at 64 rows: 4.44 against 4.25), and the bytes of
+# keys and values that one attention layer reads in the step: once they are tens of megabytes the
+# attention competes with the weight stream instead of hiding under it (34 MB: 3.43 against 3.85 ms;
+# 42 MB: 4.49 against 4.24). Heads wider than 64 need the decode kernel's large page ring, which keeps
+# the stream's blocks off the SMs earlier (17 MB: 5.39 against 5.55 ms; 34 MB: 7.80 against 5.80).
+WEIGHT_STREAM_MAX_ROWS = 48
+DECODE_BESIDE_MAX_KV_BYTES = 40 << 20
+DECODE_BESIDE_MAX_KV_BYTES_WIDE_HEADS = 24 << 20
+
+
+def decode_attention_fits_beside(kv_bytes: int, head_dim: int) -> bool:
+    """May a decode attention that reads ``kv_bytes`` of keys and values run beside a weight stream?"""
+    return kv_bytes <= (DECODE_BESIDE_MAX_KV_BYTES if head_dim <= 64 else DECODE_BESIDE_MAX_KV_BYTES_WIDE_HEADS)
 
 
 TC_LINEAR_MAX_ROWS = 128   # ptb_tc_linear_max_rows()
@@ -531,12 +575,10 @@ def tc_linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = N
     if not x.is_contiguous() or not w.is_contiguous() or (add is not None and not add.is_contiguous()):
         raise KernelError("tc_linear takes contiguous tensors")
     dev = x.device
-    if dev not in _sm_count:
-        _sm_count[dev] = torch.cuda.get_device_properties(dev).multi_processor_count
     y = torch.empty((m, n), dtype=out_dtype, device=dev)
     ybf, yf = (y, None) if out_dtype == torch.bfloat16 else (None, y)
     _check(lib().ptb_tc_linear(_ptr(x), _ptr(w), _ptr(bias), _ptr(add), _ptr(ybf), _ptr(yf), m, n, k,
-                               ACTIVATIONS[act], _sm_count[dev], _ptr(error_flag(dev)), _stream(x)), "tc_linear")
+                               ACTIVATIONS[act], sm_count(dev), _ptr(error_flag(dev)), _stream(x)), "tc_linear")
     return y
 
 

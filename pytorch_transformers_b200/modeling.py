@@ -71,6 +71,9 @@ class _CacheStepper:
     def close(self, slot: int) -> None:
         self.cache.close(slot)
 
+    def prepare(self, slots) -> None:
+        self.model.prepare_next(self.cache, slots)
+
     def step(self, slots, token_lists):
         total = sum(len(t) for t in token_lists)
         if total <= self.max_step_tokens:

@@ -15,7 +15,8 @@ engine.batch.StepContext of the running step; ``x`` is [tokens, hidden] in the m
                      ``score_bias() -> slopes float32 [heads] | None``.
 * ``mixer``:         ``forward(x, ctx, entry) -> y``; ``cache_need() -> CacheNeed | None``;
                      ``state_need() -> StateNeed | None``. ``entry`` is the ScheduleEntry being
-                     run: it names the cache entry to read and whether to write it.
+                     run: it names the cache entry to read and whether to write it. Optional:
+                     ``planner()`` (per-step arrays of its own) and ``runs_beside(ctx)``.
 * ``feed_forward``:  ``forward(x, ctx) -> y``.
 * ``block``:         ``forward(x, ctx, entry) -> x'`` from its child parts; ``x`` and ``x'`` may be a
                      ``DeferredSum`` (two terms whose sum the next norm forms); ``resolve`` gives the tensor.
@@ -163,9 +164,12 @@ class Part:
     ``param_decls`` and their family's methods.
 
     ``graph_safe``: the part's forward only launches work whose shapes and addresses depend on the
-    step's counts, and reads everything else (slots, positions, pages) from the step's device
-    arrays. Only then may a step be captured once and replayed as a CUDA graph; a part that loops
-    over the step's host lists leaves it False and the model steps without graphs."""
+    step's layout (counts, widths, plans' facts), and reads everything else (slots, positions, pages)
+    from the step's device arrays. Only then may a step be captured once and replayed as a CUDA
+    graph; a part that loops over the step's host lists leaves it False and the model steps
+    without graphs. The first step of a layout is run plainly and captured afterwards without
+    running, every later one is a replay: a part's work is done once per step either way, so a
+    part with per-sequence state needs no care for being run twice."""
     graph_safe = False
 
     def __init__(self, build: BuildContext, spec: PartSpec):
@@ -179,6 +183,19 @@ class Part:
     def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
         for name, t in tensors.items():
             setattr(self, "p_" + name.replace(".", "_"), t)
+
+    def planner(self):
+        """An object with ``plan_key`` (a string) and ``plan(ctx) -> engine.batch.StepPlan`` if this part's
+        kernels need per-step integer arrays or numbers beyond the step's own (tile lists, say); parts
+        with the same ``plan_key`` share one plan per step, found as ``ctx.plan(plan_key)``. None: the part
+        needs nothing."""
+        return None
+
+    def runs_beside(self, ctx) -> bool:
+        """For mixers: may this step's mixer work run on a second stream (a second branch of a captured
+        graph) beside the feed-forward's? A mixer says yes while its own kernels are small beside the
+        feed-forward's read of its weights; the engine uses two branches only if every mixer agrees."""
+        return False
 
     def walk(self):
         """This part and all parts below it."""

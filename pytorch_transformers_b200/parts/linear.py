@@ -18,9 +18,8 @@ import torch
 
 # Rows up to which steps of more than a few tokens use tc_linear (TMA ring, tcgen05, accumulators
 # in tensor memory, bias / activation / residual in its epilogue) instead of the library product.
-# Off: alone it reads the weights at 3.1 to 5.3 TB/s where the library reaches 4.0 to 5.8 TB/s on the
-# same matrices (the profile of the weight-stream kernels has the table), and the fused epilogue does
-# not make up for it.
+# Off: on matrices of 40 to 170 MB it is 10 to 30 % behind the library product (`bench.py --only linear`
+# times both), and the fused epilogue does not make up for it.
 TC_LINEAR_ROWS = None
 
 

@@ -27,6 +27,7 @@ class DeviceSelector:
         self.max_rows = max_rows
         self.work = torch.empty((max_rows, vocab_size), dtype=torch.float32, device=self.device)
         self.out = torch.empty(max_rows, dtype=torch.int32, device=self.device)
+        self._host = self._landed = None      # page-locked landing place of the tokens, made at first use
         eos = options.eos_ids()
         self.suppress = torch.tensor(eos, dtype=torch.int32, device=self.device) if eos else None
         self.use_history = options.repetition_penalty != 1.0
@@ -39,6 +40,17 @@ class DeviceSelector:
                histories: Optional[Sequence[Sequence[int]]] = None, suppress_stop: bool = False) -> List[int]:
         """One token per row. ``request_ids[r]`` and ``step`` key the draw of row r;
         ``histories[r]`` are the tokens that the repetition penalty looks at."""
+        return self.finish(self.begin(logits, request_ids, step, histories, suppress_stop))
+
+    def finish(self, rows: int) -> List[int]:
+        """Wait for the tokens of the selection that ``begin`` started and return them."""
+        self._landed.synchronize()
+        return self._host[:rows].tolist()
+
+    def begin(self, logits: torch.Tensor, request_ids: Sequence[int], step: int,
+              histories: Optional[Sequence[Sequence[int]]] = None, suppress_stop: bool = False) -> int:
+        """Launch the selection and the copy of its tokens to page-locked host memory without waiting:
+        the host is free (to prepare the next step, say) until ``finish``."""
         rows = logits.shape[0]
         if rows > self.max_rows:
             raise ValueError(f"selector was sized for {self.max_rows} rows, got {rows}")
@@ -64,4 +76,9 @@ class DeviceSelector:
                       repetition_penalty=float(o.repetition_penalty), history=hist, history_len=hist_len,
                       suppress=self.suppress if suppress_stop else None, seed=int(o.seed), streams=streams,
                       counters=counters)
-        return self.out[:rows].tolist()
+        if self._host is None:
+            self._host = torch.empty(self.max_rows, dtype=torch.int32, pin_memory=self.device.type == "cuda")
+            self._landed = torch.cuda.Event() if self.device.type == "cuda" else None
+        self._host[:rows].copy_(self.out[:rows], non_blocking=True)
+        self._landed.record(torch.cuda.current_stream(self.device))
+        return rows

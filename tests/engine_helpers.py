@@ -16,6 +16,7 @@ def attention_case(K, dtype, heads, kv_heads, d, pasts, news, position="rotary",
     strongly, so that the row's output is essentially that key's value."""
     from pytorch_transformers_b200.cache.paged import Cache
     from pytorch_transformers_b200.engine.batch import StepContext
+    from pytorch_transformers_b200.parts.attention import AttentionTiles
     from pytorch_transformers_b200.parts.base import CacheNeed
     from pytorch_transformers_b200.parts.position import alibi_slopes
 
@@ -53,9 +54,11 @@ def attention_case(K, dtype, heads, kv_heads, d, pasts, news, position="rotary",
         live = [(s, r) for s, r in zip(slots, ranges) if r[1] > r[0]]
         idx = [i for i, r in enumerate(ranges) if r[1] > r[0]]
         toks = [[0] * (r[1] - r[0]) for _, r in live]
-        ctx = StepContext(cache, [s for s, _ in live], toks, 1, [[] for _ in live], K.generic_tile_rows())
+        ctx = StepContext(cache, [s for s, _ in live], toks, 1, [[] for _ in live], [AttentionTiles(K)])
+        tiles = ctx.plan(AttentionTiles.plan_key)
+        mma_tokens = tiles.facts["mma_tokens"]
         x = torch.cat([fused[i][r[0]:r[1]] for i, (_, r) in zip(idx, live)]).to(dtype).cuda().contiguous()
-        if fused_decode is not None and ctx.mma_tokens == 1:
+        if fused_decode is not None and mma_tokens == 1:
             # fused_decode = (heads per tile or None, splits[, key groups[, teams]]): the one-kernel decode path
             rope = K.rope_table(ctx.dev["tok_pos"], inv_freq) if inv_freq is not None else None
             hpk = fused_decode[0] or min(qpk, 128)
@@ -74,20 +77,20 @@ def attention_case(K, dtype, heads, kv_heads, d, pasts, news, position="rotary",
             return out, idx
         q = K.split_rotate_store(x, k_pool, v_pool, ctx.batch_c[gi], inv_freq, kv_heads, qpk, d)
         if tc:
-            assert ctx.mma_tokens == K.TC_TILE_TOKENS
-            out = K.attention_tc(q, k_pool, v_pool, ctx.batch_c[gi], ctx.dev["mtile_seq"], ctx.dev["mtile_q0"],
-                                 ctx.n_mma_tiles, kv_heads, scale, slopes)
+            assert mma_tokens == K.TC_TILE_TOKENS
+            out = K.attention_tc(q, k_pool, v_pool, ctx.batch_c[gi], tiles.dev["mtile_seq"], tiles.dev["mtile_q0"],
+                                 tiles.facts["n_mma_tiles"], kv_heads, scale, slopes)
             K.check_device_errors("cuda")
         elif mma is None:
-            out = K.attention_generic(q, k_pool, v_pool, ctx.batch_c[gi], ctx.dev["tile_seq"], ctx.dev["tile_q0"],
-                                      ctx.n_tiles, slopes, kv_heads, scale, window)
+            out = K.attention_generic(q, k_pool, v_pool, ctx.batch_c[gi], tiles.dev["tile_seq"], tiles.dev["tile_q0"],
+                                      tiles.facts["n_tiles"], slopes, kv_heads, scale, window)
         else:
             # mma = (heads per tile or None for "all that fit", splits)
-            tokens = ctx.mma_tokens
+            tokens = mma_tokens
             hpk = mma[0] or (min(qpk, 128) if tokens == 1 else max(1, min(qpk, 128 // tokens)))
             warps = (hpk * tokens + 15) // 16
-            out = K.attention_mma(q, k_pool, v_pool, ctx.batch_c[gi], ctx.dev["mtile_seq"], ctx.dev["mtile_q0"],
-                                  ctx.n_mma_tiles, slopes, kv_heads, scale, window, tokens, hpk, warps, mma[1])
+            out = K.attention_mma(q, k_pool, v_pool, ctx.batch_c[gi], tiles.dev["mtile_seq"], tiles.dev["mtile_q0"],
+                                  tiles.facts["n_mma_tiles"], slopes, kv_heads, scale, window, tokens, hpk, warps, mma[1])
         ctx.commit()
         return out, idx
 

@@ -7,7 +7,8 @@ once with the reference's own FalconForCausalLM on tiny random models; the scrip
 outputs are under tests/golden/.
 
 Every function takes and returns tensors of one working dtype (float64 by default, so
-that differences seen against it are the tested engine's rounding alone).
+that differences seen against it are the tested engine's rounding alone), on the device of
+the weights they are given (the CPU, or a GPU for the widths of the large models).
 """
 from __future__ import annotations
 
@@ -172,13 +173,13 @@ def attention_core(q, k, v, c: dict, bias=None) -> torch.Tensor:
     s, nh, d = q.shape
     g = k.shape[1]
     qpk = nh // g
-    out = torch.empty(s, nh, d, dtype=q.dtype)
-    causal = torch.ones(s, s, dtype=torch.bool).tril()
+    out = torch.empty(s, nh, d, dtype=q.dtype, device=q.device)
+    causal = torch.ones(s, s, dtype=torch.bool, device=q.device).tril()
     for h in range(nh):
         kk, vv = k[:, h // qpk], v[:, h // qpk]
         scores = q[:, h] @ kk.T
         if bias is not None:
-            scores = scores + bias[h][None, :s]
+            scores = scores + bias[h][None, :s].to(q.device)
         scores = scores / math.sqrt(d)
         scores = scores.masked_fill(~causal, float("-inf"))
         out[:, h] = torch.softmax(scores, -1) @ vv
@@ -212,8 +213,8 @@ def self_attention(x, w: dict, prefix: str, c: dict) -> torch.Tensor:
     if c["alibi"]:
         bias = alibi_bias(c["num_attention_heads"], s, x.dtype)
     else:
-        pos = torch.arange(s)
-        inv = rope_inv_freq(c)
+        pos = torch.arange(s, device=x.device)
+        inv = rope_inv_freq(c).to(x.device)
         q, k = rotary(q, pos, inv), rotary(k, pos, inv)
     o = attention_core(q, k, v, c, bias)
     return linear(o, w[prefix + "dense.weight"], w.get(prefix + "dense.bias"))

@@ -126,3 +126,54 @@ def test_errors_leave_no_slot_open():
     with pytest.raises(RuntimeError, match="boom"):
         run_generation(st, sel, [[1], [2]], GenerationConfig(), budget=5, max_batch=2)
     assert st.length == {} and sorted(st.free) == [0, 1, 2, 3]
+
+
+class PreparingStepper(FakeStepper):
+    """A stepper that can build a step ahead of time; it records what it was asked to prepare."""
+
+    def __init__(self, max_slots=4):
+        super().__init__(max_slots)
+        self.prepared = []
+
+    def prepare(self, slots):
+        assert all(s in self.length for s in slots), "a step was prepared for a slot that is not open"
+        self.prepared.append((len(self.calls), list(slots)))
+
+
+class TwoPhaseSelector(ArgmaxSelector):
+    """A selector whose selection can run while the host does something else."""
+
+    def __init__(self, stop=()):
+        super().__init__(stop)
+        self.open_handle = None
+
+    def begin(self, logits, request_ids, step, histories=None, suppress_stop=False):
+        assert self.open_handle is None
+        self.open_handle = self.select(logits, request_ids, step, histories, suppress_stop)
+        return "handle"
+
+    def finish(self, handle):
+        assert handle == "handle"
+        out, self.open_handle = self.open_handle, None
+        return out
+
+
+def test_the_next_step_is_prepared_while_the_selection_runs_and_changes_no_token():
+    prompts = [[3, 4], [10], [20, 21, 22]]
+    opts = GenerationConfig(eos_token_id=[13])                       # request 1 stops at its third token
+    plain_results = run_generation(FakeStepper(), ArgmaxSelector([13]), prompts, opts, 5, 3)
+    stepper, selector = PreparingStepper(), TwoPhaseSelector([13])
+    results = run_generation(stepper, selector, prompts, opts, 5, 3)
+    assert [r.tokens for r in results] == [r.tokens for r in plain_results]
+    assert [r.finish_reason for r in results] == ["length", "stop", "length"]
+    assert selector.open_handle is None
+    # a step was prepared after every selection but the last one of the budget, for the sequences live
+    # at that moment (request 1 among them at the step at which it ends: that preparation is wasted,
+    # the step that follows names other slots)
+    assert [n for n, _ in stepper.prepared] == [1, 2, 3, 4]
+    assert stepper.prepared[0][1] == [0, 1, 2] and stepper.prepared[2][1] == [0, 1, 2]
+    assert stepper.prepared[3][1] == [0, 2]
+    assert stepper.calls[2][0] == [0, 1, 2] and stepper.calls[3][0] == [0, 2]
+    # a stepper or a selector without the optional methods is driven the plain way
+    results = run_generation(FakeStepper(), TwoPhaseSelector([13]), prompts, opts, 5, 3)
+    assert [r.tokens for r in results] == [r.tokens for r in plain_results]

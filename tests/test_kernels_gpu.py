@@ -223,7 +223,37 @@ def test_skinny_linear_k_divided_among_blocks(K, m, n, k, shares):
     for _ in range(2):
         out = K.skinny_linear(x, w, b, "gelu", a)
         torch.testing.assert_close(out.double().cpu(), ref, **tol(bf))
-    assert int(K._skinny_tickets(x.device).abs().sum()) == 0
+    assert int(K._ticket_arenas[x.device][0].abs().sum()) == 0
+
+
+def test_two_divided_launches_at_the_same_time_do_not_share_their_tickets(K):
+    """Two launches that divide K among blocks run side by side on two streams (as the two branches of a
+    block do inside a step): each counts its blocks' arrivals in words of its own, so both give what
+    they give alone. Tickets never wait for anybody, so a fault here shows as a wrong sum, not a hang."""
+    bf = torch.bfloat16
+    m, n, k = 8, 8192, 32768
+    assert K._skinny_scratch_floats(m, n, k) > 0
+    xs = [rnd(m, k, dtype=bf, seed=s, scale=0.3) for s in (1, 2)]
+    ws = [rnd(n, k, dtype=bf, seed=s, scale=0.05) for s in (3, 4)]
+    alone = [K.skinny_linear(x, w) for x, w in zip(xs, ws)]
+    torch.cuda.synchronize()
+    streams = [torch.cuda.Stream(), torch.cuda.Stream()]
+    for _ in range(10):
+        outs = []
+        for st, x, w in zip(streams, xs, ws):
+            st.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(st):
+                outs.append([K.skinny_linear(x, w) for _ in range(3)])
+        for st in streams:
+            torch.cuda.current_stream().wait_stream(st)
+        torch.cuda.synchronize()
+        for got, want in zip(outs, alone):
+            for g in got:
+                assert torch.equal(g, want)
+    assert int(K._ticket_arenas[xs[0].device][0].abs().sum()) == 0
+    # a launch's words are its own: consecutive launches get consecutive stretches of the arena
+    a, b = K._tickets(100, xs[0].device), K._tickets(100, xs[0].device)
+    assert a.data_ptr() != b.data_ptr() and a.numel() == 128
 
 
 def test_skinny_linear_refuses_what_it_does_not_take(K):
@@ -239,3 +269,25 @@ def test_skinny_linear_refuses_what_it_does_not_take(K):
         K.skinny_linear(rnd(4, 64), rnd(16, 64))
 
 
+
+
+def test_a_bounded_wait_that_runs_out_raises_on_the_host_and_leaves_the_device_usable(K):
+    """Every wait on an mbarrier in the tcgen05 kernels gives up after a number of tries, raises a flag
+    in device memory and lets the kernel return. Here a kernel waits 1,000 tries on a barrier at which
+    nobody arrives (no fault, no hang: the wait simply runs out); the host's check then raises once,
+    the flag is clean again afterwards, and a tcgen05 kernel still runs."""
+    from pytorch_transformers_b200.kernels import KernelError
+    dev = torch.device("cuda", torch.cuda.current_device())
+    K.check_device_errors(dev)                           # clean before
+    gave_up = K.selftest_bounded_wait(dev, tries=1000)
+    with pytest.raises(KernelError, match="gave up waiting .*code 99"):
+        K.check_device_errors(dev)
+    assert int(gave_up.item()) == 1
+    K.check_device_errors(dev)                           # raised once, clean again
+    bf = torch.bfloat16
+    x, w = rnd(40, 256, dtype=bf, seed=1), rnd(300, 256, dtype=bf, seed=2, scale=0.05)
+    out = K.tc_linear(x, w)
+    K.check_device_errors(dev)
+    torch.testing.assert_close(out.double().cpu(), x.double().cpu() @ w.double().cpu().T, **tol(bf))
+    with pytest.raises(KernelError):
+        K.selftest_bounded_wait(dev, tries=0)

@@ -88,7 +88,7 @@ def test_mixer_and_block_alone(name, tmp_path):
     x = [rnd(n, c["hidden_size"], seed=n) for n in lens]
     cache = model.new_cache(256)
     slots = [cache.open() for _ in lens]
-    ctx = StepContext(cache, slots, [[0] * n for n in lens], c["vocab_size"], [[] for _ in lens], 16)
+    ctx = StepContext(cache, slots, [[0] * n for n in lens], c["vocab_size"], [[] for _ in lens], model.planners)
     layer = 1
     entry = ScheduleEntry(block=layer, cache_entry=layer)
     block = model.blocks[layer]
@@ -553,3 +553,95 @@ def test_toy_architecture_with_a_full_and_a_windowed_layer(tmp_path, dtype):
         assert window_group.pool.in_use <= 2 * len(live) + 1      # a window of 40 spans at most two pages
     cache.close_all()
     cache.check()
+
+
+# ------------------------------------------ a stateful mixer whose steps are replayed as CUDA graphs
+def _register_toy_graph_state():
+    import pytorch_transformers_b200 as ptb
+    from pytorch_transformers_b200.config.base import ModelConfig
+    from pytorch_transformers_b200.parts import ModelSpec, ParamDecl, Part, PartSpec, StateNeed, register_part
+
+    @register_part("mixer", "toy_decaying_sum")
+    class DecayingSum(Part):
+        """state <- decay * state + x_t, y_t = W state: per-sequence state, updated through the step's
+        device arrays only (slots come from ctx.dev), so steps of single tokens may be captured."""
+        graph_safe = True
+
+        def __init__(self, build, spec, hidden, decay):
+            super().__init__(build, spec)
+            self.hidden, self.decay = hidden, float(decay)
+
+        def param_decls(self):
+            return {"w.weight": ParamDecl((self.hidden, self.hidden))}
+
+        def cache_need(self):
+            return None
+
+        def state_need(self):
+            return StateNeed(self.hidden)
+
+        def forward(self, x, ctx, entry):
+            state = ctx.cache.entry_state(entry.cache_entry)
+            if not ctx.is_decode:
+                raise NotImplementedError("the toy takes one token per sequence and step")
+            slots = ctx.dev["slots"].long()
+            new = state.index_select(0, slots) * self.decay + x.float()
+            state.index_copy_(0, slots, new)
+            return (new @ self.p_w_weight.float().T).to(x.dtype)
+
+    @dataclasses.dataclass
+    class ToyStateConfig(ModelConfig):
+        model_type: ClassVar[str] = "toy_graph_state"
+        vocab_size: int = 40
+        hidden_size: int = 32
+
+    def spec(cfg):
+        norm = lambda n: PartSpec("norm", "rmsnorm", {"size": cfg.hidden_size, "eps": 1e-5}, names={"weight": n})
+        ff = PartSpec("feed_forward", "dense", {"hidden": cfg.hidden_size, "inner": 48, "activation": "gelu"},
+                      names={"up.weight": "b.ff.up.weight", "down.weight": "b.ff.down.weight"})
+        mixer = PartSpec("mixer", "toy_decaying_sum", {"hidden": cfg.hidden_size, "decay": 0.5},
+                         names={"w.weight": "b.mix.w.weight"})
+        block = PartSpec("block", "sequential", children={"norm_mixer": norm("b.n1.weight"), "norm_ff": norm("b.n2.weight"),
+                                                          "mixer": mixer, "feed_forward": ff})
+        return ModelSpec(cfg.vocab_size, cfg.hidden_size, "embed.weight", [block], norm("final.weight"), None)
+
+    ptb.register_architecture("toy_graph_state", ("ToyGraphState",), ToyStateConfig, spec)
+    return ToyStateConfig
+
+
+def test_a_stateful_mixer_under_graph_replay_updates_its_state_once_per_step():
+    """A registered mixer with per-sequence state and graph_safe = True: its single-token steps are
+    captured and replayed, the first step of every batch size included, and give what the same model
+    gives without graphs (a step that ran twice would have advanced the state twice)."""
+    import pytorch_transformers_b200 as ptb
+    Cfg = _register_toy_graph_state()
+    model = ptb.AutoModelForCausalLM.from_config(Cfg(), seed=5, dtype="float32")
+    assert model.use_graphs and not model.planners
+    seqs = [[3, 9, 1, 30, 22, 8, 17], [5, 5, 12, 2], [39, 0]]
+
+    def run():
+        cache = model.new_cache(64 * 4)
+        slots = [cache.open() for _ in seqs]
+        outs = []
+        for t in range(max(map(len, seqs))):
+            live = [i for i, s in enumerate(seqs) if t < len(s)]
+            outs.append(model.step(cache, [slots[i] for i in live], [[seqs[i][t]] for i in live]))
+        return torch.cat(outs), cache
+
+    with_graphs, cache = run()
+    assert len(cache.__dict__.get("_step_graphs", {})) == 3            # batch sizes 3, 2 and 1
+    again, _ = run()                                                    # new cache, new graphs, fresh state
+    model.use_graphs = False
+    without, _ = run()
+    assert torch.equal(with_graphs, without) and torch.equal(again, without)
+    # and the state is what the recurrence says: s = sum_k 0.5^k x_{t-k}
+    model.use_graphs = True
+    cache = model.new_cache(64)
+    slot = cache.open()
+    for tok in seqs[0]:
+        model.step(cache, [slot], [[tok]])
+    emb = model.embedding[torch.tensor(seqs[0], device="cuda")].float()
+    gain = model.blocks[0].children["norm_mixer"].p_weight
+    normed = emb / torch.sqrt((emb ** 2).mean(-1, keepdim=True) + 1e-5) * gain
+    want = sum(0.5 ** (len(seqs[0]) - 1 - k) * normed[k] for k in range(len(seqs[0])))
+    torch.testing.assert_close(cache.entry_state(0)[slot], want, atol=1e-5, rtol=1e-5)
