@@ -42,6 +42,7 @@ FALCON_40B = dict(vocab_size=65024, hidden_size=8192, num_hidden_layers=60, num_
 SHAPES = {"7b": FALCON_7B, "11b": FALCON_11B, "40b": FALCON_40B}
 CONTEXT = 2048
 PREFILL_TOKENS = 2048
+SETTLE_STEPS = 40     # untimed decode steps after a prefill, before the warm-up steps (see run_ours)
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
 
@@ -230,7 +231,7 @@ def run_decode_attention(args):
     key_split = 1 if warps >= 3 else min(4 if d > 64 else 2, K.decode_max_warps(d) // warps)
     result = {"only": "decode-attention", "shape": args.shape, "batch": rows, "context": keys, "unit": "us per launch"}
     side = torch.cuda.Stream()
-    for splits, teams in ((1, 1), (4, 1), (8, 1), (8, 2), (8, 4), (8, 8), (4, 8), (1, 32)):
+    for splits, teams in ((1, 1), (2, 1), (4, 1), (8, 1), (8, 2), (8, 4), (8, 8), (4, 8), (1, 32)):
         if splits * teams * 2 > keys // 64 + 1:
             continue
         launches = {"mma": lambda: K.attention_decode(fused, k_pool, v_pool, batch, rope, None, kv, qpk, d, scale, 0, hpk,
@@ -378,6 +379,44 @@ def run_linear(args):
     return 0
 
 
+def run_fill(args):
+    """`--only fill`: device time of the random-weights kernel on one matrix of `--shape`'s feed-forward
+    (bfloat16 and float32) and of the whole model of `--layers` layers through from_config."""
+    import torch
+
+    import pytorch_transformers_b200 as ptb
+    from pytorch_transformers_b200 import kernels as K
+    from pytorch_transformers_b200.weights import generator
+
+    torch.cuda.set_device(0)
+    h, nh, kvh, d, f, v = shape_sizes(SHAPES[args.shape])
+    result = {"only": "fill", "shape": args.shape}
+    for dtype, name in ((torch.bfloat16, "bf16"), (torch.float32, "f32")):
+        out = torch.empty((f, h), dtype=dtype, device="cuda")
+        key = generator.tensor_key(0, "w")
+        K.fill_normal(out, key, 0.02)
+        torch.cuda.synchronize()
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record()
+        for _ in range(5):
+            K.fill_normal(out, key, 0.02)
+        t1.record()
+        torch.cuda.synchronize()
+        ms = t0.elapsed_time(t1) / 5
+        result[f"matrix {f}x{h} {name}"] = {"ms": round(ms, 3), "Gvalues_per_s": round(f * h / ms / 1e6, 1),
+                                            "GBps_written": round(out.numel() * out.element_size() / ms / 1e6, 1)}
+    layers = args.layers or SHAPES[args.shape]["num_hidden_layers"]
+    cfg = ptb.FalconConfig.from_dict(dict(SHAPES[args.shape], num_hidden_layers=layers))
+    torch.cuda.synchronize()
+    t = time.perf_counter()
+    model = ptb.AutoModelForCausalLM.from_config(cfg, seed=0, dtype="bfloat16", device="cuda:0")
+    torch.cuda.synchronize()
+    result["model"] = {"layers": layers, "seconds": round(time.perf_counter() - t, 2),
+                       "GB": round(model.weight_bytes() / 1e9, 2)}
+    print(json.dumps(result))
+    return 0
+
+
 def run_ours(args):
     if args.only == "sample":
         return run_sample(args)
@@ -385,6 +424,8 @@ def run_ours(args):
         return run_decode_attention(args)
     if args.only == "linear":
         return run_linear(args)
+    if args.only == "fill":
+        return run_fill(args)
     import torch
 
     import pytorch_transformers_b200 as ptb
@@ -406,7 +447,7 @@ def run_ours(args):
     def decode_run(batch, steps, warmup, sample_clocks=False, context=CONTEXT):
         """Prefill `batch` prompts of `context` tokens, then time `steps` decode steps."""
         CONTEXT = context
-        total = CONTEXT + steps + warmup + 1
+        total = CONTEXT + SETTLE_STEPS + steps + warmup + 1
         cache = model.new_cache(batch * ((total + 63) // 64 * 64))
         slots = [cache.open() for _ in range(batch)]
         opts = GenerationConfig(do_sample=False)
@@ -415,18 +456,21 @@ def run_ours(args):
         chunk = max(1, 8192 // CONTEXT)                      # prompts go in a few at a time to bound activations
         for i in range(0, batch, chunk):
             logits = model.step(cache, slots[i:i + chunk], ps[i:i + chunk], want="last")
-        toks = sel.select(model.step(cache, slots, [[1]] * batch, want="last"), list(range(batch)), 0)
+        logits = model.step(cache, slots, [[1]] * batch, want="last")
+        ids = list(range(batch))
 
         def one():
-            # as the generation loop does it: the selection runs on the device while the host builds the
-            # next step, which then only waits for its tokens
-            nonlocal toks
-            logits = model.step(cache, slots, [[t] for t in toks], want="last")
-            pending = sel.begin(logits, list(range(batch)), 0)
+            # one decode step as the generation loop runs it: the selection runs on the device, meanwhile
+            # the host builds the next step and launches it with the tokens still on the device, then
+            # reads the tokens (steps that cannot be launched ahead wait for the tokens first)
+            nonlocal logits
+            pending = sel.begin(logits, ids, 0)
             model.prepare_next(cache, slots)
+            ahead = model.step_ahead(cache, slots, sel.device_tokens(pending))
             toks = sel.finish(pending)
+            logits = ahead if ahead is not None else model.step(cache, slots, [[t] for t in toks], want="last")
 
-        for _ in range(warmup):
+        for _ in range(SETTLE_STEPS + warmup):
             one()
         torch.cuda.synchronize()
         sampler = ClockSampler() if sample_clocks else None
@@ -446,7 +490,7 @@ def run_ours(args):
             sampler.__exit__()
         ms = start.elapsed_time(end) / steps
         launches = kernels.launches - l0
-        ctx_mid = CONTEXT + 1 + warmup + steps / 2
+        ctx_mid = CONTEXT + 1 + SETTLE_STEPS + warmup + steps / 2
         cache.close_all()
         del cache
         torch.cuda.empty_cache()
@@ -514,7 +558,10 @@ def run_ours(args):
                                            "frac": round(pbytes / (pms * 1e-3) / 1e9 / pk["hbm_gbs"], 4)}
 
     # ---- end to end through generate(): host token lists in, host token lists out ----
-    n_new = args.steps + args.warmup
+    # After the prefill (seconds of tensor-core work under the power cap) the device runs its first tens of
+    # decode steps 5 to 10 % slower and comes back in stages; SETTLE_STEPS untimed steps come before the W
+    # warm-up steps so that the K timed steps measure decoding, not the prefill's aftermath.
+    n_new = SETTLE_STEPS + args.warmup + args.steps
     ps = prompts(batch, CONTEXT)
     stamps = []
     model.generate(ps, max_new_tokens=2, eos_token_id=None, max_batch_size=batch)       # sizes the cache, warms up
@@ -529,8 +576,8 @@ def run_ours(args):
     torch.cuda.synchronize()
     t_end = time.perf_counter()
     # stamps[i] is taken when step i's tokens have reached the host; steps after the warm-up count
-    e2e_s = (stamps[-1] - stamps[args.warmup - 1]) / (len(stamps) - args.warmup)
-    e2e = {"value": round(batch / e2e_s, 1), "unit": "tokens/s",
+    e2e_s = (stamps[-1] - stamps[-1 - args.steps]) / args.steps
+    e2e = {"value": round(batch / e2e_s, 1), "unit": "tokens/s", "settle_steps": SETTLE_STEPS,
            "h2d_bytes_per_step": int(model.last_h2d_bytes),
            "d2h_bytes_per_step": 4 * batch}
 
@@ -541,7 +588,8 @@ def run_ours(args):
         "impl": "ours",
         "config": workload_config(layers, batch),
         "notes": {"sampling": "greedy, on the device", "cache_page": 64, "decode_steps": "CUDA graphs",
-                  "timing": "CUDA events around K steps"},
+                  "timing": "CUDA events around K steps", "settle_steps": SETTLE_STEPS,
+                  "settle": "untimed decode steps after every prefill, before the W warm-up steps"},
         "prefill": prefill, "roofline": roofline, "points": points, "points_roofline": points_roofline, "e2e": e2e,
         "gpu_launches": launches,
         "clocks": clocks,
@@ -640,7 +688,7 @@ def main():
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration's (0: all)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--only", default="", choices=["", "decode", "prefill", "sample", "decode-attention", "config", "linear"],
+    ap.add_argument("--only", default="", choices=["", "decode", "prefill", "sample", "decode-attention", "config", "linear", "fill"],
                     help="run one section only and print its numbers (for profilers)")
     ap.add_argument("--shape", default="7b", choices=sorted(SHAPES), help="model shape for --only decode / prefill")
     ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS, help="prompt length for --only prefill")
@@ -648,8 +696,11 @@ def main():
     ap.add_argument("--rows", type=int, default=8, help="rows of the activation for --only linear")
     ap.add_argument("--decode-steps", type=int, default=0,
                     help="decode steps of --only config (0: the number BASELINE gives for the shape)")
+    ap.add_argument("--settle", type=int, default=SETTLE_STEPS,
+                    help="untimed decode steps after a prefill, before the warm-up steps (0 for profiler runs)")
     ap.add_argument("--no-graphs", action="store_true", help="launch every kernel of a decode step itself")
     args = ap.parse_args()
+    globals()["SETTLE_STEPS"] = max(0, args.settle)
     if args.gpus != 1:
         print(f"bench.py measures one GPU: this library is a single-GPU engine, --gpus {args.gpus} is not run")
         return 2

@@ -29,11 +29,26 @@ from .pool import CacheError, CacheFull, IdPool, SequenceRecord
 
 PAGE = 64
 
+# What a kind of cache entry keeps: for a sequence of `length` tokens, the first position that a later
+# query can still see (pages that lie wholly before it go back to the pool after every step).
+# ``register_cache_kind`` adds a kind without a change here; the mixer that names it reads accordingly.
+CACHE_KINDS = {
+    "full": lambda need, length: 0,
+    # the next query sits at position >= length and sees keys > position - window
+    "window": lambda need, length: max(0, length - need.window + 1),
+}
+
+
+def register_cache_kind(kind: str, first_needed) -> None:
+    """``first_needed(need: CacheNeed, length: int) -> int``: the first cached position that queries at
+    positions >= length may read."""
+    CACHE_KINDS[kind] = first_needed
+
 
 class StorageGroup:
     def __init__(self, need: CacheNeed, entries: List[int], num_pages: int, dtype: torch.dtype, device):
-        if need.kind not in ("full", "window"):
-            raise ValueError(f"unknown cache kind {need.kind!r} (kinds: full, window)")
+        if need.kind not in CACHE_KINDS:
+            raise ValueError(f"unknown cache kind {need.kind!r} (kinds: {', '.join(sorted(CACHE_KINDS))})")
         if need.kind == "window" and need.window <= 0:
             raise ValueError("a window group needs window > 0")
         self.need = need
@@ -134,9 +149,8 @@ class Cache:
         for gi, g in enumerate(self.groups):
             if rec.length > len(rec.pages[gi]) * PAGE:
                 raise CacheError(f"slot {slot} was advanced to {rec.length} tokens beyond its reserved pages")
-            if g.need.kind == "window":
-                # the next query sits at position >= length and sees keys > position - window
-                first_needed = max(0, rec.length - g.need.window + 1)
+            first_needed = CACHE_KINDS[g.need.kind](g.need, rec.length)
+            if first_needed >= PAGE:
                 dead = first_needed // PAGE
                 gone = [p for p in rec.pages[gi][:dead] if p >= 0]
                 if gone:

@@ -439,6 +439,26 @@ PTB_API int ptb_residual(int dtype, const void* x, const void* a, const void* b,
   return launch_status();
 }
 
+// x *= factor in place, the product formed in float32 and rounded once (a scale on the embeddings or on
+// the logits, where an architecture has one)
+template <typename T>
+__global__ void scale_kernel(T* __restrict__ x, float factor, size_t total) {
+  const size_t stride = size_t(gridDim.x) * blockDim.x;
+  for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride)
+    x[i] = from_f<T>(__fmul_rn(to_f(x[i]), factor));
+}
+
+PTB_API int ptb_scale(int dtype, void* x, float factor, long long total, cudaStream_t stream) {
+  if (total <= 0) return PTB_OK;
+  const int threads = 256;
+  const int blocks = grid_for(size_t(total), threads);
+  if (dtype == PTB_F32) scale_kernel<float><<<blocks, threads, 0, stream>>>((float*)x, factor, size_t(total));
+  else if (dtype == PTB_BF16)
+    scale_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>((__nv_bfloat16*)x, factor, size_t(total));
+  else return PTB_ERR_DTYPE;
+  return launch_status();
+}
+
 // float32 copy of rows of any dtype: out[r, :] = float(x[r, :]) (logits of a bfloat16 head)
 template <typename T>
 __global__ void to_float_kernel(const T* __restrict__ x, float* __restrict__ out, size_t total) {

@@ -32,13 +32,39 @@ from ..cache.paged import PAGE, Cache
 
 class PinnedRing:
     """A few page-locked host buffers used in turn for the step's index arrays, so that the copy
-    to the device is asynchronous and no buffer is rewritten before its copy has run."""
+    to the device is asynchronous and no buffer is rewritten before its copy has run. ``fill`` puts
+    a step's arrays into the next buffer (that can be done ahead of time, while the device is busy),
+    ``send`` starts the copy to the device; ``stage`` does both."""
 
     def __init__(self, depth: int = 4):
         self.depth = depth
         self.buffers = [None] * depth
+        self.views = [None] * depth     # the buffers as NumPy arrays
         self.events = [None] * depth
         self.next = 0
+
+    def fill(self, packed: np.ndarray) -> int:
+        i = self.next
+        self.next = (i + 1) % self.depth
+        buf = self.buffers[i]
+        if buf is None or buf.numel() < packed.size:
+            buf = torch.empty(max(4096, 2 * packed.size), dtype=torch.int32, pin_memory=True)
+            self.buffers[i], self.views[i] = buf, buf.numpy()
+            self.events[i] = torch.cuda.Event()
+        else:
+            self.events[i].synchronize()
+        self.views[i][:packed.size] = packed
+        return i
+
+    def send(self, i: int, size: int, device: torch.device, into: Optional[torch.Tensor] = None) -> torch.Tensor:
+        buf = self.buffers[i]
+        if into is not None:
+            into.copy_(buf[:size], non_blocking=True)
+            dev = into
+        else:
+            dev = buf[:size].to(device, non_blocking=True)
+        self.events[i].record(torch.cuda.current_stream(device))
+        return dev
 
     def stage(self, packed: np.ndarray, device: torch.device, into: Optional[torch.Tensor] = None) -> torch.Tensor:
         if device.type != "cuda":
@@ -47,23 +73,7 @@ class PinnedRing:
                 into.copy_(t)
                 return into
             return t
-        i = self.next
-        self.next = (i + 1) % self.depth
-        buf = self.buffers[i]
-        if buf is None or buf.numel() < packed.size:
-            buf = torch.empty(max(4096, 2 * packed.size), dtype=torch.int32, pin_memory=True)
-            self.buffers[i] = buf
-            self.events[i] = torch.cuda.Event()
-        else:
-            self.events[i].synchronize()
-        buf[:packed.size].numpy()[:] = packed
-        if into is not None:
-            into.copy_(buf[:packed.size], non_blocking=True)
-            dev = into
-        else:
-            dev = buf[:packed.size].to(device, non_blocking=True)
-        self.events[i].record(torch.cuda.current_stream(device))
-        return dev
+        return self.send(self.fill(packed), packed.size, device, into)
 
 
 _RING = PinnedRing()
@@ -179,6 +189,7 @@ class StepContext:
         self.h2d_bytes = packed.nbytes
         self.packed_size = packed.size
         self._packed, self._offsets, self._tables = packed, offsets, tables
+        self._pinned: Optional[int] = None      # index of the page-locked buffer that holds the arrays, if filled ahead
         self.dev: Dict[str, torch.Tensor] = {}
         self.batch_c: List[K.StepBatchC] = []
         if not defer:
@@ -194,14 +205,35 @@ class StepContext:
             bad = int(tokens[(tokens < 0) | (tokens >= vocab_size)][0])
             raise StepError(f"token id {bad} is outside the vocabulary 0..{vocab_size - 1}")
         self.host["tokens"][:] = tokens
+        if self._pinned is not None:        # the arrays are in page-locked memory already: the tokens follow
+            o, n = self._offsets["tokens"]
+            _RING.views[self._pinned][o:o + n] = tokens
+
+    def fill_ahead(self) -> None:
+        """Put the arrays into page-locked memory now (a step that is prepared ahead of time: only the
+        tokens and the copy to the device are left for later)."""
+        if self.cache.device.type == "cuda" and self._pinned is None:
+            self._pinned = _RING.fill(self._packed)
+
+    def _to_device(self, static: Optional[torch.Tensor]) -> torch.Tensor:
+        if static is not None and static.numel() != self._packed.size:
+            raise StepError("the static step buffer does not fit this step's layout")
+        if self._pinned is not None:
+            i, self._pinned = self._pinned, None
+            return _RING.send(i, self._packed.size, self.cache.device, into=static)
+        return _RING.stage(self._packed, self.cache.device, into=static)
+
+    def refill(self, static: torch.Tensor) -> None:
+        """Copy the index arrays into ``static``, the buffer that a captured graph of this layout reads:
+        all that a replay needs (its kernels hold the addresses already)."""
+        self._to_device(static)
 
     def bind(self, static: Optional[torch.Tensor] = None) -> None:
-        """Copy the index arrays to the device: into a new buffer, or into ``static`` (a buffer of
-        exactly this layout's size that a captured graph reads)."""
-        packed, offsets, tables = self._packed, self._offsets, self._tables
-        if static is not None and static.numel() != packed.size:
-            raise StepError("the static step buffer does not fit this step's layout")
-        dev = _RING.stage(packed, self.cache.device, into=static)
+        """Copy the index arrays to the device, into a new buffer or into ``static`` (a buffer of
+        exactly this layout's size that a captured graph reads), and make the views that the parts and
+        the kernels read (``dev``, the plans' ``dev``, ``batch_c``)."""
+        offsets, tables = self._offsets, self._tables
+        dev = self._to_device(static)
         self.dev = {name: dev[o:o + n] for name, (o, n) in offsets.items()}
         for key, plan in self.plans.items():
             plan.dev = {name: self.dev[f"plan.{key}.{name}"] for name in plan.arrays}

@@ -23,12 +23,15 @@ class Stepper(Protocol):
     def open(self) -> int: ...
     def close(self, slot: int) -> None: ...
     def step(self, slots: Sequence[int], token_lists: Sequence[Sequence[int]]): ...
-    # optional: prepare(slots) builds the next step of one token each ahead of time
+    # optional: prepare(slots) builds the next step of one token each ahead of time;
+    #           step_ahead(slots, device_tokens) runs that step with token ids that only the device knows yet
+    #           (returns None if it cannot: the loop then waits for the tokens and calls step)
 
 
 class Selector(Protocol):
     def select(self, logits, request_ids, step, histories=None, suppress_stop=False) -> List[int]: ...
-    # optional: begin(...) launches the selection, finish(handle) waits for its tokens
+    # optional: begin(...) launches the selection, finish(handle) waits for its tokens,
+    #           device_tokens(handle) is where the device finds them before the host does
 
 
 @dataclasses.dataclass
@@ -64,6 +67,7 @@ def run_generation(stepper: Stepper, selector: Selector, prompts: Sequence[Seque
     results = [RequestResult(prompt=list(p), tokens=[]) for p in prompts]
     # a stepper that can prepare a step ahead and a selector that can run without the host waiting
     can_overlap = all(hasattr(selector, n) for n in ("begin", "finish")) and hasattr(stepper, "prepare")
+    can_pipeline = can_overlap and hasattr(stepper, "step_ahead") and hasattr(selector, "device_tokens")
     for batch in plan_batches(len(prompts), max_batch):
         held = set()
         live = []
@@ -75,19 +79,28 @@ def run_generation(stepper: Stepper, selector: Selector, prompts: Sequence[Seque
             logits = stepper.step([s for _, s in live], [results[r].prompt for r, _ in live])
             for t in range(budget):
                 req_ids = [r for r, _ in live]
+                slots = [s for _, s in live]
                 histories = ([results[r].prompt + results[r].tokens for r in req_ids]
                              if options.repetition_penalty != 1.0 else None)
-                if can_overlap and t + 1 < budget:
-                    # the selection runs on the device; meanwhile the host builds the next step of one
-                    # token each for the sequences that are live now (used if none of them ends here)
-                    pending = selector.begin(logits, req_ids, t, histories=histories,
-                                             suppress_stop=bool(stop) and t < min_new)
-                    stepper.prepare([s for _, s in live])
+                suppress = bool(stop) and t < min_new
+                ahead = None
+                if can_overlap:
+                    # The selection runs on the device without the host waiting. Meanwhile the host builds
+                    # the next step of one token each for the sequences that are live now and, if the
+                    # stepper can take its tokens from the device, launches it at once: the device then
+                    # goes from this step's selection straight into the next step, and the host reads the
+                    # tokens (for the results, the stop tokens and the callback) while that step runs.
+                    # A sequence that turns out to end here was in that step for nothing: its row is
+                    # dropped.
+                    pending = selector.begin(logits, req_ids, t, histories=histories, suppress_stop=suppress)
+                    if t + 1 < budget:
+                        stepper.prepare(slots)
+                        if can_pipeline:
+                            ahead = stepper.step_ahead(slots, selector.device_tokens(pending))
                     chosen = selector.finish(pending)
                 else:
-                    chosen = selector.select(logits, req_ids, t, histories=histories,
-                                             suppress_stop=bool(stop) and t < min_new)
-                still = []
+                    chosen = selector.select(logits, req_ids, t, histories=histories, suppress_stop=suppress)
+                still, kept_rows = [], []
                 for row, ((r, slot), tok) in enumerate(zip(live, chosen)):
                     res = results[r]
                     res.tokens.append(int(tok))
@@ -106,10 +119,15 @@ def run_generation(stepper: Stepper, selector: Selector, prompts: Sequence[Seque
                         stepper.close(slot)       # the slot is free for the next batch right away
                     else:
                         still.append((r, slot))
+                        kept_rows.append(row)
+                n_before = len(live)
                 live = still
                 if not live:
                     break
-                logits = stepper.step([s for _, s in live], [[results[r].tokens[-1]] for r, _ in live])
+                if ahead is not None:
+                    logits = ahead if len(live) == n_before else ahead[kept_rows]
+                else:
+                    logits = stepper.step([s for _, s in live], [[results[r].tokens[-1]] for r, _ in live])
         finally:
             for slot in sorted(held):             # only after an error: what is still open goes back
                 stepper.close(slot)

@@ -31,6 +31,8 @@ class CausalLM:
         self.build = BuildContext(device=self.device, dtype=dtype, kernels=kernels)
         self.blocks: List[Part] = [make_part(self.build, b) for b in spec.blocks]
         self.final_norm: Part = make_part(self.build, spec.final_norm)
+        self.embedding_norm: Optional[Part] = (make_part(self.build, spec.embedding_norm)
+                                               if spec.embedding_norm is not None else None)
         self.schedule = spec.resolved_schedule()
         for e in self.schedule:
             if not (0 <= e.block < len(self.blocks)):
@@ -43,18 +45,21 @@ class CausalLM:
         self.head: Optional[torch.Tensor] = None
         self.status = None  # device int32 word raised by kernels that clamp a bad index
         # replay steps of single tokens as CUDA graphs, if every part allows it
-        self.use_graphs = all(p.graph_safe for top in self.blocks + [self.final_norm] for p in top.walk())
+        self.use_graphs = all(p.graph_safe for top in self._top_parts() for p in top.walk())
         self.last_h2d_bytes = 0
         self._side_stream = None
         # what the parts ask of every step: their planners (one per plan_key) and the mixers' word on streams
         self.planners, seen = [], set()
-        for top in self.blocks + [self.final_norm]:
+        for top in self._top_parts():
             for part in top.walk():
                 planner = part.planner()
                 if planner is not None and planner.plan_key not in seen:
                     seen.add(planner.plan_key)
                     self.planners.append(planner)
         self._mixers = [b.children["mixer"] for b in self.blocks if "mixer" in b.children]
+
+    def _top_parts(self) -> List[Part]:
+        return self.blocks + [self.final_norm] + ([self.embedding_norm] if self.embedding_norm is not None else [])
 
     # ------------------------------------------------------------------ parameters
     def param_table(self) -> Dict[str, Tuple[Optional[Part], str, ParamDecl]]:
@@ -64,7 +69,7 @@ class CausalLM:
         table[self.spec.embedding_name] = (None, "embedding", ParamDecl((v, h)))
         if self.spec.head_name is not None:
             table[self.spec.head_name] = (None, "head", ParamDecl((v, h)))
-        for top in self.blocks + [self.final_norm]:
+        for top in self._top_parts():
             for part in top.walk():
                 for logical, decl in part.param_decls().items():
                     try:
@@ -105,7 +110,7 @@ class CausalLM:
     def weight_bytes(self) -> int:
         seen, total = set(), 0
         tensors = [self.embedding, self.head]
-        for top in self.blocks + [self.final_norm]:
+        for top in self._top_parts():
             for part in top.walk():
                 tensors += [getattr(part, a) for a in vars(part) if a.startswith("p_")]
         for t in tensors:
@@ -113,6 +118,18 @@ class CausalLM:
                 seen.add(t.data_ptr())
                 total += t.numel() * t.element_size()
         return total
+
+    def check_errors(self) -> None:
+        """Raise if a kernel has reported trouble since the last check (synchronises): a row index that
+        had to be clamped (a token id or a wanted row that was wrong on the device although the host
+        had checked it, say in a buffer that a graph replays), or a bounded wait that ran out."""
+        if self.status is not None:
+            code = int(self.status.item())
+            if code != 0:
+                self.status.zero_()
+                raise K.KernelError(f"a row index was out of range on the device (status {code}): the step's "
+                                    "results are void")
+        self.build.kernels.check_device_errors(self.device)
 
     # ------------------------------------------------------------------ cache
     def cache_needs(self):
@@ -151,16 +168,11 @@ class CausalLM:
             else:
                 raise StepError(f"want must be 'last', 'all', 'none' or lists of positions, got {want!r}")
         single = all(len(t) == 1 for t in token_lists) and all(list(w) == [0] for w in want)
-        prepared = cache.__dict__.pop("_prepared_step", None)     # whatever was prepared is used now or never
+        ctx = self._take_prepared(cache, slots)     # whatever was prepared is used now or never
         if single and self.use_graphs and self.device.type == "cuda":
-            ctx = None
-            if prepared is not None:
-                owner, epoch, ahead = prepared
-                if (owner == id(self) and epoch == cache.epoch and ahead.slots == [int(s) for s in slots]
-                        and ahead.past == [cache.length(s) for s in ahead.slots]):
-                    ahead.set_tokens(token_lists, self.spec.vocab_size)
-                    ctx = ahead
-            if ctx is None:
+            if ctx is not None:
+                ctx.set_tokens(token_lists, self.spec.vocab_size)
+            else:
                 ctx = StepContext(cache, slots, token_lists, self.spec.vocab_size, want, self.planners,
                                   page_bucket=self.GRAPH_PAGE_BUCKET, defer=True)
             return self._step_graph(cache, ctx)
@@ -194,8 +206,44 @@ class CausalLM:
                                 page_bucket=self.GRAPH_PAGE_BUCKET, defer=True)
         except CacheFull:
             return False
+        ahead.fill_ahead()
         cache.__dict__["_prepared_step"] = (id(self), cache.epoch, ahead)
         return True
+
+    def _take_prepared(self, cache: Cache, slots: Sequence[int]) -> Optional[StepContext]:
+        """The step that prepare_next built, if it is the step for ``slots`` now; whatever was prepared
+        is used now or never."""
+        prepared = cache.__dict__.pop("_prepared_step", None)
+        if prepared is None:
+            return None
+        owner, epoch, ahead = prepared
+        if (owner == id(self) and epoch == cache.epoch and ahead.slots == [int(s) for s in slots]
+                and ahead.past == [cache.length(s) for s in ahead.slots]):
+            return ahead
+        return None
+
+    def step_ahead(self, cache: Cache, slots: Sequence[int], device_tokens: torch.Tensor) -> Optional[torch.Tensor]:
+        """Run the prepared step of one token each for ``slots`` with token ids that are on the device
+        only (``device_tokens``: int32 [len(slots)], typically what the selection kernel of the step
+        before wrote; they are read in stream order, so the selection need not have finished). Returns
+        the logits as ``step`` does, or None when there is no prepared step for these slots or no
+        captured graph for its layout yet: the caller then waits for the tokens and calls ``step``.
+        The ids are not checked against the vocabulary here: they come from the selection kernel."""
+        ctx = self._take_prepared(cache, slots)
+        if ctx is None:
+            return None
+        entry = cache.__dict__.get("_step_graphs", {}).get((id(self), ctx.layout_key))
+        if entry is None or device_tokens.dtype != torch.int32 or device_tokens.numel() < ctx.n_tokens:
+            cache.__dict__["_prepared_step"] = (id(self), cache.epoch, ctx)     # still good for step()
+            return None
+        ctx.refill(entry["static"])
+        o, n = ctx._offsets["tokens"]
+        entry["static"][o:o + n].copy_(device_tokens[:n], non_blocking=True)
+        self.last_h2d_bytes = ctx.h2d_bytes
+        entry["graph"].replay()
+        K.launches += entry["launches"]
+        ctx.commit()
+        return entry["out"].clone()
 
     def _step_graph(self, cache: Cache, ctx: StepContext) -> torch.Tensor:
         # graphs live on the cache they were captured for (they hold pointers into its storage)
@@ -224,7 +272,7 @@ class CausalLM:
             self.last_h2d_bytes = ctx.h2d_bytes
             ctx.commit()
             return first
-        ctx.bind(entry["static"])
+        ctx.refill(entry["static"])
         self.last_h2d_bytes = ctx.h2d_bytes
         entry["graph"].replay()
         K.launches += entry["launches"]
@@ -248,6 +296,10 @@ class CausalLM:
                 self._side_stream = torch.cuda.Stream(device=self.device)
             ctx.side_stream = self._side_stream
         x = k.gather_rows(ctx.dev["tokens"], self.embedding, self.status)
+        if self.spec.embedding_scale != 1.0:
+            k.scale_(x, self.spec.embedding_scale)
+        if self.embedding_norm is not None:
+            x = self.embedding_norm.forward(x)
         for entry in self.schedule:
             x = self.blocks[entry.block].forward(x, ctx, entry)   # a tensor, or a DeferredSum of two branches
         x = resolve(k, x)
@@ -258,10 +310,15 @@ class CausalLM:
         return self.logits(rows)
 
     def logits(self, rows: torch.Tensor) -> torch.Tensor:
-        """float32 logits of normed rows: rows @ head.T (no bias, modeling_falcon.py:1168)."""
+        """float32 logits of normed rows: rows @ head.T (no bias, modeling_falcon.py:1168), times the
+        spec's logit_scale where an architecture has one."""
         k = self.build.kernels
         if self.dtype == torch.float32:
-            return k.linear_f32(rows, self.head)
-        if k.skinny_linear_preferred(rows.shape[0], rows.shape[1], self.head.shape[0]):
-            return k.skinny_linear(rows, self.head, out_dtype=torch.float32)
-        return k.matmul_nt(rows, self.head, out_dtype=torch.float32)
+            out = k.linear_f32(rows, self.head)
+        elif k.skinny_linear_preferred(rows.shape[0], rows.shape[1], self.head.shape[0]):
+            out = k.skinny_linear(rows, self.head, out_dtype=torch.float32)
+        else:
+            out = k.matmul_nt(rows, self.head, out_dtype=torch.float32)
+        if self.spec.logit_scale != 1.0:
+            k.scale_(out, self.spec.logit_scale)
+        return out

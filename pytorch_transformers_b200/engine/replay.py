@@ -47,7 +47,7 @@ def replay(model, cache, lines, out_dir: str, log: IO = sys.stdout) -> None:
             logits = model.step(cache, ids, token_lists, want)
             if logits.shape[0] > 0:
                 arr = logits.detach().float().cpu().numpy().astype("<f4", copy=False)
-                model.build.kernels.check_device_errors(model.device)
+                model.check_errors()
                 tmp = os.path.join(out_dir, f".{step}.f32.tmp")
                 arr.tofile(tmp)
                 os.replace(tmp, os.path.join(out_dir, f"{step}.f32"))

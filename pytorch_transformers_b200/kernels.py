@@ -81,7 +81,7 @@ def lib():
                      "ptb_rope_table", "ptb_attention_decode", "ptb_attention_tc", "ptb_attention_tc_supports",
                      "ptb_attention_tc_tile_tokens", "ptb_tc_linear", "ptb_tc_linear_max_rows",
                      "ptb_tc_linear_k_multiple", "ptb_attention_decode_tc", "ptb_attention_decode_tc_supports",
-                     "ptb_fill_normal", "ptb_selftest_bounded_wait"):
+                     "ptb_fill_normal", "ptb_selftest_bounded_wait", "ptb_scale"):
             getattr(L, name).restype = ctypes.c_int
         _configured = True
     return L
@@ -136,6 +136,14 @@ def residual(x: torch.Tensor, a: torch.Tensor, b: Optional[torch.Tensor] = None)
     _check(lib().ptb_residual(_dtype_code(x), _ptr(x), _ptr(a), _ptr(b), _ptr(out), ctypes.c_longlong(x.numel()),
                               _stream(x)), "residual")
     return out
+
+
+def scale_(x: torch.Tensor, factor: float) -> torch.Tensor:
+    """x *= factor in place (float32 product, one rounding)."""
+    _need_cuda(x)
+    _check(lib().ptb_scale(_dtype_code(x), _ptr(x), ctypes.c_float(factor), ctypes.c_longlong(x.numel()), _stream(x)),
+           "scale")
+    return x
 
 
 def to_float(x: torch.Tensor) -> torch.Tensor:

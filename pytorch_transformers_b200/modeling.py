@@ -74,6 +74,9 @@ class _CacheStepper:
     def prepare(self, slots) -> None:
         self.model.prepare_next(self.cache, slots)
 
+    def step_ahead(self, slots, device_tokens):
+        return self.model.step_ahead(self.cache, slots, device_tokens)
+
     def step(self, slots, token_lists):
         total = sum(len(t) for t in token_lists)
         if total <= self.max_step_tokens:
@@ -205,7 +208,7 @@ class PreTrainedCausalLM(CausalLM):
         results = run_generation(_CacheStepper(self, cache, max_step_tokens), selector, expanded, opts, budget, max_batch,
                                  on_token=_on_token if on_token is not None else None,
                                  keep_logits=opts.output_logits)
-        self.build.kernels.check_device_errors(self.device)
+        self.check_errors()
         if streamer is not None:
             # the reference pushes the prompt and then every step's tokens (streamers.py:27-233);
             # with unequal lengths per request we hand over each finished request once

@@ -103,6 +103,10 @@ class ModelSpec:
     final_norm: PartSpec
     head_name: Optional[str]          # None: the head shares the embedding table
     schedule: Optional[List[ScheduleEntry]] = None
+    # what some architectures do between the table and the first block, and after the head (Falcon: nothing)
+    embedding_scale: float = 1.0                  # x = table[ids] * embedding_scale
+    embedding_norm: Optional[PartSpec] = None     # then a norm of the embeddings
+    logit_scale: float = 1.0                      # logits = (rows @ head.T) * logit_scale
 
     def resolved_schedule(self) -> List[ScheduleEntry]:
         if self.schedule is not None:

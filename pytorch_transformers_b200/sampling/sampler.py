@@ -42,6 +42,11 @@ class DeviceSelector:
         ``histories[r]`` are the tokens that the repetition penalty looks at."""
         return self.finish(self.begin(logits, request_ids, step, histories, suppress_stop))
 
+    def device_tokens(self, rows: int) -> torch.Tensor:
+        """The tokens of the selection that ``begin`` started, on the device (int32 [rows]): a step may
+        read them there (in stream order) before the host has them."""
+        return self.out[:rows]
+
     def finish(self, rows: int) -> List[int]:
         """Wait for the tokens of the selection that ``begin`` started and return them."""
         self._landed.synchronize()

@@ -141,3 +141,31 @@ def test_random_traffic_keeps_the_invariants():
     c.close_all()
     c.check()
     assert c.groups[0].pool.in_use == 0 and c.slots.in_use == 0
+
+
+def test_another_cache_kind_is_registered_not_edited_in():
+    """A kind of cache entry is a rule that says which positions later queries may still read; pages
+    wholly before them go back to the pool after every step. Here: chunks of 128 tokens, a query reads
+    its own chunk only."""
+    from pytorch_transformers_b200.cache.paged import CACHE_KINDS, register_cache_kind
+    register_cache_kind("chunk128", lambda need, length: length // 128 * 128)
+    try:
+        cache = Cache([(0, CacheNeed("chunk128", 1, 16), None), (1, CacheNeed("full", 1, 16), None)], 64 * 16,
+                      torch.float32, "cpu")
+        chunked = next(i for i, g in enumerate(cache.groups) if g.need.kind == "chunk128")
+        full = 1 - chunked
+        s = cache.open()
+        for n in (100, 100, 100):
+            cache.reserve(s, n)
+            cache.commit(s, n)
+        # 300 tokens: the chunk in use starts at 256; the pages of positions 0..255 are back in the pool
+        assert cache.pages(s, chunked)[:4] == [-1] * 4 and all(p >= 0 for p in cache.pages(s, chunked)[4:])
+        assert all(p >= 0 for p in cache.pages(s, full)) and len(cache.pages(s, full)) == 5
+        assert cache.groups[chunked].pool.in_use == 1 and cache.groups[full].pool.in_use == 5
+        cache.check()
+        cache.close(s)
+        assert cache.groups[chunked].pool.in_use == 0
+        with pytest.raises(ValueError, match="unknown cache kind"):
+            Cache([(0, CacheNeed("ring", 1, 16), None)], 64, torch.float32, "cpu")
+    finally:
+        del CACHE_KINDS["chunk128"]

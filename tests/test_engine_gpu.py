@@ -561,3 +561,43 @@ def test_generation_with_steps_prepared_ahead_gives_the_same_tokens(loaded, dtyp
     assert ahead.sequences == plain_way.sequences
     for a, b in zip(ahead.logits, plain_way.logits):
         assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_a_step_launched_with_tokens_that_only_the_device_knows(loaded, dtype):
+    """step_ahead runs the prepared step with token ids taken on the device (here: a tensor; in the
+    generation loop the selection kernel's output, before the host has read it). It needs a prepared
+    step and a captured graph of its layout, else it answers None and changes nothing."""
+    L = loaded("E", dtype)
+    model = L.model
+    reqs = tm.prompts("E", (40, 72), seed=43)
+    refs = [L.plain_logits(r) for r in reqs]
+    heads = [30, 62]
+    cache = model.new_cache(64 * 6)
+    slots = [cache.open() for _ in reqs]
+    model.step(cache, slots, [r[:h] for r, h in zip(reqs, heads)], want="none")
+
+    def dev(t):
+        return torch.tensor([r[h + t] for r, h in zip(reqs, heads)], dtype=torch.int32, device="cuda")
+
+    assert model.step_ahead(cache, slots, dev(0)) is None                 # nothing was prepared
+    assert model.prepare_next(cache, slots)
+    assert model.step_ahead(cache, slots, dev(0)) is None                 # no graph of this layout yet
+    assert [cache.length(s) for s in slots] == heads                      # and nothing has moved
+    out = model.step(cache, slots, [[r[h]] for r, h in zip(reqs, heads)])  # uses the prepared step, captures the graph
+    for t in range(1, 4):                                                 # request 1 crosses a page boundary (64)
+        for row in range(2):
+            close(out[row], refs[row][heads[row] + t - 1], dtype, f"step {t - 1}, request {row}")
+        assert model.prepare_next(cache, slots)
+        out = model.step_ahead(cache, slots, dev(t))
+        if out is None:                                                   # a wider page table: a new layout
+            out = model.step(cache, slots, [[r[h + t]] for r, h in zip(reqs, heads)])
+    for row in range(2):
+        close(out[row], refs[row][heads[row] + 3], dtype, f"last step, request {row}")
+    assert [cache.length(s) for s in slots] == [h + 4 for h in heads]
+    # other slots than the prepared ones: refused, and the next plain step is right
+    assert model.prepare_next(cache, slots)
+    assert model.step_ahead(cache, slots[:1], dev(4)[:1]) is None
+    out = model.step(cache, slots, [[r[h + 4]] for r, h in zip(reqs, heads)])
+    close(out[1], refs[1][heads[1] + 4], dtype, "after a refused step ahead")
+    model.build.kernels.check_device_errors("cuda")

@@ -177,3 +177,48 @@ def test_the_next_step_is_prepared_while_the_selection_runs_and_changes_no_token
     # a stepper or a selector without the optional methods is driven the plain way
     results = run_generation(FakeStepper(), TwoPhaseSelector([13]), prompts, opts, 5, 3)
     assert [r.tokens for r in results] == [r.tokens for r in plain_results]
+
+
+class PipelinedStepper(PreparingStepper):
+    """A stepper that can also run the prepared step with token ids that only the 'device' knows: here
+    the device is a list that the selector fills."""
+
+    def __init__(self, max_slots=4, refuse_every=0):
+        super().__init__(max_slots)
+        self.ahead = []
+        self.refuse_every = refuse_every
+
+    def step_ahead(self, slots, device_tokens):
+        assert self.prepared and self.prepared[-1] == (len(self.calls), list(slots)), "step_ahead without its preparation"
+        if self.refuse_every and (len(self.ahead) + len(self.calls)) % self.refuse_every == 0:
+            return None                                       # "no graph for this layout yet"
+        self.ahead.append(list(slots))
+        return self.step(slots, [[t] for t in device_tokens])
+
+
+class DeviceSelectorFake(TwoPhaseSelector):
+    def device_tokens(self, handle):
+        return list(self.open_handle)          # on the device the tokens exist as soon as the kernel has run
+
+
+@pytest.mark.parametrize("refuse_every", [0, 3])
+def test_steps_launched_ahead_with_device_tokens_give_the_same_results(refuse_every):
+    prompts = [[3, 4], [10], [20, 21, 22], [40], [47, 48]]
+    opts = GenerationConfig(eos_token_id=[13, 49], min_new_tokens=2)     # requests 1 and 4 stop early
+    want = run_generation(FakeStepper(), ArgmaxSelector([13, 49]), prompts, opts, 6, 3, keep_logits=True)
+    seen = []
+    stepper, selector = PipelinedStepper(refuse_every=refuse_every), DeviceSelectorFake([13, 49])
+    got = run_generation(stepper, selector, prompts, opts, 6, 3, keep_logits=True,
+                         on_token=lambda r, tok: seen.append((r, tok)))
+    assert [r.tokens for r in got] == [r.tokens for r in want]
+    assert [r.finish_reason for r in got] == [r.finish_reason for r in want]
+    for a, b in zip(got, want):
+        assert len(a.logits) == len(b.logits) and all(torch.equal(x, y) for x, y in zip(a.logits, b.logits))
+    assert [tok for r, tok in seen if r == 1] == got[1].tokens
+    assert stepper.ahead                                                  # steps did run ahead
+    # request 1 ended at its third token ([11, 12, 13]); the step launched ahead of that selection still had
+    # its slot in it, and its row was dropped: the steps after it name the other two slots only
+    assert got[1].tokens == [11, 12, 13] and got[1].finish_reason == "stop"
+    first_batch = [c[0] for c in stepper.calls[1:] if 1 in c[0] or c[0] == [0, 2]]
+    assert first_batch.count([0, 1, 2]) == 3 and [0, 2] in first_batch
+    assert sorted(stepper.free) == [0, 1, 2, 3] and not stepper.length    # every slot came back once

@@ -645,3 +645,67 @@ def test_a_stateful_mixer_under_graph_replay_updates_its_state_once_per_step():
     normed = emb / torch.sqrt((emb ** 2).mean(-1, keepdim=True) + 1e-5) * gain
     want = sum(0.5 ** (len(seqs[0]) - 1 - k) * normed[k] for k in range(len(seqs[0])))
     torch.testing.assert_close(cache.entry_state(0)[slot], want, atol=1e-5, rtol=1e-5)
+
+
+# ------------------------------------------ a toy with a scale and a norm on the embeddings, a scale on the logits
+def _register_toy_scaled():
+    import pytorch_transformers_b200 as ptb
+    from pytorch_transformers_b200.config.base import ModelConfig
+    from pytorch_transformers_b200.parts import ModelSpec, PartSpec
+
+    @dataclasses.dataclass
+    class ToyScaledConfig(ModelConfig):
+        model_type: ClassVar[str] = "toy_scaled"
+        vocab_size: int = 60
+        hidden_size: int = 48
+        heads: int = 3
+
+    def spec(cfg):
+        d = cfg.hidden_size // cfg.heads
+        ln = lambda n: PartSpec("norm", "layernorm", {"size": cfg.hidden_size, "eps": 1e-5, "bias": True},
+                                names={"weight": n + ".weight", "bias": n + ".bias"})
+        mixer = PartSpec("mixer", "attention", {"hidden": cfg.hidden_size, "heads": cfg.heads, "kv_heads": 1, "head_dim": d},
+                         children={"position": PartSpec("position", "rotary", {"head_dim": d, "theta": 1000.0})},
+                         names={"qkv.weight": "b.attn.qkv.weight", "out.weight": "b.attn.out.weight"})
+        ff = PartSpec("feed_forward", "dense", {"hidden": cfg.hidden_size, "inner": 64, "activation": "gelu"},
+                      names={"up.weight": "b.ff.up.weight", "down.weight": "b.ff.down.weight"})
+        block = PartSpec("block", "parallel", children={"norm_mixer": ln("b.ln"), "mixer": mixer, "feed_forward": ff})
+        return ModelSpec(cfg.vocab_size, cfg.hidden_size, "embed.weight", [block], ln("final"), None,
+                         embedding_scale=math.sqrt(cfg.hidden_size), embedding_norm=ln("embed_ln"), logit_scale=0.25)
+
+    ptb.register_architecture("toy_scaled", ("ToyScaled",), ToyScaledConfig, spec)
+    return ToyScaledConfig
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_toy_architecture_with_scaled_and_normed_embeddings_and_scaled_logits(tmp_path, dtype):
+    """What some architectures do between the table and the first block and after the head is data of the
+    ModelSpec (embedding_scale, embedding_norm, logit_scale), not an edit of the engine."""
+    import pytorch_transformers_b200 as ptb
+    Cfg = _register_toy_scaled()
+    cfg = Cfg()
+    folder = ptb.write_random_model(cfg, seed=8, folder=str(tmp_path / "scaled"), dtype=getattr(torch, dtype))
+    model = ptb.AutoModelForCausalLM.from_pretrained(folder, dtype=dtype)
+    assert "embed_ln.weight" in model.param_table() and model.embedding_norm is not None
+    _, w = plain.load_folder(folder, torch.float64)
+    ids = torch.randint(0, 60, (23,), generator=torch.Generator().manual_seed(1)).tolist()
+    c = {"num_attention_heads": 3, "hidden_size": 48, "new_decoder_architecture": False, "multi_query": True,
+         "rope_theta": 1000.0, "rope_scaling": None}
+    x = w["embed.weight"][torch.tensor(ids)] * math.sqrt(48)
+    if dtype == "bfloat16":
+        x = x.bfloat16().double()
+    x = plain.layer_norm(x, w["embed_ln.weight"], w["embed_ln.bias"], 1e-5)
+    a = plain.layer_norm(x, w["b.ln.weight"], w["b.ln.bias"], 1e-5)
+    q, k, v = plain.split_heads(a @ w["b.attn.qkv.weight"].T, c)
+    pos, inv = torch.arange(len(ids)), plain.rope_inv_freq(c)
+    attn = plain.attention_core(plain.rotary(q, pos, inv), plain.rotary(k, pos, inv), v, c) @ w["b.attn.out.weight"].T
+    ff = plain.activation(a @ w["b.ff.up.weight"].T, "gelu") @ w["b.ff.down.weight"].T
+    x = x + (ff + attn)
+    ref = plain.layer_norm(x, w["final.weight"], w["final.bias"], 1e-5) @ w["embed.weight"].T * 0.25
+    cache = model.new_cache(64)
+    slot = cache.open()
+    got = torch.cat([model.step(cache, [slot], [ids[:20]], want="all")] +
+                    [model.step(cache, [slot], [[t]]) for t in ids[20:]])
+    tol = dict(atol=2e-5, rtol=1e-4) if dtype == "float32" else dict(atol=3e-2, rtol=3e-2)
+    torch.testing.assert_close(got.double().cpu(), ref, **tol)
+    model.check_errors()
