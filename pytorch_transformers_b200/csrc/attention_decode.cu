@@ -28,7 +28,7 @@ namespace {
 constexpr int STAGES = 3;
 
 struct DecodeParams {
-  int heads, kv_heads, hpk, n_splits, n_teams, rot_pairs, write_cache, window;
+  int heads, kv_heads, hpk, n_splits, n_teams, rot_pairs, write_cache, window, interleaved;
   float scale;
   float* team_parts;   // [n_seqs][kv_heads * chunks][n_teams][hpk][D + 2] float32 when n_teams > 1
   int* tickets;        // [n_seqs][kv_heads * chunks][n_splits], zero before and after the launch
@@ -71,7 +71,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ fused, __nv_bfloat16* 
   const __nv_bfloat16* frow = fused + size_t(tok) * fused_width + size_t(g) * (qpk + 2) * D;
   const float* rc = rope_cos ? rope_cos + size_t(tok) * p.rot_pairs : nullptr;
   const float* rs = rope_sin ? rope_sin + size_t(tok) * p.rot_pairs : nullptr;
-  const int P = rc ? p.rot_pairs : 0;          // pairs (e, e + P) are rotated for e < P
+  const int P = rc ? p.rot_pairs : 0;          // pairs (e, e + P), or (2 e, 2 e + 1), are rotated for e < P
 
   bool row_ok[2];
   int row_head[2];
@@ -130,9 +130,10 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ fused, __nv_bfloat16* 
     const int r = idx / P, e = idx % P;
     __nv_bfloat16* row = rowbuf + size_t(r < head_valid ? r : p.hpk) * D;
     float ra, rb;
-    rotate_pair(__bfloat162float(row[e]), __bfloat162float(row[e + P]), cs[e], cs[P + e], ra, rb);
-    row[e] = __float2bfloat16_rn(ra);
-    row[e + P] = __float2bfloat16_rn(rb);
+    const int ia = p.interleaved ? 2 * e : e, ib = p.interleaved ? 2 * e + 1 : e + P;   // the pair's two dims
+    rotate_pair(__bfloat162float(row[ia]), __bfloat162float(row[ib]), cs[e], cs[P + e], ra, rb);
+    row[ia] = __float2bfloat16_rn(ra);
+    row[ib] = __float2bfloat16_rn(rb);
   }
   __syncthreads();
   const __nv_bfloat16* krow = rowbuf + size_t(p.hpk) * D;   // rotated key, value
@@ -455,9 +456,10 @@ PTB_API int ptb_attention_decode_max_splits() { return 8; }
 // (head_dim + 2) floats) and `tickets` (n_seqs * kv_heads * chunks * n_splits ints, zero before the launch
 // and after it). key_split 1, 2 or 4 groups
 // of `warps` warps each share the keys of every page (warps * key_split <= 10 for head size 64, 8 for 128). rope_cos/sin:
-// [n_seqs, rot_pairs] float32 tables for the step's tokens, or null for no rotation.
+// [n_seqs, rot_pairs] float32 tables for the step's tokens, or null for no rotation; the rotated pairs are
+// (e, e + rot_pairs), or with `interleaved` (2 e, 2 e + 1).
 PTB_API int ptb_attention_decode(const void* fused, void* k_pool, void* v_pool, void* out, const StepBatch* sb,
-                                 const float* rope_cos, const float* rope_sin, int rot_pairs,
+                                 const float* rope_cos, const float* rope_sin, int rot_pairs, int interleaved,
                                  const float* alibi_slopes, int heads, int kv_heads, int head_dim, int hpk,
                                  int n_splits, int n_teams, int warps, int key_split, float scale, int window,
                                  int write_cache, float* team_parts, size_t team_floats, int* tickets, int n_tickets,
@@ -483,6 +485,7 @@ PTB_API int ptb_attention_decode(const void* fused, void* k_pool, void* v_pool, 
   DecodeParams p;
   p.heads = heads; p.kv_heads = kv_heads; p.hpk = hpk; p.n_splits = n_splits; p.n_teams = n_teams;
   p.rot_pairs = rot_pairs; p.write_cache = write_cache; p.window = window; p.scale = scale;
+  p.interleaved = interleaved ? 1 : 0;
   p.team_parts = team_parts; p.tickets = tickets;
 #define PTB_DECODE(DD, KK) \
   return launch_decode<DD, KK>(fused, k_pool, v_pool, out, *sb, rope_cos, rope_sin, alibi_slopes, p, warps, stream)

@@ -53,7 +53,7 @@ template <int RS> __device__ __forceinline__ uint32_t swz_blk(int row, int c) {
 }
 
 struct DecodeTcParams {
-  int heads, kv_heads, n_splits, n_teams, rot_pairs, write_cache;
+  int heads, kv_heads, n_splits, n_teams, rot_pairs, write_cache, interleaved;
   float scale;
 };
 constexpr int PART = DD + 2;     // floats of a row in the teams' workspace: output, maximum, sum
@@ -110,7 +110,7 @@ attention_decode_tc_kernel(const __nv_bfloat16* __restrict__ fused, __nv_bfloat1
   const int active_warps = (qpk + 31) / 32;
   // The usual rotation (the halves of the head, or none) is done in registers, a thread per head; any
   // other number of rotated pairs goes the general way through shared memory.
-  const bool in_registers = P == DD / 2 || P == 0;
+  const bool in_registers = (P == DD / 2 && !p.interleaved) || P == 0;
   if (tid == 0) {
     for (int b = 0; b < 2; ++b) {
       mbar_init(bar_s + 8 * b, 1);
@@ -213,9 +213,10 @@ attention_decode_tc_kernel(const __nv_bfloat16* __restrict__ fused, __nv_bfloat1
       const int r = idx / P, e = idx % P;
       __nv_bfloat16* row = rowbuf + size_t(r < qpk ? r : ROWS) * DD;
       float ra, rb;
-      rotate_pair(__bfloat162float(row[e]), __bfloat162float(row[e + P]), cs[e], cs[P + e], ra, rb);
-      row[e] = __float2bfloat16_rn(ra);
-      row[e + P] = __float2bfloat16_rn(rb);
+      const int ia = p.interleaved ? 2 * e : e, ib = p.interleaved ? 2 * e + 1 : e + P;   // the pair's two dims
+      rotate_pair(__bfloat162float(row[ia]), __bfloat162float(row[ib]), cs[e], cs[P + e], ra, rb);
+      row[ia] = __float2bfloat16_rn(ra);
+      row[ib] = __float2bfloat16_rn(rb);
     }
     softmax_sync();
     const __nv_bfloat16* krow = rowbuf + size_t(ROWS) * DD;   // rotated key, then the value
@@ -533,11 +534,11 @@ static bool decode_tc_configure() {
 // [n_seqs, heads * 64]. n_teams clusters of n_splits (1 to 8) blocks share a sequence's pages; more than
 // one team needs `team_parts` (n_seqs * kv_heads * n_teams * q_per_kv * 66 floats) and `tickets`
 // (n_seqs * kv_heads * n_splits ints, zero before the launch and after it). rope_cos / rope_sin:
-// [n_seqs, rot_pairs] float32 tables for the step's tokens, or null for no rotation. No score bias, no
-// window. `error_flag`: a device int that stays 0 unless a bounded wait inside the kernel ran out.
+// [n_seqs, rot_pairs] float32 tables for the step's tokens, or null for no rotation (pairs (e, e + rot_pairs),
+// or with `interleaved` (2 e, 2 e + 1)). No score bias, no window. `error_flag`: a device int that stays 0 unless a bounded wait inside the kernel ran out.
 PTB_API int ptb_attention_decode_tc(const void* fused, void* k_pool, void* v_pool, int pool_pages, void* out,
                                     const StepBatch* sb, const float* rope_cos, const float* rope_sin, int rot_pairs,
-                                    int heads, int kv_heads, int head_dim, int n_splits, int n_teams, float scale,
+                                    int interleaved, int heads, int kv_heads, int head_dim, int n_splits, int n_teams, float scale,
                                     int write_cache, float* team_parts, size_t team_floats, int* tickets, int n_tickets,
                                     int* error_flag, cudaStream_t stream) {
   if (sb->n_seqs <= 0) return PTB_OK;
@@ -562,7 +563,7 @@ PTB_API int ptb_attention_decode_tc(const void* fused, void* k_pool, void* v_poo
   if (km == nullptr || vm == nullptr) return PTB_ERR_LAUNCH;
   DecodeTcParams p;
   p.heads = heads; p.kv_heads = kv_heads; p.n_splits = n_splits; p.n_teams = n_teams; p.rot_pairs = rot_pairs;
-  p.write_cache = write_cache; p.scale = scale;
+  p.write_cache = write_cache; p.scale = scale; p.interleaved = interleaved ? 1 : 0;
   const size_t smem = decode_tc_smem();
   if (!decode_tc_configure()) return PTB_ERR_LAUNCH;
   cudaLaunchConfig_t cfg = {};

@@ -20,7 +20,8 @@ constexpr int DPT = MAX_D / 8;
 // Fused projection [n_tokens, kv_heads * (q_per_kv + 2) * head_dim], rows grouped per K/V head as
 // (q_per_kv query heads, K, V), to: q_out [n_tokens, heads, head_dim] (query head = group *
 // q_per_kv + index in group) and the K and V pools of one layer. With inv_freq != nullptr the
-// first 2 * rot_pairs dims of every query and key head are rotated: pairs (i, i + rot_pairs),
+// first 2 * rot_pairs dims of every query and key head are rotated: pairs (i, i + rot_pairs), or with
+// `interleaved` pairs (2 i, 2 i + 1);
 // angle = position * inv_freq[i] in float32, x' = x cos - y sin, y' = y cos + x sin. With a table
 // (rope_cos, rope_sin: [n_tokens, rot_pairs], made by rope_table_kernel from the same product) the
 // cosines and sines are read instead of computed. One block per token.
@@ -28,7 +29,8 @@ template <typename T>
 __global__ void split_rotate_store_kernel(const T* __restrict__ fused, T* __restrict__ q_out, T* __restrict__ k_pool,
                                           T* __restrict__ v_pool, StepBatch sb, const float* __restrict__ inv_freq,
                                           const float* __restrict__ rope_cos, const float* __restrict__ rope_sin,
-                                          int rot_pairs, int kv_heads, int q_per_kv, int head_dim, int write_cache) {
+                                          int rot_pairs, int kv_heads, int q_per_kv, int head_dim, int write_cache,
+                                          int interleaved) {
   const int t = blockIdx.x;
   const int pos = sb.tok_pos[t];
   const int seq = sb.tok_seq[t];
@@ -41,7 +43,7 @@ __global__ void split_rotate_store_kernel(const T* __restrict__ fused, T* __rest
   // work items: (group g, row r in group, pair or plain element)
   const int rot_dims = 2 * rot_pairs;
   // bfloat16 with head sizes and rotation widths in multiples of 8 and a table of cosines: 16-byte words
-  if (sizeof(T) == 2 && head_dim % 8 == 0 && rot_pairs % 8 == 0 && (rot_pairs == 0 || rope_cos != nullptr) &&
+  if (sizeof(T) == 2 && head_dim % 8 == 0 && rot_pairs % 8 == 0 && (rot_pairs == 0 || (rope_cos != nullptr && !interleaved)) &&
       aligned16(fused) && aligned16(q_out) && (!write_cache || (aligned16(k_pool) && aligned16(v_pool)))) {
     const int chunks = head_dim / 8, rot_chunks = rot_pairs / 8;
     const int total_v = kv_heads * rows * chunks;
@@ -98,8 +100,9 @@ __global__ void split_rotate_store_kernel(const T* __restrict__ fused, T* __rest
     }
     const bool rotated_row = (r <= q_per_kv) && (inv_freq != nullptr || rope_cos != nullptr);  // queries and K, not V
     if (e < rot_pairs) {
-      const float a = to_f(src[e]);
-      const float b = to_f(src[e + rot_pairs]);
+      const int ia = interleaved ? 2 * e : e, ib = interleaved ? 2 * e + 1 : e + rot_pairs;   // the pair's two dims
+      const float a = to_f(src[ia]);
+      const float b = to_f(src[ib]);
       if (rotated_row) {
         float s, c, ra, rb;
         if (rope_cos) {
@@ -109,11 +112,11 @@ __global__ void split_rotate_store_kernel(const T* __restrict__ fused, T* __rest
           sincosf(float(pos) * inv_freq[e], &s, &c);
         }
         rotate_pair(a, b, c, s, ra, rb);
-        dst[e] = from_f<T>(ra);
-        dst[e + rot_pairs] = from_f<T>(rb);
+        dst[ia] = from_f<T>(ra);
+        dst[ib] = from_f<T>(rb);
       } else {
-        dst[e] = src[e];
-        dst[e + rot_pairs] = src[e + rot_pairs];
+        dst[ia] = src[ia];
+        dst[ib] = src[ib];
       }
     } else {
       const int i = rot_dims + (e - rot_pairs);
@@ -292,7 +295,7 @@ PTB_API int ptb_rope_table(const int* tok_pos, const float* inv_freq, float* cos
 PTB_API int ptb_split_rotate_store(int dtype, const void* fused, void* q_out, void* k_pool, void* v_pool,
                                    const StepBatch* sb, const float* inv_freq, const float* rope_cos,
                                    const float* rope_sin, int rot_pairs, int kv_heads, int q_per_kv, int head_dim,
-                                   int write_cache, cudaStream_t stream) {
+                                   int write_cache, int interleaved, cudaStream_t stream) {
   if (sb->n_tokens <= 0) return PTB_OK;
   if (kv_heads <= 0 || q_per_kv <= 0 || head_dim <= 0 || rot_pairs < 0 || 2 * rot_pairs > head_dim)
     return PTB_ERR_SIZE;
@@ -302,11 +305,11 @@ PTB_API int ptb_split_rotate_store(int dtype, const void* fused, void* q_out, vo
   if (dtype == PTB_F32)
     split_rotate_store_kernel<float><<<sb->n_tokens, threads, 0, stream>>>(
         (const float*)fused, (float*)q_out, (float*)k_pool, (float*)v_pool, *sb, inv_freq, rope_cos, rope_sin,
-        rot_pairs, kv_heads, q_per_kv, head_dim, write_cache);
+        rot_pairs, kv_heads, q_per_kv, head_dim, write_cache, interleaved);
   else if (dtype == PTB_BF16)
     split_rotate_store_kernel<__nv_bfloat16><<<sb->n_tokens, threads, 0, stream>>>(
         (const __nv_bfloat16*)fused, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, *sb,
-        inv_freq, rope_cos, rope_sin, rot_pairs, kv_heads, q_per_kv, head_dim, write_cache);
+        inv_freq, rope_cos, rope_sin, rot_pairs, kv_heads, q_per_kv, head_dim, write_cache, interleaved);
   else
     return PTB_ERR_DTYPE;
   return launch_status();

@@ -193,10 +193,11 @@ def rope_table(tok_pos: torch.Tensor, inv_freq: torch.Tensor):
 
 def split_rotate_store(fused: torch.Tensor, k_pool: Optional[torch.Tensor], v_pool: Optional[torch.Tensor],
                        batch: StepBatchC, inv_freq: Optional[torch.Tensor], kv_heads: int, q_per_kv: int,
-                       head_dim: int, write_cache: bool = True, rope=None) -> torch.Tensor:
+                       head_dim: int, write_cache: bool = True, rope=None, interleaved: bool = False) -> torch.Tensor:
     """Fused projection -> rotated queries [tokens, heads, head_dim]; K (rotated) and V go to the pools.
     The rotation comes from ``inv_freq`` (angles computed in the kernel) or from ``rope`` = (cos, sin)
-    tables of ``rope_table`` for this step's tokens."""
+    tables of ``rope_table`` for this step's tokens; the pairs are (i, i + pairs) of a head's first
+    2 * pairs dims, or (2 i, 2 i + 1) with ``interleaved``."""
     _need_cuda(fused, k_pool, v_pool, inv_freq)
     n = fused.shape[0]
     q = torch.empty((n, kv_heads * q_per_kv, head_dim), dtype=fused.dtype, device=fused.device)
@@ -211,7 +212,8 @@ def split_rotate_store(fused: torch.Tensor, k_pool: Optional[torch.Tensor], v_po
         inv_freq = None
     _check(lib().ptb_split_rotate_store(_dtype_code(fused), _ptr(fused), _ptr(q), _ptr(k_pool), _ptr(v_pool),
                                         ctypes.byref(batch), _ptr(inv_freq), _ptr(cos), _ptr(sin), pairs, kv_heads,
-                                        q_per_kv, head_dim, 1 if write_cache else 0, _stream(fused)),
+                                        q_per_kv, head_dim, 1 if write_cache else 0, 1 if interleaved else 0,
+                                        _stream(fused)),
            "split_rotate_store")
     return q
 
@@ -242,7 +244,7 @@ def decode_max_warps(head_dim: int) -> int:
 def attention_decode(fused: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, batch: StepBatchC, rope,
                      slopes: Optional[torch.Tensor], kv_heads: int, q_per_kv: int, head_dim: int, scale: float,
                      window: int, heads_per_tile: int, warps: int, n_splits: int, write_cache: bool = True,
-                     key_split: int = 1, n_teams: int = 1):
+                     key_split: int = 1, n_teams: int = 1, interleaved: bool = False):
     """One kernel for the attention of a step of single tokens: rotate q and k of each new token, put
     k and v into the cache, attend over the cache (all heads of a K/V group in one tile of ``warps``
     x 16 rows, key pages divided among ``n_splits`` blocks of one cluster, the keys of a page among
@@ -271,7 +273,8 @@ def attention_decode(fused: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Te
         n_tickets = groups * n_splits
         tickets = _tickets(n_tickets, fused.device)
     _check(lib().ptb_attention_decode(_ptr(fused), _ptr(k_pool), _ptr(v_pool), _ptr(out), ctypes.byref(batch),
-                                      _ptr(cos), _ptr(sin), pairs, _ptr(slopes), heads, kv_heads, head_dim,
+                                      _ptr(cos), _ptr(sin), pairs, 1 if interleaved else 0, _ptr(slopes), heads, kv_heads,
+                                      head_dim,
                                       heads_per_tile, n_splits, n_teams, warps, key_split, ctypes.c_float(scale),
                                       window, 1 if write_cache else 0, _ptr(parts), ctypes.c_size_t(part_floats),
                                       _ptr(tickets), n_tickets, _stream(fused)),
@@ -285,7 +288,7 @@ def attention_decode_tc_supports(head_dim: int, q_per_kv: int) -> bool:
 
 def attention_decode_tc(fused: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, batch: StepBatchC, rope,
                         kv_heads: int, q_per_kv: int, head_dim: int, scale: float, n_splits: int,
-                        write_cache: bool = True, n_teams: int = 1):
+                        write_cache: bool = True, n_teams: int = 1, interleaved: bool = False):
     """The attention of a step of single tokens on the tcgen05 tensor cores, for K/V heads that serve
     33 to 128 query heads of size 64: the query heads of a group are the rows of one tile, S, P and O
     live in tensor memory, pages come by TMA, ``n_splits`` blocks of one cluster share a sequence's
@@ -315,7 +318,8 @@ def attention_decode_tc(fused: torch.Tensor, k_pool: torch.Tensor, v_pool: torch
         n_tickets = n * kv_heads * n_splits
         tickets = _tickets(n_tickets, fused.device)
     _check(lib().ptb_attention_decode_tc(_ptr(fused), _ptr(k_pool), _ptr(v_pool), k_pool.shape[0], _ptr(out),
-                                         ctypes.byref(batch), _ptr(cos), _ptr(sin), pairs, heads, kv_heads, head_dim,
+                                         ctypes.byref(batch), _ptr(cos), _ptr(sin), pairs, 1 if interleaved else 0, heads,
+                                         kv_heads, head_dim,
                                          n_splits, n_teams, ctypes.c_float(scale), 1 if write_cache else 0,
                                          _ptr(parts), ctypes.c_size_t(part_floats), _ptr(tickets), n_tickets,
                                          _ptr(error_flag(fused.device)), _stream(fused)), "attention_decode_tc")

@@ -110,6 +110,7 @@ class Attention(Part):
         batch = ctx.batch_c[group]
         rope = ctx.rope(self.position)
         slopes = self.position.score_bias() if self.position is not None else None
+        inter = bool(getattr(self.position, "interleaved", False))   # rotated pairs (2 i, 2 i + 1) instead of (i, i + n)
         tiles = ctx.plan(AttentionTiles.plan_key)
         if tiles.facts["mma_tokens"] == 1 and fused.dtype == self._bf16 and k.attention_mma_supports(self.head_dim):
             # a step of single tokens: rotation, cache write, attention and the join in one kernel
@@ -133,15 +134,15 @@ class Attention(Part):
                 # fit beside them
                 o = k.attention_decode_tc(fused, k_pool, v_pool, batch, rope, self.kv_heads, self.q_per_kv,
                                           self.head_dim, self.scale, splits, write_cache=entry.writes_cache,
-                                          n_teams=teams)
+                                          n_teams=teams, interleaved=inter)
                 return linear(k, o, self.p_out_weight, self.p_out_bias, add=add)
             o = k.attention_decode(fused, k_pool, v_pool, batch, rope, slopes, self.kv_heads, self.q_per_kv,
                                    self.head_dim, self.scale, self.window, hpk, warps, splits,
                                    write_cache=entry.writes_cache, key_split=self._decode_key_split(warps),
-                                   n_teams=teams)
+                                   n_teams=teams, interleaved=inter)
         else:
             q = k.split_rotate_store(fused, k_pool, v_pool, batch, None, self.kv_heads, self.q_per_kv,
-                                     self.head_dim, write_cache=entry.writes_cache, rope=rope)
+                                     self.head_dim, write_cache=entry.writes_cache, rope=rope, interleaved=inter)
             o = self.attend(q, k_pool, v_pool, ctx, tiles, batch, slopes)
         return linear(k, o, self.p_out_weight, self.p_out_bias, add=add)
 

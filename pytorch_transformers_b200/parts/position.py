@@ -33,8 +33,10 @@ class NoPosition(Part):
 @register_part("position", "rotary")
 class RotaryPosition(NoPosition):
     def __init__(self, build: BuildContext, spec: PartSpec, head_dim: int, theta: float, factor: float = 1.0,
-                 rotary_dim: int = 0):
+                 rotary_dim: int = 0, interleaved: bool = False):
         super().__init__(build, spec)
+        # which dims make a rotated pair: (i, i + dim / 2), the reference's rotate_half, or (2 i, 2 i + 1)
+        self.interleaved = bool(interleaved)
         dim = int(rotary_dim) if rotary_dim else int(head_dim)
         if dim % 2 or dim > head_dim or dim <= 0:
             raise ValueError(f"rotary_dim must be even and in 2..head_dim, got {dim} for head_dim {head_dim}")

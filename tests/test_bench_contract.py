@@ -50,3 +50,21 @@ def test_bytes_and_flops_of_the_shapes():
     matrices = 2 * 2048 * layers * per_layer + 2 * v * h
     attention = layers * 71 * 4 * 64 * 2048 * 2049 / 2
     assert flops == matrices + attention
+
+
+def test_flops_of_a_ragged_prefill_and_the_baseline_runs():
+    sys.path.insert(0, ROOT)
+    import bench
+    # one prompt: the same count as the plain formula; several: sums over the prompts, a head row each
+    assert bench.prefill_flops_ragged(bench.FALCON_7B, 32, [2048]) == bench.prefill_flops(bench.FALCON_7B, 32, 2048)
+    two = bench.prefill_flops_ragged(bench.FALCON_11B, 60, [512, 8192])
+    assert two == bench.prefill_flops(bench.FALCON_11B, 60, 512) + bench.prefill_flops(bench.FALCON_11B, 60, 8192)
+    assert bench.BASELINE_RUNS["11b"] == {"prompts": 8, "shortest": 512, "longest": 8192, "steps": 128}
+    assert bench.BASELINE_RUNS["40b"] == {"prompts": 16, "shortest": 64, "longest": 2048, "steps": 256}
+    done = run_bench("--only", "config")
+    assert done.returncode == 2 and "--shape 11b" in done.stdout
+    # both arms describe the workload in the same words
+    cfg = bench.workload_config(32, 8)
+    assert len(cfg) <= 20 and all(not isinstance(v, (dict, list)) for v in cfg.values())
+    assert (cfg["hidden"], cfg["heads"], cfg["kv_heads"], cfg["head_dim"], cfg["ffn"], cfg["vocab"]) == \
+        (4544, 71, 1, 64, 18176, 65024)

@@ -659,13 +659,15 @@ def _register_toy_scaled():
         vocab_size: int = 60
         hidden_size: int = 48
         heads: int = 3
+        interleaved: bool = False       # rotated pairs (2 i, 2 i + 1) instead of (i, i + head_dim / 2)
 
     def spec(cfg):
         d = cfg.hidden_size // cfg.heads
         ln = lambda n: PartSpec("norm", "layernorm", {"size": cfg.hidden_size, "eps": 1e-5, "bias": True},
                                 names={"weight": n + ".weight", "bias": n + ".bias"})
         mixer = PartSpec("mixer", "attention", {"hidden": cfg.hidden_size, "heads": cfg.heads, "kv_heads": 1, "head_dim": d},
-                         children={"position": PartSpec("position", "rotary", {"head_dim": d, "theta": 1000.0})},
+                         children={"position": PartSpec("position", "rotary", {"head_dim": d, "theta": 1000.0,
+                                                                               "interleaved": cfg.interleaved})},
                          names={"qkv.weight": "b.attn.qkv.weight", "out.weight": "b.attn.out.weight"})
         ff = PartSpec("feed_forward", "dense", {"hidden": cfg.hidden_size, "inner": 64, "activation": "gelu"},
                       names={"up.weight": "b.ff.up.weight", "down.weight": "b.ff.down.weight"})
@@ -708,4 +710,79 @@ def test_toy_architecture_with_scaled_and_normed_embeddings_and_scaled_logits(tm
                     [model.step(cache, [slot], [[t]]) for t in ids[20:]])
     tol = dict(atol=2e-5, rtol=1e-4) if dtype == "float32" else dict(atol=3e-2, rtol=3e-2)
     torch.testing.assert_close(got.double().cpu(), ref, **tol)
+    model.check_errors()
+
+
+def _scaled_plain(ids, w, hidden, heads, interleaved, bf16):
+    """The toy_scaled model on one whole sequence in float64."""
+    c = {"num_attention_heads": heads, "hidden_size": hidden, "new_decoder_architecture": False, "multi_query": True,
+         "rope_theta": 1000.0, "rope_scaling": None}
+
+    def rot(x, pos, inv):
+        if not interleaved:
+            return plain.rotary(x, pos, inv)
+        ang = pos.float()[:, None] * inv[None, :]
+        cos, sin = ang.cos().double()[:, None, :], ang.sin().double()[:, None, :]
+        a, b = x[..., 0::2], x[..., 1::2]
+        out = torch.empty_like(x)
+        out[..., 0::2] = a * cos - b * sin
+        out[..., 1::2] = b * cos + a * sin
+        return out
+
+    x = w["embed.weight"][torch.tensor(ids)] * math.sqrt(hidden)
+    if bf16:
+        x = x.bfloat16().double()
+    x = plain.layer_norm(x, w["embed_ln.weight"], w["embed_ln.bias"], 1e-5)
+    a = plain.layer_norm(x, w["b.ln.weight"], w["b.ln.bias"], 1e-5)
+    fused = a @ w["b.attn.qkv.weight"].T
+    if bf16:
+        fused = fused.bfloat16().double()       # the engine holds the projection, and the rotated q and k, in bfloat16
+    q, k, v = plain.split_heads(fused, c)
+    pos, inv = torch.arange(len(ids)), plain.rope_inv_freq(c)
+    q, k = rot(q, pos, inv), rot(k, pos, inv)
+    if bf16:
+        q, k = q.bfloat16().double(), k.bfloat16().double()
+    attn = plain.attention_core(q, k, v, c) @ w["b.attn.out.weight"].T
+    ff = plain.activation(a @ w["b.ff.up.weight"].T, "gelu") @ w["b.ff.down.weight"].T
+    x = x + (ff + attn)
+    return plain.layer_norm(x, w["final.weight"], w["final.bias"], 1e-5) @ w["embed.weight"].T * 0.25
+
+
+@pytest.mark.parametrize("dtype,hidden,heads,larger", [("float32", 48, 3, 16.0), ("bfloat16", 2560, 40, 4.0)])
+def test_rotation_of_adjacent_pairs(tmp_path, dtype, hidden, heads, larger):
+    """A rotary part with ``interleaved=True`` rotates the pairs (2 i, 2 i + 1): in the kernel that splits
+    and stores prompts, in the one-kernel decode attention and in the tcgen05 decode attention (40 heads
+    of size 64 on one K/V head: steps of 3 and of 50 single tokens)."""
+    import pytorch_transformers_b200 as ptb
+    Cfg = _register_toy_scaled()
+    cfg = Cfg(hidden_size=hidden, heads=heads, interleaved=True)
+    folder = ptb.write_random_model(cfg, seed=10, folder=str(tmp_path / "inter"), dtype=getattr(torch, dtype))
+    model = ptb.AutoModelForCausalLM.from_pretrained(folder, dtype=dtype)
+    _, w = plain.load_folder(folder, torch.float64)
+    # With weights of 0.02 the scores are all but equal and the rotation could be anything: the fused
+    # projection is made larger (by a power of two, exact in both dtypes) on both sides, so that which
+    # dims turn together decides which keys a query finds, and the other pairing would miss the
+    # tolerance many times over.
+    model.blocks[0].children["mixer"].p_qkv_weight.mul_(larger)
+    w["b.attn.qkv.weight"] = w["b.attn.qkv.weight"] * larger
+    g = torch.Generator().manual_seed(2)
+    reqs = [torch.randint(0, 60, (n,), generator=g).tolist() for n in (75, 9, 30)]
+    refs = [_scaled_plain(r, w, hidden, heads, True, dtype == "bfloat16") for r in reqs]
+    other = _scaled_plain(reqs[0], w, hidden, heads, False, dtype == "bfloat16")
+    tol = dict(atol=2e-5, rtol=1e-4) if dtype == "float32" else dict(atol=3e-2, rtol=3e-2)
+    assert (refs[0] - other).abs().max() > 5 * (tol["atol"] + tol["rtol"] * refs[0].abs().max())
+    cache = model.new_cache(64 * 4 + 64 * 50)
+    slots = [cache.open() for _ in reqs]
+    heads_ = [70, 4, 25]
+    out = model.step(cache, slots, [r[:h] for r, h in zip(reqs, heads_)], want="last")
+    for t in range(4):
+        for row in range(3):
+            torch.testing.assert_close(out[row].double().cpu(), refs[row][heads_[row] + t - 1], **tol)
+        out = model.step(cache, slots, [[r[h + t]] for r, h in zip(reqs, heads_)])
+    if heads == 40:
+        many = [cache.open() for _ in range(50)]
+        for i in range(0, 50, 10):
+            model.step(cache, many[i:i + 10], [reqs[1][:5]] * 10, want="none")
+        out = model.step(cache, many, [[reqs[1][5]]] * 50)
+        torch.testing.assert_close(out.double().cpu(), refs[1][5][None, :].expand(50, -1), **tol)
     model.check_errors()
