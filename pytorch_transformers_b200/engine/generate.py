@@ -52,11 +52,13 @@ def plan_batches(n_requests: int, max_batch: int) -> List[List[int]]:
 def run_generation(stepper: Stepper, selector: Selector, prompts: Sequence[Sequence[int]],
                    options: GenerationConfig, budget: int, max_batch: int,
                    on_token: Optional[Callable[[int, int], None]] = None,
-                   keep_logits: bool = False) -> List[RequestResult]:
+                   keep_logits: bool = False,
+                   on_step: Optional[Callable[[dict], None]] = None) -> List[RequestResult]:
     """Generate up to ``budget`` tokens for every prompt; returns results in the prompts' order.
 
-    ``on_token(request_index, token)`` is called for every new token as it is chosen (the
-    reference's streamer, utils.py:3287-3288)."""
+    ``on_token(request_index, token)`` is called for every new token as it is chosen, and
+    ``on_step({request_index: token})`` once per step with all of the step's new tokens (the
+    reference's streamer gets a step's tokens in one call, utils.py:3287-3288)."""
     for i, p in enumerate(prompts):
         if len(p) == 0:
             raise ValueError(f"prompt {i} is empty: a sequence needs at least one token to start from")
@@ -120,6 +122,8 @@ def run_generation(stepper: Stepper, selector: Selector, prompts: Sequence[Seque
                     else:
                         still.append((r, slot))
                         kept_rows.append(row)
+                if on_step is not None:
+                    on_step({r: int(tok) for (r, _), tok in zip(live, chosen)})
                 n_before = len(live)
                 live = still
                 if not live:

@@ -205,15 +205,33 @@ class PreTrainedCausalLM(CausalLM):
             if on_token is not None:
                 on_token(r, tok)
 
+        # The reference pushes the prompts and then every step's tokens to the streamer, a row per request
+        # (streamers.py:27-233; utils.py:3287-3299; rows that have ended get the pad token). That is done
+        # here when the requests run as one batch; several batches run one after another, and then every
+        # finished request is handed over once at the end.
+        stream_steps = streamer is not None and len(expanded) <= max_batch
+        pad_stream = opts.pad_token_id if opts.pad_token_id is not None else (opts.eos_ids() or [0])[0]
+        if stream_steps:
+            if tensor_in:
+                streamer.put(ids.repeat_interleave(n_ret, 0) if n_ret > 1 else ids)
+            else:
+                first = torch.full((len(expanded), longest), int(pad_stream), dtype=torch.long)
+                for i, pr in enumerate(expanded):                  # left-padded, as the reference wants batches
+                    first[i, longest - len(pr):] = torch.tensor(pr, dtype=torch.long)
+                streamer.put(first)
+
+        def _on_step(step_tokens):
+            streamer.put(torch.tensor([step_tokens.get(i, int(pad_stream)) for i in range(len(expanded))],
+                                      dtype=torch.long))
+
         results = run_generation(_CacheStepper(self, cache, max_step_tokens), selector, expanded, opts, budget, max_batch,
                                  on_token=_on_token if on_token is not None else None,
-                                 keep_logits=opts.output_logits)
+                                 keep_logits=opts.output_logits, on_step=_on_step if stream_steps else None)
         self.check_errors()
         if streamer is not None:
-            # the reference pushes the prompt and then every step's tokens (streamers.py:27-233);
-            # with unequal lengths per request we hand over each finished request once
-            for res in results:
-                streamer.put(torch.tensor(res.prompt + res.tokens))
+            if not stream_steps:
+                for res in results:
+                    streamer.put(torch.tensor(res.prompt + res.tokens))
             streamer.end()
 
         if tensor_in:

@@ -248,6 +248,14 @@ def test_falcon_7b_widths_two_layers(tmp_path, dtype):
     g = np.random.Generator(np.random.PCG64(5))
     reqs = [g.integers(0, 1000, size=n).tolist() for n in (150, 9)]
     refs = [plain.model_logits(ids, raw, w) for ids in reqs]
+    # bfloat16 at this width: the absolute allowance is 3 % of the logits' standard deviation (1.3 here), as in
+    # the tests at the widths of the larger models below; the fixed 2e-2 of the tiny configurations is 3 % of
+    # theirs at the least, and here it sits at the rounding noise of the head's bfloat16 input
+    tol = dict(TOL[dtype], atol=0.03 * float(torch.cat(refs).std())) if dtype == "bfloat16" else TOL[dtype]
+
+    def close(a, b, dtype, what=""):
+        torch.testing.assert_close(a.double().cpu(), b.double().cpu(), msg=lambda m: f"{what}: {m}", **tol)
+
     cache = model.new_cache(512)
     slots = [cache.open() for _ in reqs]
     heads = [140, 3]
@@ -601,3 +609,41 @@ def test_a_step_launched_with_tokens_that_only_the_device_knows(loaded, dtype):
     out = model.step(cache, slots, [[r[h + 4]] for r, h in zip(reqs, heads)])
     close(out[1], refs[1][heads[1] + 4], dtype, "after a refused step ahead")
     model.build.kernels.check_device_errors("cuda")
+
+
+def test_the_streamer_gets_the_prompts_and_then_every_steps_tokens(loaded):
+    """As the reference's generate does it (src/transformers/generation/utils.py:3287-3299): put(prompts),
+    put(tokens of a step) for every step, end(); rows that have ended get the pad token."""
+    L = loaded("B", "float32")
+
+    class Collect:
+        def __init__(self):
+            self.calls, self.ended = [], False
+
+        def put(self, value):
+            self.calls.append(value.clone())
+
+        def end(self):
+            self.ended = True
+
+    prompts = tm.prompts("B", (9, 4), seed=44)
+    free = L.model.generate(prompts, max_new_tokens=6, eos_token_id=None)
+    stop = free[1][len(prompts[1]) + 2]                  # request 1 stops at its third new token
+    s = Collect()
+    out = L.model.generate(prompts, max_new_tokens=6, eos_token_id=[stop], pad_token_id=0, streamer=s)
+    assert s.ended and s.calls[0].shape == (2, 9)
+    assert s.calls[0][0].tolist() == prompts[0] and s.calls[0][1].tolist() == [0] * 5 + prompts[1]
+    steps = torch.stack(s.calls[1:])                     # [steps, requests]
+    new = [seq[len(p):] for seq, p in zip(out, prompts)]
+    for r in range(2):
+        assert steps[:len(new[r]), r].tolist() == new[r]
+        assert steps[len(new[r]):, r].tolist() == [0] * (steps.shape[0] - len(new[r]))
+    assert len(new[1]) <= 3 or stop in new[0][:3]
+    # a single request: one row, token after token (what the reference's TextStreamer takes)
+    s = Collect()
+    one = L.model.generate(torch.tensor([prompts[0]]), max_new_tokens=4, eos_token_id=None, streamer=s)
+    assert s.calls[0].shape == (1, 9) and [c.tolist() for c in s.calls[1:]] == [[t] for t in one[0, 9:].tolist()]
+    # more requests than one batch holds: each finished request is handed over once
+    s = Collect()
+    out = L.model.generate(prompts, max_new_tokens=3, eos_token_id=None, streamer=s, max_batch_size=1)
+    assert [c.tolist() for c in s.calls] == out and s.ended
