@@ -47,6 +47,7 @@ class CausalLM:
         # replay steps of single tokens as CUDA graphs, if every part allows it
         self.use_graphs = all(p.graph_safe for top in self._top_parts() for p in top.walk())
         self.last_h2d_bytes = 0
+        self.step_records: Optional[list] = None   # set by record_steps(True): one record per step
         self._side_stream = None
         # what the parts ask of every step: their planners (one per plan_key) and the mixers' word on streams
         self.planners, seen = [], set()
@@ -119,6 +120,41 @@ class CausalLM:
                 total += t.numel() * t.element_size()
         return total
 
+    def record_steps(self, on: bool = True) -> None:
+        """Keep a record of every step from now on in ``step_records`` (a list of dicts: kind "prompt",
+        "decode", "graph" or "ahead", sequences, tokens, bytes of index arrays copied, and two CUDA events
+        around the step's launches) or stop keeping it. ``step_timings()`` turns the events into
+        milliseconds. Off by default: an event pair per step is cheap but not free."""
+        self.step_records = [] if on else None
+
+    def step_timings(self) -> List[dict]:
+        """The records of ``record_steps`` with ``device_ms`` (waits for the device)."""
+        out = []
+        for r in self.step_records or ():
+            r["end"].synchronize()
+            out.append({k: v for k, v in r.items() if k not in ("begin", "end")} |
+                       {"device_ms": r["begin"].elapsed_time(r["end"])})
+        return out
+
+    def _recorded(self, kind: str, ctx: StepContext):
+        """Context manager around a step's launches that adds a record when records are kept."""
+        model = self
+
+        class _Span:
+            def __enter__(self):
+                self.on = model.step_records is not None and model.device.type == "cuda"
+                if self.on:
+                    self.begin = torch.cuda.Event(enable_timing=True)
+                    self.begin.record()
+
+            def __exit__(self, *exc):
+                if self.on and exc[0] is None:
+                    end = torch.cuda.Event(enable_timing=True)
+                    end.record()
+                    model.step_records.append({"kind": kind, "sequences": ctx.n_seqs, "tokens": ctx.n_tokens,
+                                               "h2d_bytes": ctx.h2d_bytes, "begin": self.begin, "end": end})
+        return _Span()
+
     def check_errors(self) -> None:
         """Raise if a kernel has reported trouble since the last check (synchronises): a row index that
         had to be clamped (a token id or a wanted row that was wrong on the device although the host
@@ -178,7 +214,8 @@ class CausalLM:
             return self._step_graph(cache, ctx)
         ctx = StepContext(cache, slots, token_lists, self.spec.vocab_size, want, self.planners)
         self.last_h2d_bytes = ctx.h2d_bytes     # index arrays copied to the device for this step
-        logits = self.forward(ctx)
+        with self._recorded("decode" if ctx.is_decode else "prompt", ctx):
+            logits = self.forward(ctx)
         ctx.commit()
         return logits
 
@@ -236,14 +273,16 @@ class CausalLM:
         if entry is None or device_tokens.dtype != torch.int32 or device_tokens.numel() < ctx.n_tokens:
             cache.__dict__["_prepared_step"] = (id(self), cache.epoch, ctx)     # still good for step()
             return None
-        ctx.refill(entry["static"])
-        o, n = ctx._offsets["tokens"]
-        entry["static"][o:o + n].copy_(device_tokens[:n], non_blocking=True)
-        self.last_h2d_bytes = ctx.h2d_bytes
-        entry["graph"].replay()
+        with self._recorded("ahead", ctx):
+            ctx.refill(entry["static"])
+            o, n = ctx._offsets["tokens"]
+            entry["static"][o:o + n].copy_(device_tokens[:n], non_blocking=True)
+            self.last_h2d_bytes = ctx.h2d_bytes
+            entry["graph"].replay()
+            out = entry["out"].clone()
         K.launches += entry["launches"]
         ctx.commit()
-        return entry["out"].clone()
+        return out
 
     def _step_graph(self, cache: Cache, ctx: StepContext) -> torch.Tensor:
         # graphs live on the cache they were captured for (they hold pointers into its storage)
@@ -257,7 +296,8 @@ class CausalLM:
             # initialisations (and one-time set-up inside the library) happen here, outside the capture.
             # The capture that follows records the same launches without running them, so the step's
             # work, a mixer's update of its per-sequence state included, is done exactly once.
-            first = self.forward(ctx)
+            with self._recorded("decode", ctx):
+                first = self.forward(ctx)
             graph = torch.cuda.CUDAGraph()
             before = K.launches
             with torch.cuda.graph(graph):
@@ -272,12 +312,14 @@ class CausalLM:
             self.last_h2d_bytes = ctx.h2d_bytes
             ctx.commit()
             return first
-        ctx.refill(entry["static"])
-        self.last_h2d_bytes = ctx.h2d_bytes
-        entry["graph"].replay()
+        with self._recorded("graph", ctx):
+            ctx.refill(entry["static"])
+            self.last_h2d_bytes = ctx.h2d_bytes
+            entry["graph"].replay()
+            out = entry["out"].clone()   # the graph's own output buffer is rewritten by the next replay
         K.launches += entry["launches"]
         ctx.commit()
-        return entry["out"].clone()   # the graph's own output buffer is rewritten by the next replay
+        return out
 
     def _two_streams(self, ctx: StepContext) -> bool:
         """Mixer and feed-forward of a parallel block as two branches: only for steps of few rows (whose

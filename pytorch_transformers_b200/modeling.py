@@ -35,12 +35,20 @@ _DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.
            "float": torch.float32, torch.bfloat16: torch.bfloat16, torch.float32: torch.float32}
 
 
-def resolve_dtype(dtype, config: Optional[ModelConfig] = None) -> torch.dtype:
+def resolve_dtype(dtype, config: Optional[ModelConfig] = None, folder: Optional[str] = None) -> torch.dtype:
     """``dtype`` as given, or "auto"/None: the configuration's ``torch_dtype`` if it is one of
-    ours, else bfloat16 (the serving precision)."""
+    ours, else the dtype that the folder's checkpoint is stored in (32-bit stays 32-bit, 16-bit is
+    served in bfloat16), else bfloat16 (the serving precision)."""
     if dtype in (None, "auto"):
         stored = getattr(config, "torch_dtype", None)
-        return _DTYPES.get(stored, torch.bfloat16)
+        if stored in _DTYPES:
+            return _DTYPES[stored]
+        if folder is not None:
+            from .weights.loader import checkpoint_dtype
+            found = checkpoint_dtype(folder)
+            if found is not None:
+                return found
+        return torch.bfloat16
     try:
         return _DTYPES[dtype]
     except KeyError:
@@ -125,7 +133,7 @@ class PreTrainedCausalLM(CausalLM):
         arch = lookup(raw)
         config = arch.config_cls.from_dict(raw)
         model = cls(arch.spec_builder(config), config, device=device,
-                    dtype=resolve_dtype(dtype if dtype is not None else torch_dtype, config))
+                    dtype=resolve_dtype(dtype if dtype is not None else torch_dtype, config, folder))
         load_weights(model, folder, arch.name_rules, strict=strict)
         model.generation_config = GenerationConfig.from_pretrained(folder, config)
         return model

@@ -41,6 +41,24 @@ class WeightError(RuntimeError):
         super().__init__("\n".join(lines))
 
 
+def checkpoint_dtype(folder: str) -> Optional[torch.dtype]:
+    """The dtype that the folder's archives store their matrices in: float32 if the first floating-point
+    tensor of two or more dimensions is stored in 32-bit, bfloat16 if it is stored in 16 bits (bfloat16 or
+    float16, which is converted at load), None if there is no such tensor. It is what ``dtype="auto"``
+    means when config.json names no ``torch_dtype`` (the reference looks at the first floating-point tensor
+    of the state dict too, src/transformers/modeling_utils.py:4037-4046)."""
+    files, where = open_checkpoint(folder)
+    try:
+        for name, f in where.items():
+            e = f.entries[name]
+            if e.dtype in _FLOATS and len(e.shape) >= 2:
+                return torch.float32 if e.dtype in (torch.float32, torch.float64) else torch.bfloat16
+        return None
+    finally:
+        for f in files:
+            f.close()
+
+
 def load_weights(model, folder: str, name_rules: Optional[dict] = None, strict: bool = True) -> None:
     """Read every parameter of ``model`` from the archive(s) in ``folder`` and bind them. With
     ``strict=False`` tensors that the model does not ask for are reported as a warning instead of an

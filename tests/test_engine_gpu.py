@@ -647,3 +647,21 @@ def test_the_streamer_gets_the_prompts_and_then_every_steps_tokens(loaded):
     s = Collect()
     out = L.model.generate(prompts, max_new_tokens=3, eos_token_id=None, streamer=s, max_batch_size=1)
     assert [c.tolist() for c in s.calls] == out and s.ended
+
+
+def test_step_records_name_every_step_with_its_device_time(loaded):
+    L = loaded("E", "bfloat16")
+    model = L.model
+    model.record_steps(True)
+    try:
+        prompts = tm.prompts("E", (70, 9), seed=45)
+        model.generate(prompts, max_new_tokens=5, eos_token_id=None)
+        recs = model.step_timings()
+    finally:
+        model.record_steps(False)
+    assert recs[0]["kind"] == "prompt" and recs[0]["tokens"] == 79 and recs[0]["sequences"] == 2
+    decode = recs[1:]
+    assert len(decode) == 4 and all(r["tokens"] == 2 and r["kind"] in ("decode", "graph", "ahead") for r in decode)
+    assert any(r["kind"] == "ahead" for r in decode)          # steps launched before the host had the tokens
+    assert all(r["device_ms"] > 0 and r["h2d_bytes"] > 0 for r in recs)
+    assert model.step_records is None

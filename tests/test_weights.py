@@ -198,3 +198,21 @@ def test_head_sizes_beyond_the_kernels_are_refused_when_the_model_is_built(tmp_p
     cfg = ptb.FalconConfig.from_dict(tm.config_dict("A", hidden_size=1040, num_attention_heads=2))   # head size 520
     with pytest.raises(ValueError, match="head sizes from 1 to 256"):
         ptb.AutoModelForCausalLM.from_config(cfg, device="cpu", dtype="float32")
+
+
+def test_without_a_dtype_the_checkpoints_own_precision_is_kept(tmp_path):
+    """dtype None or "auto": config.json's torch_dtype if it names one, else what the archive stores
+    (32-bit stays 32-bit; 16-bit, bfloat16 or float16, is served in bfloat16)."""
+    cfg = tm.config_dict("A")
+    w = tm.make_weights(cfg, 0)
+    f32 = tm.write_model_folder(str(tmp_path / "f32"), cfg, w)
+    bf16 = tm.write_model_folder(str(tmp_path / "bf16"), cfg, w, bf16=True)
+    f16 = tm.write_model_folder(str(tmp_path / "f16"), cfg, {k: v.astype(np.float16) for k, v in w.items()})
+    said = tm.write_model_folder(str(tmp_path / "said"), dict(cfg, torch_dtype="bfloat16"), w)
+    load = lambda folder, **kw: ptb.AutoModelForCausalLM.from_pretrained(folder, device="cpu", **kw)
+    assert load(f32).dtype == torch.float32 and load(f32, dtype="auto").embedding.dtype == torch.float32
+    assert load(bf16).dtype == torch.bfloat16 and load(f16).dtype == torch.bfloat16
+    assert load(said).dtype == torch.bfloat16                  # config.json's word comes first
+    assert load(f32, dtype="bfloat16").dtype == torch.bfloat16 and load(bf16, torch_dtype="float32").dtype == torch.float32
+    from pytorch_transformers_b200.weights.loader import checkpoint_dtype
+    assert checkpoint_dtype(f32) == torch.float32 and checkpoint_dtype(f16) == torch.bfloat16
