@@ -260,6 +260,77 @@ def run_decode_attention(args):
     return 0
 
 
+def run_prefill_attention(args):
+    """Device time of the prompt attention kernels alone (10 launches in a CUDA graph, median of 5 replays):
+    `--batch` prompts of `--prefill-tokens` tokens after `--past` cached ones, heads of `--shape`."""
+    import math
+
+    import torch
+
+    import pytorch_transformers_b200 as ptb
+    from pytorch_transformers_b200 import kernels as K
+    from pytorch_transformers_b200.cache.paged import Cache
+    from pytorch_transformers_b200.engine.batch import StepContext
+    from pytorch_transformers_b200.parts.attention import AttentionTiles
+    from pytorch_transformers_b200.parts.base import CacheNeed
+
+    torch.cuda.set_device(0)
+    cfg = ptb.FalconConfig.from_dict(SHAPES[args.shape])
+    kv, d, qpk, rows, new, past = cfg.kv_heads_eff, cfg.head_dim, cfg.q_per_kv, args.batch, args.prefill_tokens, args.past
+    heads = kv * qpk
+    cache = Cache([(0, CacheNeed("full", kv, d, 0), None)], rows * (past + new + 64), torch.bfloat16, "cuda")
+    slots = [cache.open() for _ in range(rows)]
+    for slot in slots:
+        if past:
+            cache.reserve(slot, past)
+            cache.commit(slot, past)
+    ctx = StepContext(cache, slots, [[0] * new] * rows, 1, [[]] * rows, (AttentionTiles(K),))
+    k_pool, v_pool, group = cache.entry_storage(0)
+    k_pool.normal_()
+    v_pool.normal_()
+    tiles, batch = ctx.plan(AttentionTiles.plan_key), ctx.batch_c[group]
+    q = torch.randn(rows * new, heads, d, device="cuda", dtype=torch.bfloat16)
+    scale = 1 / math.sqrt(d)
+    flops = 0.0     # causal: token t of a prompt sees past + t + 1 keys, two products of 2 * d flops per key and head
+    flops = rows * heads * 4.0 * d * (new * past + new * (new + 1) / 2)
+    result = {"only": "prefill-attention", "shape": args.shape, "batch": rows, "tokens": new, "past": past,
+              "GFLOP": round(flops / 1e9, 1)}
+    launches = {}
+    if tiles.facts["mma_tokens"] == K.TC_TILE_TOKENS and K.attention_tc_supports(d):
+        launches["tcgen05"] = lambda: K.attention_tc(q, k_pool, v_pool, batch, tiles.dev["mtile_seq"], tiles.dev["mtile_q0"],
+                                                     tiles.facts["n_mma_tiles"], kv, scale, None)
+    if K.attention_mma_supports(d) and tiles.facts["mma_tokens"] > 1:
+        tokens = tiles.facts["mma_tokens"]
+        hpk = max(1, min(qpk, 128 // tokens))
+        launches["mma"] = lambda: K.attention_mma(q, k_pool, v_pool, batch, tiles.dev["mtile_seq"], tiles.dev["mtile_q0"],
+                                                  tiles.facts["n_mma_tiles"], None, kv, scale, 0, tokens, hpk, 8, 1)
+    side = torch.cuda.Stream()
+    for name, launch in launches.items():
+        # 10 launches in a CUDA graph: the host's work for a launch is out of the time
+        with torch.cuda.stream(side):
+            for _ in range(3):
+                launch()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                for _ in range(10):
+                    launch()
+            graph.replay()
+            times = []
+            for _ in range(5):
+                t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                t0.record()
+                graph.replay()
+                t1.record()
+                t1.synchronize()
+                times.append(t0.elapsed_time(t1) * 100.0)    # ms for 10 launches -> us for one
+        torch.cuda.synchronize()
+        us = sorted(times)[len(times) // 2]
+        result[name] = {"us": round(us, 1), "TFLOPs": round(flops / us / 1e6, 1)}
+    K.check_device_errors("cuda:0")
+    print(json.dumps(result))
+    return 0
+
+
 def prefill_flops_ragged(c, layers, lengths):
     """Flops of one ragged prefill of prompts of the given lengths (logits for each prompt's last token)."""
     h, nh, kvh, d, f, v = shape_sizes(c)
@@ -422,6 +493,8 @@ def run_ours(args):
         return run_sample(args)
     if args.only == "decode-attention":
         return run_decode_attention(args)
+    if args.only == "prefill-attention":
+        return run_prefill_attention(args)
     if args.only == "linear":
         return run_linear(args)
     if args.only == "fill":
@@ -688,11 +761,13 @@ def main():
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration's (0: all)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--only", default="", choices=["", "decode", "prefill", "sample", "decode-attention", "config", "linear", "fill"],
+    ap.add_argument("--only", default="", choices=["", "decode", "prefill", "sample", "decode-attention", "prefill-attention", "config", "linear",
+                             "fill"],
                     help="run one section only and print its numbers (for profilers)")
     ap.add_argument("--shape", default="7b", choices=sorted(SHAPES), help="model shape for --only decode / prefill")
     ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS, help="prompt length for --only prefill")
     ap.add_argument("--context", type=int, default=CONTEXT, help="cached tokens per sequence for --only decode")
+    ap.add_argument("--past", type=int, default=0, help="cached tokens before the prompt for --only prefill-attention")
     ap.add_argument("--rows", type=int, default=8, help="rows of the activation for --only linear")
     ap.add_argument("--decode-steps", type=int, default=0,
                     help="decode steps of --only config (0: the number BASELINE gives for the shape)")

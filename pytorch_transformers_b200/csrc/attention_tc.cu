@@ -33,23 +33,54 @@
 // copies in flight are waited for), so a fault in the pipeline shows as an error, never as a hang.
 //
 // Two blocks fit on an SM (81 KB of shared memory and 256 columns of tensor memory each): while one
-// block's threads do softmax, the other's matrix instructions run. Threads of a block may be a page
-// or two apart, which is why "P written" has a barrier per S buffer and "O updated" one each for even and
-// odd pages: an arrival for a later page must not count for page i.
+// block's threads do softmax, the other's matrix instructions run. Warps of a block may be up to three
+// pages apart (S runs that far ahead), which is why "P written" has a barrier per S buffer and "O
+// updated" four that take turns (page % 4): a wait names a barrier's phase by its parity, and an
+// arrival for a later or an earlier page must not count for page i.
+//
+// The copy warp sets the barriers up and asks for the first four pages before the block-wide barrier:
+// they travel while the other warps fetch Q and tensor memory is allocated.
 //
 // Decisions that rest on measurements (2,048 tokens, 71 heads on one K/V head; the profile of this kernel
-// has the series): one softmax thread per row (2 to 3 % ahead of two); O is rescaled only when a row's
-// maximum has grown by more than 2^8 (136 -> 121 us); three S buffers with P in place of S (121 -> 118 us);
-// P in tensor memory rather than in shared memory (2 to 5 %); no cap on registers (a cap of 128 cost
-// 10 %). A block is one chain of dependent steps per page (about 1.5 us) and an SM holds two such chains:
-// the exponential unit is busy a third of the time, the tensor pipe a sixth.
+// has the series): one softmax thread per row; O is rescaled only when a row's maximum has grown by more
+// than 2^8; three S buffers with P in place of S; P in tensor memory rather than in shared memory; no cap
+// on registers; both halves of a row of S asked for before one wait, three-input maxima and packed
+// two-value multiply-adds and adds in the softmax (3 %); four page stages. A block is one chain of
+// dependent steps per page (about 1,500 clocks with two chains an SM, of which the exponential unit is
+// busy 1,024) plus 6 us of set-up and drain; blocks that stay and draw one tile after another from a
+// counter saved the set-up but ran their pages 10 to 25 % slower, and were taken out again.
 #include "mma_common.cuh"
 #include "tc_common.cuh"
 
 namespace {
 
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float m;
+  asm("max.f32 %0, %1, %2, %3;\n" : "=f"(m) : "f"(a), "f"(b), "f"(c));
+  return m;
+}
+// two float32 values in one 64-bit register for the packed multiply-add and add instructions
+__device__ __forceinline__ uint64_t pack2(float a, float b) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};\n" : "=l"(r) : "f"(a), "f"(b));
+  return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float& a, float& b) {
+  asm("mov.b64 {%0, %1}, %2;\n" : "=f"(a), "=f"(b) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;\n" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("add.rn.f32x2 %0, %1, %2;\n" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+
 constexpr int TQ = 128;          // query rows per block
-constexpr int STAGES_TC = 4;
+constexpr int STAGES_TC = 4;      // page stages (three are 15 to 30 % slower, five bring nothing)
 // Tiles of D = 64 or 128 dims are kept as D / 64 blocks of [rows][64 dims], one after another, each
 // block with the 128-byte swizzle: the layout that the matrix descriptors name for K-major operands
 // (Q, K: a block per 64 values of the contraction) and for the MN-major V (a block per 64 dims of
@@ -63,15 +94,10 @@ struct TcParams {
   const float* slopes;   // per-head score slopes (ALiBi), or null
 };
 
-constexpr int TPR = 1;                              // threads per query row
-constexpr int COLS = KEYS / TPR;                    // columns of a page that a thread handles
-constexpr int SOFTMAX_THREADS = TPR * TQ;
+constexpr int SOFTMAX_THREADS = TQ;                 // one thread per query row
 // one more warp whose first lane issues the matrix instructions, and one whose first lane asks the
 // tensor memory accelerator for the pages
 constexpr int BLOCK_THREADS = SOFTMAX_THREADS + 64;
-
-// barrier among the TPR warps that share 32 query rows (ids 1..4 are used)
-__device__ __forceinline__ void row_sync(int id) { asm volatile("bar.sync %0, %1;\n" ::"r"(id), "n"(TPR * 32) : "memory"); }
 
 // BIAS: a per-head slope times the key's position is added to the raw scores, formed in bfloat16 as
 // the reference forms it.
@@ -87,29 +113,25 @@ attention_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
   constexpr int TILE_Q_BYTES = TQ * D * 2;       // 16 or 32 KB
   constexpr int TILE_KV_BYTES = KEYS * D * 2;    // 8 or 16 KB
-  constexpr int COLS_O = D / TPR;                // columns of O that a thread rescales and writes
   // tensor memory: three S buffers of 64 columns (page i uses buffer i % 3), O at [192, 192 + D). P of a
   // page (64 keys as bfloat16 pairs, 32 columns) takes the place of its S: a thread has its row of S in
   // registers before it writes its row of P, nobody else touches that row, and the S of three pages later
   // is issued after the O += P V that reads this P (the tensor pipe runs in order). With three buffers S
   // runs two pages ahead of the softmax, so the softmax does not wait for a matrix product that was
   // issued only when the slowest warp finished the page before.
-  static_assert(TPR == 1, "P in place of S needs one thread per row");
   constexpr uint32_t TMEM_O = 192, TMEM_COLS = (D == 64) ? 256 : 512;
   unsigned char* q_tile = smem;
   unsigned char* k_ring = q_tile + TILE_Q_BYTES;                      // STAGES_TC pages
   unsigned char* v_ring = k_ring + STAGES_TC * TILE_KV_BYTES;         // STAGES_TC pages
-  // barriers: [0..2] S buffer written; [3], [4] O updated (even / odd pages); [5..7] P written (page % 3);
+  // barriers: [0..2] S buffer written; [3..6] O updated (page % 4); [7..9] P written (page % 3);
   // then per stage: page landed, stage free again
   uint64_t* bars = reinterpret_cast<uint64_t*>(v_ring + STAGES_TC * TILE_KV_BYTES);
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8 + 2 * STAGES_TC);
-  float* pmax = reinterpret_cast<float*>(tmem_slot + 2);   // [2 buffers][TPR parts][TQ]: partial row maxima
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10 + 2 * STAGES_TC);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const bool mma_warp = warp == SOFTMAX_THREADS / 32;
   const bool copy_warp = warp == SOFTMAX_THREADS / 32 + 1;
   const int row = tid & (TQ - 1);        // query row of a softmax thread (= its tensor-memory lane)
-  const int part = (tid >> 7) % TPR;     // which COLS of the 64 columns of a page it handles
   // heads are the fast index of the grid: the blocks of one tile start together (they read the same
   // pages), and tiles come in the order of the list, which the caller sorts by falling key count so that
   // the longest chains start first and the short ones fill the end
@@ -125,24 +147,51 @@ attention_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
   const int n_blocks = last_pos / KEYS + 1;
   const int* pages = sb.pages + size_t(seq) * sb.pages_stride;
 
-  // A thread may be two pages ahead of another one (S of page i + 2 is issued before P of page i is
+  // A warp may be up to three pages ahead of another one (S of page i + 2 is issued before P of page i is
   // complete, S of page i + 3 only after it): arrivals for pages i + 1 and i + 2 must not count for page
-  // i, hence a "P written" barrier per S buffer. "O updated" is waited for one page back only.
-  const uint32_t bar_s = smem_u32(&bars[0]), bar_o = smem_u32(&bars[3]), bar_o2 = smem_u32(&bars[4]);
-  const uint32_t bar_p = smem_u32(&bars[5]);
-  const uint32_t bar_k = smem_u32(&bars[8]), bar_free = smem_u32(&bars[8 + STAGES_TC]);
-  if (tid == 0) {
-    for (int b = 0; b < 3; ++b) {
-      mbar_init(bar_s + 8 * b, 1);
-      mbar_init(bar_p + 8 * b, SOFTMAX_THREADS);
+  // i, hence a "P written" barrier per S buffer. A wait names a barrier's phase by its parity, which is
+  // only right if the completion before the awaited one has happened already. A thread that has read S of
+  // page i knows that O += P V of page i - 3 has completed (the tensor pipe runs in order), and so the one
+  // of page i - 4: hence four "O updated" barriers that take turns. With two, a warp that reached the end
+  // of its walk pages ahead of the others could take the completion of page i - 2 for that of page i and
+  // read O before the last products were in it.
+  const uint32_t bar_s = smem_u32(&bars[0]), bar_o = smem_u32(&bars[3]);
+  const uint32_t bar_p = smem_u32(&bars[7]);
+  const uint32_t bar_k = smem_u32(&bars[10]), bar_free = smem_u32(&bars[10 + STAGES_TC]);
+  // The copy warp's first lane sets the barriers up and asks for the first pages at once (the page
+  // numbers 32 at a time, one a lane): they are on their way while the other warps fetch Q and tensor
+  // memory is allocated. Nobody else touches a barrier before the block-wide barrier below.
+  constexpr uint32_t PAGE_BYTES = 2 * TILE_KV_BYTES;
+  auto ask_page = [&](int b, int page) {
+    const int st = b % STAGES_TC;
+    const int y = (page * p.kv_heads + g) * KEYS;   // first row of the page in the pool seen as [rows][D]
+    const uint32_t full = bar_k + 8 * st;
+    mbar_expect_tx(full, PAGE_BYTES);
+#pragma unroll
+    for (int blk = 0; blk < D / 64; ++blk) {
+      tma_load_2d(smem_u32(k_ring + st * TILE_KV_BYTES + blk * (KEYS * 128)), &k_map, blk * 64, y, full);
+      tma_load_2d(smem_u32(v_ring + st * TILE_KV_BYTES + blk * (KEYS * 128)), &v_map, blk * 64, y, full);
     }
-    mbar_init(bar_o, 1);
-    mbar_init(bar_o2, 1);
-    for (int s = 0; s < STAGES_TC; ++s) {
-      mbar_init(bar_k + 8 * s, 1);      // the copy thread's expect_tx; the bytes complete it
-      mbar_init(bar_free + 8 * s, 1);   // tcgen05.commit after the stage's O += P V
+  };
+  int first_pages = 0;   // the copy warp's lanes: page numbers b = lane of the first 32 pages
+  if (copy_warp) {
+    first_pages = lane < n_blocks ? pages[lane] : 0;
+    if (lane == 0) {
+      for (int b = 0; b < 3; ++b) {
+        mbar_init(bar_s + 8 * b, 1);
+        mbar_init(bar_p + 8 * b, SOFTMAX_THREADS);
+      }
+      for (int b = 0; b < 4; ++b) mbar_init(bar_o + 8 * b, 1);
+      for (int s = 0; s < STAGES_TC; ++s) {
+        mbar_init(bar_k + 8 * s, 1);      // the copy thread's expect_tx; the bytes complete it
+        mbar_init(bar_free + 8 * s, 1);   // tcgen05.commit after the stage's O += P V
+      }
+      asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
-    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    for (int b = 0; b < STAGES_TC && b < n_blocks; ++b) {
+      const int page = __shfl_sync(0xffffffffu, first_pages, b);
+      if (lane == 0) ask_page(b, page);
+    }
   }
   if (warp == 0) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS));
@@ -174,22 +223,22 @@ attention_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
     // Page b goes into stage b % STAGES_TC as D / 64 boxes [64 keys x 64 dims] for K and for V, in
     // the swizzled layout; the stage's barrier counts the bytes. A stage is free again when the
     // O += P V that read it has completed (S of that page completed before it).
-    if (lane == 0) {
-      constexpr uint32_t PAGE_BYTES = 2 * TILE_KV_BYTES;
-      int issued = 0;
-      for (int b = 0; b < n_blocks; ++b) {
-        const int st = b % STAGES_TC;
-        if (b >= STAGES_TC && !mbar_wait(bar_free + 8 * st, ((b / STAGES_TC) - 1) & 1, error_flag, 6)) break;
-        const int y = (pages[b] * p.kv_heads + g) * KEYS;   // first row of the page in the pool seen as [rows][D]
-        const uint32_t full = bar_k + 8 * st;
-        mbar_expect_tx(full, PAGE_BYTES);
-#pragma unroll
-        for (int blk = 0; blk < D / 64; ++blk) {
-          tma_load_2d(smem_u32(k_ring + st * TILE_KV_BYTES + blk * (KEYS * 128)), &k_map, blk * 64, y, full);
-          tma_load_2d(smem_u32(v_ring + st * TILE_KV_BYTES + blk * (KEYS * 128)), &v_map, blk * 64, y, full);
+    // All lanes walk the loop (page numbers come 32 at a time, one a lane); the first lane waits and asks.
+    int issued = min(n_blocks, STAGES_TC);
+    int mine = first_pages;
+    for (int b = STAGES_TC; b < n_blocks && alive; ++b) {
+      if ((b & 31) == 0) mine = b + lane < n_blocks ? pages[b + lane] : 0;
+      const int page = __shfl_sync(0xffffffffu, mine, b & 31);
+      if (lane == 0) {
+        alive = mbar_wait(bar_free + 8 * (b % STAGES_TC), ((b / STAGES_TC) - 1) & 1, error_flag, 6);
+        if (alive) {
+          ask_page(b, page);
+          issued = b + 1;
         }
-        issued = b + 1;
       }
+      alive = __shfl_sync(0xffffffffu, alive ? 1 : 0, 0) != 0;
+    }
+    if (lane == 0) {
       if (issued < n_blocks) {
         // a wait ran out: what is in flight lands before the block ends (bounded waits again)
         for (int b = max(0, issued - STAGES_TC); b < issued; ++b)
@@ -239,63 +288,57 @@ attention_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
         for (int blk = 0; blk < D / 64; ++blk)
           tc_mma4_ts<128>(tmem_o + blk * 64, tmem_base + buf * 64, desc_v0 + st * STAGE_UNITS + blk * KV_BLOCK,
                           IDESC_PV, i > 0 ? 1u : 0u);
-        tc_commit((i & 1) ? bar_o2 : bar_o);
+        tc_commit(bar_o + 8 * (i & 3));
         tc_commit(bar_free + 8 * st);   // the copy thread may refill this stage
         if (++buf == 3) { buf = 0; phase ^= 1; }
       }
     }
   } else {
     // ------------------------------------------------------------ softmax threads
-    const uint32_t lane_addr = tmem_base + (uint32_t((warp & 3) * 32) << 16) + part * COLS;  // this warp's lanes, its columns
-    const uint32_t o_addr = tmem_base + (uint32_t((warp & 3) * 32) << 16) + TMEM_O + part * COLS_O;   // its columns of O
+    const uint32_t lane_addr = tmem_base + (uint32_t((warp & 3) * 32) << 16);   // this warp's lanes
+    const uint32_t o_addr = lane_addr + TMEM_O;
     int buf = 0, phase = 0;   // S buffer of page i (i % 3) and the parity of its barriers ((i / 3) & 1)
-    const int sync_id = 1 + (warp & 3);
-    float m_run = -INFINITY, l_run = 0.f;   // running maximum of the raw scores, this thread's half of the sum
+    float m_run = -INFINITY, l_run = 0.f;   // running maximum of the raw scores, the row's sum
     const float slope = BIAS ? p.slopes[h] : 0.f;
     const float sl2 = p.scale * 1.4426950408889634f;
+    const uint64_t sl2_2 = pack2(sl2, sl2);
     for (int i = 0; i < n_blocks; ++i) {
-      // (1) this thread's 32 columns of its row of S_i
+      // (1) this thread's row of S_i: both halves asked for, one wait
       if (alive) alive = mbar_wait(bar_s + buf * 8, phase, error_flag, 1);
       tc_fence_after();
-      float s[COLS];
-      tmem_ld<COLS>(lane_addr + buf * 64, s);
+      float s[KEYS];
+      tmem_ld64_once(lane_addr + buf * 64, s);
       if (BIAS) {
 #pragma unroll
-        for (int j = 0; j < COLS; ++j) s[j] += alibi_bias(slope, i * KEYS + part * COLS + j);
+        for (int j = 0; j < KEYS; ++j) s[j] += alibi_bias(slope, i * KEYS + j);
       }
-      // (3) maximum of the visible scores; only pages that reach past some row's position need the test
-      float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+      // (2) maximum of the visible scores; only pages that reach past some row's position need the test
       if (i * KEYS + KEYS - 1 > past + q0 || !row_ok) {   // first part is uniform over the block
-        const int visible = row_pos - i * KEYS - part * COLS;   // columns j <= visible are seen by this row
+        const int visible = row_pos - i * KEYS;   // columns j <= visible are seen by this row
 #pragma unroll
-        for (int j = 0; j < COLS; ++j) {
-          s[j] = (j <= visible) ? s[j] : -INFINITY;
-          mx[j & 3] = fmaxf(mx[j & 3], s[j]);
-        }
-      } else {
-#pragma unroll
-        for (int j = 0; j < COLS; ++j) mx[j & 3] = fmaxf(mx[j & 3], s[j]);
+        for (int j = 0; j < KEYS; ++j) s[j] = (j <= visible) ? s[j] : -INFINITY;
       }
-      const float m_part = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
-      float* pm = pmax + (i & 1) * TPR * TQ;
-      pm[part * TQ + row] = m_part;
-      row_sync(sync_id);   // the warps that share these 32 rows
-      float m_blk = m_part;
+      float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-      for (int o = 1; o < TPR; ++o) m_blk = fmaxf(m_blk, pm[((part + o) % TPR) * TQ + row]);
-      float m_new = fmaxf(m_run, m_blk);
+      for (int j = 0; j < KEYS; j += 8) {
+        mx[0] = max3(mx[0], s[j], s[j + 1]);
+        mx[1] = max3(mx[1], s[j + 2], s[j + 3]);
+        mx[2] = max3(mx[2], s[j + 4], s[j + 5]);
+        mx[3] = max3(mx[3], s[j + 6], s[j + 7]);
+      }
+      float m_new = fmaxf(m_run, fmaxf(max3(mx[0], mx[1], mx[2]), mx[3]));
       if ((m_new - m_run) * sl2 <= RESCALE_LOG2) m_new = m_run;   // (false from -inf: the first scores set it)
       const float corr = (m_run == -INFINITY) ? 0.f : fast_exp2((m_run - m_new) * sl2);
       const bool moved = (m_new != m_run) && (m_run != -INFINITY);
       m_run = m_new;
       const float m_off = (m_run == -INFINITY) ? 0.f : m_run * sl2;   // exp2(s * sl2 - m_off); exp2(-inf) = 0
-      // (4) rescale this thread's columns of its row of O if any row of the warp moved its maximum;
-      // only then this warp waits for the previous page's O += P V
+      // (3) rescale this thread's row of O if any row of the warp moved its maximum; only then this warp
+      // waits for the previous page's O += P V
       if (i > 0 && __any_sync(0xffffffffu, moved)) {
-        if (alive) alive = mbar_wait(((i - 1) & 1) ? bar_o2 : bar_o, ((i - 1) >> 1) & 1, error_flag, 2);
+        if (alive) alive = mbar_wait(bar_o + 8 * ((i - 1) & 3), ((i - 1) >> 2) & 1, error_flag, 2);
         tc_fence_after();
 #pragma unroll
-        for (int c0 = 0; c0 < COLS_O; c0 += 32) {
+        for (int c0 = 0; c0 < D; c0 += 32) {
           float o[32];
           tmem_ld32(o_addr + c0, o);
 #pragma unroll
@@ -304,40 +347,37 @@ attention_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
         }
         tmem_st_wait();
       }
-      l_run *= corr;
-      // (6) P = exp2(S - max) as bfloat16 into the swizzled P tile: row, chunks 4 part .. 4 part + 3
-      static_assert(COLS == 32 || COLS == 64, "P goes to tensor memory 16 or 32 packed columns per thread");
-      float ls[4] = {0.f, 0.f, 0.f, 0.f};
-      uint32_t w[COLS / 2];
+      // (4) P = exp2(S - max) as bfloat16 pairs, two values per packed multiply-add
+      const uint64_t moff_2 = pack2(-m_off, -m_off);
+      uint64_t acc2[4] = {0ull, 0ull, 0ull, 0ull};
+      uint32_t w[KEYS / 2];
 #pragma unroll
-      for (int e = 0; e < COLS / 2; ++e) {
-        const float a = fast_exp2(fmaf(s[2 * e], sl2, -m_off));
-        const float b = fast_exp2(fmaf(s[2 * e + 1], sl2, -m_off));
-        ls[e & 3] += a + b;
+      for (int e = 0; e < KEYS / 2; ++e) {
+        float x0, x1;
+        unpack2(fma2(pack2(s[2 * e], s[2 * e + 1]), sl2_2, moff_2), x0, x1);
+        const float a = fast_exp2(x0), b = fast_exp2(x1);
+        acc2[e & 3] = add2(acc2[e & 3], pack2(a, b));
         w[e] = pack_bf16(a, b);
       }
       // P in place of this page's S: keys 2c, 2c + 1 in column c of the buffer (this thread's row of S is in
       // registers since the load above)
-      tmem_st_u32<COLS / 2>(lane_addr + buf * 64, w);
+      tmem_st_u32<KEYS / 2>(lane_addr + buf * 64, w);
       tmem_st_wait();
-      l_run += (ls[0] + ls[1]) + (ls[2] + ls[3]);   // this thread's half of the row sum
+      float l0, l1, l2, l3;
+      unpack2(add2(acc2[0], acc2[1]), l0, l1);
+      unpack2(add2(acc2[2], acc2[3]), l2, l3);
+      l_run = l_run * corr + ((l0 + l1) + (l2 + l3));
       tc_fence_before();
-      mbar_arrive(bar_p + buf * 8);   // (7) the issuing thread starts O += P V when all rows have arrived
+      mbar_arrive(bar_p + buf * 8);   // (5) the issuing thread starts O += P V when all rows have arrived
       if (++buf == 3) { buf = 0; phase ^= 1; }
     }
-    // the parts of every row sum meet, in the buffer that the last page did not use, in one order
-    float* pl = pmax + (n_blocks & 1) * TPR * TQ;
-    pl[part * TQ + row] = l_run;
-    row_sync(sync_id);
-    float l_row = 0.f;
-#pragma unroll
-    for (int o = 0; o < TPR; ++o) l_row += pl[o * TQ + row];
-    if (alive) alive = mbar_wait(((n_blocks - 1) & 1) ? bar_o2 : bar_o, ((n_blocks - 1) >> 1) & 1, error_flag, 3);
+    // the walk's last O += P V
+    if (alive) alive = mbar_wait(bar_o + 8 * ((n_blocks - 1) & 3), ((n_blocks - 1) >> 2) & 1, error_flag, 3);
     tc_fence_after();
-    const float inv = l_row > 0.f ? 1.f / l_row : 0.f;
-    __nv_bfloat16* dst = out + (size_t(start + q0 + row) * p.heads + h) * D + part * COLS_O;
+    const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+    __nv_bfloat16* dst = out + (size_t(start + q0 + row) * p.heads + h) * D;
 #pragma unroll
-    for (int c0 = 0; c0 < COLS_O; c0 += 32) {
+    for (int c0 = 0; c0 < D; c0 += 32) {
       float o[32];
       tmem_ld32(o_addr + c0, o);
       if (row_ok) {
@@ -370,7 +410,7 @@ int launch_tc(const void* q, const void* k_pool, const void* v_pool, int pool_pa
   const CUtensorMap* km = pool_map(k_pool, pool_pages, p.kv_heads, D);
   const CUtensorMap* vm = pool_map(v_pool, pool_pages, p.kv_heads, D);
   if (km == nullptr || vm == nullptr) return PTB_ERR_LAUNCH;
-  const size_t smem = 1024 + TQ * D * 2 + 2 * STAGES_TC * KEYS * D * 2 + 192 + 2 * TPR * TQ * sizeof(float);
+  const size_t smem = 1024 + TQ * D * 2 + 2 * STAGES_TC * KEYS * D * 2 + 192;
   static bool configured = false;
   if (!configured) {
     if (cudaFuncSetAttribute(attention_tc_kernel<D, BIAS>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess)

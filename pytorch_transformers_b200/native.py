@@ -30,6 +30,9 @@ LIB_NAME = "libptb200_kernels.so"
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-lineinfo",
               "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden"]
 
+# more flags for nvcc from the environment (a -D for a trial build, say); part of the fingerprint
+NVCC_FLAGS += [f for f in os.environ.get("PTB200_NVCC_EXTRA", "").split() if f]
+
 _lock = threading.Lock()
 _lib: Optional[ctypes.CDLL] = None
 
