@@ -111,19 +111,41 @@ attention_decode_tc_kernel(const __nv_bfloat16* __restrict__ fused, __nv_bfloat1
   // The usual rotation (the halves of the head, or none) is done in registers, a thread per head; any
   // other number of rotated pairs goes the general way through shared memory.
   const bool in_registers = (P == DD / 2 && !p.interleaved) || P == 0;
-  if (tid == 0) {
-    for (int b = 0; b < 2; ++b) {
-      mbar_init(bar_s + 8 * b, 1);
-      mbar_init(bar_o + 8 * b, 1);
-      mbar_init(bar_p + 8 * b, uint32_t(active_warps) * 32);
+  // The copy warp's first lane sets the barriers up and asks for this block's first pages at once (their
+  // numbers read by the warp's lanes, one each): they travel while tensor memory is allocated and the token's
+  // row is staged. Nobody else touches a barrier before the block-wide barrier below. The token's own
+  // page waits for the token's key and value and is asked for after that barrier.
+  auto ask_page = [&](int b, int page) {
+    const int st = b % STAGES_D;
+    const int y = (page * p.kv_heads + g) * KEYS;
+    const uint32_t full = bar_k + 8 * st;
+    mbar_expect_tx(full, 2 * TILE_KV);
+    tma_load_2d(smem_u32(k_ring + st * TILE_KV), &k_map, 0, y, full);
+    tma_load_2d(smem_u32(v_ring + st * TILE_KV), &v_map, 0, y, full);
+  };
+  int my_page = 0, early = 0;   // copy warp: page number of page kb_begin + lane; pages asked for before the barrier
+  if (copy_warp) {
+    my_page = lane < n_mine ? pages[kb_begin + lane] : 0;
+    if (lane == 0) {
+      for (int b = 0; b < 2; ++b) {
+        mbar_init(bar_s + 8 * b, 1);
+        mbar_init(bar_o + 8 * b, 1);
+        mbar_init(bar_p + 8 * b, uint32_t(active_warps) * 32);
+      }
+      for (int s = 0; s < STAGES_D; ++s) {
+        mbar_init(bar_k + 8 * s, 1);
+        mbar_init(bar_free + 8 * s, 1);
+      }
+      mbar_init(bar_new, in_registers ? 1 : SOFTMAX_T);
+      mbar_init(bar_q, SOFTMAX_T);
+      asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
-    for (int s = 0; s < STAGES_D; ++s) {
-      mbar_init(bar_k + 8 * s, 1);
-      mbar_init(bar_free + 8 * s, 1);
+    early = min(n_mine, STAGES_D);
+    if (p.write_cache && covers_new) early = min(early, n_mine - 1);
+    for (int b = 0; b < early; ++b) {
+      const int page = __shfl_sync(0xffffffffu, my_page, b);
+      if (lane == 0) ask_page(b, page);
     }
-    mbar_init(bar_new, in_registers ? 1 : SOFTMAX_T);
-    mbar_init(bar_q, SOFTMAX_T);
-    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
   if (warp == 0) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(tmem_slot)), "r"(256));
@@ -242,18 +264,15 @@ attention_decode_tc_kernel(const __nv_bfloat16* __restrict__ fused, __nv_bfloat1
   }
 
   if (copy_warp) {
+    // The rest is the first lane's alone. (All lanes walking the loop, with the page numbers read 32 at a
+    // time and handed round by shuffles, made long walks 7 % slower.)
     if (lane == 0) {
-      int issued = 0;
-      for (int b = 0; b < n_mine; ++b) {
-        const int st = b % STAGES_D;
-        if (b >= STAGES_D && !mbar_wait(bar_free + 8 * st, ((b / STAGES_D) - 1) & 1, error_flag, 6)) break;
+      int issued = early;
+      for (int b = early; b < n_mine; ++b) {
+        if (b >= STAGES_D && !mbar_wait(bar_free + 8 * (b % STAGES_D), ((b / STAGES_D) - 1) & 1, error_flag, 6)) break;
         // the token's page waits for the token's key and value
         if (kb_begin + b == kb_last && p.write_cache && !mbar_wait(bar_new, 0, error_flag, 7)) break;
-        const int y = (pages[kb_begin + b] * p.kv_heads + g) * KEYS;
-        const uint32_t full = bar_k + 8 * st;
-        mbar_expect_tx(full, 2 * TILE_KV);
-        tma_load_2d(smem_u32(k_ring + st * TILE_KV), &k_map, 0, y, full);
-        tma_load_2d(smem_u32(v_ring + st * TILE_KV), &v_map, 0, y, full);
+        ask_page(b, pages[kb_begin + b]);
         issued = b + 1;
       }
       if (issued < n_mine)

@@ -158,8 +158,8 @@ attention_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
   const uint32_t bar_s = smem_u32(&bars[0]), bar_o = smem_u32(&bars[3]);
   const uint32_t bar_p = smem_u32(&bars[7]);
   const uint32_t bar_k = smem_u32(&bars[10]), bar_free = smem_u32(&bars[10 + STAGES_TC]);
-  // The copy warp's first lane sets the barriers up and asks for the first pages at once (the page
-  // numbers 32 at a time, one a lane): they are on their way while the other warps fetch Q and tensor
+  // The copy warp's first lane sets the barriers up and asks for the first pages at once (their numbers
+  // read by the warp's lanes, one each): they are on their way while the other warps fetch Q and tensor
   // memory is allocated. Nobody else touches a barrier before the block-wide barrier below.
   constexpr uint32_t PAGE_BYTES = 2 * TILE_KV_BYTES;
   auto ask_page = [&](int b, int page) {
@@ -173,7 +173,7 @@ attention_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
       tma_load_2d(smem_u32(v_ring + st * TILE_KV_BYTES + blk * (KEYS * 128)), &v_map, blk * 64, y, full);
     }
   };
-  int first_pages = 0;   // the copy warp's lanes: page numbers b = lane of the first 32 pages
+  int first_pages = 0;   // the copy warp's lanes: the number of page b = lane
   if (copy_warp) {
     first_pages = lane < n_blocks ? pages[lane] : 0;
     if (lane == 0) {
@@ -223,22 +223,14 @@ attention_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
     // Page b goes into stage b % STAGES_TC as D / 64 boxes [64 keys x 64 dims] for K and for V, in
     // the swizzled layout; the stage's barrier counts the bytes. A stage is free again when the
     // O += P V that read it has completed (S of that page completed before it).
-    // All lanes walk the loop (page numbers come 32 at a time, one a lane); the first lane waits and asks.
-    int issued = min(n_blocks, STAGES_TC);
-    int mine = first_pages;
-    for (int b = STAGES_TC; b < n_blocks && alive; ++b) {
-      if ((b & 31) == 0) mine = b + lane < n_blocks ? pages[b + lane] : 0;
-      const int page = __shfl_sync(0xffffffffu, mine, b & 31);
-      if (lane == 0) {
-        alive = mbar_wait(bar_free + 8 * (b % STAGES_TC), ((b / STAGES_TC) - 1) & 1, error_flag, 6);
-        if (alive) {
-          ask_page(b, page);
-          issued = b + 1;
-        }
-      }
-      alive = __shfl_sync(0xffffffffu, alive ? 1 : 0, 0) != 0;
-    }
+    // The first pages were asked for above; the rest is the first lane's alone.
     if (lane == 0) {
+      int issued = min(n_blocks, STAGES_TC);
+      for (int b = STAGES_TC; b < n_blocks; ++b) {
+        if (!mbar_wait(bar_free + 8 * (b % STAGES_TC), ((b / STAGES_TC) - 1) & 1, error_flag, 6)) break;
+        ask_page(b, pages[b]);
+        issued = b + 1;
+      }
       if (issued < n_blocks) {
         // a wait ran out: what is in flight lands before the block ends (bounded waits again)
         for (int b = max(0, issued - STAGES_TC); b < issued; ++b)
