@@ -275,3 +275,61 @@ def test_tc_far_key(K, d, position):
     out, ref = attention_case(K, BF, 2, 1, d, pasts=[0, 0], news=[70, 700], position=position, seed=5,
                               needle=(1, 3), tc=True)
     torch.testing.assert_close(out, ref, **tol(BF))
+
+
+# ------------------------------------------------------------------------------ the same launch again and again
+def _cache_with(K, kv, d, lengths, new):
+    """A cache of one entry whose sequences hold `lengths` tokens of random keys and values, and the
+    step that brings `new` tokens to each of them."""
+    from pytorch_transformers_b200.cache.paged import Cache
+    from pytorch_transformers_b200.engine.batch import StepContext
+    from pytorch_transformers_b200.parts.attention import AttentionTiles
+    from pytorch_transformers_b200.parts.base import CacheNeed
+    cache = Cache([(0, CacheNeed("full", kv, d, 0), None)], sum(t + new + 64 for t in lengths), BF, "cuda")
+    slots = [cache.open() for _ in lengths]
+    for slot, t in zip(slots, lengths):
+        if t:
+            cache.reserve(slot, t)
+            cache.commit(slot, t)
+    ctx = StepContext(cache, slots, [[0] * new] * len(lengths), 1, [[]] * len(lengths), (AttentionTiles(K),))
+    k_pool, v_pool, group = cache.entry_storage(0)
+    gen = torch.Generator(device="cuda").manual_seed(3)
+    k_pool.normal_(generator=gen)
+    v_pool.normal_(generator=gen)
+    return ctx, k_pool, v_pool, ctx.batch_c[group], gen
+
+
+@pytest.mark.parametrize("heads,kv,d,tokens", [(71, 1, 64, 2048), (32, 8, 128, 1500), (12, 3, 128, 700)])
+def test_tc_prompts_the_same_bits_every_time(K, heads, kv, d, tokens):
+    """The roles of the prompt kernel meet at barriers only, and its warps run pages apart: a wait that
+    takes one phase for another shows as a result that changes from launch to launch (it did, with a
+    single row or a warp of rows off in their last page), long before it shows against the plain
+    attention of a small case. Forty launches of the same work must give the same bits."""
+    ctx, k_pool, v_pool, batch, gen = _cache_with(K, kv, d, [0, 130], tokens)
+    tiles = ctx.plan("attention_tiles")
+    q = torch.randn(2 * tokens, heads, d, device="cuda", generator=gen).to(BF)
+    run = lambda: K.attention_tc(q, k_pool, v_pool, batch, tiles.dev["mtile_seq"], tiles.dev["mtile_q0"],
+                                 tiles.facts["n_mma_tiles"], kv, d ** -0.5, None)
+    first = run()
+    for _ in range(40):
+        assert torch.equal(run(), first)
+    K.check_device_errors("cuda")
+    # and they are the right bits: the general kernel on the same tiles
+    ref = K.attention_generic(q, k_pool, v_pool, batch, tiles.dev["tile_seq"], tiles.dev["tile_q0"],
+                              tiles.facts["n_tiles"], None, kv, d ** -0.5, 0)
+    torch.testing.assert_close(first.float(), ref.float(), atol=2e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("splits,teams", [(4, 1), (8, 1), (8, 4)])
+def test_fused_decode_tc_the_same_bits_every_time(K, splits, teams):
+    heads, kv, d = 71, 1, 64
+    ctx, k_pool, v_pool, batch, gen = _cache_with(K, kv, d, [2048, 5000, 300, 1777], 1)
+    fused = torch.randn(4, kv * (heads // kv + 2) * d, device="cuda", generator=gen).to(BF)
+    inv = (1.0 / (10000 ** (torch.arange(0, d, 2).float() / d))).cuda()
+    rope = K.rope_table(ctx.dev["tok_pos"], inv)
+    run = lambda: K.attention_decode_tc(fused, k_pool, v_pool, batch, rope, kv, heads // kv, d, d ** -0.5, splits,
+                                        n_teams=teams)
+    first = run()
+    for _ in range(40):
+        assert torch.equal(run(), first)
+    K.check_device_errors("cuda")
