@@ -314,20 +314,55 @@ __global__ void bias_act_kernel(T* __restrict__ y, const float* __restrict__ bia
 // approximation 7.1.26 of Abramowitz and Stegun (absolute error below 1.5e-7, three orders of
 // magnitude under bfloat16's resolution), one reciprocal and one exp2 instead of erff's long
 // polynomial. The float32 kernels keep erff.
-__device__ __forceinline__ float gelu_erf_for_bf16(float v) {
-  const float z = fabsf(v) * 0.70710678118654752440f;
-  const float t = __frcp_rn(fmaf(0.3275911f, z, 1.0f));
-  float poly = fmaf(1.061405429f, t, -1.453152027f);
-  poly = fmaf(poly, t, 1.421413741f);
-  poly = fmaf(poly, t, -0.284496736f);
-  poly = fmaf(poly, t, 0.254829592f);
-  float e;
-  asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(e) : "f"(-z * z * 1.4426950408889634f));
-  const float erf_abs = fmaf(-poly * t, e, 1.0f);
-  return 0.5f * v * (1.0f + copysignf(erf_abs, v));
+//   t = 1 / (1 + 0.3275911 z), z = |v| / sqrt 2;  erf z = 1 - (a1 t + ... + a5 t^5) exp(-z^2)
+// Two values go through it in one 64-bit register (fma.rn.f32x2 / mul.rn.f32x2: half the instructions on
+// the multiply-add pipe; 38.0 -> 29.9 us on 2,048 x 18,176 values). log2(e) is folded into the argument
+// (z' = |v| sqrt(log2 e / 2), the rational's constant divided accordingly), the sign into
+// 0.5 v + 0.5 |v| erf(|v| / sqrt 2), and the reciprocal is the approximate one (an error of one unit in
+// the last place of float32).
+__device__ __forceinline__ uint64_t f2_pack(float a, float b) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};\n" : "=l"(r) : "f"(a), "f"(b));
+  return r;
+}
+__device__ __forceinline__ void f2_unpack(uint64_t v, float& a, float& b) {
+  asm("mov.b64 {%0, %1}, %2;\n" : "=f"(a), "=f"(b) : "l"(v));
+}
+__device__ __forceinline__ uint64_t f2_fma(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;\n" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+__device__ __forceinline__ uint64_t f2_mul(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("mul.rn.f32x2 %0, %1, %2;\n" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ uint64_t f2_const(float c) { return f2_pack(c, c); }
+__device__ __forceinline__ void gelu_erf_for_bf16_x2(float& v0, float& v1) {
+  constexpr uint64_t ABS = 0x7fffffff7fffffffull, SIGN = 0x8000000080000000ull;
+  const uint64_t v = f2_pack(v0, v1);
+  const uint64_t hv = f2_mul(v, f2_const(0.5f));
+  const uint64_t z = f2_mul(v & ABS, f2_const(0.84932180028801904272f));        // |v| sqrt(log2(e) / 2)
+  float d0, d1;
+  f2_unpack(f2_fma(f2_const(0.27273748f), z, f2_const(1.0f)), d0, d1);          // 1 + 0.3275911 |v| / sqrt 2
+  float t0, t1;
+  asm("rcp.approx.ftz.f32 %0, %1;\n" : "=f"(t0) : "f"(d0));
+  asm("rcp.approx.ftz.f32 %0, %1;\n" : "=f"(t1) : "f"(d1));
+  const uint64_t t = f2_pack(t0, t1);
+  uint64_t poly = f2_fma(f2_const(1.061405429f), t, f2_const(-1.453152027f));
+  poly = f2_fma(poly, t, f2_const(1.421413741f));
+  poly = f2_fma(poly, t, f2_const(-0.284496736f));
+  poly = f2_fma(poly, t, f2_const(0.254829592f));
+  float x0, x1, e0, e1;
+  f2_unpack(f2_mul(z ^ SIGN, z), x0, x1);                                       // -(v^2 / 2) log2(e)
+  asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(e0) : "f"(x0));
+  asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(e1) : "f"(x1));
+  const uint64_t erf_abs = f2_fma(f2_mul(poly, t) ^ SIGN, f2_pack(e0, e1), f2_const(1.0f));
+  f2_unpack(f2_fma(hv & ABS, erf_abs, hv), v0, v1);                             // 0.5 v + 0.5 |v| erf
 }
 
-// the same, eight bfloat16 values per 16-byte word (width a multiple of 8, 16-byte aligned rows); a
+// eight bfloat16 values per 16-byte word (width a multiple of 8, 16-byte aligned rows); a
 // thread takes two words per step, both loads in flight before the arithmetic of either. The
 // presence of a bias is compile-time (without one the loop holds no division for the column), and
 // so is the erf GELU with its cheaper form (FAST_GELU); every other activation goes by its code.
@@ -342,8 +377,13 @@ __device__ __forceinline__ uint4 bias_act_word(uint4 word, const float* __restri
 #pragma unroll
     for (int e = 0; e < 8; ++e) f[e] += b[e];
   }
+  if constexpr (FAST_GELU) {
 #pragma unroll
-  for (int e = 0; e < 8; ++e) f[e] = FAST_GELU ? gelu_erf_for_bf16(f[e]) : apply_activation(f[e], act);
+    for (int e = 0; e < 8; e += 2) gelu_erf_for_bf16_x2(f[e], f[e + 1]);
+  } else {
+#pragma unroll
+    for (int e = 0; e < 8; ++e) f[e] = apply_activation(f[e], act);
+  }
   return pack_bf16x8(f);
 }
 template <bool FAST_GELU, bool BIAS>
