@@ -410,6 +410,12 @@ def attention_tc(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, ba
     return out
 
 
+def attention_tc_pairs(on: bool) -> None:
+    """For measurements: with False, ``attention_tc`` gives every head a block of its own also where two
+    heads of a K/V group could share one (head size 128, an even number of heads a group)."""
+    lib().ptb_attention_tc_pairs(1 if on else 0)
+
+
 def attention_mma_supports(head_dim: int) -> bool:
     return bool(lib().ptb_attention_mma_supports(int(head_dim)))
 

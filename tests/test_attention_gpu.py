@@ -257,7 +257,7 @@ def test_rope_table_equals_in_kernel_angles(K):
 
 
 # ------------------------------------------------------------------------------ tcgen05 prompt kernel
-@pytest.mark.parametrize("heads,kv", [(1, 1), (3, 1), (71, 1), (8, 2), (4, 4)])
+@pytest.mark.parametrize("heads,kv", [(1, 1), (3, 1), (71, 1), (8, 2), (4, 4), (2, 1), (12, 2)])
 @pytest.mark.parametrize("news,pasts", [([128], [0]), ([65], [0]), ([129, 300, 70], [0, 0, 0]), ([200, 66], [130, 63]),
                                         ([1000], [0])])
 @pytest.mark.parametrize("d", [64, 128])
