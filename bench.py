@@ -299,13 +299,13 @@ def run_prefill_attention(args):
     if tiles.facts["mma_tokens"] == K.TC_TILE_TOKENS and K.attention_tc_supports(d):
         launches["tcgen05"] = lambda: K.attention_tc(q, k_pool, v_pool, batch, tiles.dev["mtile_seq"], tiles.dev["mtile_q0"],
                                                      tiles.facts["n_mma_tiles"], kv, scale, None)
-    if "tcgen05" in launches and d == 128 and qpk % 2 == 0:
+    if "tcgen05" in launches and d == 128 and qpk >= 2:
         def single():
-            K.attention_tc_pairs(False)
+            K.attention_tc_pairs(0)
             try:
                 return launches["tcgen05"]()
             finally:
-                K.attention_tc_pairs(True)
+                K.attention_tc_pairs(1)
         launches["tcgen05, a head a block"] = single
     if K.attention_mma_supports(d) and tiles.facts["mma_tokens"] > 1:
         tokens = tiles.facts["mma_tokens"]

@@ -392,25 +392,35 @@ attention_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
 
 
 // ------------------------------------------------------------------------------------------------
-// Two query heads of one K/V group in a block ("pair"): for shapes whose tiles leave room for one block
-// an SM only (head size 128: 32 KB of Q and 32 KB a page), a block of one head is one chain of dependent
-// steps per page and the SM idles between them. Here a block holds two chains that share every page
-// stage: 128 tokens x heads (2j, 2j + 1), 256 softmax threads (threads 0..127 head 2j, 128..255 head
-// 2j + 1; both groups sit on tensor-memory lanes 0..127, the second on columns 256..511), one issuing
-// thread that serves whichever chain is ready, one copy warp. Per chain: two S buffers (S one page ahead
-// of the softmax, the third buffer's column space goes to the second chain), P in place of S, O.
+// Two query heads of one K/V group in a block ("pair"), keys in steps of two pages.
+//
+// The tensor pipe takes a matrix instruction about every hundred clocks whatever its N (measured: one
+// O += P V group with N = 128 instead of two with N = 64 took a seventh off the kernel above at head size
+// 128), so what a page costs is the number of instructions issued for it. Here S = Q K^T is formed for 128
+// keys at once (N = 128: half the instructions a key) and O += P V with N = D.
+//
+// A block = 128 tokens x heads (h, h + 1) of one K/V group: two chains that share every K/V stage. 256
+// softmax threads (threads 0..127 the first head, 128..255 the second; both groups sit on tensor-memory
+// lanes 0..127, the second on columns 256..511), one issuing thread, one copy warp. A group with an odd
+// number of heads ends in a block whose second chain is idle. Per chain, in tensor memory: S [128 x 128]
+// in columns 0..127, P (128 keys as bfloat16 pairs, 64 columns) in place of it, O in columns 128..128+D.
+// S has one buffer: S of step j + 1 is issued right after O += P V of step j (the pipe runs in order),
+// and while a chain waits for it the other chain's softmax has the SM. It follows that a thread that has
+// read S of step j finds O += P V of step j - 1 completed: rescaling O needs no wait, only the walk's
+// last product is waited for.
+//
+// Stages hold 128 keys: two pages side by side (rows 0..63 and 64..127 of the K-major K tile and of the
+// MN-major V tile; with head size 128 two blocks of 64 dims each). K and V stages are given back
+// separately (K after both chains' S, V after both chains' O += P V). A walk with an odd number of pages
+// takes its last page twice: the second copy's keys lie past every row's position and are masked.
 //
 // The issuing thread never blocks on one chain while the other could move: it polls (mbarrier.test_wait)
-// "P written" and "page landed" of both chains in turn; a page's stage goes back to the copy thread when
-// both chains' O += P V of that page have been issued. Its polling is bounded like every wait.
-// "O updated" has two barriers a chain: with S two pages ahead of O += P V at most, a thread that has read S
-// of page i knows that the product of page i - 2 has completed, the one before page i on its barrier.
+// "stage landed" and "P written" of both chains in turn, parks for a fraction of a microsecond when
+// nothing can be issued, and gives up like every wait when that goes on for seconds.
 constexpr int PAIR_SOFTMAX = 2 * TQ;
 constexpr int PAIR_THREADS = PAIR_SOFTMAX + 64;
-constexpr uint32_t POLL_LIMIT = 1u << 26;
-#ifndef PTB_PARK_NS
-#define PTB_PARK_NS 200
-#endif
+constexpr int STEP_KEYS = 2 * KEYS;
+constexpr uint32_t POLL_LIMIT = 1u << 24;
 
 __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
   uint32_t ok;
@@ -421,6 +431,21 @@ __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
       : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
   return ok != 0;
 }
+// one try with a time hint: parks the thread for `ns` at most (the result is not used)
+__device__ __forceinline__ void mbar_park(uint32_t bar, uint32_t parity, uint32_t ns) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%0], %1, %2;\n\t}\n"
+      ::"r"(bar), "r"(parity), "r"(ns) : "memory");
+}
+
+template <int D> struct PairShape {
+  static constexpr int STAGES = D == 64 ? 4 : 2;           // stages of 128 keys, for K and for V
+  static constexpr int TILE_Q_BYTES = TQ * D * 2;
+  static constexpr int STAGE_BYTES = STEP_KEYS * D * 2;     // 16 or 32 KB
+  static constexpr int N_BARS = 8 + 4 * STAGES;
+  static constexpr size_t SMEM = 1024 + 2 * size_t(TILE_Q_BYTES) + 2 * size_t(STAGES) * STAGE_BYTES + N_BARS * 8 + 16;
+};
 
 template <int D, bool BIAS>
 __global__ void __launch_bounds__(PAIR_THREADS, 1)
@@ -428,83 +453,84 @@ attention_tc_pair_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __r
                          const int* __restrict__ tile_seq, const int* __restrict__ tile_q0, TcParams p,
                          const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
                          int* __restrict__ error_flag) {
+  using Shape = PairShape<D>;
+  constexpr int STAGES = Shape::STAGES, TILE_Q_BYTES = Shape::TILE_Q_BYTES, STAGE_BYTES = Shape::STAGE_BYTES;
   extern __shared__ unsigned char smem_dyn[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
-  constexpr int TILE_Q_BYTES = TQ * D * 2;
-  constexpr int TILE_KV_BYTES = KEYS * D * 2;
-  // tensor memory of chain c: columns [256 c, 256 c + 256): S buffers at +0 and +64, O at +128
   constexpr uint32_t CHAIN_COLS = 256, TMEM_O = 128;
-  unsigned char* q_tiles = smem;                                       // two Q tiles
+  unsigned char* q_tiles = smem;
   unsigned char* k_ring = q_tiles + 2 * TILE_Q_BYTES;
-  unsigned char* v_ring = k_ring + STAGES_TC * TILE_KV_BYTES;
-  // barriers: per chain c at 6 c: [0..1] S written, [2..3] O updated, [4..5] P written (page % 2); then per
-  // stage: page landed, stage free again
-  uint64_t* bars = reinterpret_cast<uint64_t*>(v_ring + STAGES_TC * TILE_KV_BYTES);
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12 + 2 * STAGES_TC);
+  unsigned char* v_ring = k_ring + STAGES * STAGE_BYTES;
+  // barriers: per chain c at 3 c: S written, P written, the walk's last O += P V; [6], [7] unused; then
+  // per stage: K landed, V landed, K free, V free
+  uint64_t* bars = reinterpret_cast<uint64_t*>(v_ring + STAGES * STAGE_BYTES);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + Shape::N_BARS);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const bool mma_warp = warp == PAIR_SOFTMAX / 32;
   const bool copy_warp = warp == PAIR_SOFTMAX / 32 + 1;
-  const int chain = (tid >> 7) & 1;      // softmax threads: which head of the pair
-  const int row = tid & (TQ - 1);        // query row = tensor-memory lane
+  const int chain = (tid >> 7) & 1;
+  const int row = tid & (TQ - 1);
   const int tile = blockIdx.y;
   const int qpk = p.heads / p.kv_heads;
-  const int h0 = 2 * blockIdx.x;         // heads h0 and h0 + 1: the same K/V group (qpk is even)
-  const int g = h0 / qpk;
+  const int pairs = (qpk + 1) / 2;                 // blocks a K/V group
+  const int g = blockIdx.x / pairs;
+  const int h0 = g * qpk + 2 * (blockIdx.x % pairs);
+  const bool two = h0 + 1 < (g + 1) * qpk;          // the second chain has a head
   const int seq = tile_seq[tile], q0 = tile_q0[tile];
   const int n_new = sb.seq_new[seq], past = sb.seq_past[seq], start = sb.seq_start[seq];
   const int tok_valid = min(TQ, n_new - q0);
   const bool row_ok = row < tok_valid;
   const int row_pos = row_ok ? past + q0 + row : -1;
   const int last_pos = past + q0 + tok_valid - 1;
-  const int n_blocks = last_pos / KEYS + 1;
+  const int n_pages = last_pos / KEYS + 1;
+  const int n_steps = (n_pages + 1) / 2;
   const int* pages = sb.pages + size_t(seq) * sb.pages_stride;
 
   const uint32_t bar0 = smem_u32(bars);
-  auto bar_s = [&](int c, int b) { return bar0 + 8u * uint32_t(6 * c + b); };
-  auto bar_o = [&](int c, int b) { return bar0 + 8u * uint32_t(6 * c + 2 + b); };
-  auto bar_p = [&](int c, int b) { return bar0 + 8u * uint32_t(6 * c + 4 + b); };
-  const uint32_t bar_k = bar0 + 8u * 12, bar_free = bar_k + 8u * STAGES_TC;
-  constexpr uint32_t PAGE_BYTES = 2 * TILE_KV_BYTES;
-  auto ask_page = [&](int b, int page) {
-    const int st = b % STAGES_TC;
-    const int y = (page * p.kv_heads + g) * KEYS;
-    const uint32_t full = bar_k + 8 * st;
-    mbar_expect_tx(full, PAGE_BYTES);
+  auto bar_s = [&](int c) { return bar0 + 8u * uint32_t(3 * c); };
+  auto bar_p = [&](int c) { return bar0 + 8u * uint32_t(3 * c + 1); };
+  auto bar_end = [&](int c) { return bar0 + 8u * uint32_t(3 * c + 2); };
+  const uint32_t bar_k = bar0 + 8u * 8, bar_v = bar_k + 8u * STAGES, bar_kfree = bar_v + 8u * STAGES,
+                 bar_vfree = bar_kfree + 8u * STAGES;
+  // step j: pages 2j and 2j + 1 (or 2j again) into stage j % STAGES, per block of 64 dims rows 0..63 and 64..127
+  auto ask = [&](unsigned char* ring, const CUtensorMap* map, uint32_t full, int j, int page_a, int page_b) {
+    unsigned char* stage = ring + (j % STAGES) * STAGE_BYTES;
+    mbar_expect_tx(full, STAGE_BYTES);
 #pragma unroll
     for (int blk = 0; blk < D / 64; ++blk) {
-      tma_load_2d(smem_u32(k_ring + st * TILE_KV_BYTES + blk * (KEYS * 128)), &k_map, blk * 64, y, full);
-      tma_load_2d(smem_u32(v_ring + st * TILE_KV_BYTES + blk * (KEYS * 128)), &v_map, blk * 64, y, full);
+      tma_load_2d(smem_u32(stage + blk * (STEP_KEYS * 128)), map, blk * 64, (page_a * p.kv_heads + g) * KEYS, full);
+      tma_load_2d(smem_u32(stage + blk * (STEP_KEYS * 128) + KEYS * 128), map, blk * 64, (page_b * p.kv_heads + g) * KEYS, full);
     }
   };
-  int first_pages = 0;
-  if (copy_warp) {
-    // barriers set up and the first pages asked for before the block-wide barrier, as in the kernel above
-    first_pages = lane < n_blocks ? pages[lane] : 0;
-    if (lane == 0) {
-      for (int c = 0; c < 2; ++c)
-        for (int b = 0; b < 2; ++b) {
-          mbar_init(bar_s(c, b), 1);
-          mbar_init(bar_o(c, b), 1);
-          mbar_init(bar_p(c, b), TQ);
-        }
-      for (int s = 0; s < STAGES_TC; ++s) {
-        mbar_init(bar_k + 8 * s, 1);
-        mbar_init(bar_free + 8 * s, 1);
-      }
-      asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  // page i of the walk; past its end the last page again (an odd number of pages: its keys are masked)
+  auto page_of = [&](int i) { return pages[min(i, n_pages - 1)]; };
+  if (copy_warp && lane == 0) {
+    for (int c = 0; c < 2; ++c) {
+      mbar_init(bar_s(c), 1);
+      mbar_init(bar_p(c), TQ);
+      mbar_init(bar_end(c), 1);
     }
-    for (int b = 0; b < STAGES_TC && b < n_blocks; ++b) {
-      const int page = __shfl_sync(0xffffffffu, first_pages, b);
-      if (lane == 0) ask_page(b, page);
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(bar_k + 8 * s, 1);
+      mbar_init(bar_v + 8 * s, 1);
+      mbar_init(bar_kfree + 8 * s, 1);
+      mbar_init(bar_vfree + 8 * s, 1);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    // the first stages are asked for at once: they travel while Q is fetched and tensor memory allocated
+    for (int j = 0; j < STAGES && j < n_steps; ++j) {
+      const int pa = page_of(2 * j), pb = page_of(2 * j + 1);
+      ask(k_ring, &k_map, bar_k + 8 * (j % STAGES), j, pa, pb);
+      ask(v_ring, &v_map, bar_v + 8 * (j % STAGES), j, pa, pb);
     }
   }
   if (warp == 0) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(tmem_slot)), "r"(512));
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::);
   }
-  if (!mma_warp && !copy_warp) {
-    // Q tile of this thread's head: rows of the tile, zero beyond the valid tokens
+  const bool chain_on = chain == 0 || two;
+  if (!mma_warp && !copy_warp && chain_on) {
     unsigned char* q_tile = q_tiles + chain * TILE_Q_BYTES;
     const uint32_t qs = smem_u32(q_tile);
     const int h = h0 + chain;
@@ -527,61 +553,77 @@ attention_tc_pair_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __r
 
   if (copy_warp) {
     if (lane == 0) {
-      int issued = min(n_blocks, STAGES_TC);
-      for (int b = STAGES_TC; b < n_blocks; ++b) {
-        if (!mbar_wait(bar_free + 8 * (b % STAGES_TC), ((b / STAGES_TC) - 1) & 1, error_flag, 6)) break;
-        ask_page(b, pages[b]);
-        issued = b + 1;
+      int k_asked = min(n_steps, STAGES), v_asked = k_asked;
+      for (int j = STAGES; j < n_steps && alive; ++j) {
+        const int pa = page_of(2 * j), pb = page_of(2 * j + 1);
+        const uint32_t before = ((j / STAGES) - 1) & 1;
+        alive = mbar_wait(bar_kfree + 8 * (j % STAGES), before, error_flag, 6);
+        if (!alive) break;
+        ask(k_ring, &k_map, bar_k + 8 * (j % STAGES), j, pa, pb);
+        k_asked = j + 1;
+        alive = mbar_wait(bar_vfree + 8 * (j % STAGES), before, error_flag, 6);
+        if (!alive) break;
+        ask(v_ring, &v_map, bar_v + 8 * (j % STAGES), j, pa, pb);
+        v_asked = j + 1;
       }
-      if (issued < n_blocks)
-        for (int b = max(0, issued - STAGES_TC); b < issued; ++b)
-          mbar_wait(bar_k + 8 * (b % STAGES_TC), (b / STAGES_TC) & 1, error_flag, 6);
+      if (!alive) {
+        // a wait ran out: what is in flight lands before the block ends (bounded waits again)
+        for (int j = max(0, k_asked - STAGES); j < k_asked; ++j) mbar_wait(bar_k + 8 * (j % STAGES), (j / STAGES) & 1, error_flag, 6);
+        for (int j = max(0, v_asked - STAGES); j < v_asked; ++j) mbar_wait(bar_v + 8 * (j % STAGES), (j / STAGES) & 1, error_flag, 6);
+      }
     }
   } else if (mma_warp) {
     if (lane == 0) {
-      constexpr uint32_t IDESC_S = idesc_bf16(TQ, KEYS, false);
-      constexpr uint32_t IDESC_PV = idesc_bf16(TQ, D, true);   // all D dims of the output in one instruction
+      constexpr uint32_t IDESC_S = idesc_bf16(TQ, STEP_KEYS, false);
+      constexpr uint32_t IDESC_PV = idesc_bf16(TQ, D, true);
       const uint64_t desc_q0 = smem_desc(smem_u32(q_tiles), 16, 1024);
       const uint64_t desc_k0 = smem_desc(smem_u32(k_ring), 16, 1024);
-      const uint64_t desc_v0 = smem_desc(smem_u32(v_ring), KEYS * 128, 1024);
-      constexpr uint64_t STAGE_UNITS = TILE_KV_BYTES >> 4, Q_UNITS = TILE_Q_BYTES >> 4;
-      constexpr uint64_t Q_BLOCK = (TQ * 128) >> 4, KV_BLOCK = (KEYS * 128) >> 4;
-      int s_next[2] = {0, 0};   // next page whose S is to be issued, per chain
-      int p_next[2] = {0, 0};   // next page whose O += P V is to be issued, per chain
-      int freed = 0;            // pages whose stage has been given back
+      // V is MN-major: blocks of 64 dims lie STEP_KEYS * 128 bytes apart (the leading offset), groups of 8
+      // keys 1024 bytes (the stride offset)
+      const uint64_t desc_v0 = smem_desc(smem_u32(v_ring), STEP_KEYS * 128, 1024);
+      constexpr uint64_t STAGE_UNITS = STAGE_BYTES >> 4, Q_UNITS = TILE_Q_BYTES >> 4;
+      constexpr uint64_t Q_BLOCK = (TQ * 128) >> 4, K_BLOCK = (STEP_KEYS * 128) >> 4;
+      const int n_chains = two ? 2 : 1;
+      int s_next[2] = {0, 0};   // next step whose S is to be issued, per chain
+      int p_next[2] = {0, 0};   // next step whose O += P V is to be issued
+      int k_freed = 0, v_freed = 0;
       uint32_t idle = 0;
-      while ((p_next[0] < n_blocks || p_next[1] < n_blocks) && alive) {
+      auto behind = [&](const int* v) { return n_chains == 2 ? min(v[0], v[1]) : v[0]; };
+      while (behind(p_next) < n_steps && alive) {
         bool moved = false;
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
-          // S of page j: its buffer (j % 2) held S and P of page j - 2, whose O += P V must have been
-          // issued (the tensor pipe runs in order); the page must have landed
-          const int j = s_next[c];
-          if (j < n_blocks && j <= p_next[c] + 1 && mbar_test(bar_k + 8 * (j % STAGES_TC), (j / STAGES_TC) & 1)) {
-            tc_fence_after();
-            const int st = j % STAGES_TC;
-#pragma unroll
-            for (int blk = 0; blk < D / 64; ++blk)
-              tc_mma4<2, 2>(tmem_base + c * CHAIN_COLS + (j & 1) * 64, desc_q0 + c * Q_UNITS + blk * Q_BLOCK,
-                            desc_k0 + st * STAGE_UNITS + blk * KV_BLOCK, IDESC_S, blk > 0 ? 1u : 0u);
-            tc_commit(bar_s(c, j & 1));
-            s_next[c] = j + 1;
-            moved = true;
-          }
-          // O += P V of page i when its P is written (and O rescaled)
+          if (c >= n_chains) continue;
+          // O += P V of step i when its P is written (O rescaled) and its V has landed
           const int i = p_next[c];
-          if (i < n_blocks && i < s_next[c] && mbar_test(bar_p(c, i & 1), (i >> 1) & 1)) {
+          if (i < s_next[c] && mbar_test(bar_p(c), i & 1) && mbar_test(bar_v + 8 * (i % STAGES), (i / STAGES) & 1)) {
             tc_fence_after();
-            const int st = i % STAGES_TC;
-            tc_mma4_ts<128>(tmem_base + c * CHAIN_COLS + TMEM_O, tmem_base + c * CHAIN_COLS + (i & 1) * 64,
-                            desc_v0 + st * STAGE_UNITS, IDESC_PV, i > 0 ? 1u : 0u);
-            tc_commit(bar_o(c, i & 1));
+            const uint32_t o = tmem_base + c * CHAIN_COLS + TMEM_O, pp = tmem_base + c * CHAIN_COLS;
+            const uint64_t dv = desc_v0 + (i % STAGES) * STAGE_UNITS;
+            tc_mma4_ts<128>(o, pp, dv, IDESC_PV, i > 0 ? 1u : 0u);                       // keys 0..63 of the step
+            tc_mma4_ts<128>(o, pp + 32, dv + ((KEYS * 128) >> 4), IDESC_PV, 1u);          // keys 64..127
+            if (i + 1 == n_steps) tc_commit(bar_end(c));
             p_next[c] = i + 1;
             moved = true;
-            // a stage is free when both chains' products of its page have completed
-            while (freed < min(p_next[0], p_next[1])) {
-              tc_commit(bar_free + 8 * (freed % STAGES_TC));
-              ++freed;
+            while (v_freed < behind(p_next)) {   // both chains' products of the step have been issued
+              tc_commit(bar_vfree + 8 * (v_freed % STAGES));
+              ++v_freed;
+            }
+          }
+          // S of step j: the buffer held S and P of step j - 1, whose O += P V must have been issued
+          const int j = s_next[c];
+          if (j < n_steps && j == p_next[c] && mbar_test(bar_k + 8 * (j % STAGES), (j / STAGES) & 1)) {
+            tc_fence_after();
+#pragma unroll
+            for (int blk = 0; blk < D / 64; ++blk)
+              tc_mma4<2, 2>(tmem_base + c * CHAIN_COLS, desc_q0 + c * Q_UNITS + blk * Q_BLOCK,
+                            desc_k0 + (j % STAGES) * STAGE_UNITS + blk * K_BLOCK, IDESC_S, blk > 0 ? 1u : 0u);
+            tc_commit(bar_s(c));
+            s_next[c] = j + 1;
+            moved = true;
+            while (k_freed < behind(s_next)) {
+              tc_commit(bar_kfree + 8 * (k_freed % STAGES));
+              ++k_freed;
             }
           }
         }
@@ -590,23 +632,16 @@ attention_tc_pair_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __r
           atomicExch(error_flag, 13);
           alive = false;
         } else {
-          // nothing to issue: park on the barrier that the chain further behind waits for, for a fraction of
-          // a microsecond at most (a spinning thread would take issue slots from the softmax warps of its
-          // quarter of the SM); the tests above then look at every barrier again
-          const int c = p_next[0] <= p_next[1] ? 0 : 1;
-          const int i = p_next[c];
-          const uint32_t parked = (i < s_next[c]) ? bar_p(c, i & 1) : bar_k + 8 * (s_next[c] % STAGES_TC);
-          const uint32_t parity = (i < s_next[c]) ? uint32_t((i >> 1) & 1) : uint32_t((s_next[c] / STAGES_TC) & 1);
-          uint32_t ok;
-          asm volatile(
-              "{\n\t.reg .pred p;\n\t"
-              "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
-              "selp.u32 %0, 1, 0, p;\n\t}\n"
-              : "=r"(ok) : "r"(parked), "r"(parity), "r"(PTB_PARK_NS) : "memory");
+          // nothing to issue: park on what the chain further behind waits for (a spinning thread would take
+          // issue slots from the softmax warps of its quarter of the SM)
+          const bool second = n_chains == 2 && p_next[1] < p_next[0];
+          const int i = second ? p_next[1] : p_next[0], sn = second ? s_next[1] : s_next[0];
+          if (i < sn) mbar_park(bar_p(second ? 1 : 0), i & 1, 200);
+          else mbar_park(bar_k + 8 * (i % STAGES), (i / STAGES) & 1, 200);
         }
       }
     }
-  } else {
+  } else if (chain_on) {
     // ------------------------------------------------------------ softmax threads of chain `chain`
     const int h = h0 + chain;
     const uint32_t lane_addr = tmem_base + (uint32_t((warp & 3) * 32) << 16) + chain * CHAIN_COLS;
@@ -615,69 +650,91 @@ attention_tc_pair_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __r
     const float slope = BIAS ? p.slopes[h] : 0.f;
     const float sl2 = p.scale * 1.4426950408889634f;
     const uint64_t sl2_2 = pack2(sl2, sl2);
-    for (int i = 0; i < n_blocks; ++i) {
-      const int buf = i & 1, phase = (i >> 1) & 1;
-      if (alive) alive = mbar_wait(bar_s(chain, buf), phase, error_flag, 1);
+    for (int j = 0; j < n_steps; ++j) {
+      if (alive) alive = mbar_wait(bar_s(chain), j & 1, error_flag, 1);
       tc_fence_after();
-      float s[KEYS];
-      tmem_ld64_once(lane_addr + buf * 64, s);
-      if (BIAS) {
+      const int key0 = j * STEP_KEYS;
+      const bool masked = key0 + STEP_KEYS - 1 > past + q0 || !row_ok;   // first part is uniform over the block
+      // (1) the row's maximum over the step's 128 scores, a half of 64 at a time
+      float m_new = m_run;
 #pragma unroll
-        for (int j = 0; j < KEYS; ++j) s[j] += alibi_bias(slope, i * KEYS + j);
-      }
-      if (i * KEYS + KEYS - 1 > past + q0 || !row_ok) {
-        const int visible = row_pos - i * KEYS;
+      for (int half = 0; half < 2; ++half) {
+        float s[KEYS];
+        tmem_ld64_once(lane_addr + half * KEYS, s);
+        if (BIAS) {
 #pragma unroll
-        for (int j = 0; j < KEYS; ++j) s[j] = (j <= visible) ? s[j] : -INFINITY;
-      }
-      float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+          for (int e = 0; e < KEYS; ++e) s[e] += alibi_bias(slope, key0 + half * KEYS + e);
+        }
+        if (masked) {
+          const int visible = row_pos - key0 - half * KEYS;
 #pragma unroll
-      for (int j = 0; j < KEYS; j += 8) {
-        mx[0] = max3(mx[0], s[j], s[j + 1]);
-        mx[1] = max3(mx[1], s[j + 2], s[j + 3]);
-        mx[2] = max3(mx[2], s[j + 4], s[j + 5]);
-        mx[3] = max3(mx[3], s[j + 6], s[j + 7]);
+          for (int e = 0; e < KEYS; ++e) s[e] = (e <= visible) ? s[e] : -INFINITY;
+        }
+        float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+        for (int e = 0; e < KEYS; e += 8) {
+          mx[0] = max3(mx[0], s[e], s[e + 1]);
+          mx[1] = max3(mx[1], s[e + 2], s[e + 3]);
+          mx[2] = max3(mx[2], s[e + 4], s[e + 5]);
+          mx[3] = max3(mx[3], s[e + 6], s[e + 7]);
+        }
+        m_new = fmaxf(m_new, fmaxf(max3(mx[0], mx[1], mx[2]), mx[3]));
       }
-      float m_new = fmaxf(m_run, fmaxf(max3(mx[0], mx[1], mx[2]), mx[3]));
-      if ((m_new - m_run) * sl2 <= RESCALE_LOG2) m_new = m_run;
+      if ((m_new - m_run) * sl2 <= RESCALE_LOG2) m_new = m_run;   // (false from -inf: the first scores set it)
       const float corr = (m_run == -INFINITY) ? 0.f : fast_exp2((m_run - m_new) * sl2);
       const bool moved = (m_new != m_run) && (m_run != -INFINITY);
       m_run = m_new;
       const float m_off = (m_run == -INFINITY) ? 0.f : m_run * sl2;
-      if (i > 0 && __any_sync(0xffffffffu, moved)) {
-        if (alive) alive = mbar_wait(bar_o(chain, (i - 1) & 1), ((i - 1) >> 1) & 1, error_flag, 2);
-        tc_fence_after();
+      // (2) O rescaled if any row of the warp moved its maximum: O += P V of the step before has completed
+      // (S of this step was issued after it)
+      if (j > 0 && __any_sync(0xffffffffu, moved)) {
 #pragma unroll
         for (int c0 = 0; c0 < D; c0 += 32) {
           float o[32];
           tmem_ld32(o_addr + c0, o);
 #pragma unroll
-          for (int j = 0; j < 32; ++j) o[j] *= corr;
+          for (int e = 0; e < 32; ++e) o[e] *= corr;
           tmem_st32(o_addr + c0, o);
         }
         tmem_st_wait();
       }
+      // (3) P = exp2(S - max), a half at a time: the first half's P goes over the first half's S (read for
+      // the last time just before), the second half's P over the rest of the first half's S
       const uint64_t moff_2 = pack2(-m_off, -m_off);
       uint64_t acc2[4] = {0ull, 0ull, 0ull, 0ull};
-      uint32_t w[KEYS / 2];
 #pragma unroll
-      for (int e = 0; e < KEYS / 2; ++e) {
-        float x0, x1;
-        unpack2(fma2(pack2(s[2 * e], s[2 * e + 1]), sl2_2, moff_2), x0, x1);
-        const float a = fast_exp2(x0), b = fast_exp2(x1);
-        acc2[e & 3] = add2(acc2[e & 3], pack2(a, b));
-        w[e] = pack_bf16(a, b);
+      for (int half = 0; half < 2; ++half) {
+        float s[KEYS];
+        tmem_ld64_once(lane_addr + half * KEYS, s);
+        if (BIAS) {
+#pragma unroll
+          for (int e = 0; e < KEYS; ++e) s[e] += alibi_bias(slope, key0 + half * KEYS + e);
+        }
+        if (masked) {
+          const int visible = row_pos - key0 - half * KEYS;
+#pragma unroll
+          for (int e = 0; e < KEYS; ++e) s[e] = (e <= visible) ? s[e] : -INFINITY;
+        }
+        uint32_t w[KEYS / 2];
+#pragma unroll
+        for (int e = 0; e < KEYS / 2; ++e) {
+          float x0, x1;
+          unpack2(fma2(pack2(s[2 * e], s[2 * e + 1]), sl2_2, moff_2), x0, x1);
+          const float a = fast_exp2(x0), b = fast_exp2(x1);
+          acc2[e & 3] = add2(acc2[e & 3], pack2(a, b));
+          w[e] = pack_bf16(a, b);
+        }
+        tmem_st_u32<KEYS / 2>(lane_addr + half * (KEYS / 2), w);
       }
-      tmem_st_u32<KEYS / 2>(lane_addr + buf * 64, w);
       tmem_st_wait();
       float l0, l1, l2, l3;
       unpack2(add2(acc2[0], acc2[1]), l0, l1);
       unpack2(add2(acc2[2], acc2[3]), l2, l3);
       l_run = l_run * corr + ((l0 + l1) + (l2 + l3));
       tc_fence_before();
-      mbar_arrive(bar_p(chain, buf));
+      mbar_arrive(bar_p(chain));
     }
-    if (alive) alive = mbar_wait(bar_o(chain, (n_blocks - 1) & 1), ((n_blocks - 1) >> 1) & 1, error_flag, 3);
+    if (alive) alive = mbar_wait(bar_end(chain), 0, error_flag, 3);
     tc_fence_after();
     const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
     __nv_bfloat16* dst = out + (size_t(start + q0 + row) * p.heads + h) * D;
@@ -702,11 +759,32 @@ attention_tc_pair_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __r
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(512));
 }
 
+template <int D, bool BIAS>
+int launch_tc_pair(const void* q, const void* k_pool, const void* v_pool, int pool_pages, void* out, const StepBatch& sb,
+                   const int* tile_seq, const int* tile_q0, int n_tiles, const TcParams& p, int* error_flag,
+                   cudaStream_t stream) {
+  const CUtensorMap* km = pool_map(k_pool, pool_pages, p.kv_heads, D);
+  const CUtensorMap* vm = pool_map(v_pool, pool_pages, p.kv_heads, D);
+  if (km == nullptr || vm == nullptr) return PTB_ERR_LAUNCH;
+  constexpr size_t smem = PairShape<D>::SMEM;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(attention_tc_pair_kernel<D, BIAS>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess)
+      return PTB_ERR_LAUNCH;
+    configured = true;
+  }
+  const int qpk = p.heads / p.kv_heads;
+  dim3 grid(p.kv_heads * ((qpk + 1) / 2), n_tiles);
+  attention_tc_pair_kernel<D, BIAS><<<grid, PAIR_THREADS, smem, stream>>>(
+      (const __nv_bfloat16*)q, (__nv_bfloat16*)out, sb, tile_seq, tile_q0, p, *km, *vm, error_flag);
+  return launch_status();
+}
 }  // namespace
 
-static bool g_no_pair = false;
-// for measurements: 0 = every head its own block also where pairs would do
-PTB_API void ptb_attention_tc_pairs(int on) { g_no_pair = on == 0; }
+static int g_pair_mode = 1;
+// for measurements and tests: 0 = every head a block of its own also where pairs would do, 1 = pairs where
+// they fill the device (the default), 2 = pairs wherever a K/V group has two heads or more
+PTB_API void ptb_attention_tc_pairs(int mode) { g_pair_mode = mode; }
 PTB_API int ptb_attention_tc_supports(int head_dim) { return (head_dim == 64 || head_dim == 128) ? 1 : 0; }
 PTB_API int ptb_attention_tc_tile_tokens() { return TQ; }
 
@@ -731,25 +809,6 @@ int launch_tc(const void* q, const void* k_pool, const void* v_pool, int pool_pa
       tile_seq, tile_q0, p, *km, *vm, error_flag);
   return launch_status();
 }
-template <int D, bool BIAS>
-int launch_tc_pair(const void* q, const void* k_pool, const void* v_pool, int pool_pages, void* out, const StepBatch& sb,
-                   const int* tile_seq, const int* tile_q0, int n_tiles, const TcParams& p, int* error_flag,
-                   cudaStream_t stream) {
-  const CUtensorMap* km = pool_map(k_pool, pool_pages, p.kv_heads, D);
-  const CUtensorMap* vm = pool_map(v_pool, pool_pages, p.kv_heads, D);
-  if (km == nullptr || vm == nullptr) return PTB_ERR_LAUNCH;
-  const size_t smem = 1024 + 2 * TQ * D * 2 + 2 * STAGES_TC * KEYS * D * 2 + 256;
-  static bool configured = false;
-  if (!configured) {
-    if (cudaFuncSetAttribute(attention_tc_pair_kernel<D, BIAS>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess)
-      return PTB_ERR_LAUNCH;
-    configured = true;
-  }
-  dim3 grid(p.heads / 2, n_tiles);
-  attention_tc_pair_kernel<D, BIAS><<<grid, PAIR_THREADS, smem, stream>>>(
-      (const __nv_bfloat16*)q, (__nv_bfloat16*)out, sb, tile_seq, tile_q0, p, *km, *vm, error_flag);
-  return launch_status();
-}
 }  // namespace
 
 // Causal attention of prompt tiles of 128 tokens (tile_seq / tile_q0 as for the other attention
@@ -771,9 +830,13 @@ PTB_API int ptb_attention_tc(const void* q, const void* k_pool, const void* v_po
   if (head_dim == 64)
     return slopes ? launch_tc<64, true>(q, k_pool, v_pool, pool_pages, out, *sb, tile_seq, tile_q0, n_tiles, p, error_flag, stream)
                   : launch_tc<64, false>(q, k_pool, v_pool, pool_pages, out, *sb, tile_seq, tile_q0, n_tiles, p, error_flag, stream);
-  // head size 128 leaves room for one block an SM: two heads of a K/V group share a block where the group
-  // has an even number of heads
-  if ((heads / kv_heads) % 2 == 0 && !g_no_pair)
+  // Head size 128 leaves room for one block an SM: two heads of a K/V group share a block, with keys in
+  // steps of two pages, where a group has two heads or more and the pairs fill the device. (With head size
+  // 64 two blocks of the kernel above share an SM, each with three S buffers, and are a quarter faster than
+  // the pairs with their one S buffer a chain: 833 against 1,067 us at 8,192 tokens and 71 heads.)
+  const int qpk = heads / kv_heads;
+  const long long pair_blocks = (long long)kv_heads * ((qpk + 1) / 2) * n_tiles;
+  if (qpk >= 2 && g_pair_mode != 0 && (pair_blocks >= sm_count() || g_pair_mode == 2))
     return slopes ? launch_tc_pair<128, true>(q, k_pool, v_pool, pool_pages, out, *sb, tile_seq, tile_q0, n_tiles, p, error_flag, stream)
                   : launch_tc_pair<128, false>(q, k_pool, v_pool, pool_pages, out, *sb, tile_seq, tile_q0, n_tiles, p, error_flag, stream);
   return slopes ? launch_tc<128, true>(q, k_pool, v_pool, pool_pages, out, *sb, tile_seq, tile_q0, n_tiles, p, error_flag, stream)

@@ -1,6 +1,7 @@
 // Shared helpers of the sm_100a kernels: element access in float32 and bfloat16, reductions,
 // the step's batch description and the paged cache's addressing.
 #pragma once
+#include <cstdio>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -145,4 +146,10 @@ __device__ __forceinline__ void rotate_pair(float a, float b, float c, float s, 
   out_b = __fadd_rn(__fmul_rn(b, c), __fmul_rn(a, s));
 }
 
-inline int launch_status() { return cudaGetLastError() == cudaSuccess ? PTB_OK : PTB_ERR_LAUNCH; }
+// the status of the launch just made; a failure is said on stderr with the runtime's own words
+inline int launch_status() {
+  const cudaError_t e = cudaGetLastError();
+  if (e == cudaSuccess) return PTB_OK;
+  fprintf(stderr, "[pytorch_transformers_b200] a CUDA launch failed: %s (%s)\n", cudaGetErrorName(e), cudaGetErrorString(e));
+  return PTB_ERR_LAUNCH;
+}

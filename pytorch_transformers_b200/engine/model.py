@@ -9,6 +9,7 @@ on the last ``num_logits_to_keep`` positions), without padding or mask tensors.
 """
 from __future__ import annotations
 
+import gc
 from typing import Dict, List, Optional, Sequence, Tuple, Union
 
 import torch
@@ -18,6 +19,43 @@ from ..cache.paged import Cache
 from ..parts.base import BuildContext, ModelSpec, ParamDecl, Part, make_part, resolve
 from ..parts.linear import linear
 from .batch import StepContext, StepError
+
+
+class _StepSpan:
+    """Context manager around a step's launches: two CUDA events and a record, if records are kept."""
+
+    def __init__(self, model, kind: str, ctx: StepContext):
+        self.model, self.kind, self.ctx = model, kind, ctx
+        self.on = model.step_records is not None and model.device.type == "cuda"
+
+    def __enter__(self):
+        if self.on:
+            self.begin = torch.cuda.Event(enable_timing=True)
+            self.begin.record()
+
+    def __exit__(self, *exc):
+        if self.on and exc[0] is None:
+            end = torch.cuda.Event(enable_timing=True)
+            end.record()
+            ctx = self.ctx
+            self.model.step_records.append({"kind": self.kind, "sequences": ctx.n_seqs, "tokens": ctx.n_tokens,
+                                            "h2d_bytes": ctx.h2d_bytes, "begin": self.begin, "end": end})
+
+
+class _NoCollection:
+    """No cyclic garbage collection inside: while a stream is being captured into a CUDA graph, an
+    object that the collector happens to free then (a dropped cache with its graphs and page-locked
+    buffers, a stream, an event) runs CUDA calls that are not allowed during a capture and void it.
+    Garbage is collected before, and the collector goes back to what it was after."""
+
+    def __enter__(self):
+        gc.collect()
+        self.was = gc.isenabled()
+        gc.disable()
+
+    def __exit__(self, *exc):
+        if self.was:
+            gc.enable()
 
 
 class CausalLM:
@@ -138,22 +176,7 @@ class CausalLM:
 
     def _recorded(self, kind: str, ctx: StepContext):
         """Context manager around a step's launches that adds a record when records are kept."""
-        model = self
-
-        class _Span:
-            def __enter__(self):
-                self.on = model.step_records is not None and model.device.type == "cuda"
-                if self.on:
-                    self.begin = torch.cuda.Event(enable_timing=True)
-                    self.begin.record()
-
-            def __exit__(self, *exc):
-                if self.on and exc[0] is None:
-                    end = torch.cuda.Event(enable_timing=True)
-                    end.record()
-                    model.step_records.append({"kind": kind, "sequences": ctx.n_seqs, "tokens": ctx.n_tokens,
-                                               "h2d_bytes": ctx.h2d_bytes, "begin": self.begin, "end": end})
-        return _Span()
+        return _StepSpan(self, kind, ctx)
 
     def check_errors(self) -> None:
         """Raise if a kernel has reported trouble since the last check (synchronises): a row index that
@@ -300,7 +323,7 @@ class CausalLM:
                 first = self.forward(ctx)
             graph = torch.cuda.CUDAGraph()
             before = K.launches
-            with torch.cuda.graph(graph):
+            with _NoCollection(), torch.cuda.graph(graph):
                 out = self.forward(ctx)
             # kernels of this library that one replay launches (for the launch count of benchmarks);
             # the capture itself launched nothing

@@ -410,10 +410,11 @@ def attention_tc(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, ba
     return out
 
 
-def attention_tc_pairs(on: bool) -> None:
-    """For measurements: with False, ``attention_tc`` gives every head a block of its own also where two
-    heads of a K/V group could share one (head size 128, an even number of heads a group)."""
-    lib().ptb_attention_tc_pairs(1 if on else 0)
+def attention_tc_pairs(mode) -> None:
+    """For measurements and tests. ``attention_tc`` with head size 128 puts two heads of a K/V group in one
+    block where the pairs fill the device (mode 1 or True, the default); 0 or False: never; 2: wherever a
+    group has two heads or more."""
+    lib().ptb_attention_tc_pairs(int(mode))
 
 
 def attention_mma_supports(head_dim: int) -> bool:

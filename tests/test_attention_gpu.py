@@ -269,6 +269,32 @@ def test_tc_prompts(K, heads, kv, news, pasts, d, position):
     torch.testing.assert_close(out, ref, **tol(BF))
 
 
+@pytest.mark.parametrize("heads,kv", [(2, 1), (3, 1), (8, 2), (12, 2), (5, 1)])
+@pytest.mark.parametrize("news,pasts", [([128], [0]), ([65], [0]), ([129, 300, 70], [0, 0, 0]), ([200, 66], [130, 63]),
+                                        ([1000], [0]), ([300], [200])])
+@pytest.mark.parametrize("position", ["rotary", "alibi"])
+def test_tc_prompts_two_heads_a_block(K, heads, kv, news, pasts, position):
+    """Head size 128: two heads of a K/V group in one block, keys in steps of two pages (walks of an odd
+    and an even number of pages, groups with an odd number of heads, whose last block has one chain)."""
+    K.attention_tc_pairs(2)
+    try:
+        out, ref = attention_case(K, BF, heads, kv, 128, pasts=pasts, news=news, position=position, seed=12, tc=True)
+    finally:
+        K.attention_tc_pairs(1)
+    torch.testing.assert_close(out, ref, **tol(BF))
+
+
+@pytest.mark.parametrize("position", ["none", "alibi"])
+def test_tc_far_key_two_heads_a_block(K, position):
+    K.attention_tc_pairs(2)
+    try:
+        out, ref = attention_case(K, BF, 4, 2, 128, pasts=[0, 0], news=[70, 700], position=position, seed=5,
+                                  needle=(1, 3), tc=True)
+    finally:
+        K.attention_tc_pairs(1)
+    torch.testing.assert_close(out, ref, **tol(BF))
+
+
 @pytest.mark.parametrize("d", [64, 128])
 @pytest.mark.parametrize("position", ["none", "alibi"])
 def test_tc_far_key(K, d, position):
@@ -307,12 +333,16 @@ def test_tc_prompts_the_same_bits_every_time(K, heads, kv, d, tokens):
     attention of a small case. Forty launches of the same work must give the same bits."""
     ctx, k_pool, v_pool, batch, gen = _cache_with(K, kv, d, [0, 130], tokens)
     tiles = ctx.plan("attention_tiles")
+    K.attention_tc_pairs(2)       # head size 128: two heads a block also where the pairs do not fill the device
     q = torch.randn(2 * tokens, heads, d, device="cuda", generator=gen).to(BF)
     run = lambda: K.attention_tc(q, k_pool, v_pool, batch, tiles.dev["mtile_seq"], tiles.dev["mtile_q0"],
                                  tiles.facts["n_mma_tiles"], kv, d ** -0.5, None)
-    first = run()
-    for _ in range(40):
-        assert torch.equal(run(), first)
+    try:
+        first = run()
+        for _ in range(40):
+            assert torch.equal(run(), first)
+    finally:
+        K.attention_tc_pairs(1)
     K.check_device_errors("cuda")
     # and they are the right bits: the general kernel on the same tiles
     ref = K.attention_generic(q, k_pool, v_pool, batch, tiles.dev["tile_seq"], tiles.dev["tile_q0"],

@@ -665,3 +665,33 @@ def test_step_records_name_every_step_with_its_device_time(loaded):
     assert any(r["kind"] == "ahead" for r in decode)          # steps launched before the host had the tokens
     assert all(r["device_ms"] > 0 and r["h2d_bytes"] > 0 for r in recs)
     assert model.step_records is None
+
+
+def test_no_garbage_collection_while_a_step_is_captured(loaded):
+    """An object freed by the cyclic collector during a stream capture (a dropped cache with its graphs
+    and page-locked buffers) runs CUDA calls that void the capture; it showed as a step that failed only
+    after other tests had left such garbage. The collector must be off while a step is captured and back
+    on afterwards."""
+    import gc
+    L = loaded("D", "bfloat16")
+    model = L.model
+    seen = []
+    forward = model.forward
+
+    def watched(ctx):
+        seen.append((torch.cuda.is_current_stream_capturing(), gc.isenabled()))
+        return forward(ctx)
+
+    model.forward = watched
+    try:
+        cache = model.new_cache(256)
+        slot = cache.open()
+        model.step(cache, [slot], [tm.prompts("D", (20,), seed=3)[0]], want="last")
+        model.step(cache, [slot], [[5]], want="last")          # plain run, then the capture
+        model.step(cache, [slot], [[6]], want="last")          # replay: no forward
+    finally:
+        del model.forward
+    assert gc.isenabled()
+    capturing = [s for s in seen if s[0]]
+    assert len(capturing) == 1 and capturing[0][1] is False
+    assert all(enabled for cap, enabled in seen if not cap)
