@@ -339,6 +339,30 @@ def run_prefill_attention(args):
     return 0
 
 
+def run_mma_cadence(args):
+    """Clocks per tcgen05.mma (M = 128, K = 16) for several N, issued back to back by one thread a block on
+    operands that are already in shared or tensor memory: one block alone, and two blocks on every SM."""
+    import torch
+
+    from pytorch_transformers_b200 import kernels as K
+
+    torch.cuda.set_device(0)
+    sms = K.sm_count("cuda:0")
+    result = {"only": "mma-cadence", "unit": "clocks per instruction", "reps": 4000}
+    for name, tmem, blocks in (("smem A, one block", False, 1), ("tmem A, one block", True, 1),
+                               ("smem A, two blocks an SM", False, 2 * sms), ("tmem A, two blocks an SM", True, 2 * sms)):
+        row = {}
+        for n in (16, 32, 64, 128, 256):
+            if tmem and n > 128:
+                continue
+            K.selftest_mma_cadence("cuda:0", n, 50, tmem, blocks)     # warm-up
+            row[str(n)] = round(K.selftest_mma_cadence("cuda:0", n, 1000, tmem, blocks), 1)
+        result[name] = row
+    K.check_device_errors("cuda:0")
+    print(json.dumps(result))
+    return 0
+
+
 def prefill_flops_ragged(c, layers, lengths):
     """Flops of one ragged prefill of prompts of the given lengths (logits for each prompt's last token)."""
     h, nh, kvh, d, f, v = shape_sizes(c)
@@ -503,6 +527,8 @@ def run_ours(args):
         return run_decode_attention(args)
     if args.only == "prefill-attention":
         return run_prefill_attention(args)
+    if args.only == "mma-cadence":
+        return run_mma_cadence(args)
     if args.only == "linear":
         return run_linear(args)
     if args.only == "fill":
@@ -770,7 +796,7 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration's (0: all)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--only", default="", choices=["", "decode", "prefill", "sample", "decode-attention", "prefill-attention", "config", "linear",
-                             "fill"],
+                             "fill", "mma-cadence"],
                     help="run one section only and print its numbers (for profilers)")
     ap.add_argument("--shape", default="7b", choices=sorted(SHAPES), help="model shape for --only decode / prefill")
     ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS, help="prompt length for --only prefill")

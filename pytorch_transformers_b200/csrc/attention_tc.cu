@@ -241,8 +241,8 @@ attention_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
     // ------------------------------------------------------------ the thread that issues matrix instructions
     if (lane == 0) {
       constexpr uint32_t IDESC_S = idesc_bf16(TQ, KEYS, false);
-      // all D dims of the output in one instruction: the tensor pipe takes a matrix instruction about every
-      // hundred clocks whatever its N, so their number is what a page costs
+      // all D dims of the output in one instruction: an instruction of M = 128, K = 16 takes 51 clocks at
+      // least whatever its N (N / 2 clocks from N = 128 on), so their number is what a page costs
       constexpr uint32_t IDESC_PV = idesc_bf16(TQ, D, true);
       const uint64_t desc_q = smem_desc(smem_u32(q_tile), 16, 1024);
       const uint64_t desc_k0 = smem_desc(smem_u32(k_ring), 16, 1024);
@@ -394,10 +394,12 @@ attention_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
 // ------------------------------------------------------------------------------------------------
 // Two query heads of one K/V group in a block ("pair"), keys in steps of two pages.
 //
-// The tensor pipe takes a matrix instruction about every hundred clocks whatever its N (measured: one
-// O += P V group with N = 128 instead of two with N = 64 took a seventh off the kernel above at head size
-// 128), so what a page costs is the number of instructions issued for it. Here S = Q K^T is formed for 128
-// keys at once (N = 128: half the instructions a key) and O += P V with N = D.
+// A tcgen05.mma of M = 128, K = 16 takes 51 clocks at least whatever its N, N / 2 clocks from N = 128 on,
+// and no less than its operands take to come from shared memory at 128 bytes a clock (4 KB of A, 32 N
+// bytes of B); measured by issuing them back to back. With N = 64 half of the pipe's time is that floor,
+// and what a page costs is the number of instructions issued for it (one O += P V group with N = 128
+// instead of two with N = 64 took a seventh off the kernel above at head size 128). Here S = Q K^T is
+// formed for 128 keys at once (N = 128: half the instructions a key) and O += P V with N = D.
 //
 // A block = 128 tokens x heads (h, h + 1) of one K/V group: two chains that share every K/V stage. 256
 // softmax threads (threads 0..127 the first head, 128..255 the second; both groups sit on tensor-memory

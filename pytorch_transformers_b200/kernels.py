@@ -81,7 +81,7 @@ def lib():
                      "ptb_rope_table", "ptb_attention_decode", "ptb_attention_tc", "ptb_attention_tc_supports",
                      "ptb_attention_tc_tile_tokens", "ptb_tc_linear", "ptb_tc_linear_max_rows",
                      "ptb_tc_linear_k_multiple", "ptb_attention_decode_tc", "ptb_attention_decode_tc_supports",
-                     "ptb_fill_normal", "ptb_selftest_bounded_wait", "ptb_scale"):
+                     "ptb_fill_normal", "ptb_selftest_bounded_wait", "ptb_scale", "ptb_selftest_mma_cadence"):
             getattr(L, name).restype = ctypes.c_int
         _configured = True
     return L
@@ -373,6 +373,18 @@ def check_device_errors(device) -> None:
         if code != 0:
             flag.zero_()
             raise KernelError(f"a kernel gave up waiting inside its pipeline (code {code}): its results are void")
+
+
+def selftest_mma_cadence(device, n: int, reps: int = 1000, a_in_tmem: bool = False, blocks: int = 1) -> float:
+    """Clocks per tcgen05.mma (M = 128, K = 16, N = ``n``) when one thread of each of ``blocks`` blocks issues
+    ``4 * reps`` of them back to back on operands that sit in shared (or tensor) memory."""
+    device = torch.device(device)
+    clocks = torch.zeros(1, dtype=torch.int64, device=device)
+    _check(lib().ptb_selftest_mma_cadence(int(n), int(reps), 1 if a_in_tmem else 0, int(blocks), _ptr(clocks),
+                                          _ptr(error_flag(device)),
+                                          ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)),
+           "selftest_mma_cadence")
+    return float(clocks.item()) / (4 * reps)
 
 
 def selftest_bounded_wait(device, tries: int = 1000) -> torch.Tensor:
