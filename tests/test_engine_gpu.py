@@ -695,3 +695,31 @@ def test_no_garbage_collection_while_a_step_is_captured(loaded):
     capturing = [s for s in seen if s[0]]
     assert len(capturing) == 1 and capturing[0][1] is False
     assert all(enabled for cap, enabled in seen if not cap)
+
+
+def test_a_long_prompt_at_the_11b_width_with_two_heads_a_block():
+    """A prompt long enough for the prompt attention to put two heads of a K/V group in one block
+    (head size 128, keys in steps of two pages): the model's logits against those with a block a head,
+    which the tests above hold to the plain implementation."""
+    import pytorch_transformers_b200 as ptb
+    cfg = ptb.FalconConfig.from_dict(dict(WIDE["11b"], model_type="falcon"))
+    model = ptb.AutoModelForCausalLM.from_config(cfg, seed=22, dtype="bfloat16")
+    K = model.build.kernels
+    g = np.random.Generator(np.random.PCG64(10))
+    prompts = [g.integers(0, 1000, size=n).tolist() for n in (2700, 1341)]    # an odd and an even number of pages
+    want = [[0, 127, 128, 1000, len(p) - 1] for p in prompts]
+    outs = []
+    for mode in (1, 0):
+        K.attention_tc_pairs(mode)
+        try:
+            cache = model.new_cache(64 * 70)
+            slots = [cache.open(), cache.open()]
+            outs.append(model.step(cache, slots, prompts, want=want))
+            outs.append(model.step(cache, slots, [[7], [8]], want="last"))      # and a token on top of that cache
+        finally:
+            K.attention_tc_pairs(1)
+    K.check_device_errors("cuda")
+    spread = float(outs[0].std())
+    for a, b in ((outs[0], outs[2]), (outs[1], outs[3])):
+        torch.testing.assert_close(a, b, atol=0.03 * spread, rtol=3e-2)
+    assert not torch.equal(outs[0], outs[2])      # two kernels, two orders of summation: the pairs did run
