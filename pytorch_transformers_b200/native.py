@@ -5,6 +5,8 @@ points and loaded with ctypes: no Python binding code is compiled, so a first ca
 checkout takes about a minute. The library is kept inside the package (``_lib/``) when that
 folder can be written, else under the user's temporary folder; it is rebuilt when a source file
 or a flag changes. There is no fallback: without nvcc, or if compilation fails, loading raises.
+Environment: ``PTB200_NVCC`` (the compiler), ``PTB200_BUILD_DIR`` (where the library goes),
+``PTB200_NVCC_EXTRA`` (more flags, a ``-D`` for a trial build; they are part of the fingerprint).
 """
 from __future__ import annotations
 
