@@ -46,10 +46,10 @@ class _NoCollection:
     """No cyclic garbage collection inside: while a stream is being captured into a CUDA graph, an
     object that the collector happens to free then (a dropped cache with its graphs and page-locked
     buffers, a stream, an event) runs CUDA calls that are not allowed during a capture and void it.
-    Garbage is collected before, and the collector goes back to what it was after."""
+    torch.cuda.graph collects what is garbage already when the capture begins; the collector goes back to
+    what it was after."""
 
     def __enter__(self):
-        gc.collect()
         self.was = gc.isenabled()
         gc.disable()
 
