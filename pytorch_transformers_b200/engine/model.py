@@ -42,7 +42,7 @@ class _StepSpan:
                                             "h2d_bytes": ctx.h2d_bytes, "begin": self.begin, "end": end})
 
 
-class _NoCollection:
+class NoCollection:
     """No cyclic garbage collection inside: while a stream is being captured into a CUDA graph, an
     object that the collector happens to free then (a dropped cache with its graphs and page-locked
     buffers, a stream, an event) runs CUDA calls that are not allowed during a capture and void it.
@@ -323,7 +323,7 @@ class CausalLM:
                 first = self.forward(ctx)
             graph = torch.cuda.CUDAGraph()
             before = K.launches
-            with _NoCollection(), torch.cuda.graph(graph):
+            with NoCollection(), torch.cuda.graph(graph):
                 out = self.forward(ctx)
             # kernels of this library that one replay launches (for the launch count of benchmarks);
             # the capture itself launched nothing
