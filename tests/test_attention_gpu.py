@@ -363,3 +363,53 @@ def test_fused_decode_tc_the_same_bits_every_time(K, splits, teams):
     for _ in range(40):
         assert torch.equal(run(), first)
     K.check_device_errors("cuda")
+
+
+# ------------------------------------------------------------------------------ random shapes
+@pytest.mark.parametrize("first_seed", range(0, 80, 20))
+def test_tensor_core_kernels_on_random_shapes(K, first_seed):
+    """The four tensor-core attention kernels on drawn head counts, groups, lengths, pasts and divisions of
+    the pages (blocks a cluster, clusters a sequence, warp groups a page), against the plain attention. A
+    division that a kernel refuses is a refusal with its error, never a wrong result."""
+    import random
+    from pytorch_transformers_b200.kernels import KernelError
+    for seed in range(first_seed, first_seed + 20):
+        r = random.Random(seed)
+        kind = r.choice(["prompt", "prompt, two heads a block", "decode tcgen05", "decode mma"])
+        try:
+            if kind.startswith("prompt"):
+                pair = kind != "prompt"
+                d = 128 if pair else r.choice([64, 128])
+                kv, qpk = r.choice([1, 2, 3]), (r.choice([2, 3, 4, 5]) if pair else r.choice([1, 2, 3, 4, 7]))
+                n = r.choice([1, 2, 3])
+                news = [r.randint(65, r.choice([130, 400, 900])) for _ in range(n)]
+                pasts = [r.choice([0, 0, r.randint(65, 300)]) for _ in range(n)]
+                if any(pasts) and not all(pasts):
+                    pasts = [max(p, 70) for p in pasts]
+                K.attention_tc_pairs(2 if pair else r.choice([0, 1]))
+                try:
+                    out, ref = attention_case(K, BF, kv * qpk, kv, d, pasts=pasts, news=news,
+                                              position=r.choice(["rotary", "alibi"]), seed=seed, tc=True)
+                finally:
+                    K.attention_tc_pairs(1)
+            elif kind == "decode tcgen05":
+                kv, qpk, n = r.choice([1, 2]), r.choice([33, 40, 71, 100, 128]), r.choice([1, 2, 4])
+                pasts = [r.randint(1, r.choice([100, 700, 2500])) for _ in range(n)]
+                out, ref = attention_case(K, BF, kv * qpk, kv, 64, pasts=pasts, news=[1] * n,
+                                          position=r.choice(["rotary", "none"]), seed=seed,
+                                          fused_decode=("tc", r.choice([1, 2, 3, 4, 8]), r.choice([1, 1, 2, 3])))
+            else:
+                kv, qpk, d = r.choice([1, 2, 3, 8]), r.choice([1, 2, 4, 5, 16, 71]), r.choice([16, 32, 64, 128])
+                qpk = 4 if kv * qpk > 142 else qpk
+                n = r.choice([1, 2, 4])
+                pasts = [r.randint(1, r.choice([100, 700, 2000])) for _ in range(n)]
+                groups = r.choice([1, 1, 2, 4])
+                if (min(qpk, 128) + 15) // 16 * groups > K.decode_max_warps(d):
+                    groups = 1
+                out, ref = attention_case(K, BF, kv * qpk, kv, d, pasts=pasts, news=[1] * n,
+                                          position=r.choice(["rotary", "alibi"]), seed=seed,
+                                          fused_decode=(None, r.choice([1, 2, 3, 4, 8]), groups, r.choice([1, 1, 2, 3])))
+        except KernelError as refusal:
+            assert "does not take" in str(refusal) or "too many" in str(refusal), (seed, kind, refusal)
+            continue
+        torch.testing.assert_close(out, ref, msg=lambda m: f"seed {seed} {kind}: {m}", **tol(BF))
