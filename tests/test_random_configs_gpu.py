@@ -89,3 +89,30 @@ def test_random_configurations_and_cuttings(tmp_path, first_seed):
             live = [i for i in live if pos[i] < lengths[i]]
         model.check_errors()
         cache.check()
+
+
+@pytest.mark.parametrize("first_seed", range(100, 130, 10))
+def test_greedy_generation_on_random_configurations(tmp_path, first_seed):
+    """`generate` in float32 with drawn limits on the batch and on the tokens of a step, with and without a
+    stop token: the new tokens are the plain implementation's, token for token (a difference is allowed only
+    where the plain logits' two largest lie within 1e-4 of each other)."""
+    import pytorch_transformers_b200 as ptb
+    for seed in range(first_seed, first_seed + 10):
+        r = random.Random(seed)
+        cfg = random_config(r)
+        folder = tm.write_model_folder(os.path.join(str(tmp_path), f"g{seed}"), cfg, tm.make_weights(cfg, seed))
+        model = ptb.AutoModelForCausalLM.from_pretrained(folder, dtype="float32")
+        raw, w = plain.load_folder(folder, torch.float64)
+        g = np.random.Generator(np.random.PCG64(seed))
+        prompts = [g.integers(0, cfg["vocab_size"], size=int(g.integers(1, r.choice([10, 80, 200])))).tolist()
+                   for _ in range(r.choice([1, 2, 3, 5, 7]))]
+        new = r.choice([1, 3, 8, 20])
+        eos = [int(g.integers(0, cfg["vocab_size"]))] if r.random() < 0.5 else None
+        out = model.generate(prompts, max_new_tokens=new, eos_token_id=eos, do_sample=False,
+                             max_batch_size=r.choice([1, 2, 3, 64]), max_step_tokens=r.choice([16, 100, 16384]))
+        for p, o in zip(prompts, out):
+            got, ref = list(o)[len(p):], plain.greedy(p, raw, w, new, eos or ())
+            if got != ref:
+                k = next((i for i, (a, b) in enumerate(zip(got, ref)) if a != b), min(len(got), len(ref)))
+                top = torch.topk(plain.model_logits(list(p) + ref[:k], raw, w)[-1], 2).values
+                assert float(top[0] - top[1]) <= 1e-4, (seed, k, got, ref)
